@@ -1,0 +1,108 @@
+/* FlexTree for B200 — C API of libflextree.so.
+ *
+ * Three groups of entry points:
+ *   1. planner / cost model / CPU executors (pure host, usable without a GPU);
+ *   2. single-GPU n-way reduction kernels (ft_reduce_nway*);
+ *   3. multi-GPU communicator over NVLink peer memory (ft_comm_*), in flextree_comm.h.
+ *
+ * Tree shapes are passed as (widths, nw, lonely, ring): bottom-up level widths whose
+ * product plus `lonely` equals the world size; ring != 0 selects the ring schedule.
+ * Functions that return text write a NUL-terminated string into (buf, cap) and return
+ * the number of bytes needed (excluding NUL); a return >= cap means it was truncated.
+ */
+#ifndef FLEXTREE_H_
+#define FLEXTREE_H_
+
+#include "ft_types.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+const char* ft_version(void);
+
+/* ---- factorisation tools (reference: cost_model/GetPrimeFactor.h, IsPrimeNumber.h,
+ *      GetWidth.h, ChooseWidth.h, PrintTreeStructure.h; topo_count/factor_count.py) ---- */
+int ft_prime_factors(int n, int* out, int cap);
+int ft_is_prime(int n);       /* mathematical: 1 is not prime */
+int ft_is_prime_loose(int n); /* the reference's predicate: 1 counts as prime */
+uint64_t ft_count_ordered_factorizations(int n);
+/* one shape per line, "2*2*2\n2*4\n...": legacy != 0 uses the divisor-tuple enumerator */
+size_t ft_candidate_shapes(int n, int legacy, char* buf, size_t cap);
+/* one candidate per line with "+1" / "-1" suffixes */
+size_t ft_choose_width(int world, char* buf, size_t cap);
+
+/* ---- cost models ---- */
+double ft_cost_v0(const int* widths, int nw, int n, double chunk);
+/* arg-min over ft_candidate_shapes(n); returns number of widths written, cost in *cost,
+ * number of candidates scored in *ncand */
+int ft_choose_v0(int n, double chunk, int* widths, int cap, double* cost, uint64_t* ncand);
+
+typedef struct ft_v1_params {
+  double launch_us, sync_us, link_gbs, hbm_gbs, stage_floor_us, nvls_gbs, oneshot_max_bytes;
+  double peer_eff[FT_MAX_RANKS + 1];
+} ft_v1_params;
+void ft_v1_defaults(ft_v1_params* p);
+double ft_cost_v1(int world, const int* widths, int nw, int lonely, int ring, uint64_t bytes, const ft_v1_params* p);
+double ft_cost_v1_oneshot(int world, uint64_t bytes, const ft_v1_params* p);
+double ft_cost_v1_nvls(int world, uint64_t bytes, const ft_v1_params* p);
+/* writes the winning shape; algo_out receives "staged", "oneshot" or "nvls" */
+int ft_pick_algorithm(int world, uint64_t bytes, const ft_v1_params* p, int allow_oneshot, int allow_nvls,
+                      int* widths, int cap, int* lonely, int* ring, char* algo_out, size_t algo_cap, double* us);
+/* every executable shape for `world`, one per line ("2*4", "2*2+1", "ring8") */
+size_t ft_executable_shapes(int world, char* buf, size_t cap);
+
+/* ---- configuration (reference: get_stages, mpi_mod.hpp:1419-1486) ---- */
+/* returns FT_OK or FT_ERR_INVALID_TOPO (message in err) */
+int ft_parse_topo(const char* topo, const char* lonely_str, int world, int* widths, int cap, int* nw, int* lonely,
+                  int* ring, int* is_auto, char* err, size_t err_cap);
+
+/* ---- planner ---- */
+int ft_validate_shape(int world, const int* widths, int nw, int lonely, int ring, char* err, size_t err_cap);
+/* static race check of the in-place schedule; FT_OK or FT_ERR_INVALID_TOPO + message */
+int ft_plan_check(int world, const int* widths, int nw, int lonely, int ring, char* err, size_t err_cap);
+int ft_plan_num_stages(int world, const int* widths, int nw, int lonely, int ring);
+int ft_plan_max_fanin(int world, const int* widths, int nw, int lonely, int ring);
+/* elements moved between ranks by the whole schedule; 2*(world-1)*count for every valid shape */
+uint64_t ft_plan_traffic(int world, const int* widths, int nw, int lonely, int ring, uint64_t count,
+                         uint64_t block_elems);
+size_t ft_plan_describe(int world, const int* widths, int nw, int lonely, int ring, int rank, uint64_t count,
+                        uint64_t block_elems, char* buf, size_t cap);
+/* machine-readable plan: JSON {"world":..,"stages":..,"ranks":[[{"rs":1,"sync":[..],"pulls":[[block,reduce,[srcs]],..]},..],..]} */
+size_t ft_plan_json(int world, const int* widths, int nw, int lonely, int ring, char* buf, size_t cap);
+
+/* ---- CPU reductions and executors ---- */
+int ft_cpu_reduce(int op, int dtype, const void* const* src, void* dst, int n, size_t len, int threads);
+/* all ranks in the calling thread, in place on bufs[rank] */
+int ft_run_plan_snapshot(int world, const int* widths, int nw, int lonely, int ring, int op, int dtype,
+                         void* const* bufs, uint64_t count, uint64_t block_elems);
+
+/* thread-per-rank world: every rank thread calls ft_cpu_allreduce with the same shape */
+typedef struct ft_cpu_world ft_cpu_world;
+ft_cpu_world* ft_cpu_world_create(int world, double timeout_s);
+void ft_cpu_world_destroy(ft_cpu_world* w);
+/* fault_kind: 0 none, 1 never-signal, 2 wrong-epoch, 3 leave-early (applies when fault_rank == rank).
+ * status_out[0..2] = {ft_status, rendezvous index, peer}.  Returns status_out[0]. */
+int ft_cpu_allreduce(ft_cpu_world* w, int rank, const int* widths, int nw, int lonely, int ring, int op, int dtype,
+                     const void* sendbuf, void* recvbuf, uint64_t count, uint64_t block_elems, int fault_kind,
+                     int fault_rank, int fault_stage, int* status_out);
+
+/* ---- single-GPU n-way reduction (reference: vector_add/reduce_sum_gpu.h) ---- */
+/* dst[i] = src[0][i] (op) ... (op) src[n-1][i], n in [1, FT_MAX_FANIN]; src/dst are device
+ * pointers, `stream` a cudaStream_t.  variant: 0 auto, 1 vector loads, 2 TMA bulk pipeline.
+ * Returns ft_status; CUDA launch errors map to FT_ERR_CUDA (see ft_last_cuda_error). */
+int ft_reduce_nway(int op, int dtype, const void* const* src, void* dst, int n, size_t len, int variant,
+                   void* stream);
+/* out = scale * sum(src) with fp32 accumulation, optionally converting fp32 inputs to a
+ * bf16 result (the cast/scale epilogue used for gradient averaging).  in_dtype FT_F32 or
+ * FT_BF16; out_dtype FT_F32 or FT_BF16. */
+int ft_reduce_nway_scaled(int in_dtype, int out_dtype, const void* const* src, void* dst, int n, size_t len,
+                          float scale, void* stream);
+const char* ft_last_cuda_error(void);
+/* number of kernels launched by this library in this process (all entry points) */
+uint64_t ft_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLEXTREE_H_ */

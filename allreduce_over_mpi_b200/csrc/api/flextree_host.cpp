@@ -1,0 +1,231 @@
+// Host half of the C API: planner, cost models, configuration, CPU executors.
+// Pure C++17; nothing here touches CUDA, so it runs (and is tested) without a GPU.
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <sstream>
+#include <string>
+
+#include "../planner/config.hpp"
+#include "../planner/cost_model.hpp"
+#include "../planner/cpu_executor.hpp"
+#include "../planner/factorize.hpp"
+#include "../planner/plan.hpp"
+#include "flextree.h"
+
+namespace {
+
+size_t put(const std::string& s, char* buf, size_t cap) {
+  if (buf && cap) {
+    size_t n = s.size() < cap - 1 ? s.size() : cap - 1;
+    std::memcpy(buf, s.data(), n);
+    buf[n] = '\0';
+  }
+  return s.size();
+}
+
+ft::Shape make_shape(const int* widths, int nw, int lonely, int ring) {
+  ft::Shape s;
+  if (widths && nw > 0) s.widths.assign(widths, widths + nw);
+  s.lonely = lonely;
+  s.ring = ring != 0;
+  return s;
+}
+
+// Plans depend on (world, shape) only; they are built once and shared.
+const ft::Plan& cached_plan(int world, const ft::Shape& s) {
+  static std::mutex mu;
+  static std::map<std::string, ft::Plan> cache;
+  std::string key = std::to_string(world) + ":" + s.str();
+  std::lock_guard<std::mutex> lk(mu);
+  auto it = cache.find(key);
+  if (it == cache.end()) it = cache.emplace(key, ft::build_plan(world, s)).first;
+  return it->second;
+}
+
+ft::V1Params to_params(const ft_v1_params* p) {
+  ft::V1Params k;
+  if (!p) return k;
+  k.launch_us = p->launch_us; k.sync_us = p->sync_us; k.link_gbs = p->link_gbs; k.hbm_gbs = p->hbm_gbs;
+  k.stage_floor_us = p->stage_floor_us; k.nvls_gbs = p->nvls_gbs; k.oneshot_max_bytes = p->oneshot_max_bytes;
+  k.peer_eff.assign(p->peer_eff, p->peer_eff + FT_MAX_RANKS + 1);
+  return k;
+}
+
+}  // namespace
+
+struct ft_cpu_world { ft::CpuWorld w; explicit ft_cpu_world(int n) : w(n) {} };
+
+extern "C" {
+
+const char* ft_version(void) { return "flextree-b200 0.1"; }
+
+int ft_prime_factors(int n, int* out, int cap) {
+  auto v = ft::prime_factors(n);
+  for (int i = 0; i < (int)v.size() && i < cap; ++i) out[i] = v[i];
+  return (int)v.size();
+}
+int ft_is_prime(int n) { return ft::is_prime(n); }
+int ft_is_prime_loose(int n) { return ft::is_prime_loose(n); }
+uint64_t ft_count_ordered_factorizations(int n) { return ft::count_ordered_factorizations(n); }
+
+size_t ft_candidate_shapes(int n, int legacy, char* buf, size_t cap) {
+  std::string s;
+  for (auto& w : (legacy ? ft::candidate_shapes_legacy(n) : ft::candidate_shapes(n))) s += ft::shape_to_string(w) + "\n";
+  return put(s, buf, cap);
+}
+size_t ft_choose_width(int world, char* buf, size_t cap) {
+  std::string s;
+  for (auto& c : ft::choose_width(world)) s += ft::shape_to_string(c) + "\n";
+  return put(s, buf, cap);
+}
+
+double ft_cost_v0(const int* widths, int nw, int n, double chunk) {
+  return ft::cost_v0(ft::Widths(widths, widths + nw), n, chunk);
+}
+int ft_choose_v0(int n, double chunk, int* widths, int cap, double* cost, uint64_t* ncand) {
+  auto c = ft::choose_v0(n, chunk);
+  for (int i = 0; i < (int)c.widths.size() && i < cap; ++i) widths[i] = c.widths[i];
+  if (cost) *cost = c.cost;
+  if (ncand) *ncand = c.candidates;
+  return (int)c.widths.size();
+}
+
+void ft_v1_defaults(ft_v1_params* p) {
+  ft::V1Params k;
+  p->launch_us = k.launch_us; p->sync_us = k.sync_us; p->link_gbs = k.link_gbs; p->hbm_gbs = k.hbm_gbs;
+  p->stage_floor_us = k.stage_floor_us; p->nvls_gbs = k.nvls_gbs; p->oneshot_max_bytes = k.oneshot_max_bytes;
+  for (int i = 0; i <= FT_MAX_RANKS; ++i) p->peer_eff[i] = 1.0;
+}
+double ft_cost_v1(int world, const int* widths, int nw, int lonely, int ring, uint64_t bytes, const ft_v1_params* p) {
+  return ft::cost_v1(cached_plan(world, make_shape(widths, nw, lonely, ring)), bytes, to_params(p));
+}
+double ft_cost_v1_oneshot(int world, uint64_t bytes, const ft_v1_params* p) { return ft::cost_v1_oneshot(world, bytes, to_params(p)); }
+double ft_cost_v1_nvls(int world, uint64_t bytes, const ft_v1_params* p) { return ft::cost_v1_nvls(world, bytes, to_params(p)); }
+int ft_pick_algorithm(int world, uint64_t bytes, const ft_v1_params* p, int allow_oneshot, int allow_nvls, int* widths,
+                      int cap, int* lonely, int* ring, char* algo_out, size_t algo_cap, double* us) {
+  auto c = ft::pick_algorithm(world, bytes, to_params(p), allow_oneshot != 0, allow_nvls != 0);
+  for (int i = 0; i < (int)c.shape.widths.size() && i < cap; ++i) widths[i] = c.shape.widths[i];
+  if (lonely) *lonely = c.shape.lonely;
+  if (ring) *ring = c.shape.ring;
+  if (us) *us = c.us;
+  put(c.algo, algo_out, algo_cap);
+  return (int)c.shape.widths.size();
+}
+size_t ft_executable_shapes(int world, char* buf, size_t cap) {
+  std::string s;
+  for (auto& sh : ft::executable_shapes(world)) s += sh.str() + "\n";
+  return put(s, buf, cap);
+}
+
+int ft_parse_topo(const char* topo, const char* lonely_str, int world, int* widths, int cap, int* nw, int* lonely,
+                  int* ring, int* is_auto, char* err, size_t err_cap) {
+  auto c = ft::parse_topo(topo ? topo : "", lonely_str ? lonely_str : "", world);
+  if (!c.ok()) { put(c.error, err, err_cap); return FT_ERR_INVALID_TOPO; }
+  for (int i = 0; i < (int)c.shape.widths.size() && i < cap; ++i) widths[i] = c.shape.widths[i];
+  if (nw) *nw = (int)c.shape.widths.size();
+  if (lonely) *lonely = c.shape.lonely;
+  if (ring) *ring = c.shape.ring;
+  if (is_auto) *is_auto = c.is_auto;
+  put("", err, err_cap);
+  return FT_OK;
+}
+
+int ft_validate_shape(int world, const int* widths, int nw, int lonely, int ring, char* err, size_t err_cap) {
+  std::string e = ft::validate_shape(world, make_shape(widths, nw, lonely, ring));
+  put(e, err, err_cap);
+  return e.empty() ? FT_OK : FT_ERR_INVALID_TOPO;
+}
+int ft_plan_check(int world, const int* widths, int nw, int lonely, int ring, char* err, size_t err_cap) {
+  std::string e = ft::check_hazards(cached_plan(world, make_shape(widths, nw, lonely, ring)));
+  put(e, err, err_cap);
+  return e.empty() ? FT_OK : FT_ERR_INVALID_TOPO;
+}
+int ft_plan_num_stages(int world, const int* widths, int nw, int lonely, int ring) {
+  const auto& p = cached_plan(world, make_shape(widths, nw, lonely, ring));
+  return p.ok() ? p.num_stages : -1;
+}
+int ft_plan_max_fanin(int world, const int* widths, int nw, int lonely, int ring) {
+  const auto& p = cached_plan(world, make_shape(widths, nw, lonely, ring));
+  return p.ok() ? ft::plan_stats(p).max_fan_in : -1;
+}
+uint64_t ft_plan_traffic(int world, const int* widths, int nw, int lonely, int ring, uint64_t count,
+                         uint64_t block_elems) {
+  const auto& p = cached_plan(world, make_shape(widths, nw, lonely, ring));
+  if (!p.ok()) return 0;
+  return ft::plan_traffic_elems(p, ft::Blocks(count, world, block_elems));
+}
+size_t ft_plan_describe(int world, const int* widths, int nw, int lonely, int ring, int rank, uint64_t count,
+                        uint64_t block_elems, char* buf, size_t cap) {
+  const auto& p = cached_plan(world, make_shape(widths, nw, lonely, ring));
+  if (p.ok() && (rank < 0 || rank >= world)) return put("invalid rank\n", buf, cap);
+  return put(ft::describe(p, rank, count, block_elems), buf, cap);
+}
+size_t ft_plan_json(int world, const int* widths, int nw, int lonely, int ring, char* buf, size_t cap) {
+  const auto& p = cached_plan(world, make_shape(widths, nw, lonely, ring));
+  std::ostringstream os;
+  if (!p.ok()) {
+    os << "{\"error\":\"" << p.error << "\"}";
+    return put(os.str(), buf, cap);
+  }
+  os << "{\"world\":" << p.world << ",\"shape\":\"" << p.shape.str() << "\",\"stages\":" << p.num_stages << ",\"ranks\":[";
+  for (int r = 0; r < p.world; ++r) {
+    os << (r ? "," : "") << "[";
+    for (int s = 0; s < p.num_stages; ++s) {
+      const auto& st = p.stages[r][s];
+      os << (s ? "," : "") << "{\"rs\":" << (st.reduce_scatter ? 1 : 0) << ",\"sync\":[";
+      for (size_t i = 0; i < p.sync[s][r].size(); ++i) os << (i ? "," : "") << p.sync[s][r][i];
+      os << "],\"pulls\":[";
+      for (size_t i = 0; i < st.pulls.size(); ++i) {
+        os << (i ? "," : "") << "[" << st.pulls[i].block << "," << (st.pulls[i].reduce ? 1 : 0) << ",[";
+        for (size_t j = 0; j < st.pulls[i].srcs.size(); ++j) os << (j ? "," : "") << st.pulls[i].srcs[j];
+        os << "]]";
+      }
+      os << "]}";
+    }
+    os << "]";
+  }
+  os << "],\"end_sync\":[";
+  for (int r = 0; r < p.world; ++r) {
+    os << (r ? "," : "") << "[";
+    for (size_t i = 0; i < p.sync[p.num_stages][r].size(); ++i) os << (i ? "," : "") << p.sync[p.num_stages][r][i];
+    os << "]";
+  }
+  os << "]}";
+  return put(os.str(), buf, cap);
+}
+
+int ft_cpu_reduce(int op, int dtype, const void* const* src, void* dst, int n, size_t len, int threads) {
+  if (n < 0 || (n > 0 && (!src || !dst))) return FT_ERR_INVALID_ARG;
+  return ft::reduce_nway_cpu_dispatch((ft_op)op, (ft_dtype)dtype, src, dst, n, len, threads);
+}
+int ft_run_plan_snapshot(int world, const int* widths, int nw, int lonely, int ring, int op, int dtype,
+                         void* const* bufs, uint64_t count, uint64_t block_elems) {
+  return ft::run_plan_snapshot(cached_plan(world, make_shape(widths, nw, lonely, ring)), (ft_op)op, (ft_dtype)dtype,
+                               bufs, count, block_elems);
+}
+
+ft_cpu_world* ft_cpu_world_create(int world, double timeout_s) {
+  if (world < 1 || world > 4096) return nullptr;
+  auto* w = new ft_cpu_world(world);
+  if (timeout_s > 0) w->w.timeout_s = timeout_s;
+  return w;
+}
+void ft_cpu_world_destroy(ft_cpu_world* w) { delete w; }
+int ft_cpu_allreduce(ft_cpu_world* w, int rank, const int* widths, int nw, int lonely, int ring, int op, int dtype,
+                     const void* sendbuf, void* recvbuf, uint64_t count, uint64_t block_elems, int fault_kind,
+                     int fault_rank, int fault_stage, int* status_out) {
+  if (!w || rank < 0 || rank >= w->w.n) return FT_ERR_INVALID_ARG;
+  ft::FaultSpec f;
+  f.kind = (ft::Fault)fault_kind;
+  f.rank = fault_rank;
+  f.stage = fault_stage;
+  const auto& p = cached_plan(w->w.n, make_shape(widths, nw, lonely, ring));
+  ft::RankStatus st = ft::cpu_allreduce(w->w, rank, p, (ft_op)op, (ft_dtype)dtype, sendbuf, recvbuf, count,
+                                        block_elems, fault_kind ? &f : nullptr);
+  if (status_out) { status_out[0] = st.code; status_out[1] = st.stage; status_out[2] = st.peer; }
+  return st.code;
+}
+
+}  // extern "C"

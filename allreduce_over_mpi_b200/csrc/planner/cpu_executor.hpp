@@ -1,0 +1,165 @@
+// Host executors for FlexTree plans.
+//
+// (1) run_plan_snapshot(): all ranks in one thread, stage by stage, every stage reading
+//     the state as it was before the stage.  This is the "fake backend" for planner
+//     tests and the oracle for GPU results; a plan that has a read/write race inside a
+//     stage gives a wrong answer here instead of passing by luck.
+// (2) CpuWorld / cpu_allreduce(): ranks are threads of one process that pull blocks
+//     straight out of each other's buffers and synchronise with per-pair epoch flags,
+//     i.e. the same protocol the device kernels use (flag = monotonically increasing
+//     rendezvous number, release on signal, acquire on wait, every wait bounded).
+//     Fault injection lives here, on the host: a rank that never signals, signals a
+//     wrong epoch, or leaves early makes its peers return FT_ERR_TIMEOUT /
+//     FT_ERR_PROTOCOL instead of hanging.
+//
+// Role in the reference: tree_allreduce / ring_allreduce (allreduce_over_mpi/
+// mpi_mod.hpp:1510-1671, :1673-1719), where the transport is MPI_Isend/Irecv into a
+// staging buffer followed by handle_reduce (:1316-1415) and an MPI_Barrier per stage.
+#pragma once
+#include <atomic>
+#include <chrono>
+#include <cstring>
+#include <memory>
+#include <thread>
+#include <vector>
+
+#include "cpu_reduce.hpp"
+#include "plan.hpp"
+
+namespace ft {
+
+// In-place execution over bufs[rank] (each `count` elements of dtype).
+inline ft_status run_plan_snapshot(const Plan& p, ft_op op, ft_dtype dt, void* const* bufs, uint64_t count,
+                                   uint64_t block_elems = 0) {
+  if (!p.ok()) return FT_ERR_INVALID_TOPO;
+  if (!ft_op_supported(op, dt)) return ((int)op < 0 || op >= FT_OP_COUNT) ? FT_ERR_UNSUPPORTED_OP : FT_ERR_UNSUPPORTED_TYPE;
+  const size_t es = ft_dtype_size(dt);
+  Blocks g(count, p.world, block_elems);
+  struct Pending { int rank; uint64_t off; std::vector<char> bytes; };
+  for (int s = 0; s < p.num_stages; ++s) {
+    std::vector<Pending> pend;
+    for (int r = 0; r < p.world; ++r)
+      for (const Pull& pl : p.stages[r][s].pulls) {
+        const uint64_t off = g.offset(pl.block), len = g.length(pl.block);
+        if (!len) continue;
+        Pending w{r, off, std::vector<char>(len * es)};
+        if (pl.reduce) {
+          const void* src[FT_MAX_FANIN];
+          int n = 0;
+          src[n++] = (const char*)bufs[r] + off * es;
+          for (int q : pl.srcs) src[n++] = (const char*)bufs[q] + off * es;
+          ft_status st = reduce_nway_cpu_dispatch(op, dt, src, w.bytes.data(), n, len, 1);
+          if (st != FT_OK) return st;
+        } else {
+          std::memcpy(w.bytes.data(), (const char*)bufs[pl.srcs[0]] + off * es, len * es);
+        }
+        pend.push_back(std::move(w));
+      }
+    for (auto& w : pend) std::memcpy((char*)bufs[w.rank] + w.off * es, w.bytes.data(), w.bytes.size());
+  }
+  return FT_OK;
+}
+
+enum class Fault { None, NeverSignal, WrongEpoch, LeaveEarly };
+struct FaultSpec {
+  Fault kind = Fault::None;
+  int rank = -1;   // which rank misbehaves
+  int stage = 0;   // at (NeverSignal: from) which rendezvous index; 0 = opening
+};
+
+struct RankStatus {
+  ft_status code = FT_OK;
+  int stage = -1;  // rendezvous index where the wait gave up
+  int peer = -1;
+};
+
+// Shared state of a thread-per-rank world.
+struct CpuWorld {
+  int n;
+  std::unique_ptr<std::atomic<uint32_t>[]> flags;  // flags[dst * n + src]
+  std::unique_ptr<std::atomic<void*>[]> bufs;      // buffer each rank exposes for the current call
+  std::vector<uint32_t> epoch;                     // per-rank local rendezvous counter
+  double timeout_s = 5.0;
+  explicit CpuWorld(int n_) : n(n_), flags(new std::atomic<uint32_t>[(size_t)n_ * n_]), bufs(new std::atomic<void*>[n_]), epoch(n_, 0) {
+    for (int i = 0; i < n * n; ++i) flags[i].store(0);
+    for (int i = 0; i < n; ++i) bufs[i].store(nullptr);
+  }
+};
+
+namespace detail {
+// A peer may legitimately be ahead of `value`: it can already have signalled the next
+// rendezvous the two ranks share, at most `max_ahead` numbers later (the opening one of
+// the next call).  Anything beyond that is a protocol violation.
+inline RankStatus rendezvous(CpuWorld& w, int rank, const std::vector<int>& peers, uint32_t value, int index,
+                             int max_ahead, const FaultSpec* fault) {
+  RankStatus st;
+  uint32_t sig = value;
+  bool skip = false;
+  if (fault && fault->rank == rank) {
+    // a silent rank stays silent: a later signal would heal the missed one (waits are ">=")
+    if (fault->kind == Fault::NeverSignal && index >= fault->stage) skip = true;
+    if (fault->kind == Fault::WrongEpoch && index == fault->stage) sig = value + 1000;
+  }
+  if (!skip)
+    for (int q : peers) w.flags[(size_t)q * w.n + rank].store(sig, std::memory_order_release);
+  const auto t0 = std::chrono::steady_clock::now();
+  for (int q : peers) {
+    for (;;) {
+      const uint32_t f = w.flags[(size_t)rank * w.n + q].load(std::memory_order_acquire);
+      const int32_t ahead = (int32_t)(f - value);
+      if (ahead > max_ahead) { st = {FT_ERR_PROTOCOL, index, q}; return st; }
+      if (ahead >= 0) break;
+      if (std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() > w.timeout_s) {
+        st = {FT_ERR_TIMEOUT, index, q};
+        return st;
+      }
+      std::this_thread::yield();
+    }
+  }
+  return st;
+}
+}  // namespace detail
+
+// One rank's part of an all-reduce; call from n threads with the same arguments
+// (sendbuf == nullptr or == recvbuf means in place).  Returns the rank's status.
+inline RankStatus cpu_allreduce(CpuWorld& w, int rank, const Plan& p, ft_op op, ft_dtype dt, const void* sendbuf,
+                                void* recvbuf, uint64_t count, uint64_t block_elems = 0,
+                                const FaultSpec* fault = nullptr, int threads = 1) {
+  RankStatus st;
+  if (!p.ok() || p.world != w.n) { st.code = FT_ERR_INVALID_TOPO; return st; }
+  if (!ft_op_supported(op, dt)) {
+    st.code = ((int)op < 0 || op >= FT_OP_COUNT) ? FT_ERR_UNSUPPORTED_OP : FT_ERR_UNSUPPORTED_TYPE;
+    return st;
+  }
+  const size_t es = ft_dtype_size(dt);
+  if (sendbuf && sendbuf != recvbuf) std::memcpy(recvbuf, sendbuf, count * es);
+  if (w.n == 1) return st;
+  Blocks g(count, p.world, block_elems);
+  const uint32_t base = w.epoch[rank];
+  w.epoch[rank] = base + (uint32_t)p.num_stages + 1;
+  w.bufs[rank].store(recvbuf, std::memory_order_release);
+  for (int s = 0; s <= p.num_stages; ++s) {
+    if (fault && fault->rank == rank && fault->kind == Fault::LeaveEarly && fault->stage == s) return st;
+    st = detail::rendezvous(w, rank, p.sync[s][rank], base + (uint32_t)s + 1, s, p.num_stages + 1, fault);
+    if (st.code != FT_OK) return st;
+    if (s == p.num_stages) break;
+    for (const Pull& pl : p.stages[rank][s].pulls) {
+      const uint64_t off = g.offset(pl.block), len = g.length(pl.block);
+      if (!len) continue;
+      char* mine = (char*)recvbuf + off * es;
+      if (pl.reduce) {
+        const void* src[FT_MAX_FANIN];
+        int n = 0;
+        src[n++] = mine;
+        for (int q : pl.srcs) src[n++] = (const char*)w.bufs[q].load(std::memory_order_acquire) + off * es;
+        st.code = reduce_nway_cpu_dispatch(op, dt, src, mine, n, len, threads);
+        if (st.code != FT_OK) return st;
+      } else {
+        std::memcpy(mine, (const char*)w.bufs[pl.srcs[0]].load(std::memory_order_acquire) + off * es, len * es);
+      }
+    }
+  }
+  return st;
+}
+
+}  // namespace ft

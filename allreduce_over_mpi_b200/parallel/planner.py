@@ -1,0 +1,281 @@
+"""Python face of the C++ planner, cost models and CPU executors.
+
+Everything here calls into ``libflextree.so`` (``csrc/planner/*.hpp`` behind
+``csrc/api/flextree_host.cpp``); nothing is re-implemented in Python.  Reference
+counterparts: cost_model/*.h, topo_count/factor_count.py and the planner classes of
+allreduce_over_mpi/mpi_mod.hpp:80-766 (also shipped as tmp_tree.cpp).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+import os
+import threading
+from dataclasses import dataclass, field
+from typing import Sequence
+
+import torch
+
+from .._lib import FlexTreeError, V1Params, check, lib, text_call
+from ..ops.reduce import ft_dtype
+from .._lib import OPS
+
+
+@dataclass(frozen=True)
+class Shape:
+    """Tree shape: bottom-up level widths, lonely ranks, or the ring."""
+    widths: tuple[int, ...]
+    lonely: int = 0
+    ring: bool = False
+
+    @staticmethod
+    def parse(text: str) -> "Shape":
+        """``"2*4"``, ``"2x2+1"``, ``"8"``, ``"ring8"``."""
+        t = text.strip().lower()
+        if t.startswith("ring"):
+            return Shape((int(t[4:]),), 0, True)
+        lonely = 0
+        if "+" in t:
+            t, l = t.split("+")
+            lonely = int(l)
+        widths = tuple(int(x) for x in t.replace("x", "*").replace(",", "*").split("*") if x)
+        return Shape(widths, lonely, False)
+
+    @staticmethod
+    def flat(world: int) -> "Shape":
+        return Shape((world,))
+
+    @property
+    def world(self) -> int:
+        if self.ring:
+            return self.widths[0]
+        n = 1
+        for w in self.widths:
+            n *= w
+        return n + self.lonely
+
+    def __str__(self) -> str:
+        if self.ring:
+            return f"ring{self.widths[0]}"
+        return "*".join(map(str, self.widths)) + (f"+{self.lonely}" if self.lonely else "")
+
+    def c_args(self):
+        arr = (C.c_int * max(1, len(self.widths)))(*self.widths)
+        return arr, len(self.widths), self.lonely, int(self.ring)
+
+
+def _lines(s: str) -> list[str]:
+    return [x for x in s.split("\n") if x]
+
+
+# ---- factorisation tools ----------------------------------------------------------------
+def prime_factors(n: int) -> list[int]:
+    out = (C.c_int * 64)()
+    k = lib().ft_prime_factors(n, out, 64)
+    return list(out[:k])
+
+
+def is_prime(n: int, loose: bool = False) -> bool:
+    """``loose=True`` is the reference's predicate, which calls 1 prime."""
+    return bool(lib().ft_is_prime_loose(n) if loose else lib().ft_is_prime(n))
+
+
+def count_ordered_factorizations(n: int) -> int:
+    return int(lib().ft_count_ordered_factorizations(n))
+
+
+def candidate_shapes(n: int, legacy: bool = False) -> list[str]:
+    """Candidate tree shapes for n ranks as ``"w0*w1*..."`` strings (incl. ``1*n`` / ``n*1``)."""
+    return _lines(text_call(lib().ft_candidate_shapes, n, int(legacy)))
+
+
+def choose_width(world: int) -> list[str]:
+    """Shapes of ``world`` plus the ``-1`` / ``+1`` neighbours (lonely candidates)."""
+    return _lines(text_call(lib().ft_choose_width, world))
+
+
+def executable_shapes(world: int) -> list[Shape]:
+    return [Shape.parse(s) for s in _lines(text_call(lib().ft_executable_shapes, world))]
+
+
+# ---- cost models ------------------------------------------------------------------------
+def cost_v0(widths: Sequence[int], n: int, chunk: float = 100.0) -> float:
+    arr = (C.c_int * len(widths))(*widths)
+    return float(lib().ft_cost_v0(arr, len(widths), n, chunk))
+
+
+def choose_v0(n: int, chunk: float = 100.0) -> tuple[str, float, int]:
+    """Arg-min of the original analytic model: (shape string, cost, candidates scored)."""
+    w = (C.c_int * 64)()
+    cost = C.c_double()
+    ncand = C.c_uint64()
+    k = lib().ft_choose_v0(n, chunk, w, 64, C.byref(cost), C.byref(ncand))
+    return "*".join(str(w[i]) for i in range(k)), cost.value, int(ncand.value)
+
+
+@dataclass
+class CostParams:
+    """Measured parameters of the NVSwitch cost model (v1); see csrc/planner/cost_model.hpp."""
+    launch_us: float = 4.0
+    sync_us: float = 2.5
+    link_gbs: float = 700.0
+    hbm_gbs: float = 6000.0
+    stage_floor_us: float = 0.5
+    nvls_gbs: float = 0.0
+    oneshot_max_bytes: float = float(1 << 20)
+    peer_eff: dict[int, float] = field(default_factory=dict)
+
+    def to_c(self) -> V1Params:
+        p = V1Params()
+        lib().ft_v1_defaults(C.byref(p))
+        for k in ("launch_us", "sync_us", "link_gbs", "hbm_gbs", "stage_floor_us", "nvls_gbs", "oneshot_max_bytes"):
+            setattr(p, k, float(getattr(self, k)))
+        for k, v in self.peer_eff.items():
+            p.peer_eff[int(k)] = float(v)
+        return p
+
+    def to_json(self) -> str:
+        return json.dumps(self.__dict__, indent=1, sort_keys=True)
+
+    @staticmethod
+    def from_json(text: str) -> "CostParams":
+        d = json.loads(text)
+        d["peer_eff"] = {int(k): float(v) for k, v in d.get("peer_eff", {}).items()}
+        return CostParams(**d)
+
+    @staticmethod
+    def load(path: str | os.PathLike | None = None) -> "CostParams":
+        """Calibration table: ``path``, else $FT_CALIBRATION, else the packaged default."""
+        path = path or os.environ.get("FT_CALIBRATION") or os.path.join(os.path.dirname(__file__), "calibration_b200.json")
+        if os.path.exists(path):
+            with open(path) as f:
+                return CostParams.from_json(f.read())
+        return CostParams()
+
+
+def cost_v1(world: int, shape: Shape, nbytes: int, params: CostParams | None = None) -> float:
+    p = (params or CostParams()).to_c()
+    return float(lib().ft_cost_v1(world, *shape.c_args(), nbytes, C.byref(p)))
+
+
+def cost_v1_oneshot(world: int, nbytes: int, params: CostParams | None = None) -> float:
+    p = (params or CostParams()).to_c()
+    return float(lib().ft_cost_v1_oneshot(world, nbytes, C.byref(p)))
+
+
+def cost_v1_nvls(world: int, nbytes: int, params: CostParams | None = None) -> float:
+    p = (params or CostParams()).to_c()
+    return float(lib().ft_cost_v1_nvls(world, nbytes, C.byref(p)))
+
+
+def pick_algorithm(world: int, nbytes: int, params: CostParams | None = None, allow_oneshot: bool = True,
+                   allow_nvls: bool = True) -> tuple[str, Shape, float]:
+    """(algorithm, shape, predicted microseconds) for a message of ``nbytes``."""
+    p = (params or CostParams()).to_c()
+    w = (C.c_int * 64)()
+    lonely, ring, us = C.c_int(), C.c_int(), C.c_double()
+    algo = C.create_string_buffer(32)
+    k = lib().ft_pick_algorithm(world, nbytes, C.byref(p), int(allow_oneshot), int(allow_nvls), w, 64,
+                                C.byref(lonely), C.byref(ring), algo, 32, C.byref(us))
+    return algo.value.decode(), Shape(tuple(w[i] for i in range(k)), lonely.value, bool(ring.value)), us.value
+
+
+# ---- configuration ----------------------------------------------------------------------
+def parse_topo(topo: str | None, lonely: str | None, world: int) -> tuple[Shape, bool]:
+    """``FT_TOPO`` / ``FT_LONELY`` syntax -> (shape, is_auto); raises on an invalid layout."""
+    w = (C.c_int * 64)()
+    nw, l, ring, is_auto = C.c_int(), C.c_int(), C.c_int(), C.c_int()
+    err = C.create_string_buffer(512)
+    code = lib().ft_parse_topo((topo or "").encode(), (lonely or "").encode(), world, w, 64, C.byref(nw), C.byref(l),
+                               C.byref(ring), C.byref(is_auto), err, 512)
+    if code:
+        raise FlexTreeError(code, err.value.decode())
+    return Shape(tuple(w[i] for i in range(nw.value)), l.value, bool(ring.value)), bool(is_auto.value)
+
+
+def shape_from_env(world: int) -> tuple[Shape, bool]:
+    return parse_topo(os.environ.get("FT_TOPO"), os.environ.get("FT_LONELY"), world)
+
+
+# ---- planner ----------------------------------------------------------------------------
+def validate_shape(world: int, shape: Shape) -> str:
+    """Empty string when executable, else the reason."""
+    err = C.create_string_buffer(512)
+    lib().ft_validate_shape(world, *shape.c_args(), err, 512)
+    return err.value.decode()
+
+
+def plan_check(world: int, shape: Shape) -> str:
+    """Static race check of the in-place schedule: empty string when race-free."""
+    err = C.create_string_buffer(1024)
+    lib().ft_plan_check(world, *shape.c_args(), err, 1024)
+    return err.value.decode()
+
+
+def plan_num_stages(world: int, shape: Shape) -> int:
+    return lib().ft_plan_num_stages(world, *shape.c_args())
+
+
+def plan_max_fanin(world: int, shape: Shape) -> int:
+    return lib().ft_plan_max_fanin(world, *shape.c_args())
+
+
+def plan_traffic(world: int, shape: Shape, count: int, block_elems: int = 0) -> int:
+    return int(lib().ft_plan_traffic(world, *shape.c_args(), count, block_elems))
+
+
+def describe(world: int, shape: Shape, rank: int, count: int = 0, block_elems: int = 0) -> str:
+    return text_call(lib().ft_plan_describe, world, *shape.c_args(), rank, count, block_elems)
+
+
+def plan_json(world: int, shape: Shape) -> dict:
+    return json.loads(text_call(lib().ft_plan_json, world, *shape.c_args(), cap=1 << 20))
+
+
+# ---- CPU executors ----------------------------------------------------------------------
+def run_plan_snapshot(shape: Shape, bufs: Sequence[torch.Tensor], op: str = "sum", block_elems: int = 0) -> None:
+    """All ranks in this thread, in place on ``bufs[rank]`` (CPU tensors)."""
+    world = len(bufs)
+    ptrs = (C.c_void_p * world)(*[b.data_ptr() for b in bufs])
+    check(lib().ft_run_plan_snapshot(world, *shape.c_args(), OPS[op], ft_dtype(bufs[0].dtype), ptrs, bufs[0].numel(),
+                                     block_elems), f"shape {shape} for world {world}")
+
+
+class CpuWorld:
+    """Thread-per-rank world running the device protocol (epoch flags, bounded waits) on the host."""
+
+    def __init__(self, world: int, timeout_s: float = 5.0):
+        self.world = world
+        self._h = lib().ft_cpu_world_create(world, timeout_s)
+        if not self._h:
+            raise ValueError("bad world size")
+
+    def close(self):
+        if self._h:
+            lib().ft_cpu_world_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
+
+    def allreduce_rank(self, rank: int, shape: Shape, recv: torch.Tensor, send: torch.Tensor | None = None,
+                       op: str = "sum", block_elems: int = 0, fault=(0, -1, 0)) -> tuple[int, int, int]:
+        """One rank's call (blocking); returns (status, rendezvous index, peer)."""
+        st = (C.c_int * 3)()
+        lib().ft_cpu_allreduce(self._h, rank, *shape.c_args(), OPS[op], ft_dtype(recv.dtype),
+                               send.data_ptr() if send is not None else None, recv.data_ptr(), recv.numel(),
+                               block_elems, fault[0], fault[1], fault[2], st)
+        return st[0], st[1], st[2]
+
+    def allreduce(self, shape: Shape, bufs: Sequence[torch.Tensor], op: str = "sum", block_elems: int = 0,
+                  fault=(0, -1, 0)) -> list[tuple[int, int, int]]:
+        """Run every rank on its own thread, in place on ``bufs``; returns per-rank status."""
+        out: list = [None] * self.world
+
+        def work(r):
+            out[r] = self.allreduce_rank(r, shape, bufs[r], None, op, block_elems, fault)
+
+        ts = [threading.Thread(target=work, args=(r,)) for r in range(self.world)]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+        return out
