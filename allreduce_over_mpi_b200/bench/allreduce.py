@@ -1,0 +1,308 @@
+"""All-reduce bus-bandwidth benchmark: FlexTree kernels vs NCCL on the same GPUs.
+
+Launch one process per GPU:
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29511 \
+        -m allreduce_over_mpi_b200.bench.allreduce --min-bytes 1024 --max-bytes 1073741824 \
+        --dtypes float32 bfloat16 --shapes auto 8 2*4 4*2 2*2*2 --algos staged oneshot nvls --nccl
+
+Every timing is a CUDA-event interval on the launching stream after warm-up; L2 is flushed
+between timed iterations; the reported time is the median over iterations of the MAX over
+ranks; busbw = bytes / t * 2(N-1)/N.  One JSON line per (size, dtype, implementation).
+
+Counterpart of the reference's benchmark driver (allreduce_over_mpi/benchmark.cpp:31-243:
+--size/--repeat/--comm-type/--check/--to-file, MPI_Wtime on rank 0, default 35 floats) with
+NCCL in the place of the MPI library's own MPI_Allreduce as the comparison arm.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+
+import torch
+import torch.distributed as dist
+
+from ..parallel.comm import FlexTreeComm
+from ..parallel.planner import Shape, validate_shape
+from ..utils import flush_l2
+
+
+def init_dist() -> tuple[int, int, int]:
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def time_collective(fn, iters: int, warmup: int, flush: bool = True) -> float:
+    """Median over iterations of the max-over-ranks device time of ``fn`` in milliseconds."""
+    for _ in range(max(warmup, 3)):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(iters)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(iters)]
+    for i in range(iters):
+        if flush:
+            flush_l2()
+        starts[i].record()
+        fn()
+        stops[i].record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([a.elapsed_time(b) for a, b in zip(starts, stops)], dtype=torch.float64, device="cuda")
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return statistics.median(ms.tolist())
+
+
+def busbw(nbytes: int, ms: float, world: int) -> float:
+    return nbytes / (ms * 1e-3) / 1e9 * (2 * (world - 1) / world)
+
+
+def fill(t: torch.Tensor, rank: int, it: int = 0):
+    g = torch.Generator(device=t.device).manual_seed(1000 * it + rank)
+    t.copy_((torch.rand(t.numel(), generator=g, device=t.device) * 2 - 1).to(t.dtype))
+
+
+def expected(count: int, dtype, world: int, device, it: int = 0) -> torch.Tensor:
+    acc = torch.zeros(count, dtype=torch.float64, device=device)
+    tmp = torch.empty(count, dtype=dtype, device=device)
+    for r in range(world):
+        fill(tmp, r, it)
+        acc += tmp.double()
+    return acc
+
+
+def sweep(a, comm: FlexTreeComm, rank: int, world: int) -> list[dict]:
+    rows = []
+    sizes = []
+    s = a.min_bytes
+    while s <= a.max_bytes:
+        sizes.append(s)
+        s *= a.step
+    dev = comm.device
+    for dt_name in a.dtypes:
+        dtype = getattr(torch, dt_name)
+        es = torch.empty((), dtype=dtype).element_size()
+        for nbytes in sizes:
+            count = nbytes // es
+            comm.free_all()
+            sym = comm.alloc(count, dtype)          # zero-copy path
+            loc = torch.empty(count, dtype=dtype, device=dev)   # staged path / NCCL
+            iters = a.iters if nbytes <= (64 << 20) else max(3, a.iters // 2)
+            impls = []
+            for shape in a.shapes:
+                for algo in a.algos:
+                    if algo in ("oneshot", "nvls") and shape != a.shapes[0]:
+                        continue
+                    if algo == "oneshot" and nbytes > min(comm.staging_bytes, a.oneshot_cap):
+                        continue
+                    if algo == "nvls" and (not comm.has_nvls or nbytes % 16):
+                        continue
+                    if algo == "staged" and shape != "auto" and validate_shape(world, Shape.parse(shape)):
+                        continue
+                    impls.append((shape, algo))
+            for shape, algo in impls:
+                label = f"flextree/{algo}/{shape}"
+                if shape == "auto" and algo == "staged":
+                    # "auto": whatever the cost model picks for this size
+                    name, shp = comm.choose(nbytes, True, dtype)
+                    fn = lambda: comm.all_reduce(sym)  # noqa: E731
+                    label = f"flextree/auto->{name}/{shp}"
+                elif algo == "staged":
+                    fn = lambda shape=shape: comm.all_reduce(sym, shape=shape, algo="staged")  # noqa: E731
+                elif algo == "nvls":
+                    fn = lambda: comm.all_reduce(sym, algo="nvls")  # noqa: E731
+                else:
+                    fn = lambda: comm.all_reduce(loc, algo="oneshot")  # noqa: E731
+                row = {"bench": "allreduce", "impl": label, "bytes": nbytes, "dtype": dt_name, "world": world}
+                if a.check:
+                    tgt = loc if algo == "oneshot" else sym
+                    fill(tgt, rank)
+                    fn()
+                    torch.cuda.synchronize()
+                    want = expected(count, dtype, world, dev)
+                    err = (tgt.double() - want).abs().max().item()
+                    row["max_abs_err"] = err
+                    row["ok"] = err <= (1e-4 if dtype == torch.float32 else 0.25) * max(1.0, world / 8)
+                    comm.check()
+                ms = time_collective(fn, iters, a.warmup, flush=not a.no_flush)
+                comm.check()
+                row.update(ms=round(ms, 5), algbw_GBps=round(nbytes / ms / 1e6, 2), busbw_GBps=round(busbw(nbytes, ms, world), 2))
+                rows.append(row)
+                if rank == 0:
+                    print(json.dumps(row), flush=True)
+            if a.staged_copy and nbytes <= comm.staging_bytes:
+                fn = lambda: comm.all_reduce(loc, shape=Shape.flat(world), algo="staged")  # noqa: E731
+                ms = time_collective(fn, iters, a.warmup, flush=not a.no_flush)
+                row = {"bench": "allreduce", "impl": "flextree/staged-through-slots/flat", "bytes": nbytes, "dtype": dt_name,
+                       "world": world, "ms": round(ms, 5), "busbw_GBps": round(busbw(nbytes, ms, world), 2)}
+                rows.append(row)
+                if rank == 0:
+                    print(json.dumps(row), flush=True)
+            if a.nccl:
+                ms = time_collective(lambda: dist.all_reduce(loc), iters, a.warmup, flush=not a.no_flush)
+                row = {"bench": "allreduce", "impl": "nccl", "bytes": nbytes, "dtype": dt_name, "world": world,
+                       "ms": round(ms, 5), "algbw_GBps": round(nbytes / ms / 1e6, 2), "busbw_GBps": round(busbw(nbytes, ms, world), 2)}
+                rows.append(row)
+                if rank == 0:
+                    print(json.dumps(row), flush=True)
+            del sym, loc
+    return rows
+
+
+def make_comm(max_bytes: int, staging: int = 64 << 20) -> FlexTreeComm:
+    return FlexTreeComm(heap_bytes=max_bytes + (4 << 20), staging_bytes=staging)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--min-bytes", type=int, default=1024)
+    ap.add_argument("--max-bytes", type=int, default=1 << 30)
+    ap.add_argument("--step", type=int, default=4)
+    ap.add_argument("--dtypes", nargs="+", default=["float32"])
+    ap.add_argument("--shapes", nargs="+", default=["auto"])
+    ap.add_argument("--algos", nargs="+", default=["staged", "oneshot", "nvls"])
+    ap.add_argument("--oneshot-cap", type=int, default=4 << 20)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--nccl", action="store_true")
+    ap.add_argument("--check", action="store_true")
+    ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--staged-copy", action="store_true", help="also time the path for tensors outside the symmetric heap")
+    ap.add_argument("--out", default=None)
+    a = ap.parse_args(argv)
+    rank, world, _ = init_dist()
+    comm = make_comm(a.max_bytes)
+    if rank == 0:
+        print(json.dumps({"bench": "allreduce", "world": world, "nvls": comm.has_nvls, "mem_kind": comm.mem_kind}), flush=True)
+    rows = sweep(a, comm, rank, world)
+    if rank == 0 and a.out:
+        with open(a.out, "a") as f:
+            for r in rows:
+                f.write(json.dumps(r) + "\n")
+    bad = [r for r in rows if r.get("ok") is False]
+    comm.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    return 1 if bad else 0
+
+
+# ---- entry used by the repository's bench.py ---------------------------------------------
+def bench_allreduce_main(a) -> dict:
+    """Headline number: in-place all-reduce of ``a.bytes`` in the symmetric heap, ``a.steps`` timed steps."""
+    from ..ops import launch_count
+    from ..utils import ClockSampler
+    rank, world, local = init_dist()
+    dtype = getattr(torch, a.dtype)
+    es = torch.empty((), dtype=dtype).element_size()
+    count = a.bytes // es
+    comm = make_comm(a.bytes)
+    buf = comm.alloc(count, dtype)
+    fill(buf, rank)
+    comm.all_reduce(buf)
+    torch.cuda.synchronize()
+    err = (buf.double() - expected(count, dtype, world, comm.device)).abs().max().item()
+    comm.check()
+    name, shp = comm.choose(a.bytes, True, dtype)
+    warm = max(a.warmup, 3)
+    sampler = ClockSampler(gpu_index=local).start() if rank == 0 else None
+
+    def step():
+        comm.all_reduce(buf)
+
+    for _ in range(warm):
+        step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    l0 = launch_count()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(a.steps):
+        step()
+    e.record()
+    torch.cuda.synchronize()
+    launches = launch_count() - l0
+    dist.barrier()
+    t = torch.tensor([s.elapsed_time(e)], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = t.item() / a.steps
+    comm.check()
+    # keep the same load running (untimed) until the clock sampler has seen ~0.8 s of it
+    for _ in range(min(4000, int(800.0 / max(ms, 1e-3)) + 1)):
+        step()
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler is not None else None
+    nccl_ms = time_collective(lambda: dist.all_reduce(buf), min(a.steps, 10), warm, flush=False)
+    value = busbw(a.bytes, ms, world)
+    res = {
+        "metric": "all-reduce bus bandwidth GB/s (bytes/t * 2(N-1)/N), t = max over ranks",
+        "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": a.steps, "warmup": warm,
+        "ms_per_step": round(ms, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": a.dtype, "data": "synthetic uniform[-1,1) seeded per rank",
+        "config": {"model": "all-reduce", "message_bytes": a.bytes, "global_batch": None, "seq_len": None,
+                   "parallelism": f"dp{world}", "algorithm": name, "shape": str(shp), "in_place": "symmetric heap (zero copy)",
+                   "l2": "input larger than L2" if a.bytes > (126 << 20) else "input smaller than L2, not flushed inside the back-to-back loop"},
+        "impl": "flextree", "nvls": comm.has_nvls, "max_abs_err_first_call": err,
+        "nccl_same_buffer": {"ms": round(nccl_ms, 5), "busbw_GBps": round(busbw(a.bytes, nccl_ms, world), 1)},
+        "frac_of_nvlink_770GBps": round(value / 770.0, 3),
+        "gpu_launches": int(launches), "clocks": clocks,
+    }
+    if not a.no_e2e:
+        res["e2e"] = e2e_allreduce(a, comm, buf, count, dtype, world)
+    if not a.no_sweep:
+        ns = argparse.Namespace(min_bytes=1024, max_bytes=min(a.bytes, 1 << 30), step=16, dtypes=[a.dtype], shapes=["auto"],
+                                algos=["staged"], oneshot_cap=4 << 20, iters=10, warmup=3, nccl=True, check=False,
+                                no_flush=False, staged_copy=False)
+        import contextlib
+        import io
+        with contextlib.redirect_stdout(io.StringIO()):
+            rows = sweep(ns, comm, rank, world)
+        res["sweep"] = [{k: r[k] for k in ("impl", "bytes", "ms", "busbw_GBps")} for r in rows]
+    comm.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    return res
+
+
+def e2e_allreduce(a, comm, buf, count, dtype, world) -> dict:
+    """Same step through the public API with the input copied from pinned host memory into the
+    symmetric tensor and a scalar of the result read back every step."""
+    host = torch.empty(count, dtype=dtype).pin_memory()
+    host.copy_(torch.rand(count).to(dtype))
+    probe = torch.empty(16, dtype=dtype).pin_memory()
+    steps = max(2, min(a.steps, 5))
+
+    def step():
+        buf.copy_(host, non_blocking=True)
+        comm.all_reduce(buf)
+        probe.copy_(buf[:16], non_blocking=True)
+
+    step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(steps):
+        step()
+    e.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([s.elapsed_time(e)], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = t.item() / steps
+    nbytes = count * host.element_size()
+    return {"value": round(busbw(nbytes, ms, world), 1), "unit": "GB/s", "ms_per_step": round(ms, 4),
+            "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": probe.numel() * probe.element_size(), "steps": steps}
+
+
+if __name__ == "__main__":
+    sys.exit(main())

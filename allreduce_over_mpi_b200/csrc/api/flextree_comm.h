@@ -1,0 +1,114 @@
+/* FlexTree multi-GPU communicator — C API.
+ *
+ * One communicator per (process, GPU, stream of use).  Each rank owns a "symmetric heap":
+ * device memory that every other rank maps into its own address space (CUDA VMM
+ * allocations shared as POSIX file descriptors, or cudaMalloc + CUDA IPC handles), plus
+ * a flag array for rendezvous.  Collective kernels read peers' heaps directly over
+ * NVLink; nothing on the data path calls NCCL or MPI.
+ *
+ * Set-up protocol (the bootstrap that carries handles between processes is the
+ * caller's: torch.distributed in the Python package):
+ *     ft_comm_create                       every rank
+ *     ft_comm_export_fd / _export_ipc      every rank, handle goes to all peers
+ *     ft_comm_import_fd / _import_ipc      once per peer
+ *     [ft_comm_mc_create on rank 0, ft_comm_mc_join on all, barrier, ft_comm_mc_bind on all]
+ *     ft_comm_finalize
+ * or ft_comm_connect_local() for communicators that live in one process.
+ *
+ * Role in the reference: MPI_COMM_WORLD + the per-call staging buffer
+ * (flextree_register_the_buffer, allreduce_over_mpi/mpi_mod.hpp:1489-1507) + the
+ * MPI_Comm_split sub-communicators (:1541-1548).
+ */
+#ifndef FLEXTREE_COMM_H_
+#define FLEXTREE_COMM_H_
+
+#include "ft_types.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct ft_comm ft_comm;
+
+enum { FT_MEM_IPC = 0, FT_MEM_VMM = 1 };
+enum { FT_ALGO_AUTO = 0, FT_ALGO_STAGED = 1, FT_ALGO_ONESHOT = 2, FT_ALGO_NVLS = 3 };
+
+/* heap_bytes: symmetric memory for user tensors (ft_comm_alloc) and internal staging.
+ * staging_bytes: size of ONE staging slot (two are carved out of the heap); bounds the
+ * message size of calls on tensors that do not live in the heap.
+ * mem_kind: FT_MEM_VMM or FT_MEM_IPC.  The calling thread's current device must be `device`. */
+int ft_comm_create(int rank, int world, int device, size_t heap_bytes, size_t staging_bytes, int mem_kind,
+                   ft_comm** out);
+int ft_comm_destroy(ft_comm* c);
+const char* ft_comm_last_error(ft_comm* c);
+
+int ft_comm_export_fd(ft_comm* c, int* fd_out);                 /* VMM: fd of my heap allocation */
+int ft_comm_import_fd(ft_comm* c, int peer, int fd);            /* VMM: map a peer's heap */
+int ft_comm_export_ipc(ft_comm* c, void* blob64);               /* IPC: 64-byte cudaIpcMemHandle_t */
+int ft_comm_import_ipc(ft_comm* c, int peer, const void* blob64);
+/* communicators of one process (any mix of devices, or several ranks on one device for
+ * single-GPU emulation): map each other directly, then finalize all of them */
+int ft_comm_connect_local(ft_comm** comms, int n);
+int ft_comm_finalize(ft_comm* c);
+
+/* NVLS multicast (optional; VMM heaps only) */
+int ft_comm_mc_supported(ft_comm* c);
+int ft_comm_mc_create(ft_comm* c, int* fd_out);                 /* one rank creates the multicast object */
+int ft_comm_mc_join(ft_comm* c, int fd);                        /* fd < 0: the creator joins its own object */
+int ft_comm_mc_bind(ft_comm* c);                                /* after EVERY rank has joined */
+int ft_comm_has_nvls(ft_comm* c);
+
+/* symmetric heap */
+void* ft_comm_heap_base(ft_comm* c);
+size_t ft_comm_heap_bytes(ft_comm* c);       /* bytes available to ft_comm_alloc */
+/* bump allocation of `bytes` (256-byte aligned) at the same offset on every rank, provided
+ * every rank issues the same sequence of calls; returns NULL when the heap is exhausted */
+void* ft_comm_alloc(ft_comm* c, size_t bytes);
+void ft_comm_alloc_reset(ft_comm* c);
+int ft_comm_rank(ft_comm* c);
+int ft_comm_world(ft_comm* c);
+int ft_comm_mem_kind(ft_comm* c);
+
+/* tuning knobs */
+void ft_comm_set_timeout_ms(ft_comm* c, double ms);             /* bound of every device-side wait */
+void ft_comm_set_max_lanes(ft_comm* c, int lanes);              /* CTAs per collective kernel (<= 512) */
+
+/* All-reduce of `count` elements.  recvbuf inside the symmetric heap: in place, zero copy
+ * (sendbuf must be NULL or == recvbuf).  Otherwise the input is staged through the
+ * internal slots and the result lands in recvbuf (count * size <= staging_bytes).
+ * shape: (widths, nw, lonely, ring) as in flextree.h; nw == 0 means flat.
+ * algo: FT_ALGO_*; AUTO picks one-shot below `oneshot_max_bytes` (64 KiB unless changed with
+ * ft_comm_set_oneshot_max), else the staged plan.
+ * scale: multiplied into floating-point results (1/world for averaging).
+ * Asynchronous on `stream`; errors of device-side waits surface in ft_comm_status. */
+int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op, const int* widths,
+                 int nw, int lonely, int ring, int algo, float scale, void* stream);
+void ft_comm_set_oneshot_max(ft_comm* c, size_t bytes);
+
+/* Single-GPU emulation helper: run only stages [stage_begin, stage_end) of the plan with no
+ * rendezvous (the caller serialises ranks and stages on one stream). */
+int ft_allreduce_emulate_stage(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op,
+                               const int* widths, int nw, int lonely, int ring, float scale, int stage_begin,
+                               int stage_end, void* stream);
+/* one-shot emulation: phase 1 = publish input (all ranks first), phase 4 = reduce */
+int ft_allreduce_emulate_oneshot(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op,
+                                 float scale, int phase, uint64_t call, void* stream);
+
+/* status block written by kernels whose bounded wait ran out: out[0..4] =
+ * {ft_status, rendezvous index, peer, lane, calls completed}.  Synchronises nothing: call
+ * after the stream is idle.  ft_comm_clear_status resets it. */
+int ft_comm_status(ft_comm* c, int* out5);
+void ft_comm_clear_status(ft_comm* c);
+/* launches a kernel that waits `timeout_ms` for a signal from `peer` that never comes */
+int ft_comm_wait_probe(ft_comm* c, int peer, double timeout_ms, void* stream);
+
+/* fd passing between processes of one node over abstract unix sockets */
+int ft_fd_listen(const char* name);                                   /* -> listening socket or -1 */
+int ft_fd_send(const char* name, int fd_to_send, int tag, int timeout_ms);   /* 0 on success */
+int ft_fd_recv(int listen_sock, int* tag_out, int timeout_ms);        /* -> received fd or -1 */
+void ft_fd_close(int fd);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLEXTREE_COMM_H_ */

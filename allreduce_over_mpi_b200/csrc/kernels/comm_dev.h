@@ -1,0 +1,95 @@
+// Structures shared by the communicator runtime (host) and the collective kernels.
+#pragma once
+#include <stdint.h>
+
+#include "../api/ft_types.h"
+
+namespace ftk {
+
+constexpr int kMaxLanes = 512;     // CTAs of one collective kernel
+constexpr int kMaxStages = 128;    // ring over 64 ranks has 126
+
+struct Status {          // lives in pinned host memory, read by the host after a sync
+  int code;              // ft_status; first failure wins
+  int index;             // rendezvous index inside the call
+  int peer;
+  int lane;
+  unsigned int calls;    // bumped by lane 0 of every collective kernel (progress marker)
+};
+
+typedef unsigned long long flag_t;
+constexpr flag_t kCallStride = 256;  // rendezvous numbers reserved per call (> kMaxStages + 2)
+
+
+// Per-rank view of the world: where every rank's symmetric heap and flag array are
+// mapped in THIS process, plus local bookkeeping.  Passed by value to every kernel.
+struct CommDev {
+  unsigned char* heap[FT_MAX_RANKS];   // heap[r] = base of rank r's symmetric heap (peer mapping)
+  unsigned long long* flags[FT_MAX_RANKS];  // flags[r] = rank r's flag array [kMaxLanes][FT_MAX_RANKS]
+  unsigned char* mc_heap;              // multicast mapping of the heaps (NVLS), or null
+  unsigned long long* call_count;      // local: number of collective calls so far (read by every CTA)
+  unsigned int* arrived;               // local: CTAs of the running kernel that have read call_count
+  Status* status;                      // pinned host memory
+  int rank, world;
+  unsigned long long timeout_ns;
+};
+
+// One pull of the plan, device form.
+struct DevPull {
+  uint16_t block;
+  uint8_t nsrc;
+  uint8_t reduce;
+  uint8_t src[FT_MAX_FANIN];
+};
+struct DevStage {
+  uint32_t pull_begin, pull_end;
+  uint64_t sync_mask;     // ranks met before this stage
+  uint32_t last_rs;       // 1 when this is the final reduce-scatter stage (scale applies here)
+  uint32_t is_ag;
+};
+struct DevPlan {
+  uint32_t nstages, npulls;
+  uint64_t end_sync_mask;
+  DevStage stages[kMaxStages];
+  // DevPull pulls[npulls] follow
+};
+
+// Arguments of one staged all-reduce launch.
+struct StagedArgs {
+  const DevPlan* plan;
+  const DevPull* pulls;
+  uint64_t work_off;          // byte offset of the work buffer inside every rank's heap
+  uint64_t alt_stride;        // staging mode: odd calls use work_off + alt_stride (double buffer); else 0
+  const void* user_in;        // not null: copied into the work buffer first (lane-sliced)
+  void* user_out;             // not null: every finished block is also written here
+  uint64_t count;             // elements
+  uint64_t block_elems;       // elements per block (block bytes are a multiple of 16)
+  uint32_t elem_size;
+  uint32_t stage_begin, stage_end;   // [begin, end) — the full plan unless emulating
+  uint32_t do_sync;           // 0: no rendezvous at all (single-GPU emulation, one stage per launch)
+  uint32_t end_sync;          // closing rendezvous wanted
+  uint32_t user_vec_ok;       // user_in / user_out are 16-byte aligned
+  float scale;                // applied when a block's reduction completes (float types)
+};
+
+struct OneShotArgs {
+  uint64_t slot_off;          // byte offset of staging slot 0 in every heap (slot 1 follows it)
+  uint64_t emu_call;          // call number to assume when the rendezvous phase is off (emulation)
+  const void* user_in;
+  void* user_out;
+  uint64_t count;
+  uint32_t elem_size;
+  uint32_t phase_mask;        // bit0 copy-in, bit1 rendezvous, bit2 reduce (all three normally)
+  uint32_t user_vec_ok;
+  float scale;
+};
+
+struct NvlsArgs {
+  uint64_t work_off;
+  uint64_t count;
+  uint64_t block_elems;
+  uint32_t elem_size;
+  float scale;
+};
+
+}  // namespace ftk

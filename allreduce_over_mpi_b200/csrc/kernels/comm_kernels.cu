@@ -1,0 +1,385 @@
+// Multi-GPU collective kernels over NVLink peer memory (sm_100a).
+//
+//  * staged_allreduce_kernel   executes a FlexTree plan (flat, multi-level tree, lonely
+//    layouts, ring): per stage, rendezvous with the stage's peers, then for every pull
+//    load the block from the listed peers' symmetric heaps with 16-byte loads over
+//    NVSwitch, add them to the own copy in fp32 registers, store once.  Transfer and
+//    reduction are one pass; there is no staging buffer and no library call.  This is
+//    the device form of the reference's per-stage Isend/Irecv/Waitall + handle_reduce +
+//    Barrier loop (allreduce_over_mpi/mpi_mod.hpp:1550-1596, :1620-1644).
+//  * oneshot_allreduce_kernel  every rank publishes its input in a staging slot, one
+//    rendezvous, every rank sums all N copies itself (latency-optimal for small sizes).
+//  * nvls_allreduce_kernel     multimem.ld_reduce / multimem.st through the NVSwitch
+//    multicast mapping (in-switch reduction), where the box exposes it.
+//
+// Work split: CTA c ("lane" c) of every rank owns the same byte sub-range of every
+// block, so all dependencies between ranks are lane-local and a rendezvous never needs
+// a grid-wide barrier.  Remote data is read with plain per-thread loads; no TMA or
+// multicast load ever targets another GPU's memory.
+#include <cstdio>
+
+#include "comm_dev.h"
+#include "signal.cuh"
+#include "vec.cuh"
+
+extern "C" void ft_count_launch(uint64_t n);
+
+namespace ftk {
+
+constexpr int kThreads = 512;
+constexpr int kUnroll = 4;
+
+// Read the communicator's call number; the last CTA to read it bumps it for the next
+// kernel on the stream.  Returns the number of THIS call to every thread.
+__device__ __forceinline__ unsigned long long begin_call(const CommDev& c, unsigned long long* smem_slot) {
+  if (threadIdx.x == 0) {
+    const unsigned long long call = *(volatile unsigned long long*)c.call_count;
+    *smem_slot = call;
+    __threadfence();
+    if (atomicAdd(c.arrived, 1u) == gridDim.x - 1) {
+      *(volatile unsigned int*)c.arrived = 0;
+      *(volatile unsigned long long*)c.call_count = call + 1;
+      if (c.status) c.status->calls = (unsigned int)(call + 1);
+    }
+  }
+  __syncthreads();
+  return *smem_slot;
+}
+
+// dst[i] = fin( init(p0[i]) + p1[i] + ... ) for 16-byte vectors i in [0, nvec_total) where
+// the last vector may be partial (`total_bytes` not a multiple of 16).  ptrs[] live in
+// shared memory.  dst_user (optional) receives the same result; it may be unaligned.
+template <class P>
+__device__ __forceinline__ void pull_range(const unsigned char* const* ptrs, int n, unsigned char* dst_work,
+                                           unsigned char* dst_user, bool user_vec_ok, uint64_t total_bytes,
+                                           uint32_t es, bool do_scale, float scale) {
+  const uint64_t nvec = (total_bytes + 15) / 16;
+  const uint64_t step = (uint64_t)blockDim.x * kUnroll;
+  for (uint64_t base = 0; base < nvec; base += step) {
+    uint64_t idx[kUnroll];
+    bool ok[kUnroll];
+    typename P::Acc acc[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      idx[u] = base + (uint64_t)u * blockDim.x + threadIdx.x;
+      ok[u] = idx[u] < nvec;
+    }
+    {
+      uint4 v[kUnroll];
+      const unsigned char* p0 = ptrs[0];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) v[u] = ok[u] ? ld_stream(p0 + idx[u] * 16) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) P::init(acc[u], v[u]);
+    }
+    int k = 1;
+    for (; k + 2 <= n; k += 2) {
+      uint4 v[2][kUnroll];
+      const unsigned char* pa = ptrs[k];
+      const unsigned char* pb = ptrs[k + 1];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) v[0][u] = ok[u] ? ld_stream(pa + idx[u] * 16) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) v[1][u] = ok[u] ? ld_stream(pb + idx[u] * 16) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) { P::add(acc[u], v[0][u]); P::add(acc[u], v[1][u]); }
+    }
+    if (k < n) {
+      uint4 v[kUnroll];
+      const unsigned char* pa = ptrs[k];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) v[u] = ok[u] ? ld_stream(pa + idx[u] * 16) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) P::add(acc[u], v[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      if (!ok[u]) continue;
+      const uint4 out = do_scale ? P::fins(acc[u], scale) : P::fin(acc[u]);
+      const uint64_t off = idx[u] * 16;
+      const uint32_t valid = (uint32_t)(total_bytes - off < 16 ? total_bytes - off : 16);
+      if (dst_work) {
+        if (valid == 16) st_vec(dst_work + off, out);
+        else st_partial(dst_work + off, out, valid, es);
+      }
+      if (dst_user) {
+        if (valid == 16 && user_vec_ok) st_vec(dst_user + off, out);
+        else st_partial(dst_user + off, out, valid, es);
+      }
+    }
+  }
+}
+
+// Plain lane-sliced copy src -> dst (src may be unaligned user memory).
+__device__ __forceinline__ void copy_range(const unsigned char* src, bool src_vec_ok, unsigned char* dst, bool dst_vec_ok,
+                                           uint64_t total_bytes, uint32_t es) {
+  const uint64_t nvec = (total_bytes + 15) / 16;
+  for (uint64_t i = threadIdx.x; i < nvec; i += blockDim.x) {
+    const uint64_t off = i * 16;
+    const uint32_t valid = (uint32_t)(total_bytes - off < 16 ? total_bytes - off : 16);
+    const uint4 v = (valid == 16 && src_vec_ok) ? ld_stream(src + off) : ld_partial(src + off, valid, es);
+    if (valid == 16 && dst_vec_ok) st_vec(dst + off, v);
+    else st_partial(dst + off, v, valid, es);
+  }
+}
+
+struct LaneSlice { uint64_t off, bytes; };
+// Sub-range of a region of `region_bytes` owned by `lane` of `nlanes` when every lane
+// takes a 16-byte-aligned chunk of `chunk` bytes.
+__device__ __forceinline__ LaneSlice lane_slice(uint64_t region_bytes, uint64_t chunk, int lane) {
+  LaneSlice s;
+  s.off = (uint64_t)lane * chunk;
+  s.bytes = s.off >= region_bytes ? 0 : (region_bytes - s.off < chunk ? region_bytes - s.off : chunk);
+  return s;
+}
+
+// ------------------------------------------------------------------------------- staged
+template <int POL>
+__global__ void __launch_bounds__(kThreads) staged_allreduce_kernel(const __grid_constant__ CommDev c, const __grid_constant__ StagedArgs a) {
+  using P = typename PolById<POL>::type;
+  __shared__ const unsigned char* ptrs[2][FT_MAX_FANIN];
+  __shared__ int abort_flag;
+  __shared__ unsigned long long call_slot;
+  const int lane = blockIdx.x, nlanes = gridDim.x;
+  if (threadIdx.x == 0) abort_flag = 0;
+  unsigned long long call = 0;
+  if (a.do_sync) call = begin_call(c, &call_slot);
+  else __syncthreads();
+
+  LaneSync sync{c.flags, c.flags[c.rank], c.rank, c.world, lane, FT_MAX_RANKS, c.timeout_ns, c.status, &abort_flag};
+  const uint32_t es = a.elem_size;
+  const uint64_t block_bytes = a.block_elems * es;               // multiple of 16
+  const uint64_t total_bytes = a.count * es;
+  uint64_t chunk = (block_bytes + nlanes - 1) / nlanes;
+  chunk = (chunk + 15) & ~15ull;
+  // staging mode alternates between two work buffers with the call parity, so that a rank
+  // may refill one while a slow peer still gathers from the other
+  const uint64_t work_off = a.work_off + (call & 1) * a.alt_stride;
+  unsigned char* my_work = c.heap[c.rank] + work_off;
+
+  auto block_len = [&](int b) -> uint64_t {   // bytes of block b that hold data
+    const uint64_t lo = (uint64_t)b * block_bytes;
+    return lo >= total_bytes ? 0 : (total_bytes - lo < block_bytes ? total_bytes - lo : block_bytes);
+  };
+
+  // stage the caller's input into the symmetric work buffer, lane-sliced like everything else
+  if (a.user_in && a.stage_begin == 0) {
+    for (int b = 0; b < c.world; ++b) {
+      const LaneSlice s = lane_slice(block_len(b), chunk, lane);
+      if (s.bytes) {
+        const uint64_t off = (uint64_t)b * block_bytes + s.off;
+        copy_range((const unsigned char*)a.user_in + off, a.user_vec_ok, my_work + off, true, s.bytes, es);
+      }
+    }
+  }
+
+  int pp = 0;
+  for (uint32_t s = a.stage_begin; s < a.stage_end; ++s) {
+    const DevStage st = a.plan->stages[s];
+    if (a.do_sync) {
+      lane_rendezvous(sync, st.sync_mask, call * kCallStride + s + 1, (int)s);
+      if (abort_flag) break;
+    }
+    for (uint32_t q = st.pull_begin; q < st.pull_end; ++q) {
+      const DevPull pl = a.pulls[q];
+      const LaneSlice sl = lane_slice(block_len(pl.block), chunk, lane);
+      if (!sl.bytes) continue;   // uniform across the CTA
+      const uint64_t off = (uint64_t)pl.block * block_bytes + sl.off;
+      const int n = pl.reduce ? pl.nsrc + 1 : 1;
+      if ((int)threadIdx.x < n) {
+        const unsigned char* p;
+        if (pl.reduce) p = threadIdx.x == 0 ? my_work + off : c.heap[pl.src[threadIdx.x - 1]] + work_off + off;
+        else p = c.heap[pl.src[0]] + work_off + off;
+        ptrs[pp][threadIdx.x] = p;
+      }
+      __syncthreads();
+      // a block is final for this rank when its last reduction happens here or when it is gathered
+      const bool final_here = st.is_ag || st.last_rs;
+      // the very last stage's gathers are read by nobody: skip the work-buffer copy when the
+      // caller takes the result elsewhere
+      const bool need_work = !(a.user_out && s + 1 == a.plan->nstages);
+      pull_range<P>(ptrs[pp], n, need_work ? my_work + off : nullptr,
+                    (a.user_out && final_here) ? (unsigned char*)a.user_out + off : nullptr, a.user_vec_ok, sl.bytes, es,
+                    st.last_rs && pl.reduce, a.scale);
+      pp ^= 1;
+    }
+  }
+  if (a.do_sync && a.end_sync && !abort_flag && a.stage_end == a.plan->nstages)
+    lane_rendezvous(sync, a.plan->end_sync_mask, call * kCallStride + a.plan->nstages + 1, (int)a.plan->nstages);
+}
+
+// ------------------------------------------------------------------------------- one-shot
+template <int POL>
+__global__ void __launch_bounds__(kThreads) oneshot_allreduce_kernel(const __grid_constant__ CommDev c, const __grid_constant__ OneShotArgs a,
+                                                                      uint64_t slot_bytes) {
+  using P = typename PolById<POL>::type;
+  __shared__ const unsigned char* ptrs[FT_MAX_RANKS];
+  __shared__ int abort_flag;
+  __shared__ unsigned long long call_slot;
+  const int lane = blockIdx.x, nlanes = gridDim.x;
+  if (threadIdx.x == 0) abort_flag = 0;
+  unsigned long long call = 0;
+  if (a.phase_mask & 2) call = begin_call(c, &call_slot);
+  else { call = a.emu_call; __syncthreads(); }
+  const uint32_t es = a.elem_size;
+  const uint64_t total_bytes = a.count * es;
+  uint64_t chunk = (total_bytes + nlanes - 1) / nlanes;
+  chunk = (chunk + 15) & ~15ull;
+  const LaneSlice sl = lane_slice(total_bytes, chunk, lane);
+  // two staging slots alternate with the call parity: a slot is rewritten only after every
+  // rank has entered the call after its last readers
+  const uint64_t slot = a.slot_off + (call & 1) * slot_bytes;
+
+  if ((a.phase_mask & 1) && sl.bytes)
+    copy_range((const unsigned char*)a.user_in + sl.off, a.user_vec_ok, c.heap[c.rank] + slot + sl.off, true, sl.bytes, es);
+  if (a.phase_mask & 2) {
+    LaneSync sync{c.flags, c.flags[c.rank], c.rank, c.world, lane, FT_MAX_RANKS, c.timeout_ns, c.status, &abort_flag};
+    unsigned long long all = c.world >= 64 ? ~0ull : ((1ull << c.world) - 1);
+    lane_rendezvous(sync, all, call * kCallStride + 1, 0);
+    if (abort_flag) return;
+  }
+  if ((a.phase_mask & 4) && sl.bytes) {
+    if ((int)threadIdx.x < c.world) ptrs[threadIdx.x] = c.heap[threadIdx.x] + slot + sl.off;   // rank order: same sum order everywhere
+    __syncthreads();
+    pull_range<P>(ptrs, c.world, nullptr, (unsigned char*)a.user_out + sl.off, a.user_vec_ok, sl.bytes, es, a.scale != 1.0f, a.scale);
+  }
+}
+
+// ------------------------------------------------------------------------------- NVLS
+// multimem.ld_reduce sums one 16-byte vector across every GPU bound to the multicast
+// object inside the switch; multimem.st writes one to all of them.
+template <int POL> struct Nvls;
+template <> struct Nvls<POL_F32> {
+  __device__ static __forceinline__ uint4 ld(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+};
+template <> struct Nvls<POL_BF16> {
+  __device__ static __forceinline__ uint4 ld(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+};
+template <> struct Nvls<POL_F16> {
+  __device__ static __forceinline__ uint4 ld(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+};
+__device__ __forceinline__ void multimem_st(void* p, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// In place on the symmetric work buffer: rank r reduces block r (lane-sliced) through the
+// switch and broadcasts the result to every rank.  Requires count*es to be a multiple of 16.
+template <int POL>
+__global__ void __launch_bounds__(kThreads) nvls_allreduce_kernel(const __grid_constant__ CommDev c, const __grid_constant__ NvlsArgs a) {
+  using P = typename PolById<POL>::type;
+  __shared__ int abort_flag;
+  __shared__ unsigned long long call_slot;
+  const int lane = blockIdx.x, nlanes = gridDim.x;
+  if (threadIdx.x == 0) abort_flag = 0;
+  const unsigned long long call = begin_call(c, &call_slot);
+  LaneSync sync{c.flags, c.flags[c.rank], c.rank, c.world, lane, FT_MAX_RANKS, c.timeout_ns, c.status, &abort_flag};
+  const unsigned long long all = c.world >= 64 ? ~0ull : ((1ull << c.world) - 1);
+  const uint32_t es = a.elem_size;
+  const uint64_t block_bytes = a.block_elems * es, total_bytes = a.count * es;
+  uint64_t chunk = (block_bytes + nlanes - 1) / nlanes;
+  chunk = (chunk + 15) & ~15ull;
+  const uint64_t lo = (uint64_t)c.rank * block_bytes;
+  const uint64_t len = lo >= total_bytes ? 0 : (total_bytes - lo < block_bytes ? total_bytes - lo : block_bytes);
+  const LaneSlice sl = lane_slice(len, chunk, lane);
+
+  lane_rendezvous(sync, all, call * kCallStride + 1, 0);   // every rank's input is in place
+  if (abort_flag) return;
+  unsigned char* mc = c.mc_heap + a.work_off + lo + sl.off;
+  const uint64_t nvec = sl.bytes / 16;
+  for (uint64_t i = threadIdx.x; i < nvec; i += (uint64_t)blockDim.x * 2) {
+    const uint64_t j = i + blockDim.x;
+    uint4 v0 = Nvls<POL>::ld(mc + i * 16), v1 = make_uint4(0, 0, 0, 0);
+    if (j < nvec) v1 = Nvls<POL>::ld(mc + j * 16);
+    if (a.scale != 1.0f) {
+      typename P::Acc t;
+      P::init(t, v0); v0 = P::fins(t, a.scale);
+      P::init(t, v1); v1 = P::fins(t, a.scale);
+    }
+    multimem_st(mc + i * 16, v0);
+    if (j < nvec) multimem_st(mc + j * 16, v1);
+  }
+  // all my broadcasts are ordered before my signal; after the rendezvous every rank's
+  // slice has landed here too
+  __threadfence_system();
+  lane_rendezvous(sync, all, call * kCallStride + 2, 1);
+}
+
+// ------------------------------------------------------------------------------- bounded-wait probe
+// One CTA waits on one of its own flags for a rendezvous number that nobody will signal.
+// With a short limit it must come back with FT_ERR_TIMEOUT in the status block.
+__global__ void wait_probe_kernel(const __grid_constant__ CommDev c, int peer, unsigned long long timeout_ns) {
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    const flag_t never = ~0ull - 1;
+    if (!wait_flag(c.flags[c.rank] + (size_t)(kMaxLanes - 1) * FT_MAX_RANKS + peer, never, timeout_ns))
+      report(c.status, FT_ERR_TIMEOUT, 0, peer, kMaxLanes - 1);
+  }
+}
+
+// ------------------------------------------------------------------------------- launchers
+template <int POL> static cudaError_t launch_staged_t(const CommDev& c, const StagedArgs& a, int lanes, cudaStream_t st) {
+  staged_allreduce_kernel<POL><<<lanes, kThreads, 0, st>>>(c, a);
+  return cudaGetLastError();
+}
+template <int POL> static cudaError_t launch_oneshot_t(const CommDev& c, const OneShotArgs& a, uint64_t slot_bytes, int lanes, cudaStream_t st) {
+  oneshot_allreduce_kernel<POL><<<lanes, kThreads, 0, st>>>(c, a, slot_bytes);
+  return cudaGetLastError();
+}
+
+#define FT_POL_SWITCH(pol, CALL)                        \
+  switch (pol) {                                        \
+    case POL_ADD8: return CALL(POL_ADD8);               \
+    case POL_ADD16: return CALL(POL_ADD16);             \
+    case POL_ADD32: return CALL(POL_ADD32);             \
+    case POL_ADD64: return CALL(POL_ADD64);             \
+    case POL_OR: return CALL(POL_OR);                   \
+    case POL_AND: return CALL(POL_AND);                 \
+    case POL_F32: return CALL(POL_F32);                 \
+    case POL_F64: return CALL(POL_F64);                 \
+    case POL_BF16: return CALL(POL_BF16);               \
+    case POL_F16: return CALL(POL_F16);                 \
+    default: return cudaErrorInvalidValue;              \
+  }
+
+cudaError_t launch_staged(int pol, const CommDev& c, const StagedArgs& a, int lanes, cudaStream_t st) {
+  ft_count_launch(1);
+#define CALL(P) launch_staged_t<P>(c, a, lanes, st)
+  FT_POL_SWITCH(pol, CALL)
+#undef CALL
+}
+cudaError_t launch_oneshot(int pol, const CommDev& c, const OneShotArgs& a, uint64_t slot_bytes, int lanes, cudaStream_t st) {
+  ft_count_launch(1);
+#define CALL(P) launch_oneshot_t<P>(c, a, slot_bytes, lanes, st)
+  FT_POL_SWITCH(pol, CALL)
+#undef CALL
+}
+cudaError_t launch_nvls(int pol, const CommDev& c, const NvlsArgs& a, int lanes, cudaStream_t st) {
+  ft_count_launch(1);
+  switch (pol) {
+    case POL_F32: nvls_allreduce_kernel<POL_F32><<<lanes, kThreads, 0, st>>>(c, a); break;
+    case POL_BF16: nvls_allreduce_kernel<POL_BF16><<<lanes, kThreads, 0, st>>>(c, a); break;
+    case POL_F16: nvls_allreduce_kernel<POL_F16><<<lanes, kThreads, 0, st>>>(c, a); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+cudaError_t launch_wait_probe(const CommDev& c, int peer, unsigned long long timeout_ns, cudaStream_t st) {
+  ft_count_launch(1);
+  wait_probe_kernel<<<1, 32, 0, st>>>(c, peer, timeout_ns);
+  return cudaGetLastError();
+}
+
+}  // namespace ftk

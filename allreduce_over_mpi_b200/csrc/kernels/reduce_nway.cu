@@ -286,13 +286,14 @@ static int run_policy(NwayArgs& a, size_t bytes, int variant, cudaStream_t st) {
         case 11: e = launch_vec<POL, 2, 2>(a, 512, 4, st); done = true; break;
         case 12: e = launch_vec<POL, 2, 4>(a, 512, 4, st); done = true; break;
         case 13: e = launch_vec<POL, 4, 2>(a, 512, 2, st); done = true; break;
-        case 14: e = launch_vec<POL, 4, 4>(a, 256, 4, st); done = true; break;
+        case 14: e = launch_vec<POL, 4, 2>(a, 512, 4, st); done = true; break;
         case 15: e = launch_vec<POL, 4, 2>(a, 256, 8, st); done = true; break;
         case 16: e = launch_vec<POL, 8, 1>(a, 256, 4, st); done = true; break;
         default: break;
       }
     }
-    if (!done) e = launch_vec<POL, 4, 2>(a, 512, 4, st);
+    // default picked from a B200 sweep: 4 vectors x 4 sources in flight, 256 threads, 4 CTAs per SM
+    if (!done) e = launch_vec<POL, 4, 4>(a, 256, 4, st);
     if (e != cudaSuccess) return cuda_fail(e, "reduce_nway vector launch");
   }
   e = launch_scalar<POL>(a, a.nvec * 16 / unit, st);
@@ -352,8 +353,8 @@ int ft_reduce_nway(int op, int dtype, const void* const* src, void* dst, int n, 
   const int pol = policy_id(op, dtype);
   if (pol < 0) return FT_ERR_UNSUPPORTED_TYPE;
   if (n < 1 || n > FT_MAX_FANIN) return n > FT_MAX_FANIN ? FT_ERR_TOO_LARGE : FT_ERR_INVALID_ARG;
-  if (!src || !dst) return FT_ERR_INVALID_ARG;
   if (len == 0) return FT_OK;
+  if (!src || !dst) return FT_ERR_INVALID_ARG;
   NwayArgs a{};
   for (int k = 0; k < n; ++k) {
     if (!src[k]) return FT_ERR_INVALID_ARG;
@@ -381,8 +382,9 @@ int ft_reduce_nway(int op, int dtype, const void* const* src, void* dst, int n, 
 int ft_reduce_nway_scaled(int in_dtype, int out_dtype, const void* const* src, void* dst, int n, size_t len, float scale, void* stream) {
   using namespace ftk;
   if ((in_dtype != FT_F32 && in_dtype != FT_BF16) || (out_dtype != FT_F32 && out_dtype != FT_BF16)) return FT_ERR_UNSUPPORTED_TYPE;
-  if (n < 1 || n > FT_MAX_FANIN || !src || !dst) return FT_ERR_INVALID_ARG;
+  if (n < 1 || n > FT_MAX_FANIN) return FT_ERR_INVALID_ARG;
   if (len == 0) return FT_OK;
+  if (!src || !dst) return FT_ERR_INVALID_ARG;
   NwayArgs a{};
   bool aligned = ((uintptr_t)dst & 15) == 0;
   for (int k = 0; k < n; ++k) { a.src[k] = src[k]; aligned = aligned && (((uintptr_t)src[k] & 15) == 0); }

@@ -11,6 +11,7 @@
 #include <stdint.h>
 
 #include "../api/ft_types.h"
+#include "pol_ids.h"
 
 namespace ftk {
 
@@ -35,6 +36,30 @@ __device__ __forceinline__ void st_vec(void* p, uint4 v) {
 }
 __device__ __forceinline__ void st_vec_cs(void* p, uint4 v) {  // evict-first: written once, not re-read by this kernel
   asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Store the first `nbytes` (< 16, a multiple of `es`) bytes of v with element-sized stores.
+__device__ __forceinline__ void st_partial(void* p, uint4 v, uint32_t nbytes, uint32_t es) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  unsigned char* d = (unsigned char*)p;
+  for (uint32_t b = 0; b < nbytes; b += es) {
+    if (es == 8) { ((volatile uint32_t*)(d + b))[0] = w[b / 4]; ((volatile uint32_t*)(d + b))[1] = w[b / 4 + 1]; }
+    else if (es == 4) *(volatile uint32_t*)(d + b) = w[b / 4];
+    else if (es == 2) *(volatile uint16_t*)(d + b) = (uint16_t)(w[b / 4] >> ((b & 2) * 8));
+    else *(volatile uint8_t*)(d + b) = (uint8_t)(w[b / 4] >> ((b & 3) * 8));
+  }
+}
+// Gather `nbytes` (<= 16) from an address that is only element-aligned.
+__device__ __forceinline__ uint4 ld_partial(const void* p, uint32_t nbytes, uint32_t es) {
+  uint32_t w[4] = {0, 0, 0, 0};
+  const unsigned char* s = (const unsigned char*)p;
+  for (uint32_t b = 0; b < nbytes; b += es) {
+    if (es == 8) { w[b / 4] = ((const volatile uint32_t*)(s + b))[0]; w[b / 4 + 1] = ((const volatile uint32_t*)(s + b))[1]; }
+    else if (es == 4) w[b / 4] = *(const volatile uint32_t*)(s + b);
+    else if (es == 2) w[b / 4] |= (uint32_t)(*(const volatile uint16_t*)(s + b)) << ((b & 2) * 8);
+    else w[b / 4] |= (uint32_t)(*(const volatile uint8_t*)(s + b)) << ((b & 3) * 8);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 // ---- element types --------------------------------------------------------------------
@@ -62,6 +87,8 @@ struct PolWordsBase {
   struct Acc { uint4 v; };
   __device__ static __forceinline__ void init(Acc& a, uint4 v) { a.v = v; }
   __device__ static __forceinline__ uint4 fin(const Acc& a) { return a.v; }
+  // integer / bitwise results are never scaled
+  __device__ static __forceinline__ uint4 fins(const Acc& a, float) { return a.v; }
 };
 #define FT_WORD_POLICY(NAME, EXPR)                                              \
   struct NAME : PolWordsBase {                                                  \
@@ -95,6 +122,7 @@ struct PolF64 {
   __device__ static __forceinline__ uint4 fin(const Acc& s) {
     return make_uint4((uint32_t)__double2loint(s.a), (uint32_t)__double2hiint(s.a), (uint32_t)__double2loint(s.b), (uint32_t)__double2hiint(s.b));
   }
+  __device__ static __forceinline__ uint4 fins(const Acc& s, float k) { Acc t{s.a * (double)k, s.b * (double)k}; return fin(t); }
 };
 struct PolF32 {
   struct Acc { float f[4]; };
@@ -106,6 +134,9 @@ struct PolF32 {
   }
   __device__ static __forceinline__ uint4 fin(const Acc& s) {
     return make_uint4(__float_as_uint(s.f[0]), __float_as_uint(s.f[1]), __float_as_uint(s.f[2]), __float_as_uint(s.f[3]));
+  }
+  __device__ static __forceinline__ uint4 fins(const Acc& s, float k) {
+    return make_uint4(__float_as_uint(s.f[0] * k), __float_as_uint(s.f[1] * k), __float_as_uint(s.f[2] * k), __float_as_uint(s.f[3] * k));
   }
 };
 __device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
@@ -127,6 +158,9 @@ struct PolBF16 {
   }
   __device__ static __forceinline__ uint4 fin(const Acc& s) {
     return make_uint4(pack_bf16x2(s.f[0], s.f[1]), pack_bf16x2(s.f[2], s.f[3]), pack_bf16x2(s.f[4], s.f[5]), pack_bf16x2(s.f[6], s.f[7]));
+  }
+  __device__ static __forceinline__ uint4 fins(const Acc& s, float k) {
+    return make_uint4(pack_bf16x2(s.f[0] * k, s.f[1] * k), pack_bf16x2(s.f[2] * k, s.f[3] * k), pack_bf16x2(s.f[4] * k, s.f[5] * k), pack_bf16x2(s.f[6] * k, s.f[7] * k));
   }
 };
 __device__ __forceinline__ float2 h2f(uint32_t w) {
@@ -151,6 +185,9 @@ struct PolF16 {
   __device__ static __forceinline__ uint4 fin(const Acc& s) {
     return make_uint4(f2h(s.f[0], s.f[1]), f2h(s.f[2], s.f[3]), f2h(s.f[4], s.f[5]), f2h(s.f[6], s.f[7]));
   }
+  __device__ static __forceinline__ uint4 fins(const Acc& s, float k) {
+    return make_uint4(f2h(s.f[0] * k, s.f[1] * k), f2h(s.f[2] * k, s.f[3] * k), f2h(s.f[4] * k, s.f[5] * k), f2h(s.f[6] * k, s.f[7] * k));
+  }
 };
 
 template <int DT, int OP> struct Policy;
@@ -165,7 +202,6 @@ FT_POL(FT_I32, FT_BAND, PolAnd) FT_POL(FT_U32, FT_BAND, PolAnd) FT_POL(FT_I64, F
 
 // Policy ids used by the type-erased kernels: many (dtype, op) pairs share one policy,
 // so kernels are instantiated per policy, not per pair.
-enum PolId { POL_ADD8 = 0, POL_ADD16, POL_ADD32, POL_ADD64, POL_OR, POL_AND, POL_F32, POL_F64, POL_BF16, POL_F16, POL_COUNT };
 template <int ID> struct PolById;
 template <> struct PolById<POL_ADD8> { using type = PolAdd8; };
 template <> struct PolById<POL_ADD16> { using type = PolAdd16; };
@@ -177,29 +213,6 @@ template <> struct PolById<POL_F32> { using type = PolF32; };
 template <> struct PolById<POL_F64> { using type = PolF64; };
 template <> struct PolById<POL_BF16> { using type = PolBF16; };
 template <> struct PolById<POL_F16> { using type = PolF16; };
-
-// -1 when (op, dtype) has no kernel.
-inline int policy_id(int op, int dt) {
-  if (op == FT_BAND) {
-    switch (dt) {
-      case FT_U8: case FT_I8: case FT_U16: case FT_I16: case FT_I32: case FT_U32: case FT_I64: case FT_U64: return POL_AND;
-      default: return -1;
-    }
-  }
-  if (op != FT_SUM) return -1;
-  switch (dt) {
-    case FT_U8: case FT_I8: return POL_ADD8;
-    case FT_U16: case FT_I16: return POL_ADD16;
-    case FT_I32: case FT_U32: return POL_ADD32;
-    case FT_I64: case FT_U64: return POL_ADD64;
-    case FT_BOOL: return POL_OR;
-    case FT_F32: return POL_F32;
-    case FT_F64: return POL_F64;
-    case FT_BF16: return POL_BF16;
-    case FT_F16: return POL_F16;
-    default: return -1;
-  }
-}
 
 // ---- scalar fallbacks (unaligned bases, ragged tails) ------------------------------------
 // One element at a time, same arithmetic as the vector policies.

@@ -1,0 +1,671 @@
+// FlexTree communicator runtime: symmetric heaps, peer mappings, NVLS multicast binding,
+// device plan tables and the host side of every collective launch.
+//
+// The CUDA driver API (virtual memory management, multicast objects) is resolved at run
+// time through cudaGetDriverEntryPoint, so the library has no link-time dependency on
+// libcuda and still loads on a machine without a driver.
+//
+// Reference counterpart: FlexTree_Context (allreduce_over_mpi/mpi_mod.hpp:776-809), the
+// grow-only staging buffer (:1489-1507), the entry point's dispatch (:1723-1778) and
+// tree_allreduce's per-call planning (:1520-1548) — with the plan cached per shape
+// instead of rebuilt on every call.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../api/flextree.h"
+#include "../api/flextree_comm.h"
+#include "../kernels/comm_dev.h"
+#include "../kernels/pol_ids.h"
+#include "../planner/plan.hpp"
+#include <unistd.h>
+
+namespace ftk {
+cudaError_t launch_staged(int pol, const CommDev& c, const StagedArgs& a, int lanes, cudaStream_t st);
+cudaError_t launch_oneshot(int pol, const CommDev& c, const OneShotArgs& a, uint64_t slot_bytes, int lanes, cudaStream_t st);
+cudaError_t launch_nvls(int pol, const CommDev& c, const NvlsArgs& a, int lanes, cudaStream_t st);
+cudaError_t launch_wait_probe(const CommDev& c, int peer, unsigned long long timeout_ns, cudaStream_t st);
+}  // namespace ftk
+
+namespace {
+
+// ---- driver API, resolved lazily -------------------------------------------------------
+struct Driver {
+  bool ok = false;
+  std::string why;
+#define FT_DRV(name) decltype(&name) p_##name = nullptr;
+  FT_DRV(cuMemCreate) FT_DRV(cuMemRelease) FT_DRV(cuMemGetAllocationGranularity) FT_DRV(cuMemAddressReserve)
+  FT_DRV(cuMemAddressFree) FT_DRV(cuMemMap) FT_DRV(cuMemUnmap) FT_DRV(cuMemSetAccess)
+  FT_DRV(cuMemExportToShareableHandle) FT_DRV(cuMemImportFromShareableHandle) FT_DRV(cuDeviceGetAttribute)
+  FT_DRV(cuMulticastCreate) FT_DRV(cuMulticastAddDevice) FT_DRV(cuMulticastBindMem) FT_DRV(cuMulticastUnbind)
+  FT_DRV(cuMulticastGetGranularity) FT_DRV(cuGetErrorString)
+#undef FT_DRV
+};
+
+Driver& driver() {
+  static Driver d;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    cudaFree(nullptr);  // make sure the runtime (and with it the driver) is initialised
+    auto get = [&](const char* name, void** fn) {
+      cudaDriverEntryPointQueryResult q;
+      if (cudaGetDriverEntryPoint(name, fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || !*fn) {
+        if (d.why.empty()) d.why = std::string("driver entry point missing: ") + name;
+        cudaGetLastError();
+        return false;
+      }
+      return true;
+    };
+    bool all = true;
+#define FT_GET(name) all = get(#name, (void**)&d.p_##name) && all;
+    FT_GET(cuMemCreate) FT_GET(cuMemRelease) FT_GET(cuMemGetAllocationGranularity) FT_GET(cuMemAddressReserve)
+    FT_GET(cuMemAddressFree) FT_GET(cuMemMap) FT_GET(cuMemUnmap) FT_GET(cuMemSetAccess)
+    FT_GET(cuMemExportToShareableHandle) FT_GET(cuMemImportFromShareableHandle) FT_GET(cuDeviceGetAttribute)
+    FT_GET(cuGetErrorString)
+#undef FT_GET
+    d.ok = all;
+    // multicast is optional
+    get("cuMulticastCreate", (void**)&d.p_cuMulticastCreate);
+    get("cuMulticastAddDevice", (void**)&d.p_cuMulticastAddDevice);
+    get("cuMulticastBindMem", (void**)&d.p_cuMulticastBindMem);
+    get("cuMulticastUnbind", (void**)&d.p_cuMulticastUnbind);
+    get("cuMulticastGetGranularity", (void**)&d.p_cuMulticastGetGranularity);
+  });
+  return d;
+}
+
+std::string cu_err(CUresult r) {
+  const char* s = nullptr;
+  if (driver().p_cuGetErrorString) driver().p_cuGetErrorString(r, &s);
+  return s ? s : ("CUresult " + std::to_string((int)r));
+}
+
+constexpr size_t kFlagBytes = (size_t)ftk::kMaxLanes * FT_MAX_RANKS * sizeof(ftk::flag_t);
+size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+struct DevPlanEntry {
+  ftk::DevPlan* plan = nullptr;   // device
+  ftk::DevPull* pulls = nullptr;  // device
+  int nstages = 0;
+};
+
+}  // namespace
+
+struct ft_comm {
+  int rank = 0, world = 1, device = 0, mem_kind = FT_MEM_VMM;
+  size_t user_bytes = 0, staging_bytes = 0, total_bytes = 0, staging_off = 0, flags_off = 0, bump = 0;
+  // local allocation
+  CUmemGenericAllocationHandle handle = 0;
+  CUdeviceptr va = 0;
+  void* ipc_ptr = nullptr;
+  // peers
+  unsigned char* peer_base[FT_MAX_RANKS] = {};
+  CUmemGenericAllocationHandle peer_handle[FT_MAX_RANKS] = {};
+  bool peer_is_ipc[FT_MAX_RANKS] = {};
+  bool peer_is_vmm[FT_MAX_RANKS] = {};
+  // multicast
+  CUmemGenericAllocationHandle mc_handle = 0;
+  CUdeviceptr mc_va = 0;
+  bool mc_have = false, mc_joined = false, mc_bound = false;
+  // local device state
+  unsigned long long* call_count = nullptr;
+  unsigned int* arrived = nullptr;
+  ftk::Status* status_host = nullptr;
+  ftk::Status* status_dev = nullptr;
+  double timeout_ms = 10000.0;
+  int max_lanes = 0, sms = 148;
+  size_t oneshot_max = 64 << 10;
+  std::map<std::string, DevPlanEntry> plans;
+  ftk::CommDev dev{};
+  bool finalized = false;
+  std::string err;
+};
+
+namespace {
+
+int fail(ft_comm* c, int code, const std::string& what) {
+  if (c) c->err = what;
+  return code;
+}
+#define FT_CUDA(c, call)                                                                        \
+  do {                                                                                          \
+    cudaError_t e_ = (call);                                                                    \
+    if (e_ != cudaSuccess) return fail(c, FT_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(e_)); \
+  } while (0)
+#define FT_CU(c, call)                                                                          \
+  do {                                                                                          \
+    CUresult r_ = (call);                                                                       \
+    if (r_ != CUDA_SUCCESS) return fail(c, FT_ERR_CUDA, std::string(#call) + ": " + cu_err(r_)); \
+  } while (0)
+
+CUmemAllocationProp vmm_prop(int device) {
+  CUmemAllocationProp p{};
+  p.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+  p.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  p.location.id = device;
+  p.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+  return p;
+}
+
+int map_handle(ft_comm* c, CUmemGenericAllocationHandle h, size_t bytes, CUdeviceptr* out) {
+  Driver& d = driver();
+  CUdeviceptr va = 0;
+  FT_CU(c, d.p_cuMemAddressReserve(&va, bytes, 0, 0, 0));
+  FT_CU(c, d.p_cuMemMap(va, bytes, 0, h, 0));
+  CUmemAccessDesc acc{};
+  acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  acc.location.id = c->device;
+  acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+  FT_CU(c, d.p_cuMemSetAccess(va, bytes, &acc, 1));
+  *out = va;
+  return FT_OK;
+}
+
+unsigned char* local_base(ft_comm* c) { return c->mem_kind == FT_MEM_VMM ? (unsigned char*)c->va : (unsigned char*)c->ipc_ptr; }
+
+ft::Shape make_shape(int world, const int* widths, int nw, int lonely, int ring) {
+  ft::Shape s;
+  if (widths && nw > 0) s.widths.assign(widths, widths + nw);
+  else s.widths = {world};
+  s.lonely = lonely;
+  s.ring = ring != 0;
+  return s;
+}
+
+// Build (once per shape) this rank's device plan table.
+int get_plan(ft_comm* c, const ft::Shape& shape, DevPlanEntry** out) {
+  const std::string key = shape.str();
+  auto it = c->plans.find(key);
+  if (it != c->plans.end()) { *out = &it->second; return FT_OK; }
+  ft::Plan p = ft::build_plan(c->world, shape);
+  if (!p.ok()) return fail(c, FT_ERR_INVALID_TOPO, "invalid FT_TOPO " + key + " (" + p.error + ")");
+  if (p.num_stages > ftk::kMaxStages) return fail(c, FT_ERR_TOO_LARGE, "plan has too many stages");
+  std::vector<ftk::DevPull> pulls;
+  ftk::DevPlan hp{};
+  hp.nstages = (uint32_t)p.num_stages;
+  auto mask_of = [](const std::vector<int>& v) {
+    uint64_t m = 0;
+    for (int q : v) m |= 1ull << q;
+    return m;
+  };
+  const int last_rs = p.num_stages / 2 - 1;
+  for (int s = 0; s < p.num_stages; ++s) {
+    ftk::DevStage& ds = hp.stages[s];
+    ds.pull_begin = (uint32_t)pulls.size();
+    for (const ft::Pull& pl : p.stages[c->rank][s].pulls) {
+      ftk::DevPull dp{};
+      dp.block = (uint16_t)pl.block;
+      dp.nsrc = (uint8_t)pl.srcs.size();
+      dp.reduce = pl.reduce ? 1 : 0;
+      for (size_t i = 0; i < pl.srcs.size() && i < FT_MAX_FANIN; ++i) dp.src[i] = (uint8_t)pl.srcs[i];
+      pulls.push_back(dp);
+    }
+    ds.pull_end = (uint32_t)pulls.size();
+    ds.sync_mask = mask_of(p.sync[s][c->rank]);
+    ds.last_rs = (s == last_rs);
+    ds.is_ag = !p.stages[c->rank][s].reduce_scatter || s > last_rs;
+  }
+  hp.npulls = (uint32_t)pulls.size();
+  hp.end_sync_mask = mask_of(p.sync[p.num_stages][c->rank]);
+  DevPlanEntry e;
+  e.nstages = p.num_stages;
+  FT_CUDA(c, cudaMalloc(&e.plan, sizeof(ftk::DevPlan)));
+  FT_CUDA(c, cudaMalloc(&e.pulls, sizeof(ftk::DevPull) * (pulls.size() + 1)));
+  FT_CUDA(c, cudaMemcpy(e.plan, &hp, sizeof hp, cudaMemcpyHostToDevice));
+  if (!pulls.empty()) FT_CUDA(c, cudaMemcpy(e.pulls, pulls.data(), sizeof(ftk::DevPull) * pulls.size(), cudaMemcpyHostToDevice));
+  *out = &c->plans.emplace(key, e).first->second;
+  return FT_OK;
+}
+
+bool in_heap(ft_comm* c, const void* p, size_t bytes) {
+  const unsigned char* b = local_base(c);
+  const unsigned char* q = (const unsigned char*)p;
+  return b && q >= b && q + bytes <= b + c->user_bytes;
+}
+
+// Elements per block: ceil(count/world) rounded up so that a block is a whole number of
+// 16-byte vectors (trailing blocks come out short or empty, like the reference's split).
+uint64_t pick_block_elems(uint64_t count, int world, uint32_t es) {
+  const uint64_t per = 16 / es;
+  uint64_t b = (count + world - 1) / (uint64_t)world;
+  b = (b + per - 1) / per * per;
+  return b ? b : per;
+}
+
+int pick_lanes(ft_comm* c, uint64_t region_bytes, uint64_t min_chunk) {
+  uint64_t lanes = region_bytes / min_chunk;
+  if (lanes < 1) lanes = 1;
+  const int cap = c->max_lanes > 0 ? c->max_lanes : c->sms;
+  if (lanes > (uint64_t)cap) lanes = cap;
+  if (lanes > (uint64_t)ftk::kMaxLanes) lanes = ftk::kMaxLanes;
+  return (int)lanes;
+}
+
+struct Prepared {
+  int pol;
+  uint32_t es;
+  uint64_t bytes;
+  bool heap_resident;
+};
+int prepare(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op, Prepared* out) {
+  if (!c || !c->finalized) return fail(c, FT_ERR_INVALID_ARG, "communicator not finalized");
+  if (op < 0 || op >= FT_OP_COUNT) return fail(c, FT_ERR_UNSUPPORTED_OP, "Unsupported op " + std::to_string(op));
+  const int pol = ftk::policy_id(op, dtype);
+  if (pol < 0) return fail(c, FT_ERR_UNSUPPORTED_TYPE, std::string("Type ") + ft_dtype_name((ft_dtype)dtype) + " is not supported");
+  if (!recvbuf && count) return fail(c, FT_ERR_INVALID_ARG, "recvbuf is null");
+  out->pol = pol;
+  out->es = (uint32_t)ft_dtype_size((ft_dtype)dtype);
+  out->bytes = (uint64_t)count * out->es;
+  out->heap_resident = in_heap(c, recvbuf, out->bytes);
+  (void)sendbuf;
+  return FT_OK;
+}
+
+int launch_staged_call(ft_comm* c, const Prepared& pr, const void* sendbuf, void* recvbuf, size_t count,
+                       const ft::Shape& shape, float scale, int stage_begin, int stage_end, bool do_sync, cudaStream_t st) {
+  DevPlanEntry* pe = nullptr;
+  int rc = get_plan(c, shape, &pe);
+  if (rc != FT_OK) return rc;
+  ftk::StagedArgs a{};
+  a.plan = pe->plan;
+  a.pulls = pe->pulls;
+  a.count = count;
+  a.elem_size = pr.es;
+  a.block_elems = pick_block_elems(count, c->world, pr.es);
+  a.scale = scale;
+  a.do_sync = do_sync ? 1 : 0;
+  a.stage_begin = stage_begin < 0 ? 0 : (uint32_t)stage_begin;
+  a.stage_end = stage_end < 0 ? (uint32_t)pe->nstages : (uint32_t)stage_end;
+  if (pr.heap_resident) {
+    if (sendbuf && sendbuf != recvbuf) {
+      if (a.stage_begin == 0) FT_CUDA(c, cudaMemcpyAsync(recvbuf, sendbuf, pr.bytes, cudaMemcpyDeviceToDevice, st));
+    }
+    a.work_off = (uint64_t)((unsigned char*)recvbuf - local_base(c));
+    a.alt_stride = 0;
+    a.end_sync = 1;
+    a.user_vec_ok = 1;
+  } else {
+    if (pr.bytes > c->staging_bytes)
+      return fail(c, FT_ERR_TOO_LARGE, "message of " + std::to_string(pr.bytes) + " bytes exceeds the staging slot (" +
+                                           std::to_string(c->staging_bytes) + "); allocate the tensor in the symmetric heap or split it");
+    a.work_off = c->staging_off;
+    a.alt_stride = c->staging_bytes;
+    a.user_in = sendbuf ? sendbuf : recvbuf;
+    a.user_out = recvbuf;
+    a.end_sync = 0;
+    a.user_vec_ok = (((uintptr_t)a.user_in | (uintptr_t)a.user_out) & 15) == 0;
+  }
+  const int lanes = pick_lanes(c, a.block_elems * pr.es, 8192);
+  cudaError_t e = ftk::launch_staged(pr.pol, c->dev, a, lanes, st);
+  if (e != cudaSuccess) return fail(c, FT_ERR_CUDA, std::string("staged launch: ") + cudaGetErrorString(e));
+  return FT_OK;
+}
+
+int launch_oneshot_call(ft_comm* c, const Prepared& pr, const void* sendbuf, void* recvbuf, size_t count, float scale,
+                        uint32_t phase_mask, uint64_t emu_call, cudaStream_t st) {
+  if (pr.bytes > c->staging_bytes) return fail(c, FT_ERR_TOO_LARGE, "one-shot message exceeds the staging slot");
+  ftk::OneShotArgs a{};
+  a.slot_off = c->staging_off;
+  a.emu_call = emu_call;
+  a.user_in = sendbuf ? sendbuf : recvbuf;
+  a.user_out = recvbuf;
+  a.count = count;
+  a.elem_size = pr.es;
+  a.phase_mask = phase_mask;
+  a.user_vec_ok = (((uintptr_t)a.user_in | (uintptr_t)a.user_out) & 15) == 0;
+  a.scale = scale;
+  const int lanes = pick_lanes(c, pr.bytes, 4096);
+  cudaError_t e = ftk::launch_oneshot(pr.pol, c->dev, a, c->staging_bytes, lanes, st);
+  if (e != cudaSuccess) return fail(c, FT_ERR_CUDA, std::string("one-shot launch: ") + cudaGetErrorString(e));
+  return FT_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ft_comm_create(int rank, int world, int device, size_t heap_bytes, size_t staging_bytes, int mem_kind, ft_comm** out) {
+  if (!out || world < 1 || world > FT_MAX_RANKS || rank < 0 || rank >= world) return FT_ERR_INVALID_ARG;
+  ft_comm* c = new ft_comm;
+  *out = c;
+  c->rank = rank; c->world = world; c->device = device; c->mem_kind = mem_kind;
+  FT_CUDA(c, cudaSetDevice(device));
+  FT_CUDA(c, cudaFree(nullptr));
+  cudaDeviceGetAttribute(&c->sms, cudaDevAttrMultiProcessorCount, device);
+  c->user_bytes = round_up(heap_bytes, 256);
+  c->staging_bytes = round_up(staging_bytes ? staging_bytes : 256, 256);
+  c->staging_off = c->user_bytes;
+  c->flags_off = round_up(c->staging_off + 2 * c->staging_bytes, 4096);
+  size_t total = c->flags_off + kFlagBytes;
+  if (mem_kind == FT_MEM_VMM) {
+    Driver& d = driver();
+    if (!d.ok) return fail(c, FT_ERR_NOT_AVAILABLE, "CUDA VMM driver API unavailable: " + d.why);
+    CUmemAllocationProp prop = vmm_prop(device);
+    size_t gran = 0;
+    FT_CU(c, d.p_cuMemGetAllocationGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED));
+    int mc = 0;
+    d.p_cuDeviceGetAttribute(&mc, CU_DEVICE_ATTRIBUTE_MULTICAST_SUPPORTED, device);
+    if (mc && d.p_cuMulticastGetGranularity) {
+      CUmulticastObjectProp mp{};
+      mp.numDevices = (unsigned)world;
+      mp.size = round_up(total, gran);
+      mp.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+      size_t mg = 0;
+      if (d.p_cuMulticastGetGranularity(&mg, &mp, CU_MULTICAST_GRANULARITY_RECOMMENDED) == CUDA_SUCCESS && mg > gran) gran = mg;
+    }
+    total = round_up(total, gran);
+    FT_CU(c, d.p_cuMemCreate(&c->handle, total, &prop, 0));
+    c->total_bytes = total;
+    int rc = map_handle(c, c->handle, total, &c->va);
+    if (rc != FT_OK) return rc;
+  } else {
+    total = round_up(total, 2 << 20);
+    FT_CUDA(c, cudaMalloc(&c->ipc_ptr, total));
+    c->total_bytes = total;
+  }
+  FT_CUDA(c, cudaMemset(local_base(c) + c->flags_off, 0, kFlagBytes));
+  FT_CUDA(c, cudaMalloc(&c->call_count, sizeof(unsigned long long)));
+  FT_CUDA(c, cudaMalloc(&c->arrived, sizeof(unsigned int)));
+  FT_CUDA(c, cudaMemset(c->call_count, 0, sizeof(unsigned long long)));
+  FT_CUDA(c, cudaMemset(c->arrived, 0, sizeof(unsigned int)));
+  FT_CUDA(c, cudaHostAlloc(&c->status_host, sizeof(ftk::Status), cudaHostAllocMapped));
+  std::memset(c->status_host, 0, sizeof(ftk::Status));
+  FT_CUDA(c, cudaHostGetDevicePointer((void**)&c->status_dev, c->status_host, 0));
+  c->peer_base[rank] = local_base(c);
+  FT_CUDA(c, cudaDeviceSynchronize());
+  return FT_OK;
+}
+
+int ft_comm_destroy(ft_comm* c) {
+  if (!c) return FT_OK;
+  cudaSetDevice(c->device);
+  cudaDeviceSynchronize();
+  Driver& d = driver();
+  if (c->mc_bound || c->mc_joined || c->mc_have) {
+    if (c->mc_va) { d.p_cuMemUnmap(c->mc_va, c->total_bytes); d.p_cuMemAddressFree(c->mc_va, c->total_bytes); }
+    if (c->mc_bound && d.p_cuMulticastUnbind) d.p_cuMulticastUnbind(c->mc_handle, c->device, 0, c->total_bytes);
+    if (c->mc_handle) d.p_cuMemRelease(c->mc_handle);
+  }
+  for (int r = 0; r < c->world; ++r) {
+    if (r == c->rank || !c->peer_base[r]) continue;
+    if (c->peer_is_vmm[r]) {
+      d.p_cuMemUnmap((CUdeviceptr)c->peer_base[r], c->total_bytes);
+      d.p_cuMemAddressFree((CUdeviceptr)c->peer_base[r], c->total_bytes);
+      d.p_cuMemRelease(c->peer_handle[r]);
+    } else if (c->peer_is_ipc[r]) {
+      cudaIpcCloseMemHandle(c->peer_base[r]);
+    }
+  }
+  if (c->mem_kind == FT_MEM_VMM && c->va) {
+    d.p_cuMemUnmap(c->va, c->total_bytes);
+    d.p_cuMemAddressFree(c->va, c->total_bytes);
+    d.p_cuMemRelease(c->handle);
+  } else if (c->ipc_ptr) {
+    cudaFree(c->ipc_ptr);
+  }
+  for (auto& kv : c->plans) { cudaFree(kv.second.plan); cudaFree(kv.second.pulls); }
+  cudaFree(c->call_count);
+  cudaFree(c->arrived);
+  if (c->status_host) cudaFreeHost(c->status_host);
+  delete c;
+  return FT_OK;
+}
+
+const char* ft_comm_last_error(ft_comm* c) { return c ? c->err.c_str() : "null communicator"; }
+
+int ft_comm_export_fd(ft_comm* c, int* fd_out) {
+  if (!c || c->mem_kind != FT_MEM_VMM || !fd_out) return fail(c, FT_ERR_INVALID_ARG, "export_fd needs a VMM heap");
+  int fd = -1;
+  FT_CU(c, driver().p_cuMemExportToShareableHandle(&fd, c->handle, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0));
+  *fd_out = fd;
+  return FT_OK;
+}
+
+int ft_comm_import_fd(ft_comm* c, int peer, int fd) {
+  if (!c || peer < 0 || peer >= c->world || peer == c->rank) return fail(c, FT_ERR_INVALID_ARG, "bad peer");
+  FT_CUDA(c, cudaSetDevice(c->device));
+  CUmemGenericAllocationHandle h = 0;
+  FT_CU(c, driver().p_cuMemImportFromShareableHandle(&h, (void*)(uintptr_t)fd, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR));
+  CUdeviceptr va = 0;
+  int rc = map_handle(c, h, c->total_bytes, &va);
+  if (rc != FT_OK) return rc;
+  c->peer_handle[peer] = h;
+  c->peer_base[peer] = (unsigned char*)va;
+  c->peer_is_vmm[peer] = true;
+  return FT_OK;
+}
+
+int ft_comm_export_ipc(ft_comm* c, void* blob64) {
+  if (!c || c->mem_kind != FT_MEM_IPC || !blob64) return fail(c, FT_ERR_INVALID_ARG, "export_ipc needs a cudaMalloc heap");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  FT_CUDA(c, cudaIpcGetMemHandle((cudaIpcMemHandle_t*)blob64, c->ipc_ptr));
+  return FT_OK;
+}
+
+int ft_comm_import_ipc(ft_comm* c, int peer, const void* blob64) {
+  if (!c || peer < 0 || peer >= c->world || peer == c->rank) return fail(c, FT_ERR_INVALID_ARG, "bad peer");
+  FT_CUDA(c, cudaSetDevice(c->device));
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, blob64, sizeof h);
+  void* p = nullptr;
+  FT_CUDA(c, cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  c->peer_base[peer] = (unsigned char*)p;
+  c->peer_is_ipc[peer] = true;
+  return FT_OK;
+}
+
+int ft_comm_connect_local(ft_comm** comms, int n) {
+  if (!comms || n < 1) return FT_ERR_INVALID_ARG;
+  for (int i = 0; i < n; ++i)
+    if (!comms[i] || comms[i]->world != n || comms[i]->rank != i || comms[i]->total_bytes != comms[0]->total_bytes)
+      return fail(comms[i], FT_ERR_INVALID_ARG, "connect_local: communicators must be ranks 0..n-1 of one world with equal heaps");
+  for (int i = 0; i < n; ++i) {
+    ft_comm* c = comms[i];
+    for (int j = 0; j < n; ++j) {
+      if (i == j) continue;
+      ft_comm* o = comms[j];
+      if (o->device != c->device) {
+        if (o->mem_kind == FT_MEM_VMM) {  // let c's device reach o's allocation through o's own mapping
+          CUmemAccessDesc acc{};
+          acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+          acc.location.id = c->device;
+          acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+          FT_CU(c, driver().p_cuMemSetAccess(o->va, o->total_bytes, &acc, 1));
+        } else {
+          FT_CUDA(c, cudaSetDevice(c->device));
+          cudaError_t e = cudaDeviceEnablePeerAccess(o->device, 0);
+          if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) return fail(c, FT_ERR_CUDA, cudaGetErrorString(e));
+          cudaGetLastError();
+        }
+      }
+      c->peer_base[j] = local_base(o);
+    }
+  }
+  for (int i = 0; i < n; ++i) {
+    int rc = ft_comm_finalize(comms[i]);
+    if (rc != FT_OK) return rc;
+  }
+  return FT_OK;
+}
+
+int ft_comm_finalize(ft_comm* c) {
+  if (!c) return FT_ERR_INVALID_ARG;
+  for (int r = 0; r < c->world; ++r)
+    if (!c->peer_base[r]) return fail(c, FT_ERR_INVALID_ARG, "peer " + std::to_string(r) + " was never imported");
+  ftk::CommDev& d = c->dev;
+  std::memset(&d, 0, sizeof d);
+  for (int r = 0; r < c->world; ++r) {
+    d.heap[r] = c->peer_base[r];
+    d.flags[r] = (unsigned long long*)(c->peer_base[r] + c->flags_off);
+  }
+  d.mc_heap = c->mc_bound ? (unsigned char*)c->mc_va : nullptr;
+  d.call_count = c->call_count;
+  d.arrived = c->arrived;
+  d.status = c->status_dev;
+  d.rank = c->rank;
+  d.world = c->world;
+  d.timeout_ns = (unsigned long long)(c->timeout_ms * 1e6);
+  c->finalized = true;
+  return FT_OK;
+}
+
+// ---- multicast -------------------------------------------------------------------------
+int ft_comm_mc_supported(ft_comm* c) {
+  if (!c || c->mem_kind != FT_MEM_VMM) return 0;
+  Driver& d = driver();
+  if (!d.ok || !d.p_cuMulticastCreate || !d.p_cuMulticastAddDevice || !d.p_cuMulticastBindMem) return 0;
+  int mc = 0;
+  if (d.p_cuDeviceGetAttribute(&mc, CU_DEVICE_ATTRIBUTE_MULTICAST_SUPPORTED, c->device) != CUDA_SUCCESS) return 0;
+  return mc;
+}
+
+int ft_comm_mc_create(ft_comm* c, int* fd_out) {
+  if (!ft_comm_mc_supported(c) || !fd_out) return fail(c, FT_ERR_NOT_AVAILABLE, "multicast not supported");
+  CUmulticastObjectProp mp{};
+  mp.numDevices = (unsigned)c->world;
+  mp.size = c->total_bytes;
+  mp.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+  FT_CU(c, driver().p_cuMulticastCreate(&c->mc_handle, &mp));
+  c->mc_have = true;
+  int fd = -1;
+  FT_CU(c, driver().p_cuMemExportToShareableHandle(&fd, c->mc_handle, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0));
+  *fd_out = fd;
+  return FT_OK;
+}
+
+int ft_comm_mc_join(ft_comm* c, int fd) {
+  if (!ft_comm_mc_supported(c)) return fail(c, FT_ERR_NOT_AVAILABLE, "multicast not supported");
+  if (fd >= 0) {
+    FT_CU(c, driver().p_cuMemImportFromShareableHandle(&c->mc_handle, (void*)(uintptr_t)fd, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR));
+    c->mc_have = true;
+  }
+  if (!c->mc_have) return fail(c, FT_ERR_INVALID_ARG, "no multicast object");
+  FT_CU(c, driver().p_cuMulticastAddDevice(c->mc_handle, c->device));
+  c->mc_joined = true;
+  return FT_OK;
+}
+
+int ft_comm_mc_bind(ft_comm* c) {
+  if (!c || !c->mc_joined) return fail(c, FT_ERR_INVALID_ARG, "join the multicast object first");
+  FT_CU(c, driver().p_cuMulticastBindMem(c->mc_handle, 0, c->handle, 0, c->total_bytes, 0));
+  c->mc_bound = true;
+  int rc = map_handle(c, c->mc_handle, c->total_bytes, &c->mc_va);
+  if (rc != FT_OK) return rc;
+  if (c->finalized) c->dev.mc_heap = (unsigned char*)c->mc_va;
+  return FT_OK;
+}
+
+int ft_comm_has_nvls(ft_comm* c) { return c && c->mc_bound && c->mc_va; }
+
+// ---- heap ------------------------------------------------------------------------------
+void* ft_comm_heap_base(ft_comm* c) { return c ? local_base(c) : nullptr; }
+size_t ft_comm_heap_bytes(ft_comm* c) { return c ? c->user_bytes : 0; }
+void* ft_comm_alloc(ft_comm* c, size_t bytes) {
+  if (!c) return nullptr;
+  const size_t need = round_up(bytes ? bytes : 1, 256);
+  if (c->bump + need > c->user_bytes) return nullptr;
+  void* p = local_base(c) + c->bump;
+  c->bump += need;
+  return p;
+}
+void ft_comm_alloc_reset(ft_comm* c) { if (c) c->bump = 0; }
+int ft_comm_rank(ft_comm* c) { return c ? c->rank : -1; }
+int ft_comm_world(ft_comm* c) { return c ? c->world : 0; }
+int ft_comm_mem_kind(ft_comm* c) { return c ? c->mem_kind : -1; }
+void ft_comm_set_timeout_ms(ft_comm* c, double ms) {
+  if (!c) return;
+  c->timeout_ms = ms;
+  c->dev.timeout_ns = (unsigned long long)(ms * 1e6);
+}
+void ft_comm_set_max_lanes(ft_comm* c, int lanes) { if (c) c->max_lanes = lanes; }
+void ft_comm_set_oneshot_max(ft_comm* c, size_t bytes) { if (c) c->oneshot_max = bytes; }
+
+// ---- collectives -----------------------------------------------------------------------
+int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op, const int* widths,
+                 int nw, int lonely, int ring, int algo, float scale, void* stream) {
+  Prepared pr;
+  int rc = prepare(c, sendbuf, recvbuf, count, dtype, op, &pr);
+  if (rc != FT_OK) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (count == 0) return FT_OK;
+  if (c->world == 1) {  // single rank: the reference's memcpy shortcut (mpi_mod.hpp:1739-1746)
+    if (sendbuf && sendbuf != recvbuf) FT_CUDA(c, cudaMemcpyAsync(recvbuf, sendbuf, pr.bytes, cudaMemcpyDeviceToDevice, st));
+    if (scale != 1.0f && (dtype == FT_F32 || dtype == FT_BF16)) {
+      const void* src[1] = {recvbuf};
+      return ft_reduce_nway_scaled(dtype, dtype, src, recvbuf, 1, count, scale, stream);
+    }
+    return FT_OK;
+  }
+  if (algo == FT_ALGO_AUTO) {
+    if (nw > 0 || ring) algo = FT_ALGO_STAGED;
+    else if (pr.bytes <= c->oneshot_max && pr.bytes <= c->staging_bytes) algo = FT_ALGO_ONESHOT;
+    else algo = FT_ALGO_STAGED;
+  }
+  if (algo == FT_ALGO_ONESHOT) return launch_oneshot_call(c, pr, sendbuf, recvbuf, count, scale, 7, 0, st);
+  if (algo == FT_ALGO_NVLS) {
+    if (!ft_comm_has_nvls(c)) return fail(c, FT_ERR_NOT_AVAILABLE, "NVLS multicast is not bound on this communicator");
+    if (!pr.heap_resident) return fail(c, FT_ERR_INVALID_ARG, "NVLS all-reduce needs a tensor in the symmetric heap");
+    if (pr.bytes % 16) return fail(c, FT_ERR_INVALID_ARG, "NVLS all-reduce needs a multiple of 16 bytes");
+    if (sendbuf && sendbuf != recvbuf) FT_CUDA(c, cudaMemcpyAsync(recvbuf, sendbuf, pr.bytes, cudaMemcpyDeviceToDevice, st));
+    ftk::NvlsArgs a{};
+    a.work_off = (uint64_t)((unsigned char*)recvbuf - local_base(c));
+    a.count = count;
+    a.elem_size = pr.es;
+    a.block_elems = pick_block_elems(count, c->world, pr.es);
+    a.scale = scale;
+    const int lanes = pick_lanes(c, a.block_elems * pr.es, 8192);
+    cudaError_t e = ftk::launch_nvls(pr.pol, c->dev, a, lanes, st);
+    if (e != cudaSuccess) return fail(c, e == cudaErrorInvalidValue ? FT_ERR_UNSUPPORTED_TYPE : FT_ERR_CUDA, std::string("NVLS launch: ") + cudaGetErrorString(e));
+    return FT_OK;
+  }
+  return launch_staged_call(c, pr, sendbuf, recvbuf, count, make_shape(c->world, widths, nw, lonely, ring), scale, -1, -1, true, st);
+}
+
+int ft_allreduce_emulate_stage(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op,
+                               const int* widths, int nw, int lonely, int ring, float scale, int stage_begin,
+                               int stage_end, void* stream) {
+  Prepared pr;
+  int rc = prepare(c, sendbuf, recvbuf, count, dtype, op, &pr);
+  if (rc != FT_OK) return rc;
+  if (count == 0 || c->world == 1) return FT_OK;
+  return launch_staged_call(c, pr, sendbuf, recvbuf, count, make_shape(c->world, widths, nw, lonely, ring), scale,
+                            stage_begin, stage_end, false, (cudaStream_t)stream);
+}
+
+int ft_allreduce_emulate_oneshot(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op,
+                                 float scale, int phase, uint64_t call, void* stream) {
+  Prepared pr;
+  int rc = prepare(c, sendbuf, recvbuf, count, dtype, op, &pr);
+  if (rc != FT_OK) return rc;
+  if (count == 0) return FT_OK;
+  return launch_oneshot_call(c, pr, sendbuf, recvbuf, count, scale, (uint32_t)phase & 5u, call, (cudaStream_t)stream);
+}
+
+int ft_plan_num_stages_for(ft_comm* c, const int* widths, int nw, int lonely, int ring) {
+  DevPlanEntry* pe = nullptr;
+  if (get_plan(c, make_shape(c->world, widths, nw, lonely, ring), &pe) != FT_OK) return -1;
+  return pe->nstages;
+}
+
+int ft_comm_status(ft_comm* c, int* out5) {
+  if (!c || !out5) return FT_ERR_INVALID_ARG;
+  out5[0] = c->status_host->code; out5[1] = c->status_host->index; out5[2] = c->status_host->peer;
+  out5[3] = c->status_host->lane; out5[4] = (int)c->status_host->calls;
+  return c->status_host->code;
+}
+void ft_comm_clear_status(ft_comm* c) {
+  if (c) { c->status_host->code = 0; c->status_host->index = c->status_host->peer = c->status_host->lane = 0; }
+}
+int ft_comm_wait_probe(ft_comm* c, int peer, double timeout_ms, void* stream) {
+  if (!c || !c->finalized || peer < 0 || peer >= FT_MAX_RANKS) return FT_ERR_INVALID_ARG;
+  cudaError_t e = ftk::launch_wait_probe(c->dev, peer, (unsigned long long)(timeout_ms * 1e6), (cudaStream_t)stream);
+  return e == cudaSuccess ? FT_OK : fail(c, FT_ERR_CUDA, cudaGetErrorString(e));
+}
+
+}  // extern "C"

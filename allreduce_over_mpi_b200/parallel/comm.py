@@ -1,0 +1,427 @@
+"""FlexTree communicator: all-reduce over NVLink peer memory with hand-written kernels.
+
+``FlexTreeComm`` is the per-process object (one process per GPU).  ``torch.distributed`` is
+used only as the bootstrap that carries memory handles between ranks; the data path is
+``libflextree.so``'s kernels reading peers' symmetric heaps directly.
+
+    comm = FlexTreeComm(heap_bytes=1 << 30)          # after dist.init_process_group
+    g = comm.alloc((n,), torch.bfloat16)             # tensor in the symmetric heap: zero-copy
+    comm.all_reduce(g, shape="auto")                 # picks one-shot / tree / NVLS per size
+    comm.all_reduce(any_cuda_tensor, shape="2*4")    # staged through internal slots
+
+``LocalWorld`` puts all ranks in one process: on several GPUs (micro-benchmarks), or on ONE
+GPU with the ranks emulated stage by stage in stream order (tests without a multi-GPU box).
+
+Reference counterpart: ``MPI_Allreduce_FT`` and its FT_TOPO / FT_LONELY configuration
+(allreduce_over_mpi/mpi_mod.hpp:1419-1486, :1723-1778).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import uuid
+from typing import Sequence
+
+import torch
+
+from .._lib import FlexTreeError, OPS, lib
+from ..ops.reduce import ft_dtype
+from ..utils import log
+from . import planner
+from .planner import CostParams, Shape
+
+ALGOS = {"auto": 0, "staged": 1, "oneshot": 2, "nvls": 3}
+MEM_IPC, MEM_VMM = 0, 1
+
+
+class _Span:
+    """Exposes raw device memory to torch through __cuda_array_interface__."""
+
+    def __init__(self, ptr: int, nbytes: int, owner):
+        self.owner = owner
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3,
+                                         "strides": None}
+
+
+def tensor_from_ptr(ptr: int, shape, dtype: torch.dtype, device, owner=None) -> torch.Tensor:
+    n = 1
+    for s in shape:
+        n *= int(s)
+    nbytes = n * torch.empty((), dtype=dtype).element_size()
+    flat = torch.as_tensor(_Span(ptr, max(nbytes, 1), owner), device=device)
+    return flat[:nbytes].view(dtype).view(*shape)
+
+
+def _as_shape(shape, world) -> Shape | None:
+    if shape is None or isinstance(shape, Shape):
+        return shape
+    if isinstance(shape, str):
+        return None if shape in ("auto", "") else Shape.parse(shape)
+    return Shape(tuple(int(x) for x in shape))
+
+
+class _CommBase:
+    """Shared by process-per-GPU and in-process communicators: one native ft_comm handle."""
+
+    def __init__(self):
+        self._h = C.c_void_p()
+        self.rank = 0
+        self.world = 1
+        self.device = torch.device("cuda", 0)
+        self.cost = CostParams.load()
+        self.default_shape: Shape | None = None
+        self.auto = True
+        self.has_nvls = False
+        self.nvls_min_bytes = int(os.environ.get("FT_NVLS_MIN_BYTES", 1 << 20))
+
+    # -- errors
+    def _check(self, code: int):
+        if code:
+            raise FlexTreeError(code, lib().ft_comm_last_error(self._h).decode())
+
+    def _create(self, rank, world, device_index, heap_bytes, staging_bytes, mem_kind):
+        self.rank, self.world = rank, world
+        self.device = torch.device("cuda", device_index)
+        self.heap_bytes, self.staging_bytes = heap_bytes, staging_bytes
+        code = lib().ft_comm_create(rank, world, device_index, heap_bytes, staging_bytes, mem_kind, C.byref(self._h))
+        return code
+
+    def _configure_from_env(self):
+        shape, is_auto = planner.shape_from_env(self.world)
+        self.auto = is_auto or not (os.environ.get("FT_TOPO") or os.environ.get("FT_LONELY"))
+        self.default_shape = None if self.auto else shape
+        if os.environ.get("FT_TIMEOUT_MS"):
+            self.set_timeout_ms(float(os.environ["FT_TIMEOUT_MS"]))
+        if os.environ.get("FT_MAX_LANES"):
+            self.set_max_lanes(int(os.environ["FT_MAX_LANES"]))
+
+    # -- knobs
+    def set_timeout_ms(self, ms: float):
+        lib().ft_comm_set_timeout_ms(self._h, ms)
+
+    def set_max_lanes(self, lanes: int):
+        lib().ft_comm_set_max_lanes(self._h, lanes)
+
+    def set_oneshot_max(self, nbytes: int):
+        lib().ft_comm_set_oneshot_max(self._h, nbytes)
+
+    # -- symmetric heap
+    def alloc(self, shape, dtype=torch.float32) -> torch.Tensor:
+        """Tensor inside the symmetric heap (same offset on every rank when every rank allocates
+        in the same order).  All-reduce on such a tensor is in place and copy-free."""
+        if isinstance(shape, int):
+            shape = (shape,)
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        ptr = lib().ft_comm_alloc(self._h, nbytes)
+        if not ptr:
+            raise MemoryError(f"symmetric heap exhausted ({self.heap_bytes} bytes); pass a larger heap_bytes")
+        return tensor_from_ptr(ptr, shape, dtype, self.device, owner=self)
+
+    def free_all(self):
+        """Forget every alloc() (tensors handed out before must no longer be used)."""
+        lib().ft_comm_alloc_reset(self._h)
+
+    def in_heap(self, t: torch.Tensor) -> bool:
+        base = lib().ft_comm_heap_base(self._h) or 0
+        return base <= t.data_ptr() and t.data_ptr() + t.numel() * t.element_size() <= base + lib().ft_comm_heap_bytes(self._h)
+
+    # -- selection
+    def choose(self, nbytes: int, in_heap: bool, dtype: torch.dtype) -> tuple[str, Shape]:
+        """Algorithm and shape for a message, from the calibrated cost model."""
+        nvls_ok = self.has_nvls and in_heap and dtype in (torch.float32, torch.bfloat16, torch.float16) and nbytes % 16 == 0
+        algo, shape, _ = planner.pick_algorithm(self.world, nbytes, self.cost, allow_oneshot=nbytes <= self.staging_bytes,
+                                                allow_nvls=nvls_ok)
+        return algo, shape
+
+    # -- the collective
+    def all_reduce(self, tensor: torch.Tensor, op: str = "sum", shape=None, algo: str = "auto", scale: float = 1.0,
+                   out: torch.Tensor | None = None, stream: torch.cuda.Stream | None = None) -> torch.Tensor:
+        """All-reduce ``tensor`` across the world on ``stream`` (default: current stream).
+
+        ``op``: "sum", "band" or "avg" (sum scaled by 1/world, floating types).  ``shape``: None/"auto"
+        (cost model, or FT_TOPO/FT_LONELY when set), a :class:`Shape`, or text such as "2*4", "2*2+1",
+        "ring8".  ``out``: result tensor (default in place).  Tensors that live in the symmetric
+        heap are reduced in place with no copy; others are staged through internal slots (and
+        split when larger than one slot)."""
+        if not tensor.is_cuda or not tensor.is_contiguous():
+            raise ValueError("all_reduce needs a contiguous CUDA tensor")
+        if op == "avg":
+            op, scale = "sum", scale / self.world
+        dst = tensor if out is None else out
+        if dst.numel() != tensor.numel() or dst.dtype != tensor.dtype or not dst.is_contiguous():
+            raise ValueError("out must match the input")
+        shp = _as_shape(shape, self.world)
+        if shp is None and not self.auto:
+            shp = self.default_shape
+        a = ALGOS[algo]
+        nbytes = tensor.numel() * tensor.element_size()
+        resident = self.in_heap(dst)
+        if shp is None and a == 0 and self.world > 1:
+            name, shp = self.choose(nbytes, resident, tensor.dtype)
+            a = ALGOS[name]
+            if name != "staged":
+                shp = None
+        st = (stream or torch.cuda.current_stream(self.device)).cuda_stream
+        dt = ft_dtype(tensor.dtype)
+        es = tensor.element_size()
+
+        def call(src_ptr, dst_ptr, count):
+            if shp is None:
+                arr, nw, lonely, ring = None, 0, 0, 0
+            else:
+                arr, nw, lonely, ring = shp.c_args()
+            self._check(lib().ft_allreduce(self._h, src_ptr, dst_ptr, count, dt, OPS[op], arr, nw, lonely, ring, a,
+                                           float(scale), C.c_void_p(st)))
+
+        with torch.cuda.device(self.device):
+            src_ptr = None if dst.data_ptr() == tensor.data_ptr() else tensor.data_ptr()
+            if resident or nbytes <= self.staging_bytes or self.world == 1:
+                call(src_ptr, dst.data_ptr(), tensor.numel())
+            else:  # larger than a staging slot: go through it piecewise
+                per = (self.staging_bytes // es) // 64 * 64
+                for lo in range(0, tensor.numel(), per):
+                    n = min(per, tensor.numel() - lo)
+                    call((src_ptr + lo * es) if src_ptr else None, dst.data_ptr() + lo * es, n)
+        return dst
+
+    # -- health
+    def status(self) -> dict:
+        """Status block written by device-side bounded waits (call after synchronising)."""
+        out = (C.c_int * 5)()
+        lib().ft_comm_status(self._h, out)
+        return {"code": out[0], "rendezvous": out[1], "peer": out[2], "lane": out[3], "calls": out[4]}
+
+    def check(self, synchronize: bool = True):
+        """Raise if a device-side wait timed out (a peer never arrived)."""
+        if synchronize:
+            torch.cuda.synchronize(self.device)
+        s = self.status()
+        if s["code"]:
+            lib().ft_comm_clear_status(self._h)
+            raise FlexTreeError(s["code"], f"rank {self.rank}: wait on rank {s['peer']} at rendezvous {s['rendezvous']} (lane {s['lane']})")
+
+    def wait_probe(self, peer: int, timeout_ms: float = 1.0):
+        """Launch a kernel that waits ``timeout_ms`` for a signal from ``peer`` that never comes."""
+        st = torch.cuda.current_stream(self.device).cuda_stream
+        self._check(lib().ft_comm_wait_probe(self._h, peer, timeout_ms, C.c_void_p(st)))
+
+    def close(self):
+        if self._h:
+            lib().ft_comm_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class FlexTreeComm(_CommBase):
+    """One rank of a multi-process world (launch with torchrun, one process per GPU)."""
+
+    def __init__(self, group=None, heap_bytes: int = 1 << 30, staging_bytes: int = 64 << 20, mem: str | None = None,
+                 nvls: bool | None = None, device: int | None = None):
+        super().__init__()
+        import torch.distributed as dist
+        if not dist.is_initialized():
+            raise RuntimeError("init torch.distributed first (it only carries the memory handles)")
+        self.group = group
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        dev = device if device is not None else int(os.environ.get("LOCAL_RANK", rank % max(1, torch.cuda.device_count())))
+        torch.cuda.set_device(dev)
+        mem = (mem or os.environ.get("FT_MEM", "auto")).lower()
+        kinds = {"auto": [MEM_VMM, MEM_IPC], "vmm": [MEM_VMM], "ipc": [MEM_IPC]}[mem]
+        last = None
+        for kind in kinds:
+            code = self._create(rank, world, dev, heap_bytes, staging_bytes, kind)
+            ok = self._exchange(kind) if code == 0 else False
+            oks = [None] * world
+            dist.all_gather_object(oks, bool(ok), group=group)
+            if all(oks):
+                break
+            last = lib().ft_comm_last_error(self._h).decode() if self._h else "create failed"
+            log.warn(f"symmetric memory kind {kind} unavailable ({last}); trying the next one", rank)
+            self.close()
+        else:
+            raise FlexTreeError(9, f"no usable symmetric memory mechanism: {last}")
+        self.mem_kind = lib().ft_comm_mem_kind(self._h)
+        want_nvls = nvls if nvls is not None else os.environ.get("FT_NVLS", "1") != "0"
+        if want_nvls and self.mem_kind == MEM_VMM and world > 1:
+            self.has_nvls = self._setup_multicast()
+        self._check(lib().ft_comm_finalize(self._h))
+        self._configure_from_env()
+        dist.barrier(group=group)
+
+    # handles travel as pickled bytes (IPC) or as descriptors over unix sockets (VMM)
+    def _exchange(self, kind: int) -> bool:
+        import torch.distributed as dist
+        L, world, rank = lib(), self.world, self.rank
+        if world == 1:
+            return True
+        try:
+            if kind == MEM_IPC:
+                blob = C.create_string_buffer(64)
+                if L.ft_comm_export_ipc(self._h, blob):
+                    return False
+                blobs = [None] * world
+                dist.all_gather_object(blobs, blob.raw, group=self.group)
+                for p in range(world):
+                    if p != rank and L.ft_comm_import_ipc(self._h, p, C.create_string_buffer(blobs[p], 64)):
+                        return False
+                return True
+            session = [uuid.uuid4().hex if rank == 0 else None]
+            dist.broadcast_object_list(session, src=0, group=self.group)
+            self._session = session[0]
+            sock = L.ft_fd_listen(f"ft-{self._session}-{rank}".encode())
+            fd = C.c_int(-1)
+            ok = sock >= 0 and L.ft_comm_export_fd(self._h, C.byref(fd)) == 0
+            oks = [None] * world
+            dist.all_gather_object(oks, bool(ok), group=self.group)   # also: every listener is up
+            if not all(oks):
+                return False
+            for p in range(world):
+                if p != rank and L.ft_fd_send(f"ft-{self._session}-{p}".encode(), fd.value, rank, 20000):
+                    ok = False
+            for _ in range(world - 1):
+                tag = C.c_int(-1)
+                got = L.ft_fd_recv(sock, C.byref(tag), 20000)
+                if got < 0 or L.ft_comm_import_fd(self._h, tag.value, got):
+                    ok = False
+                if got >= 0:
+                    L.ft_fd_close(got)
+            L.ft_fd_close(fd.value)
+            self._sock = sock
+            return ok
+        except Exception as e:  # noqa: BLE001 - any bootstrap failure means "try the next mechanism"
+            log.warn(f"handle exchange failed: {e}", rank)
+            return False
+
+    def _setup_multicast(self) -> bool:
+        import torch.distributed as dist
+        L, world, rank = lib(), self.world, self.rank
+
+        def agree(flag: bool) -> bool:
+            oks = [None] * world
+            dist.all_gather_object(oks, bool(flag), group=self.group)
+            return all(oks)
+
+        if not agree(bool(L.ft_comm_mc_supported(self._h))):
+            return False
+        ok = True
+        if rank == 0:
+            fd = C.c_int(-1)
+            ok = L.ft_comm_mc_create(self._h, C.byref(fd)) == 0
+            if ok:
+                for p in range(1, world):
+                    ok = L.ft_fd_send(f"ft-{self._session}-{p}".encode(), fd.value, 1000, 20000) == 0 and ok
+                ok = L.ft_comm_mc_join(self._h, -1) == 0 and ok
+                L.ft_fd_close(fd.value)
+        if not agree(ok):   # rank 0 could not create: nobody waits for a descriptor
+            return False
+        if rank != 0:
+            tag = C.c_int(-1)
+            got = L.ft_fd_recv(self._sock, C.byref(tag), 20000)
+            ok = got >= 0 and tag.value == 1000 and L.ft_comm_mc_join(self._h, got) == 0
+            if got >= 0:
+                L.ft_fd_close(got)
+        if not agree(ok):   # everyone must have joined before anyone binds
+            return False
+        ok = L.ft_comm_mc_bind(self._h) == 0
+        if not ok:
+            log.warn("multicast bind failed: " + L.ft_comm_last_error(self._h).decode(), rank)
+        return agree(ok)
+
+    def close(self):
+        sock = getattr(self, "_sock", -1)
+        if sock is not None and sock >= 0:
+            lib().ft_fd_close(sock)
+            self._sock = -1
+        super().close()
+
+
+class _LocalRank(_CommBase):
+    pass
+
+
+class LocalWorld:
+    """All ranks in this process.
+
+    ``devices`` lists one CUDA device per rank.  With distinct devices the ranks' kernels really
+    run concurrently and rendezvous over NVLink.  With every rank on the SAME device the world is
+    *emulated*: each stage of the plan is launched rank after rank on one stream with the
+    rendezvous switched off, so kernels never wait on one another.
+    """
+
+    def __init__(self, world: int, devices: Sequence[int] | None = None, heap_bytes: int = 64 << 20,
+                 staging_bytes: int = 16 << 20, mem: str = "ipc"):
+        devices = list(devices) if devices is not None else [0] * world
+        assert len(devices) == world
+        self.world = world
+        self.emulated = len(set(devices)) < world
+        self.ranks: list[_LocalRank] = []
+        kind = MEM_VMM if mem == "vmm" else MEM_IPC
+        for r in range(world):
+            c = _LocalRank()
+            with torch.cuda.device(devices[r]):
+                code = c._create(r, world, devices[r], heap_bytes, staging_bytes, kind)
+            if code:
+                raise FlexTreeError(code, lib().ft_comm_last_error(c._h).decode())
+            self.ranks.append(c)
+        arr = (C.c_void_p * world)(*[c._h for c in self.ranks])
+        code = lib().ft_comm_connect_local(arr, world)
+        if code:
+            raise FlexTreeError(code, lib().ft_comm_last_error(self.ranks[0]._h).decode())
+        self._emu_call = 0
+
+    def all_reduce(self, tensors: Sequence[torch.Tensor], op: str = "sum", shape=None, algo: str = "staged",
+                   scale: float = 1.0, outs: Sequence[torch.Tensor] | None = None):
+        """Rank r reduces ``tensors[r]`` (in place unless ``outs`` is given)."""
+        world = self.world
+        shp = _as_shape(shape, world) or Shape.flat(world)
+        if op == "avg":
+            op, scale = "sum", scale / world
+        outs = list(outs) if outs is not None else list(tensors)
+        if not self.emulated:
+            for r, c in enumerate(self.ranks):
+                with torch.cuda.device(c.device):
+                    c.all_reduce(tensors[r], op=op, shape=shp if algo == "staged" else None, algo=algo, scale=scale, out=outs[r])
+            return outs
+        L = lib()
+        dt = ft_dtype(tensors[0].dtype)
+        st = C.c_void_p(torch.cuda.current_stream(self.ranks[0].device).cuda_stream)
+
+        def ptrs(r):
+            src = None if outs[r].data_ptr() == tensors[r].data_ptr() else tensors[r].data_ptr()
+            return src, outs[r].data_ptr()
+
+        if world == 1:
+            self.ranks[0].all_reduce(tensors[0], op=op, scale=scale, out=outs[0])
+            return outs
+        if algo == "oneshot":
+            for phase in (1, 4):
+                for r, c in enumerate(self.ranks):
+                    src, dst = ptrs(r)
+                    c._check(L.ft_allreduce_emulate_oneshot(c._h, src, dst, tensors[r].numel(), dt, OPS[op], float(scale),
+                                                            phase, self._emu_call, st))
+            self._emu_call += 1
+            return outs
+        nstages = planner.plan_num_stages(world, shp)
+        if nstages < 0:
+            raise FlexTreeError(4, f"invalid FT_TOPO {shp} ({planner.validate_shape(world, shp)})")
+        arr, nw, lonely, ring = shp.c_args()
+        # pass -1 publishes every rank's input (the real kernel does this before its opening rendezvous)
+        for s in range(-1, nstages):
+            for r, c in enumerate(self.ranks):
+                src, dst = ptrs(r)
+                c._check(L.ft_allreduce_emulate_stage(c._h, src, dst, tensors[r].numel(), dt, OPS[op], arr, nw, lonely, ring,
+                                                      float(scale), max(s, 0), s + 1, st))
+        return outs
+
+    def close(self):
+        for c in self.ranks:
+            c.close()
+        self.ranks = []

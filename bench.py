@@ -1,0 +1,182 @@
+#!/usr/bin/env python
+"""Headline benchmark.
+
+  python bench.py --gpus 1 --steps K --warmup W
+      n-way reduce-sum on one B200: a step is one fp32 reduce for each fan-in n in {2,3,4,8}
+      over 64 Mi-element vectors (inputs larger than L2); value = sum((n+1)*bytes) / time, GB/s.
+
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N --steps K --warmup W
+      FlexTree all-reduce over NVLink peer memory on N B200s: a step is one in-place all-reduce of
+      --bytes (default 256 MiB) fp32; value = bus bandwidth (bytes/t) * 2(N-1)/N in GB/s,
+      t = max over ranks of CUDA-event time.  The NCCL number for the same buffer rides along.
+
+  --impl reference runs the unmodified reference code for the same metric (its CUDA reduce_sum_gpu
+  launcher at N = 1, its MPI_Allreduce_FT over a shared-memory MPI shim at N > 1).
+
+Rank 0 prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="flextree", choices=["flextree", "reference"])
+    ap.add_argument("--bytes", type=int, default=256 << 20)
+    ap.add_argument("--dtype", default="float32", choices=["float32", "bfloat16"])
+    ap.add_argument("--elems", type=int, default=64 << 20, help="vector length of the 1-GPU n-way reduce")
+    ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+# ------------------------------------------------------------------------------ N = 1
+FANINS = (2, 3, 4, 8)
+
+
+def bench_nway(a) -> dict:
+    import torch
+    from allreduce_over_mpi_b200.ops import launch_count, reduce_nway
+    from allreduce_over_mpi_b200.utils import ClockSampler
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    dtype = getattr(torch, a.dtype)
+    elems = a.elems
+    g = torch.Generator(device=dev).manual_seed(2024)
+    vecs = [(torch.rand(elems, generator=g, device=dev) * 2 - 1).to(dtype) for _ in range(max(FANINS))]
+    outs = {n: torch.empty_like(vecs[0]) for n in FANINS}
+    nbytes = elems * vecs[0].element_size()
+    step_bytes = sum((n + 1) * nbytes for n in FANINS)
+
+    def step():
+        for n in FANINS:
+            reduce_nway(vecs[:n], out=outs[n])
+
+    for _ in range(max(a.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    per_n = {}
+    sampler = ClockSampler(gpu_index=None).start()
+    l0 = launch_count()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(a.steps + 1)]
+    torch.cuda.synchronize()
+    ev[0].record()
+    for i in range(a.steps):
+        step()
+        ev[i + 1].record()
+    torch.cuda.synchronize()
+    launches = launch_count() - l0
+    clocks = sampler.stop()
+    total_ms = ev[0].elapsed_time(ev[-1])
+    ms_per_step = total_ms / a.steps
+    value = step_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # per fan-in detail (same buffers, event pair per kernel)
+    for n in FANINS:
+        ms = []
+        for _ in range(5):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record(); reduce_nway(vecs[:n], out=outs[n]); e.record(); e.synchronize()
+            ms.append(s.elapsed_time(e))
+        t = statistics.median(ms)
+        per_n[str(n)] = {"ms": round(t, 4), "GBps": round((n + 1) * nbytes / (t * 1e-3) / 1e9, 1)}
+    # correctness of what was timed
+    want = torch.stack([v.float() for v in vecs[:4]]).sum(0)
+    err = (outs[4].float() - want).abs().max().item()
+
+    pk, how = peaks()
+    res = {
+        "metric": "n-way reduce-sum GB/s (sum over n in {2,3,4,8} of (n+1)*bytes / time)",
+        "value": round(value, 1), "unit": "GB/s", "n_gpus": 1, "steps": a.steps, "warmup": max(a.warmup, 3),
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": a.dtype, "data": "synthetic uniform[-1,1) seeded",
+        "config": {"model": "n-way reduce-sum, n in {2,3,4,8}", "elems_per_vector": elems, "global_batch": None,
+                   "seq_len": None, "parallelism": "single GPU", "l2": "inputs larger than L2 (256 MiB per vector)",
+                   "accumulate": "fp32"},
+        "impl": "flextree", "per_fanin": per_n, "frac_of_hbm_copy_peak": round(value / pk["hbm_gbs"], 3),
+        "peak_source": f"of {how} ({pk['hbm_gbs']} GB/s copy)", "max_abs_err": err,
+        "gpu_launches": int(launches), "clocks": clocks,
+    }
+    if not a.no_e2e:
+        res["e2e"] = e2e_nway(a, vecs, outs, step_bytes)
+    return res
+
+
+def e2e_nway(a, vecs, outs, step_bytes) -> dict:
+    """Same step through the public API with the inputs copied from pinned host memory and the
+    results read back every step."""
+    import torch
+    from allreduce_over_mpi_b200.ops import reduce_nway
+    host_in = [torch.empty(v.shape, dtype=v.dtype).pin_memory() for v in vecs]
+    for h, v in zip(host_in, vecs):
+        h.copy_(v)
+    host_out = {n: torch.empty(vecs[0].shape, dtype=vecs[0].dtype).pin_memory() for n in FANINS}
+    steps = max(2, min(a.steps, 4))
+
+    def step():
+        for h, v in zip(host_in, vecs):
+            v.copy_(h, non_blocking=True)
+        for n in FANINS:
+            reduce_nway(vecs[:n], out=outs[n])
+            host_out[n].copy_(outs[n], non_blocking=True)
+
+    step()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(steps):
+        step()
+    e.record()
+    torch.cuda.synchronize()
+    ms = s.elapsed_time(e) / steps
+    h2d = sum(h.numel() * h.element_size() for h in host_in)
+    d2h = sum(h.numel() * h.element_size() for h in host_out.values())
+    return {"value": round(step_bytes / (ms * 1e-3) / 1e9, 1), "unit": "GB/s", "ms_per_step": round(ms, 3),
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": steps}
+
+
+# ------------------------------------------------------------------------------ main
+def main():
+    a = parse()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if a.impl == "reference":
+        from baseline.reference_arm import run_reference
+        out = run_reference(a, world, rank)
+        if rank == 0:
+            print(json.dumps(out), flush=True)
+        return 0
+    if a.gpus <= 1 and world <= 1:
+        out = bench_nway(a)
+        print(json.dumps(out), flush=True)
+        return 0
+    from allreduce_over_mpi_b200.bench.allreduce import bench_allreduce_main
+    out = bench_allreduce_main(a)
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

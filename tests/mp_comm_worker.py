@@ -1,0 +1,148 @@
+"""Worker run under torch.distributed.run by test_comm_multigpu.py (one process per GPU)."""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from allreduce_over_mpi_b200.bench.allreduce import expected, fill, init_dist  # noqa: E402
+from allreduce_over_mpi_b200.parallel import planner  # noqa: E402
+from allreduce_over_mpi_b200.parallel.comm import FlexTreeComm  # noqa: E402
+
+
+def main():
+    mode = sys.argv[1] if len(sys.argv) > 1 else "correctness"
+    rank, world, local = init_dist()
+    comm = FlexTreeComm(heap_bytes=96 << 20, staging_bytes=8 << 20, mem=os.environ.get("FT_MEM", "auto"))
+    dev = comm.device
+    report = {"world": world, "nvls": comm.has_nvls, "mem_kind": comm.mem_kind, "cases": 0}
+
+    if mode == "timeout":
+        # the last rank sits one call out; the others must come back with a timeout status, not hang
+        comm.set_timeout_ms(300.0)
+        x = torch.ones(4096, device=dev)
+        comm.all_reduce(x, algo="oneshot")
+        comm.check()
+        if rank != world - 1:
+            comm.all_reduce(x, shape=str(world), algo="staged")
+            try:
+                comm.check()
+                report["timeout_seen"] = False
+            except Exception as e:  # noqa: BLE001
+                report["timeout_seen"] = "timeout" in str(e)
+        else:
+            report["timeout_seen"] = True
+        torch.cuda.synchronize()
+        flags = [None] * world
+        dist.all_gather_object(flags, report["timeout_seen"])
+        if rank == 0:
+            print("RESULT " + json.dumps({"ok": all(flags), **report}), flush=True)
+        comm.close()
+        dist.destroy_process_group()
+        return 0
+
+    ok = True
+
+    def verify(t, count, dtype, it, what):
+        nonlocal ok
+        torch.cuda.synchronize()
+        comm.check()
+        want = expected(count, dtype, world, dev, it)
+        tol = 1e-4 if dtype == torch.float32 else 0.3
+        err = (t.double() - want).abs().max().item()
+        if not err <= tol:
+            ok = False
+            print(f"[rank {rank}] MISMATCH {what}: err {err}", flush=True)
+        # every rank must hold the same bits
+        h = t.view(torch.uint8).long().sum().reshape(1)
+        lo, hi = h.clone(), h.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        if lo.item() != hi.item():
+            ok = False
+            print(f"[rank {rank}] ranks disagree for {what}", flush=True)
+        report["cases"] += 1
+
+    shapes = [str(s) for s in planner.executable_shapes(world)]
+    it = 0
+    for dtype in (torch.float32, torch.bfloat16):
+        for count in (1, 35, 4099, 1 << 20, (5 << 20) + 3):
+            for shape in shapes:
+                it += 1
+                # tensor in the symmetric heap: in place, zero copy
+                comm.free_all()
+                sym = comm.alloc(count, dtype)
+                fill(sym, rank, it)
+                comm.all_reduce(sym, shape=shape, algo="staged")
+                verify(sym, count, dtype, it, f"heap {shape} {dtype} {count}")
+                # ordinary tensor: staged through the slots (split when larger than a slot)
+                loc = torch.empty(count, dtype=dtype, device=dev)
+                fill(loc, rank, it)
+                comm.all_reduce(loc, shape=shape, algo="staged")
+                verify(loc, count, dtype, it, f"slots {shape} {dtype} {count}")
+            if count * 4 <= comm.staging_bytes:
+                it += 1
+                loc = torch.empty(count, dtype=dtype, device=dev)
+                fill(loc, rank, it)
+                comm.all_reduce(loc, algo="oneshot")
+                verify(loc, count, dtype, it, f"oneshot {dtype} {count}")
+            if comm.has_nvls and (count * loc.element_size()) % 16 == 0:
+                it += 1
+                comm.free_all()
+                sym = comm.alloc(count, dtype)
+                fill(sym, rank, it)
+                comm.all_reduce(sym, algo="nvls")
+                verify(sym, count, dtype, it, f"nvls {dtype} {count}")
+            it += 1
+            comm.free_all()
+            sym = comm.alloc(count, dtype)
+            fill(sym, rank, it)
+            comm.all_reduce(sym)      # cost model's pick
+            verify(sym, count, dtype, it, f"auto {dtype} {count}")
+
+    # back-to-back calls without host synchronisation: slots, call numbers and flags must keep up
+    comm.free_all()
+    count = 300_000
+    sym = comm.alloc(count, torch.float32)
+    loc = torch.empty(count, dtype=torch.float32, device=dev)
+    small = torch.empty(1000, dtype=torch.float32, device=dev)
+    sym.fill_(1.0); loc.fill_(1.0); small.fill_(1.0)
+    rounds = 12
+    for i in range(rounds):
+        comm.all_reduce(sym, op="avg", shape=shapes[i % len(shapes)], algo="staged")
+        comm.all_reduce(loc, op="avg", shape=shapes[(i + 1) % len(shapes)], algo="staged")
+        comm.all_reduce(small, op="avg", algo="oneshot")
+        if comm.has_nvls:
+            comm.all_reduce(sym, op="avg", algo="nvls")
+    torch.cuda.synchronize()
+    comm.check()
+    for t, name in ((sym, "sym"), (loc, "loc"), (small, "small")):
+        if not torch.allclose(t, torch.ones_like(t), atol=1e-5):
+            ok = False
+            print(f"[rank {rank}] back-to-back {name} drifted: {t[:4].tolist()}", flush=True)
+
+    # int32 sum and bitwise AND over the wire
+    comm.free_all()
+    xi = torch.full((10_001,), rank + 1, dtype=torch.int32, device=dev)
+    comm.all_reduce(xi, shape=shapes[0], algo="staged")
+    torch.cuda.synchronize()
+    ok = ok and bool((xi == world * (world + 1) // 2).all())
+    xb = torch.full((777,), 0x7fffffff ^ (1 << rank), dtype=torch.int32, device=dev)
+    comm.all_reduce(xb, op="band", algo="oneshot")
+    torch.cuda.synchronize()
+    ok = ok and bool((xb == (0x7fffffff ^ ((1 << world) - 1))).all())
+
+    flags = [None] * world
+    dist.all_gather_object(flags, ok)
+    if rank == 0:
+        print("RESULT " + json.dumps({"ok": all(flags), **report}), flush=True)
+    comm.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    return 0 if all(flags) else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())
