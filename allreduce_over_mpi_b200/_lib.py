@@ -73,6 +73,17 @@ def _declare(lib):
         "ft_cpu_world_create": (vp, [i, dbl]),
         "ft_cpu_world_destroy": (None, [vp]),
         "ft_cpu_allreduce": (i, [vp, i, *shape, i, i, vp, vp, u64, u64, i, i, i, ip]),
+        "ft_mpi_thread_rank": (vp, [vp, i]),
+        "ft_mpi_from_comm": (vp, [vp, vp]),
+        "ft_mpi_comm_free": (None, [vp]),
+        "FT_Comm_size": (i, [vp, ip]),
+        "FT_Comm_rank": (i, [vp, ip]),
+        "FT_Type_size": (i, [i, ip]),
+        "FT_Type_get_name": (i, [i, cp, ip]),
+        "MPI_Allreduce_FT": (i, [vp, vp, i, i, i, vp]),
+        "MPI_Allreduce_FT_c": (i, [vp, vp, sz, i, i, vp]),
+        "FT_enabled": (None, []),
+        "ft_mpi_last_error": (cp, []),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)

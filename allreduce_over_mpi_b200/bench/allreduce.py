@@ -89,6 +89,9 @@ def sweep(a, comm: FlexTreeComm, rank: int, world: int) -> list[dict]:
         sizes.append(s)
         s *= a.step
     dev = comm.device
+    if "all" in a.shapes:   # every executable shape for this world, cost model's pick first
+        from ..parallel.planner import executable_shapes
+        a.shapes = ["auto"] + [str(x) for x in executable_shapes(world)]
     for dt_name in a.dtypes:
         dtype = getattr(torch, dt_name)
         es = torch.empty((), dtype=dtype).element_size()

@@ -55,7 +55,7 @@ ft::V1Params to_params(const ft_v1_params* p) {
 
 }  // namespace
 
-struct ft_cpu_world { ft::CpuWorld w; explicit ft_cpu_world(int n) : w(n) {} };
+struct ft_cpu_world { ft::CpuWorld w; };
 
 extern "C" {
 
@@ -208,7 +208,7 @@ int ft_run_plan_snapshot(int world, const int* widths, int nw, int lonely, int r
 
 ft_cpu_world* ft_cpu_world_create(int world, double timeout_s) {
   if (world < 1 || world > 4096) return nullptr;
-  auto* w = new ft_cpu_world(world);
+  auto* w = new ft_cpu_world{ft::CpuWorld(world)};
   if (timeout_s > 0) w->w.timeout_s = timeout_s;
   return w;
 }

@@ -1,0 +1,164 @@
+// MPI_Allreduce-compatible entry point (see flextree_mpi.h).
+#include "flextree_mpi.h"
+
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "../planner/config.hpp"
+#include "../planner/cost_model.hpp"
+#include "../planner/cpu_executor.hpp"
+
+struct ft_cpu_world { ft::CpuWorld w; };  // layout shared with flextree_host.cpp
+
+struct ft_mpi_comm {
+  ft_cpu_world* threads = nullptr;  // thread world ...
+  int rank = 0;
+  ft_comm* gpu = nullptr;           // ... or GPU communicator
+  void* stream = nullptr;
+  void* bounce = nullptr;           // symmetric-heap region for host buffers (GPU communicator)
+  size_t bounce_bytes = 0;
+};
+
+namespace {
+thread_local std::string g_err;
+int fail(int code, const std::string& msg) {
+  g_err = msg;
+  std::fprintf(stderr, "%s\n", msg.c_str());
+  return code;
+}
+bool is_device_pointer(const void* p) {
+  cudaPointerAttributes a;
+  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
+  return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+}  // namespace
+
+extern "C" {
+
+void FT_enabled(void) { std::puts("FlexTree enabled"); }
+const char* ft_mpi_last_error(void) { return g_err.c_str(); }
+
+FT_Comm ft_mpi_thread_rank(ft_cpu_world* world, int rank) {
+  if (!world || rank < 0 || rank >= world->w.n) return nullptr;
+  auto* c = new ft_mpi_comm;
+  c->threads = world;
+  c->rank = rank;
+  return c;
+}
+FT_Comm ft_mpi_from_comm(ft_comm* comm, void* stream) {
+  if (!comm) return nullptr;
+  auto* c = new ft_mpi_comm;
+  c->gpu = comm;
+  c->rank = ft_comm_rank(comm);
+  c->stream = stream;
+  return c;
+}
+void ft_mpi_comm_free(FT_Comm c) { delete c; }
+
+int FT_Comm_size(FT_Comm c, int* size) {
+  if (!c || !size) return FT_ERR_INVALID_ARG;
+  *size = c->threads ? c->threads->w.n : ft_comm_world(c->gpu);
+  return 0;
+}
+int FT_Comm_rank(FT_Comm c, int* rank) {
+  if (!c || !rank) return FT_ERR_INVALID_ARG;
+  *rank = c->rank;
+  return 0;
+}
+int FT_Type_size(FT_Datatype t, int* size) {
+  if (!size) return FT_ERR_INVALID_ARG;
+  *size = (int)ft_dtype_size((ft_dtype)t);
+  return *size ? 0 : FT_ERR_UNSUPPORTED_TYPE;
+}
+int FT_Type_get_name(FT_Datatype t, char* name, int* len) {
+  const char* s = ft_dtype_name((ft_dtype)t);
+  if (name) std::strcpy(name, s);
+  if (len) *len = (int)std::strlen(s);
+  return 0;
+}
+
+int MPI_Allreduce_FT_c(const void* sendbuf, void* recvbuf, size_t count, FT_Datatype datatype, FT_Op op, FT_Comm comm) {
+  if (!comm || !recvbuf) return fail(FT_ERR_INVALID_ARG, "MPI_Allreduce_FT: null communicator or receive buffer");
+  int world = 1;
+  FT_Comm_size(comm, &world);
+  const bool in_place = sendbuf == FT_IN_PLACE || sendbuf == nullptr || sendbuf == recvbuf;
+  const size_t es = ft_dtype_size((ft_dtype)datatype);
+  if (op != FT_SUM && op != FT_BAND) return fail(FT_ERR_UNSUPPORTED_OP, "Unsupported op " + std::to_string(op));
+  if (!es || !ft_op_supported((ft_op)op, (ft_dtype)datatype))
+    return fail(FT_ERR_UNSUPPORTED_TYPE, std::string("Type ") + ft_dtype_name((ft_dtype)datatype) + " is not supported in MPI mode.");
+
+  // tree shape from the environment, on every call like the reference
+  ft::ShapeConfig cfg = ft::shape_from_env(world);
+  if (!cfg.ok()) return fail(FT_ERR_INVALID_TOPO, cfg.error);
+  ft::Shape shape = cfg.shape;
+
+  if (comm->threads) {
+    if (world <= 1) {
+      if (!in_place) std::memcpy(recvbuf, sendbuf, count * es);
+      return 0;
+    }
+    if (cfg.is_auto) shape = ft::Shape::flat(world);  // on shared host memory every shape moves the same bytes
+    ft::Plan plan = ft::build_plan(world, shape);
+    ft::RankStatus st = ft::cpu_allreduce(comm->threads->w, comm->rank, plan, (ft_op)op, (ft_dtype)datatype,
+                                          in_place ? nullptr : sendbuf, recvbuf, count, 0, nullptr, 1);
+    if (st.code != FT_OK)
+      return fail(st.code, std::string("MPI_Allreduce_FT: ") + ft_status_name(st.code) + " at rendezvous " +
+                               std::to_string(st.stage) + " (peer " + std::to_string(st.peer) + ")");
+    return 0;
+  }
+
+  // ---- GPU communicator
+  ft_comm* g = comm->gpu;
+  const int nw = cfg.is_auto ? 0 : (int)shape.widths.size();
+  const int* widths = cfg.is_auto ? nullptr : shape.widths.data();
+  const int explicit_shape = !(cfg.is_auto || (!std::getenv("FT_TOPO") && !std::getenv("FT_LONELY")));
+  const int algo = explicit_shape ? FT_ALGO_STAGED : FT_ALGO_AUTO;
+  const bool dev_recv = is_device_pointer(recvbuf);
+  const bool dev_send = in_place ? dev_recv : is_device_pointer(sendbuf);
+  if (dev_recv && dev_send) {
+    int rc = ft_allreduce(g, in_place ? nullptr : sendbuf, recvbuf, count, datatype, op, explicit_shape ? widths : nullptr,
+                          explicit_shape ? nw : 0, explicit_shape ? shape.lonely : 0, explicit_shape ? shape.ring : 0, algo,
+                          1.0f, comm->stream);
+    if (rc != FT_OK) return fail(rc, ft_comm_last_error(g));
+    return 0;
+  }
+  // host buffers: bounce through a region of the symmetric heap, piecewise if need be
+  const size_t bytes = count * es;
+  if (!comm->bounce) {
+    size_t want = ft_comm_heap_bytes(g) / 4;
+    if (want > (256u << 20)) want = 256u << 20;
+    want = want / 256 * 256;
+    comm->bounce = want ? ft_comm_alloc(g, want) : nullptr;
+    comm->bounce_bytes = comm->bounce ? want : 0;
+    if (!comm->bounce) return fail(FT_ERR_TOO_LARGE, "MPI_Allreduce_FT: no room in the symmetric heap for host-buffer staging");
+  }
+  cudaStream_t st = (cudaStream_t)comm->stream;
+  const size_t per = comm->bounce_bytes / es;
+  const char* src = (const char*)(in_place ? recvbuf : sendbuf);
+  for (size_t lo = 0; lo < count; lo += per) {
+    const size_t n = count - lo < per ? count - lo : per;
+    if (cudaMemcpyAsync(comm->bounce, src + lo * es, n * es, cudaMemcpyDefault, st) != cudaSuccess)
+      return fail(FT_ERR_CUDA, "MPI_Allreduce_FT: host-to-device copy failed");
+    int rc = ft_allreduce(g, nullptr, comm->bounce, n, datatype, op, explicit_shape ? widths : nullptr, explicit_shape ? nw : 0,
+                          explicit_shape ? shape.lonely : 0, explicit_shape ? shape.ring : 0, algo, 1.0f, comm->stream);
+    if (rc != FT_OK) return fail(rc, ft_comm_last_error(g));
+    if (cudaMemcpyAsync((char*)recvbuf + lo * es, comm->bounce, n * es, cudaMemcpyDefault, st) != cudaSuccess ||
+        cudaStreamSynchronize(st) != cudaSuccess)
+      return fail(FT_ERR_CUDA, "MPI_Allreduce_FT: device-to-host copy failed");
+  }
+  (void)bytes;
+  int status[5];
+  if (ft_comm_status(g, status) != FT_OK)
+    return fail(status[0], std::string("MPI_Allreduce_FT: ") + ft_status_name((ft_status)status[0]) + " waiting for rank " + std::to_string(status[2]));
+  return 0;
+}
+
+int MPI_Allreduce_FT(const void* sendbuf, void* recvbuf, int count, FT_Datatype datatype, FT_Op op, FT_Comm comm) {
+  if (count < 0) return fail(FT_ERR_INVALID_ARG, "MPI_Allreduce_FT: negative count");
+  return MPI_Allreduce_FT_c(sendbuf, recvbuf, (size_t)count, datatype, op, comm);
+}
+
+}  // extern "C"

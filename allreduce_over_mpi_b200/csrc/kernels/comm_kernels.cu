@@ -298,17 +298,26 @@ __global__ void __launch_bounds__(kThreads) nvls_allreduce_kernel(const __grid_c
   if (abort_flag) return;
   unsigned char* mc = c.mc_heap + a.work_off + lo + sl.off;
   const uint64_t nvec = sl.bytes / 16;
-  for (uint64_t i = threadIdx.x; i < nvec; i += (uint64_t)blockDim.x * 2) {
-    const uint64_t j = i + blockDim.x;
-    uint4 v0 = Nvls<POL>::ld(mc + i * 16), v1 = make_uint4(0, 0, 0, 0);
-    if (j < nvec) v1 = Nvls<POL>::ld(mc + j * 16);
-    if (a.scale != 1.0f) {
-      typename P::Acc t;
-      P::init(t, v0); v0 = P::fins(t, a.scale);
-      P::init(t, v1); v1 = P::fins(t, a.scale);
+  constexpr int kU = 4;   // independent in-switch reductions in flight per thread
+  for (uint64_t base = 0; base < nvec; base += (uint64_t)blockDim.x * kU) {
+    uint4 v[kU];
+    uint64_t idx[kU];
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      idx[u] = base + (uint64_t)u * blockDim.x + threadIdx.x;
+      v[u] = idx[u] < nvec ? Nvls<POL>::ld(mc + idx[u] * 16) : make_uint4(0, 0, 0, 0);
     }
-    multimem_st(mc + i * 16, v0);
-    if (j < nvec) multimem_st(mc + j * 16, v1);
+    if (a.scale != 1.0f) {
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        typename P::Acc t;
+        P::init(t, v[u]);
+        v[u] = P::fins(t, a.scale);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kU; ++u)
+      if (idx[u] < nvec) multimem_st(mc + idx[u] * 16, v[u]);
   }
   // all my broadcasts are ordered before my signal; after the rendezvous every rank's
   // slice has landed here too

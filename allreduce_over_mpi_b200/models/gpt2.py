@@ -1,0 +1,90 @@
+"""GPT-2 (decoder-only transformer) used as the data-parallel training workload.
+
+The reference has no model code; this is the workload its all-reduce exists to serve
+(gradient averaging across data-parallel ranks).  GEMMs and attention go through PyTorch's
+library kernels (cuBLAS, fused SDPA) - the part of the step this framework owns is the
+gradient all-reduce (``parallel/ddp.py``).
+
+``GPT2Config.small()`` is the benchmark configuration: 12 layers, d_model 768, 12 heads,
+vocabulary 50257, context 1024.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+@dataclass
+class GPT2Config:
+    vocab_size: int = 50257
+    n_ctx: int = 1024
+    n_layer: int = 12
+    n_head: int = 12
+    d_model: int = 768
+    dropout: float = 0.0
+
+    @staticmethod
+    def small() -> "GPT2Config":
+        return GPT2Config()
+
+    @staticmethod
+    def tiny() -> "GPT2Config":
+        return GPT2Config(vocab_size=512, n_ctx=64, n_layer=2, n_head=4, d_model=64)
+
+
+class Block(nn.Module):
+    def __init__(self, c: GPT2Config):
+        super().__init__()
+        self.n_head = c.n_head
+        self.ln1 = nn.LayerNorm(c.d_model)
+        self.qkv = nn.Linear(c.d_model, 3 * c.d_model)
+        self.proj = nn.Linear(c.d_model, c.d_model)
+        self.ln2 = nn.LayerNorm(c.d_model)
+        self.fc = nn.Linear(c.d_model, 4 * c.d_model)
+        self.out = nn.Linear(4 * c.d_model, c.d_model)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        b, t, d = x.shape
+        q, k, v = self.qkv(self.ln1(x)).view(b, t, 3, self.n_head, d // self.n_head).permute(2, 0, 3, 1, 4)
+        a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        x = x + self.proj(a.transpose(1, 2).reshape(b, t, d))
+        return x + self.out(F.gelu(self.fc(self.ln2(x)), approximate="tanh"))
+
+
+class GPT2(nn.Module):
+    def __init__(self, c: GPT2Config):
+        super().__init__()
+        self.config = c
+        self.wte = nn.Embedding(c.vocab_size, c.d_model)
+        self.wpe = nn.Embedding(c.n_ctx, c.d_model)
+        self.blocks = nn.ModuleList(Block(c) for _ in range(c.n_layer))
+        self.ln_f = nn.LayerNorm(c.d_model)
+        self.apply(self._init)
+        for blk in self.blocks:  # scaled init of the residual projections
+            for lin in (blk.proj, blk.out):
+                nn.init.normal_(lin.weight, std=0.02 / math.sqrt(2 * c.n_layer))
+
+    @staticmethod
+    def _init(m):
+        if isinstance(m, (nn.Linear, nn.Embedding)):
+            nn.init.normal_(m.weight, std=0.02)
+        if isinstance(m, nn.Linear) and m.bias is not None:
+            nn.init.zeros_(m.bias)
+
+    def forward(self, idx: torch.Tensor, targets: torch.Tensor | None = None):
+        b, t = idx.shape
+        pos = torch.arange(t, device=idx.device)
+        x = self.wte(idx) + self.wpe(pos)
+        for blk in self.blocks:
+            x = blk(x)
+        logits = F.linear(self.ln_f(x), self.wte.weight)  # tied output embedding
+        if targets is None:
+            return logits
+        return F.cross_entropy(logits.float().view(-1, logits.size(-1)), targets.view(-1))
+
+    def num_params(self) -> int:
+        return sum(p.numel() for p in self.parameters())

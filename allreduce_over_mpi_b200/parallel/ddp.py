@@ -1,0 +1,156 @@
+"""Data-parallel gradient all-reduce through FlexTree, overlapped with backward.
+
+Two integrations:
+
+* :class:`FlexTreeDDP` - a DDP-style wrapper that owns the gradient storage.  Gradients live
+  in flat buckets (25 MB by default) allocated *inside the symmetric heap*, every parameter's
+  ``.grad`` is a view into its bucket, and as soon as the last gradient of a bucket has been
+  accumulated the bucket is all-reduced in place on a side stream (zero copy, averaging fused
+  into the kernel) while backward continues on the main stream.
+* :func:`flextree_allreduce_hook` - a communication hook for ``torch.nn.parallel.
+  DistributedDataParallel.register_comm_hook``; DDP keeps its own buckets, which are staged
+  through the communicator's slots.
+
+The reference has no trainer: its benchmark calls the all-reduce in a loop
+(allreduce_over_mpi/benchmark.cpp:155-182).  This module is what connects the collective to
+a training step.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Iterable, Sequence
+
+import torch
+import torch.nn as nn
+
+
+@dataclass
+class Bucket:
+    params: list = field(default_factory=list)
+    offsets: list = field(default_factory=list)   # element offsets inside the flat buffer
+    numel: int = 0
+    dtype: torch.dtype = torch.float32
+    flat: torch.Tensor | None = None
+    pending: int = 0
+
+
+def build_buckets(params: Iterable[nn.Parameter], bucket_bytes: int = 25 << 20, align_elems: int = 64) -> list[Bucket]:
+    """Assign parameters to buckets in reverse order (the order gradients become ready), one dtype
+    per bucket, each parameter's slice aligned to ``align_elems`` elements."""
+    buckets: list[Bucket] = []
+    cur: dict[torch.dtype, Bucket] = {}
+    for p in reversed([p for p in params if p.requires_grad]):
+        b = cur.get(p.dtype)
+        es = p.element_size()
+        if b is None or (b.numel and (b.numel + p.numel()) * es > bucket_bytes):
+            b = Bucket(dtype=p.dtype)
+            cur[p.dtype] = b
+            buckets.append(b)
+        b.params.append(p)
+        b.offsets.append(b.numel)
+        b.numel += -(-p.numel() // align_elems) * align_elems
+    return buckets
+
+
+class FlexTreeDDP(nn.Module):
+    """Wrap ``module`` for data-parallel training over ``comm`` (a FlexTreeComm or any object with
+    ``alloc``, ``all_reduce``, ``world`` and ``device``)."""
+
+    def __init__(self, module: nn.Module, comm, bucket_bytes: int = 25 << 20, shape=None, algo: str = "auto",
+                 broadcast_from: int | None = 0, stream: torch.cuda.Stream | None = None):
+        super().__init__()
+        self.module = module
+        self.comm = comm
+        self.shape, self.algo = shape, algo
+        self.buckets = build_buckets(module.parameters(), bucket_bytes)
+        self._bucket_of: dict[int, tuple[Bucket, int]] = {}
+        on_gpu = torch.cuda.is_available() and getattr(comm, "device", torch.device("cpu")).type == "cuda"
+        self.stream = stream or (torch.cuda.Stream(device=comm.device) if on_gpu else None)
+        self._callback_queued = False
+        self.launched = 0
+        for b in self.buckets:
+            b.flat = comm.alloc(b.numel, b.dtype)
+            b.flat.zero_()
+            for p, off in zip(b.params, b.offsets):
+                p.grad = b.flat[off:off + p.numel()].view_as(p)
+                self._bucket_of[id(p)] = (b, off)
+                p.register_post_accumulate_grad_hook(self._on_grad)
+            b.pending = len(b.params)
+        if broadcast_from is not None and comm.world > 1:
+            self._sync_parameters(broadcast_from)
+
+    def _sync_parameters(self, src: int):
+        """Make every rank start from rank ``src``'s weights: zero everywhere else, then sum."""
+        with torch.no_grad():
+            for p in list(self.module.parameters()) + list(self.module.buffers()):
+                if not p.is_floating_point():
+                    continue
+                if self.comm.rank != src:
+                    p.zero_()
+                self.comm.all_reduce(p.data, shape=self.shape)
+        if self.stream is not None:
+            torch.cuda.synchronize(self.comm.device)
+
+    def forward(self, *args, **kwargs):
+        return self.module(*args, **kwargs)
+
+    # -- backward-time machinery
+    def _on_grad(self, p: nn.Parameter):
+        b, off = self._bucket_of[id(p)]
+        if p.grad.data_ptr() != b.flat.data_ptr() + off * p.element_size():
+            # something replaced .grad (e.g. zero_grad(set_to_none=True)): fold it back into the bucket
+            view = b.flat[off:off + p.numel()].view_as(p)
+            view.copy_(p.grad)
+            p.grad = view
+        if not self._callback_queued:
+            self._callback_queued = True
+            torch.autograd.Variable._execution_engine.queue_callback(self._finish)
+        b.pending -= 1
+        if b.pending == 0:
+            self._launch(b)
+
+    def _launch(self, b: Bucket):
+        self.launched += 1
+        if self.stream is None:
+            self.comm.all_reduce(b.flat, op="avg", shape=self.shape, algo=self.algo)
+            return
+        self.stream.wait_stream(torch.cuda.current_stream(self.comm.device))
+        with torch.cuda.stream(self.stream):
+            self.comm.all_reduce(b.flat, op="avg", shape=self.shape, algo=self.algo)
+
+    def _finish(self):
+        """End of backward: flush buckets whose parameters got no gradient, join the side stream."""
+        for b in self.buckets:
+            if 0 < b.pending < len(b.params):
+                self._launch(b)
+            b.pending = len(b.params)
+        if self.stream is not None:
+            torch.cuda.current_stream(self.comm.device).wait_stream(self.stream)
+        self._callback_queued = False
+
+    def zero_grad(self, set_to_none: bool = False):
+        """Gradients are views of the symmetric buckets; they are zeroed in place, never released."""
+        for b in self.buckets:
+            b.flat.zero_()
+
+
+# ---- torch DDP communication hook ----------------------------------------------------------
+class HookState:
+    def __init__(self, comm, shape=None, algo: str = "auto"):
+        self.comm, self.shape, self.algo = comm, shape, algo
+        self.stream = torch.cuda.Stream(device=comm.device)
+        self.calls = 0
+
+
+def flextree_allreduce_hook(state: HookState, bucket) -> torch.futures.Future:
+    """``ddp.register_comm_hook(HookState(comm), flextree_allreduce_hook)``: average the bucket with
+    FlexTree on a side stream and hand DDP a future that is complete in stream order."""
+    buf = bucket.buffer()
+    dev = state.comm.device
+    state.calls += 1
+    state.stream.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(state.stream):
+        state.comm.all_reduce(buf, op="avg", shape=state.shape, algo=state.algo)
+        fut: torch.futures.Future = torch.futures.Future(devices=[dev])
+        fut.set_result(buf)
+    return fut

@@ -1,0 +1,128 @@
+"""MPI_Allreduce-compatible entry point with ranks as threads (host buffers): the benchmark
+configuration of the reference - N = 6 with FT_TOPO=2,3 and N = 7 with FT_TOPO=2,3 FT_LONELY=1,
+1 048 576 floats per rank, uniform[-1,1) seeded by rank, checked against an fp64 sum."""
+import os
+import threading
+
+import pytest
+import torch
+
+from allreduce_over_mpi_b200.parallel import mpi_compat as M
+
+
+def run_world(world, fn):
+    tw = M.ThreadWorld(world, timeout_s=20)
+    out = [None] * world
+
+    def work(r):
+        comm = tw.comm(r)
+        out[r] = fn(r, comm)
+        comm.free()
+
+    ts = [threading.Thread(target=work, args=(r,)) for r in range(world)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    tw.close()
+    return out
+
+
+def make(rank, n=1_048_576, dtype=torch.float32):
+    g = torch.Generator().manual_seed(rank)
+    return (torch.rand(n, generator=g, dtype=torch.float64) * 2 - 1).to(dtype)
+
+
+@pytest.fixture
+def env():
+    saved = {k: os.environ.get(k) for k in ("FT_TOPO", "FT_LONELY")}
+    yield os.environ
+    for k, v in saved.items():
+        if v is None:
+            os.environ.pop(k, None)
+        else:
+            os.environ[k] = v
+
+
+@pytest.mark.parametrize("world,topo,lonely", [(6, "2,3", None), (7, "2,3", "1"), (6, None, None), (5, "1", None),
+                                               (8, "2,2,2", None), (6, "2,2", "2"), (4, "auto", None)])
+def test_reference_benchmark_configs(env, world, topo, lonely):
+    env.pop("FT_TOPO", None); env.pop("FT_LONELY", None)
+    if topo:
+        env["FT_TOPO"] = topo
+    if lonely:
+        env["FT_LONELY"] = lonely
+    n = 1_048_576 if world <= 7 else 100_003
+    want = torch.stack([make(r, n).double() for r in range(world)]).sum(0)
+
+    def rank_fn(r, comm):
+        assert comm.size() == world and comm.rank() == r
+        data = make(r, n)
+        rc = M.MPI_Allreduce_FT(M.IN_PLACE, data, n, M.MPI_FLOAT, M.MPI_SUM, comm)
+        # out of place as well
+        src, dst = make(r, n), torch.zeros(n)
+        rc2 = M.MPI_Allreduce_FT(src, dst, n, M.MPI_FLOAT, M.MPI_SUM, comm)
+        return rc, rc2, data, dst, torch.equal(src, make(r, n))
+
+    for rc, rc2, data, dst, src_intact in run_world(world, rank_fn):
+        assert rc == 0 and rc2 == 0 and src_intact
+        assert torch.allclose(data.double(), want, atol=2e-5)
+        assert torch.equal(data, dst)
+
+
+def test_single_rank_is_memcpy(env):
+    def rank_fn(r, comm):
+        a, b = torch.arange(10.0), torch.zeros(10)
+        assert M.MPI_Allreduce_FT(a, b, 10, M.MPI_FLOAT, M.MPI_SUM, comm) == 0
+        c = torch.arange(10.0)
+        assert M.MPI_Allreduce_FT(M.IN_PLACE, c, 10, M.MPI_FLOAT, M.MPI_SUM, comm) == 0
+        return b, c
+
+    (b, c), = run_world(1, rank_fn)
+    assert torch.equal(b, torch.arange(10.0)) and torch.equal(c, torch.arange(10.0))
+
+
+def test_datatypes_and_band(env):
+    env.pop("FT_TOPO", None); env.pop("FT_LONELY", None)
+    cases = [(M.MPI_UINT8_T, torch.uint8), (M.MPI_INT8_T, torch.int8), (M.MPI_INT16_T, torch.int16), (M.MPI_INT32_T, torch.int32),
+             (M.MPI_INT64_T, torch.int64), (M.MPI_LONG_LONG, torch.int64), (M.MPI_DOUBLE, torch.float64), (M.MPI_C_BOOL, torch.bool),
+             (M.FT_BFLOAT16, torch.bfloat16), (M.FT_FLOAT16, torch.float16)]
+
+    def rank_fn(r, comm):
+        res = []
+        for code, dt in cases:
+            t = (torch.arange(50) % 3 == r % 3) if dt == torch.bool else torch.full((50,), r + 1).to(dt)
+            rc = M.MPI_Allreduce_FT(M.IN_PLACE, t, 50, code, M.MPI_SUM, comm)
+            res.append((rc, t))
+        b = torch.full((9,), 0xFF ^ (1 << r), dtype=torch.int32)
+        res.append((M.MPI_Allreduce_FT(M.IN_PLACE, b, 9, M.MPI_INT32_T, M.MPI_BAND, comm), b))
+        return res
+
+    out = run_world(4, rank_fn)
+    for (code, dt), (rc, t) in zip(cases, out[0][:-1]):
+        assert rc == 0
+        if dt == torch.bool:
+            assert bool(t.all())
+        else:
+            assert bool((t.double() == 10).all()), dt
+    rc, b = out[2][-1]
+    assert rc == 0 and bool((b == 0xF0).all())
+
+
+def test_errors_are_returned_not_fatal(env, capfd):
+    env["FT_TOPO"] = "2,3"
+    env.pop("FT_LONELY", None)
+
+    def bad_topo(r, comm):
+        return M.MPI_Allreduce_FT(M.IN_PLACE, torch.zeros(4), 4, M.MPI_FLOAT, M.MPI_SUM, comm)
+
+    assert run_world(4, bad_topo) == [4] * 4                      # 2*3 != 4 ranks
+    assert "invalid FT_TOPO 2,3" in capfd.readouterr().err
+    env.pop("FT_TOPO")
+
+    def bad_type(r, comm):
+        return (M.MPI_Allreduce_FT(M.IN_PLACE, torch.zeros(4), 4, M.MPI_FLOAT, M.MPI_BAND, comm),
+                M.MPI_Allreduce_FT(M.IN_PLACE, torch.zeros(4), 4, M.MPI_FLOAT, M.MPI_MAX, comm),
+                M.MPI_Allreduce_FT(M.IN_PLACE, torch.zeros(4), 4, 77, M.MPI_SUM, comm))
+
+    assert run_world(2, bad_type) == [(2, 3, 2)] * 2
+    err = capfd.readouterr().err
+    assert "is not supported in MPI mode." in err and "Unsupported op 100" in err
