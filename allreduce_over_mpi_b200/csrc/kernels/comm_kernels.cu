@@ -123,6 +123,43 @@ __device__ __forceinline__ void copy_range(const unsigned char* src, bool src_ve
   }
 }
 
+// One gather step of a stage: `ng` independent copies (one per source rank), all in flight
+// together so that a small message pays one NVLink round trip for the whole stage and a
+// large one pulls from every peer's link at once instead of queueing on one peer.
+struct CopyJob { const unsigned char* src; unsigned char* dst_work; unsigned char* dst_user; uint64_t bytes; };
+constexpr int kMaxGroup = FT_MAX_FANIN;
+constexpr int kGroupUnroll = 8;
+__device__ __forceinline__ void copy_group(const CopyJob* jobs, int ng, uint64_t max_bytes, bool user_vec_ok, uint32_t es) {
+  const uint64_t max_nvec = (max_bytes + 15) / 16;
+  for (uint64_t base = 0; base < max_nvec; base += blockDim.x) {
+    const uint64_t idx = base + threadIdx.x;
+    const uint64_t off = idx * 16;
+    for (int j0 = 0; j0 < ng; j0 += kGroupUnroll) {
+      uint4 v[kGroupUnroll];
+      bool ok[kGroupUnroll];
+#pragma unroll
+      for (int u = 0; u < kGroupUnroll; ++u) {
+        ok[u] = j0 + u < ng && off < jobs[j0 + u < ng ? j0 + u : 0].bytes;
+        v[u] = ok[u] ? ld_stream(jobs[j0 + u].src + off) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < kGroupUnroll; ++u) {
+        if (!ok[u]) continue;
+        const CopyJob& jb = jobs[j0 + u];
+        const uint32_t valid = (uint32_t)(jb.bytes - off < 16 ? jb.bytes - off : 16);
+        if (jb.dst_work) {
+          if (valid == 16) st_vec(jb.dst_work + off, v[u]);
+          else st_partial(jb.dst_work + off, v[u], valid, es);
+        }
+        if (jb.dst_user) {
+          if (valid == 16 && user_vec_ok) st_vec(jb.dst_user + off, v[u]);
+          else st_partial(jb.dst_user + off, v[u], valid, es);
+        }
+      }
+    }
+  }
+}
+
 struct LaneSlice { uint64_t off, bytes; };
 // Sub-range of a region of `region_bytes` owned by `lane` of `nlanes` when every lane
 // takes a 16-byte-aligned chunk of `chunk` bytes.
@@ -138,6 +175,7 @@ template <int POL>
 __global__ void __launch_bounds__(kThreads) staged_allreduce_kernel(const __grid_constant__ CommDev c, const __grid_constant__ StagedArgs a) {
   using P = typename PolById<POL>::type;
   __shared__ const unsigned char* ptrs[2][FT_MAX_FANIN];
+  __shared__ CopyJob jobs[kMaxGroup];
   __shared__ int abort_flag;
   __shared__ unsigned long long call_slot;
   const int lane = blockIdx.x, nlanes = gridDim.x;
@@ -180,28 +218,49 @@ __global__ void __launch_bounds__(kThreads) staged_allreduce_kernel(const __grid
       lane_rendezvous(sync, st.sync_mask, call * kCallStride + s + 1, (int)s);
       if (abort_flag) break;
     }
-    for (uint32_t q = st.pull_begin; q < st.pull_end; ++q) {
+    // the very last stage's gathers are read by nobody: skip the work-buffer copy when the
+    // caller takes the result elsewhere
+    const bool need_work = !(a.user_out && s + 1 == a.plan->nstages);
+    uint32_t q = st.pull_begin;
+    while (q < st.pull_end) {
       const DevPull pl = a.pulls[q];
-      const LaneSlice sl = lane_slice(block_len(pl.block), chunk, lane);
-      if (!sl.bytes) continue;   // uniform across the CTA
-      const uint64_t off = (uint64_t)pl.block * block_bytes + sl.off;
-      const int n = pl.reduce ? pl.nsrc + 1 : 1;
-      if ((int)threadIdx.x < n) {
-        const unsigned char* p;
-        if (pl.reduce) p = threadIdx.x == 0 ? my_work + off : c.heap[pl.src[threadIdx.x - 1]] + work_off + off;
-        else p = c.heap[pl.src[0]] + work_off + off;
-        ptrs[pp][threadIdx.x] = p;
+      if (pl.reduce) {
+        ++q;
+        const LaneSlice sl = lane_slice(block_len(pl.block), chunk, lane);
+        if (!sl.bytes) continue;   // uniform across the CTA
+        const uint64_t off = (uint64_t)pl.block * block_bytes + sl.off;
+        const int n = pl.nsrc + 1;
+        if ((int)threadIdx.x < n)
+          ptrs[pp][threadIdx.x] = threadIdx.x == 0 ? my_work + off : c.heap[pl.src[threadIdx.x - 1]] + work_off + off;
+        __syncthreads();
+        // a block is final for this rank when its last reduction happens here
+        pull_range<P>(ptrs[pp], n, need_work ? my_work + off : nullptr,
+                      (a.user_out && st.last_rs) ? (unsigned char*)a.user_out + off : nullptr, a.user_vec_ok, sl.bytes, es,
+                      st.last_rs != 0, a.scale);
+        pp ^= 1;
+        continue;
+      }
+      // a run of gathers: collect them and move them together
+      int ng = 0;
+      uint64_t max_bytes = 0;
+      for (; q < st.pull_end && ng < kMaxGroup; ++q) {
+        const DevPull g = a.pulls[q];
+        if (g.reduce) break;
+        const LaneSlice sl = lane_slice(block_len(g.block), chunk, lane);
+        if (!sl.bytes) continue;
+        const uint64_t off = (uint64_t)g.block * block_bytes + sl.off;
+        if (threadIdx.x == 0) {
+          jobs[ng].src = c.heap[g.src[0]] + work_off + off;
+          jobs[ng].dst_work = need_work ? my_work + off : nullptr;
+          jobs[ng].dst_user = a.user_out ? (unsigned char*)a.user_out + off : nullptr;
+          jobs[ng].bytes = sl.bytes;
+        }
+        max_bytes = sl.bytes > max_bytes ? sl.bytes : max_bytes;
+        ++ng;
       }
       __syncthreads();
-      // a block is final for this rank when its last reduction happens here or when it is gathered
-      const bool final_here = st.is_ag || st.last_rs;
-      // the very last stage's gathers are read by nobody: skip the work-buffer copy when the
-      // caller takes the result elsewhere
-      const bool need_work = !(a.user_out && s + 1 == a.plan->nstages);
-      pull_range<P>(ptrs[pp], n, need_work ? my_work + off : nullptr,
-                    (a.user_out && final_here) ? (unsigned char*)a.user_out + off : nullptr, a.user_vec_ok, sl.bytes, es,
-                    st.last_rs && pl.reduce, a.scale);
-      pp ^= 1;
+      if (ng) copy_group(jobs, ng, max_bytes, a.user_vec_ok, es);
+      __syncthreads();
     }
   }
   if (a.do_sync && a.end_sync && !abort_flag && a.stage_end == a.plan->nstages)

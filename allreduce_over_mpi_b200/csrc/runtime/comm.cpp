@@ -13,6 +13,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <algorithm>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -198,7 +199,14 @@ int get_plan(ft_comm* c, const ft::Shape& shape, DevPlanEntry** out) {
   for (int s = 0; s < p.num_stages; ++s) {
     ftk::DevStage& ds = hp.stages[s];
     ds.pull_begin = (uint32_t)pulls.size();
-    for (const ft::Pull& pl : p.stages[c->rank][s].pulls) {
+    std::vector<ft::Pull> ordered = p.stages[c->rank][s].pulls;
+    // gathers start at the next rank up and wrap around, so that at any moment the ranks of a
+    // stage read from different peers instead of all queueing on the lowest-numbered one
+    if (std::none_of(ordered.begin(), ordered.end(), [](const ft::Pull& x) { return x.reduce; }))
+      std::stable_sort(ordered.begin(), ordered.end(), [&](const ft::Pull& x, const ft::Pull& y) {
+        return (x.srcs[0] - c->rank + c->world) % c->world < (y.srcs[0] - c->rank + c->world) % c->world;
+      });
+    for (const ft::Pull& pl : ordered) {
       ftk::DevPull dp{};
       dp.block = (uint16_t)pl.block;
       dp.nsrc = (uint8_t)pl.srcs.size();

@@ -69,10 +69,12 @@ class _CommBase:
         self.world = 1
         self.device = torch.device("cuda", 0)
         self.cost = CostParams.load()
+        self.table = planner.load_choice_table()
         self.default_shape: Shape | None = None
         self.auto = True
         self.has_nvls = False
-        self.nvls_min_bytes = int(os.environ.get("FT_NVLS_MIN_BYTES", 1 << 20))
+        self._choices: dict = {}
+        self._heap_range = None
 
     # -- errors
     def _check(self, code: int):
@@ -125,16 +127,30 @@ class _CommBase:
         lib().ft_comm_alloc_reset(self._h)
 
     def in_heap(self, t: torch.Tensor) -> bool:
-        base = lib().ft_comm_heap_base(self._h) or 0
-        return base <= t.data_ptr() and t.data_ptr() + t.numel() * t.element_size() <= base + lib().ft_comm_heap_bytes(self._h)
+        if self._heap_range is None:
+            base = lib().ft_comm_heap_base(self._h) or 0
+            self._heap_range = (base, base + lib().ft_comm_heap_bytes(self._h))
+        p = t.data_ptr()
+        return self._heap_range[0] <= p and p + t.numel() * t.element_size() <= self._heap_range[1]
 
     # -- selection
     def choose(self, nbytes: int, in_heap: bool, dtype: torch.dtype) -> tuple[str, Shape]:
         """Algorithm and shape for a message, from the calibrated cost model."""
         nvls_ok = self.has_nvls and in_heap and dtype in (torch.float32, torch.bfloat16, torch.float16) and nbytes % 16 == 0
-        algo, shape, _ = planner.pick_algorithm(self.world, nbytes, self.cost, allow_oneshot=nbytes <= self.staging_bytes,
-                                                allow_nvls=nvls_ok)
-        return algo, shape
+        key = (nbytes, nvls_ok)
+        hit = self._choices.get(key)
+        if hit is None and self.table:   # measured winners for this world size, nearest size on a log scale
+            import math
+            rows = [r for r in self.table.get(str(self.world), []) if (r[1] != "nvls" or nvls_ok) and
+                    (r[1] != "oneshot" or nbytes <= self.staging_bytes)]
+            if rows:
+                b = min(rows, key=lambda r: abs(math.log(max(r[0], 1)) - math.log(max(nbytes, 1))))
+                hit = self._choices[key] = (b[1], Shape.parse(b[2]))
+        if hit is None:   # scoring every shape costs ~0.1 ms of host time: do it once per message size
+            algo, shape, _ = planner.pick_algorithm(self.world, nbytes, self.cost, allow_oneshot=nbytes <= self.staging_bytes,
+                                                    allow_nvls=nvls_ok)
+            hit = self._choices[key] = (algo, shape)
+        return hit
 
     # -- the collective
     def all_reduce(self, tensor: torch.Tensor, op: str = "sum", shape=None, algo: str = "auto", scale: float = 1.0,

@@ -140,6 +140,8 @@ class CostParams:
     @staticmethod
     def from_json(text: str) -> "CostParams":
         d = json.loads(text)
+        d = d.get("params", d)   # a calibration file nests the parameters next to the choice table
+        d = {k: v for k, v in d.items() if k in CostParams.__dataclass_fields__}
         d["peer_eff"] = {int(k): float(v) for k, v in d.get("peer_eff", {}).items()}
         return CostParams(**d)
 
@@ -151,6 +153,19 @@ class CostParams:
             with open(path) as f:
                 return CostParams.from_json(f.read())
         return CostParams()
+
+
+def calibration_path(path: str | os.PathLike | None = None) -> str:
+    return str(path or os.environ.get("FT_CALIBRATION") or os.path.join(os.path.dirname(__file__), "calibration_b200.json"))
+
+
+def load_choice_table(path: str | os.PathLike | None = None) -> dict:
+    """Measured winners per world size: {"8": [[bytes, algo, shape], ...]} (empty when not calibrated)."""
+    path = calibration_path(path)
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f).get("table", {})
+    return {}
 
 
 def cost_v1(world: int, shape: Shape, nbytes: int, params: CostParams | None = None) -> float:
