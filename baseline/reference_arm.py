@@ -1,0 +1,109 @@
+"""Reference arm of bench.py: runs the UNMODIFIED reference binaries built by
+baseline/install_reference.py and reports the same metric as the FlexTree arm.
+
+N = 1   baseline/_ref/ref_nway: the reference's CUDA launcher reduce_sum_gpu<float>
+        (vector_add/reduce_sum_gpu.h) on n in {2,3,4,8} x 64 Mi floats.
+N > 1   baseline/_ref/ref_mpi_bench: the reference's benchmark.cpp + mpi_mod.hpp (MPI_Allreduce_FT,
+        flat tree unless FT_TOPO is set) over the shared-memory MPI shim, one process per rank, host
+        memory (the reference has no GPU data path).  Per-repeat times come from the file the
+        reference's own --to-file option writes (host MPI_Wtime on rank 0).
+"""
+from __future__ import annotations
+
+import glob
+import json
+import os
+import subprocess
+import tempfile
+import uuid
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF = os.path.join(HERE, "_ref")
+FANINS = (2, 3, 4, 8)
+
+
+def unavailable(why: str) -> dict:
+    return {"impl": "reference", "unavailable": why}
+
+
+def run_reference(a, world: int, rank: int) -> dict:
+    if world <= 1 and a.gpus <= 1:
+        return _nway(a)
+    return _mpi(a, world, rank)
+
+
+def _nway(a) -> dict:
+    exe = os.path.join(REF, "ref_nway")
+    if not os.path.exists(exe):
+        return unavailable("baseline/_ref/ref_nway is not built (run python baseline/install_reference.py)")
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return unavailable("no CUDA device")
+    except Exception as e:  # noqa: BLE001
+        return unavailable(f"torch import failed: {e}")
+    warm = max(a.warmup, 3)
+    r = subprocess.run([exe, str(a.elems), str(a.steps), str(warm)], capture_output=True, text=True, timeout=1200)
+    if r.returncode != 0:
+        return unavailable(f"ref_nway exited {r.returncode}: {r.stderr[-200:]}")
+    d = json.loads(r.stdout.strip().splitlines()[-1])
+    nbytes = a.elems * 4
+    step_bytes = sum((n + 1) * nbytes for n in FANINS)
+    value = step_bytes / (d["ms_per_step"] * 1e-3) / 1e9
+    return {"metric": "n-way reduce-sum GB/s (sum over n in {2,3,4,8} of (n+1)*bytes / time)", "value": round(value, 1),
+            "unit": "GB/s", "n_gpus": 1, "steps": a.steps, "warmup": warm, "ms_per_step": d["ms_per_step"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "float32",
+            "data": "synthetic uniform[-1,1) seeded", "impl": "reference",
+            "config": {"model": "n-way reduce-sum, n in {2,3,4,8}", "elems_per_vector": a.elems, "parallelism": "single GPU",
+                       "kernel": "reference reduce_sum_gpu<float>, 256 threads/block, one element per thread, recompiled for sm_100a",
+                       "l2": "inputs larger than L2"},
+            "per_fanin": {str(n): {"ms": ms, "GBps": round((n + 1) * nbytes / (ms * 1e-3) / 1e9, 1)}
+                          for n, ms in zip(FANINS, d["per_fanin_ms"])},
+            "max_abs_err": d["max_abs_err"], "gpu_launches": 4 * a.steps}
+
+
+def _mpi(a, world: int, rank: int) -> dict:
+    exe = os.path.join(REF, "ref_mpi_bench")
+    if not os.path.exists(exe):
+        return unavailable("baseline/_ref/ref_mpi_bench is not built (run python baseline/install_reference.py)")
+    import torch.distributed as dist
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    if not dist.is_initialized():
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+    box = [f"{uuid.uuid4().hex[:12]}" if rank == 0 else None, tempfile.mkdtemp(prefix="ftref-") if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    session, workdir = box
+    count = a.bytes // 4
+    warm = max(a.warmup, 3)
+    repeat = a.steps + warm
+    env = dict(os.environ, FTSHIM_RANK=str(rank), FTSHIM_SIZE=str(world), FTSHIM_SESSION=session, OMP_NUM_THREADS="14")
+    # With FT_TOPO unset the reference's own validity check rejects every world > 1 (its width
+    # product stays 1, allreduce_over_mpi/mpi_mod.hpp:1447-1475), so the flat tree is named explicitly.
+    env.setdefault("FT_TOPO", str(world))
+    cmd = [exe, "--size", str(count), "--repeat", str(repeat), "--to-file", "--tag", "bench"]
+    r = subprocess.run(cmd, capture_output=True, text=True, cwd=workdir, env=env, timeout=3000)
+    codes = [None] * world
+    dist.all_gather_object(codes, r.returncode)
+    out = None
+    if rank == 0:
+        files = glob.glob(os.path.join(workdir, "bench.*.txt"))
+        if any(codes) or not files:
+            out = unavailable(f"ref_mpi_bench failed: rc={codes} {r.stderr[-200:]}")
+        else:
+            times = [float(x) for x in open(files[0]).read().split()][-a.steps:]
+            sec = sum(times) / len(times)
+            value = a.bytes / sec / 1e9 * (2 * (world - 1) / world)
+            topo = env["FT_TOPO"]
+            out = {"metric": "all-reduce bus bandwidth GB/s (bytes/t * 2(N-1)/N), t = max over ranks", "value": round(value, 3),
+                   "unit": "GB/s", "n_gpus": world, "steps": a.steps, "warmup": warm, "ms_per_step": round(sec * 1e3, 3),
+                   "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "float32",
+                   "data": "reference benchmark's own fill (i * 0.1 on every rank)", "impl": "reference",
+                   "config": {"model": "all-reduce", "message_bytes": a.bytes, "parallelism": f"dp{world}",
+                              "path": "reference MPI_Allreduce_FT (benchmark.cpp --size --repeat --to-file), CPU ranks in host "
+                                      "memory over a shared-memory MPI shim; time is the reference's own host MPI_Wtime on rank 0",
+                              "FT_TOPO": topo, "FT_LONELY": os.environ.get("FT_LONELY", "0")},
+                   "gpu_launches": 0}
+    dist.barrier()
+    dist.destroy_process_group()
+    return out
