@@ -45,31 +45,39 @@ __global__ void __launch_bounds__(512) reduce_nway_vec_kernel(const __grid_const
       idx[u] = base + (unsigned long long)u * blockDim.x + threadIdx.x;
       ok[u] = idx[u] < a.nvec;
     }
+    // sources are consumed GROUP at a time: all GROUP x UNROLL loads of a group are issued
+    // before the first add, whatever the fan-in (the bounds test is uniform across the grid)
     {
-      uint4 v[UNROLL];
-#pragma unroll
-      for (int u = 0; u < UNROLL; ++u) v[u] = ok[u] ? ld_stream((const uint4*)a.src[0] + idx[u]) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-      for (int u = 0; u < UNROLL; ++u) P::init(acc[u], v[u]);
-    }
-    int k = 1;
-    for (; k + GROUP <= a.n; k += GROUP) {
       uint4 v[GROUP][UNROLL];
 #pragma unroll
       for (int g = 0; g < GROUP; ++g)
+        if (g < a.n) {
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) v[g][u] = ok[u] ? ld_stream((const uint4*)a.src[k + g] + idx[u]) : make_uint4(0, 0, 0, 0);
+          for (int u = 0; u < UNROLL; ++u) v[g][u] = ok[u] ? ld_stream((const uint4*)a.src[g] + idx[u]) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) P::init(acc[u], v[0][u]);
+#pragma unroll
+      for (int g = 1; g < GROUP; ++g)
+        if (g < a.n) {
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) P::add(acc[u], v[g][u]);
+        }
+    }
+    for (int k = GROUP; k < a.n; k += GROUP) {
+      uint4 v[GROUP][UNROLL];
 #pragma unroll
       for (int g = 0; g < GROUP; ++g)
+        if (k + g < a.n) {
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) P::add(acc[u], v[g][u]);
-    }
-    for (; k < a.n; ++k) {
-      uint4 v[UNROLL];
+          for (int u = 0; u < UNROLL; ++u) v[g][u] = ok[u] ? ld_stream((const uint4*)a.src[k + g] + idx[u]) : make_uint4(0, 0, 0, 0);
+        }
 #pragma unroll
-      for (int u = 0; u < UNROLL; ++u) v[u] = ok[u] ? ld_stream((const uint4*)a.src[k] + idx[u]) : make_uint4(0, 0, 0, 0);
+      for (int g = 0; g < GROUP; ++g)
+        if (k + g < a.n) {
 #pragma unroll
-      for (int u = 0; u < UNROLL; ++u) P::add(acc[u], v[u]);
+          for (int u = 0; u < UNROLL; ++u) P::add(acc[u], v[g][u]);
+        }
     }
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u)
@@ -216,7 +224,7 @@ template <int POL, int UNROLL, int GROUP>
 static cudaError_t launch_vec(const NwayArgs& a, int threads, int ctas_per_sm, cudaStream_t st) {
   const unsigned long long per_cta = (unsigned long long)threads * UNROLL;
   unsigned long long want = (a.nvec + per_cta - 1) / per_cta;
-  unsigned long long cap = (unsigned long long)dev_info().sms * ctas_per_sm;
+  unsigned long long cap = ctas_per_sm > 0 ? (unsigned long long)dev_info().sms * ctas_per_sm : 0x7fffffffull;
   int grid = (int)(want < cap ? want : cap);
   if (grid < 1) grid = 1;
   reduce_nway_vec_kernel<POL, UNROLL, GROUP><<<grid, threads, 0, st>>>(a);
@@ -288,12 +296,20 @@ static int run_policy(NwayArgs& a, size_t bytes, int variant, cudaStream_t st) {
         case 13: e = launch_vec<POL, 4, 2>(a, 512, 2, st); done = true; break;
         case 14: e = launch_vec<POL, 4, 2>(a, 512, 4, st); done = true; break;
         case 15: e = launch_vec<POL, 4, 2>(a, 256, 8, st); done = true; break;
-        case 16: e = launch_vec<POL, 8, 1>(a, 256, 4, st); done = true; break;
+        case 16: e = launch_vec<POL, 2, 8>(a, 256, 4, st); done = true; break;
+        case 17: e = launch_vec<POL, 1, 8>(a, 256, 0, st); done = true; break;
+        case 18: e = launch_vec<POL, 2, 4>(a, 256, 0, st); done = true; break;
+        case 19: e = launch_vec<POL, 4, 4>(a, 256, 0, st); done = true; break;
+        case 20: e = launch_vec<POL, 1, 4>(a, 512, 0, st); done = true; break;
+        case 21: e = launch_vec<POL, 2, 8>(a, 256, 8, st); done = true; break;
+        case 22: e = launch_vec<POL, 1, 8>(a, 512, 4, st); done = true; break;
         default: break;
       }
     }
-    // default picked from a B200 sweep: 4 vectors x 4 sources in flight, 256 threads, 4 CTAs per SM
-    if (!done) e = launch_vec<POL, 4, 4>(a, 256, 4, st);
+    // defaults picked from a B200 sweep (fp32 and bf16, 64 Mi elements): low fan-in runs a
+    // persistent grid of 2 CTAs x 512 threads per SM with 4 vectors x 2 sources in flight; from
+    // fan-in 6 up one CTA per tile with 1 vector x 4 sources in flight does better
+    if (!done) e = a.n >= 6 ? launch_vec<POL, 1, 4>(a, 512, 0, st) : launch_vec<POL, 4, 2>(a, 512, 2, st);
     if (e != cudaSuccess) return cuda_fail(e, "reduce_nway vector launch");
   }
   e = launch_scalar<POL>(a, a.nvec * 16 / unit, st);
