@@ -104,11 +104,17 @@ def sweep(a, comm: FlexTreeComm, rank: int, world: int) -> list[dict]:
             impls = []
             for shape in a.shapes:
                 for algo in a.algos:
-                    if algo in ("oneshot", "nvls") and shape != a.shapes[0]:
+                    if algo != "staged" and shape != a.shapes[0]:
                         continue
                     if algo == "oneshot" and nbytes > min(comm.staging_bytes, a.oneshot_cap):
                         continue
-                    if algo == "nvls" and (not comm.has_nvls or nbytes % 16):
+                    if algo == "ll" and nbytes > (32 << 10):
+                        continue
+                    if algo in ("nvls", "hybrid") and (not comm.has_nvls or nbytes % 16):
+                        continue
+                    if algo == "hybrid":
+                        if nbytes >= a.hybrid_min:
+                            impls += [(f"{bf},{lf}", "hybrid") for bf, lf in a.hybrid]
                         continue
                     if algo == "staged" and shape != "auto" and validate_shape(world, Shape.parse(shape)):
                         continue
@@ -124,11 +130,18 @@ def sweep(a, comm: FlexTreeComm, rank: int, world: int) -> list[dict]:
                     fn = lambda shape=shape: comm.all_reduce(sym, shape=shape, algo="staged")  # noqa: E731
                 elif algo == "nvls":
                     fn = lambda: comm.all_reduce(sym, algo="nvls")  # noqa: E731
+                elif algo == "hybrid":
+                    bf, lf = (float(x) for x in shape.split(","))
+                    comm.set_hybrid(bf, lf)
+                    fn = lambda: comm.all_reduce(sym, algo="hybrid")  # noqa: E731
+                    label = f"flextree/hybrid-{bf}-{lf}/{world}"
+                elif algo == "ll":
+                    fn = lambda: comm.all_reduce(loc, algo="ll")  # noqa: E731
                 else:
                     fn = lambda: comm.all_reduce(loc, algo="oneshot")  # noqa: E731
                 row = {"bench": "allreduce", "impl": label, "bytes": nbytes, "dtype": dt_name, "world": world}
                 if a.check:
-                    tgt = loc if algo == "oneshot" else sym
+                    tgt = loc if algo in ("oneshot", "ll") else sym
                     fill(tgt, rank)
                     fn()
                     torch.cuda.synchronize()
@@ -173,8 +186,10 @@ def main(argv=None):
     ap.add_argument("--step", type=int, default=4)
     ap.add_argument("--dtypes", nargs="+", default=["float32"])
     ap.add_argument("--shapes", nargs="+", default=["auto"])
-    ap.add_argument("--algos", nargs="+", default=["staged", "oneshot", "nvls"])
+    ap.add_argument("--algos", nargs="+", default=["staged", "ll", "oneshot", "nvls"])
     ap.add_argument("--oneshot-cap", type=int, default=4 << 20)
+    ap.add_argument("--hybrid", nargs="*", default=["0.7,0.5"], help="byte_fraction,lane_fraction pairs tried by algo hybrid")
+    ap.add_argument("--hybrid-min", type=int, default=4 << 20)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--nccl", action="store_true")
@@ -183,6 +198,7 @@ def main(argv=None):
     ap.add_argument("--staged-copy", action="store_true", help="also time the path for tensors outside the symmetric heap")
     ap.add_argument("--out", default=None)
     a = ap.parse_args(argv)
+    a.hybrid = [tuple(float(x) for x in h.split(",")) for h in a.hybrid]
     rank, world, _ = init_dist()
     comm = make_comm(a.max_bytes)
     if rank == 0:
@@ -265,7 +281,7 @@ def bench_allreduce_main(a) -> dict:
     if not a.no_sweep:
         ns = argparse.Namespace(min_bytes=1024, max_bytes=min(a.bytes, 1 << 30), step=16, dtypes=[a.dtype], shapes=["auto"],
                                 algos=["staged"], oneshot_cap=4 << 20, iters=10, warmup=3, nccl=True, check=False,
-                                no_flush=False, staged_copy=False)
+                                no_flush=False, staged_copy=False, hybrid=[], hybrid_min=1 << 62)
         import contextlib
         import io
         with contextlib.redirect_stdout(io.StringIO()):

@@ -31,7 +31,7 @@ extern "C" {
 typedef struct ft_comm ft_comm;
 
 enum { FT_MEM_IPC = 0, FT_MEM_VMM = 1 };
-enum { FT_ALGO_AUTO = 0, FT_ALGO_STAGED = 1, FT_ALGO_ONESHOT = 2, FT_ALGO_NVLS = 3 };
+enum { FT_ALGO_AUTO = 0, FT_ALGO_STAGED = 1, FT_ALGO_ONESHOT = 2, FT_ALGO_NVLS = 3, FT_ALGO_HYBRID = 4, FT_ALGO_LL = 5 };
 
 /* heap_bytes: symmetric memory for user tensors (ft_comm_alloc) and internal staging.
  * staging_bytes: size of ONE staging slot (two are carved out of the heap); bounds the
@@ -77,19 +77,27 @@ void ft_comm_set_max_lanes(ft_comm* c, int lanes);              /* CTAs per coll
  * (sendbuf must be NULL or == recvbuf).  Otherwise the input is staged through the
  * internal slots and the result lands in recvbuf (count * size <= staging_bytes).
  * shape: (widths, nw, lonely, ring) as in flextree.h; nw == 0 means flat.
- * algo: FT_ALGO_*; AUTO picks one-shot below `oneshot_max_bytes` (64 KiB unless changed with
- * ft_comm_set_oneshot_max), else the staged plan.
+ * algo: FT_ALGO_*; AUTO picks the low-latency push protocol up to 8 KiB, one-shot up to
+ * `oneshot_max_bytes` (64 KiB unless changed with ft_comm_set_oneshot_max), else the staged plan.
  * scale: multiplied into floating-point results (1/world for averaging).
  * Asynchronous on `stream`; errors of device-side waits surface in ft_comm_status. */
 int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op, const int* widths,
                  int nw, int lonely, int ring, int algo, float scale, void* stream);
 void ft_comm_set_oneshot_max(ft_comm* c, size_t bytes);
+/* FT_ALGO_HYBRID: fraction of every block reduced inside the switch (the rest goes over peer
+ * loads at the same time) and fraction of the kernel's CTAs given to that part */
+void ft_comm_set_hybrid(ft_comm* c, double byte_fraction, double lane_fraction);
 
 /* Single-GPU emulation helper: run only stages [stage_begin, stage_end) of the plan with no
  * rendezvous (the caller serialises ranks and stages on one stream). */
 int ft_allreduce_emulate_stage(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op,
                                const int* widths, int nw, int lonely, int ring, float scale, int stage_begin,
                                int stage_end, void* stream);
+/* low-latency push emulation: phase 1 = push (all ranks first), phase 2 = receive and reduce */
+int ft_allreduce_emulate_ll(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op, float scale,
+                            int phase, uint64_t call, void* stream);
+/* largest message AUTO sends through the low-latency push protocol (<= 32 KiB) */
+void ft_comm_set_ll_max(ft_comm* c, size_t bytes);
 /* one-shot emulation: phase 1 = publish input (all ranks first), phase 4 = reduce */
 int ft_allreduce_emulate_oneshot(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op,
                                  float scale, int phase, uint64_t call, void* stream);

@@ -84,6 +84,22 @@ struct OneShotArgs {
   float scale;
 };
 
+// Low-latency push all-reduce: data travels as 8-byte words {32 data bits, 32-bit tag}.
+constexpr uint64_t kLLMaxBytes = 32 << 10;              // largest message (payload bytes)
+constexpr uint64_t kLLSrcStride = 2 * kLLMaxBytes;      // wire bytes one source rank may deposit per parity
+struct LLArgs {
+  uint64_t ll_off;            // byte offset of the receive area in every heap: [2 parities][world][kLLSrcStride]
+  const void* user_in;
+  void* user_out;
+  uint64_t count;
+  uint32_t elem_size;
+  uint32_t phase_mask;        // bit0 send, bit1 receive+reduce (both normally; split only for emulation)
+  uint32_t user_vec_ok;
+  uint32_t use_call_counter;  // 0: take the call number from emu_call (emulation)
+  uint64_t emu_call;
+  float scale;
+};
+
 struct NvlsArgs {
   uint64_t work_off;
   uint64_t count;

@@ -11,6 +11,9 @@
 //    rendezvous, every rank sums all N copies itself (latency-optimal for small sizes).
 //  * nvls_allreduce_kernel     multimem.ld_reduce / multimem.st through the NVSwitch
 //    multicast mapping (in-switch reduction), where the box exposes it.
+//  * hybrid_allreduce_kernel   both at once on disjoint parts of the message.
+//  * ll_allreduce_kernel       push protocol with the flag inside every 8-byte word, no
+//    rendezvous at all (smallest messages).
 //
 // Work split: CTA c ("lane" c) of every rank owns the same byte sub-range of every
 // block, so all dependencies between ranks are lane-local and a rendezvous never needs
@@ -304,6 +307,89 @@ __global__ void __launch_bounds__(kThreads) oneshot_allreduce_kernel(const __gri
   }
 }
 
+// ------------------------------------------------------------------------------- low-latency push
+// For messages of a few KB the cost is all latency.  Here nothing waits for a rendezvous:
+// every rank pushes its input straight into a receive area in every peer's heap as 8-byte
+// words {32 bits of data, 32-bit tag of this call}; 8-byte stores are single-copy atomic, so
+// a word whose tag matches carries valid data.  Each rank then polls its own memory, sums the
+// N contributions in rank order (identical bits on every rank) and writes the result.  Two
+// receive areas alternate with the call parity; a peer cannot be two calls ahead because
+// finishing a call needs this rank's data of that call.
+__device__ __forceinline__ void st_ll(unsigned char* p, uint32_t d0, uint32_t d1, uint32_t tag) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(d0), "r"(tag), "r"(d1), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint4 ld_ll(const unsigned char* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+template <int POL>
+__global__ void __launch_bounds__(kThreads) ll_allreduce_kernel(const __grid_constant__ CommDev c, const __grid_constant__ LLArgs a) {
+  using P = typename PolById<POL>::type;
+  __shared__ unsigned long long call_slot;
+  unsigned long long call;
+  if (a.use_call_counter) call = begin_call(c, &call_slot);
+  else call = a.emu_call;
+  const uint32_t tag = (uint32_t)(call + 1) | 0x80000000u;   // never 0, differs between consecutive calls of a parity
+  const uint32_t es = a.elem_size;
+  const uint64_t total_bytes = a.count * es;
+  const uint64_t nitems = (total_bytes + 15) / 16;            // 16 payload bytes = 32 wire bytes per item
+  const uint64_t area = a.ll_off + (call & 1) * (uint64_t)c.world * kLLSrcStride;
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nitems) return;
+  const uint32_t valid = (uint32_t)(total_bytes - i * 16 < 16 ? total_bytes - i * 16 : 16);
+  uint4 mine = make_uint4(0, 0, 0, 0);
+  if (a.phase_mask & 1) {
+    const unsigned char* src = (const unsigned char*)a.user_in + i * 16;
+    mine = (valid == 16 && a.user_vec_ok) ? ld_stream(src) : ld_partial(src, valid, es);
+    for (int k = 1; k < c.world; ++k) {
+      const int p = (c.rank + k) % c.world;
+      unsigned char* dst = c.heap[p] + area + (uint64_t)c.rank * kLLSrcStride + i * 32;
+      st_ll(dst, mine.x, mine.y, tag);
+      st_ll(dst + 16, mine.z, mine.w, tag);
+    }
+    if (!(a.phase_mask & 2)) {   // emulation: park the own contribution like a peer would
+      unsigned char* dst = c.heap[c.rank] + area + (uint64_t)c.rank * kLLSrcStride + i * 32;
+      st_ll(dst, mine.x, mine.y, tag);
+      st_ll(dst + 16, mine.z, mine.w, tag);
+    }
+  }
+  if (!(a.phase_mask & 2)) return;
+  const bool own_from_mem = !(a.phase_mask & 1);
+  typename P::Acc acc;
+  const unsigned long long t0 = globaltimer_ns();
+  for (int q = 0; q < c.world; ++q) {
+    uint4 v;
+    if (q == c.rank && !own_from_mem) {
+      v = mine;
+    } else {
+      const unsigned char* src = c.heap[c.rank] + area + (uint64_t)q * kLLSrcStride + i * 32;
+      uint4 lo, hi;
+      int spins = 0;
+      for (;;) {
+        lo = ld_ll(src);
+        hi = ld_ll(src + 16);
+        if (lo.y == tag && lo.w == tag && hi.y == tag && hi.w == tag) break;
+        if (++spins >= 64) {
+          spins = 0;
+          if (globaltimer_ns() - t0 > c.timeout_ns) {
+            report(c.status, FT_ERR_TIMEOUT, 0, q, blockIdx.x);
+            return;
+          }
+        }
+      }
+      v = make_uint4(lo.x, lo.z, hi.x, hi.z);
+    }
+    if (q == 0) P::init(acc, v);
+    else P::add(acc, v);
+  }
+  const uint4 out = a.scale != 1.0f ? P::fins(acc, a.scale) : P::fin(acc);
+  unsigned char* dst = (unsigned char*)a.user_out + i * 16;
+  if (valid == 16 && a.user_vec_ok) st_vec(dst, out);
+  else st_partial(dst, out, valid, es);
+}
+
 // ------------------------------------------------------------------------------- NVLS
 // multimem.ld_reduce sums one 16-byte vector across every GPU bound to the multicast
 // object inside the switch; multimem.st writes one to all of them.
@@ -384,6 +470,117 @@ __global__ void __launch_bounds__(kThreads) nvls_allreduce_kernel(const __grid_c
   lane_rendezvous(sync, all, call * kCallStride + 2, 1);
 }
 
+// ------------------------------------------------------------------------------- hybrid NVLS + peer loads
+// The in-switch reduction tops out well below the bandwidth of the GPU's links, and a
+// two-shot all-reduce over plain peer loads uses the same links in a different way (no
+// switch arithmetic).  This kernel runs both at once on disjoint parts of every block: the
+// first `nvls_bytes` of each block go through multimem.ld_reduce / multimem.st on lanes
+// [0, nvls_lanes), the remainder through a flat reduce-scatter + gather over peer loads on
+// the other lanes.  The two lane groups never wait for each other.
+template <int POL>
+__global__ void __launch_bounds__(kThreads) hybrid_allreduce_kernel(const __grid_constant__ CommDev c, const __grid_constant__ NvlsArgs a,
+                                                                     uint32_t nvls_lanes, uint64_t nvls_bytes) {
+  using P = typename PolById<POL>::type;
+  __shared__ const unsigned char* ptrs[FT_MAX_RANKS];
+  __shared__ CopyJob jobs[kMaxGroup];
+  __shared__ int abort_flag;
+  __shared__ unsigned long long call_slot;
+  const int lane = blockIdx.x;
+  if (threadIdx.x == 0) abort_flag = 0;
+  const unsigned long long call = begin_call(c, &call_slot);
+  LaneSync sync{c.flags, c.flags[c.rank], c.rank, c.world, lane, FT_MAX_RANKS, c.timeout_ns, c.status, &abort_flag};
+  const unsigned long long all = c.world >= 64 ? ~0ull : ((1ull << c.world) - 1);
+  const uint32_t es = a.elem_size;
+  const uint64_t block_bytes = a.block_elems * es, total_bytes = a.count * es;
+  auto block_len = [&](int b) -> uint64_t {
+    const uint64_t lo = (uint64_t)b * block_bytes;
+    return lo >= total_bytes ? 0 : (total_bytes - lo < block_bytes ? total_bytes - lo : block_bytes);
+  };
+  // part of block b handled by this lane group: [part_lo, part_hi) inside the block
+  const bool is_nvls = (uint32_t)lane < nvls_lanes;
+  const int group_lanes = is_nvls ? (int)nvls_lanes : (int)(gridDim.x - nvls_lanes);
+  const int group_lane = is_nvls ? lane : lane - (int)nvls_lanes;
+  const uint64_t region = is_nvls ? nvls_bytes : block_bytes - nvls_bytes;
+  uint64_t chunk = (region + group_lanes - 1) / group_lanes;
+  chunk = (chunk + 15) & ~15ull;
+  auto my_slice = [&](int b) -> LaneSlice {   // offsets relative to the block start
+    const uint64_t len = block_len(b);
+    const uint64_t lo = is_nvls ? 0 : nvls_bytes, hi = is_nvls ? (len < nvls_bytes ? len : nvls_bytes) : len;
+    LaneSlice sl{0, 0};
+    if (hi <= lo) return sl;
+    sl = lane_slice(hi - lo, chunk, group_lane);
+    sl.off += lo;
+    return sl;
+  };
+
+  lane_rendezvous(sync, all, call * kCallStride + 1, 0);
+  if (abort_flag) return;
+  if (is_nvls) {
+    const LaneSlice sl = my_slice(c.rank);
+    unsigned char* mc = c.mc_heap + a.work_off + (uint64_t)c.rank * block_bytes + sl.off;
+    const uint64_t nvec = sl.bytes / 16;
+    constexpr int kU = 4;
+    for (uint64_t base = 0; base < nvec; base += (uint64_t)blockDim.x * kU) {
+      uint4 v[kU];
+      uint64_t idx[kU];
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        idx[u] = base + (uint64_t)u * blockDim.x + threadIdx.x;
+        v[u] = idx[u] < nvec ? Nvls<POL>::ld(mc + idx[u] * 16) : make_uint4(0, 0, 0, 0);
+      }
+      if (a.scale != 1.0f) {
+#pragma unroll
+        for (int u = 0; u < kU; ++u) { typename P::Acc t; P::init(t, v[u]); v[u] = P::fins(t, a.scale); }
+      }
+#pragma unroll
+      for (int u = 0; u < kU; ++u)
+        if (idx[u] < nvec) multimem_st(mc + idx[u] * 16, v[u]);
+    }
+    __threadfence_system();
+    lane_rendezvous(sync, all, call * kCallStride + 2, 1);
+    return;
+  }
+  // ---- peer-load group: flat reduce-scatter of my block's part, then gather of the others'
+  unsigned char* my_work = c.heap[c.rank] + a.work_off;
+  {
+    const LaneSlice sl = my_slice(c.rank);
+    if (sl.bytes) {
+      const uint64_t off = (uint64_t)c.rank * block_bytes + sl.off;
+      if ((int)threadIdx.x < c.world) ptrs[threadIdx.x] = c.heap[(c.rank + threadIdx.x) % c.world] + a.work_off + off;
+      __syncthreads();
+      pull_range<P>(ptrs, c.world, my_work + off, nullptr, true, sl.bytes, es, a.scale != 1.0f, a.scale);
+    }
+  }
+  lane_rendezvous(sync, all, call * kCallStride + 2, 1);
+  if (abort_flag) return;
+  {
+    int ng = 0;
+    uint64_t max_bytes = 0;
+    for (int k = 1; k < c.world; ++k) {
+      const int src = (c.rank + k) % c.world;
+      const LaneSlice sl = my_slice(src);
+      if (!sl.bytes) continue;
+      const uint64_t off = (uint64_t)src * block_bytes + sl.off;
+      if (threadIdx.x == 0) {
+        jobs[ng].src = c.heap[src] + a.work_off + off;
+        jobs[ng].dst_work = my_work + off;
+        jobs[ng].dst_user = nullptr;
+        jobs[ng].bytes = sl.bytes;
+      }
+      max_bytes = sl.bytes > max_bytes ? sl.bytes : max_bytes;
+      if (++ng == kMaxGroup) {
+        __syncthreads();
+        copy_group(jobs, ng, max_bytes, true, es);
+        __syncthreads();
+        ng = 0; max_bytes = 0;
+      }
+    }
+    __syncthreads();
+    if (ng) copy_group(jobs, ng, max_bytes, true, es);
+  }
+  lane_rendezvous(sync, all, call * kCallStride + 3, 2);
+}
+
 // ------------------------------------------------------------------------------- bounded-wait probe
 // One CTA waits on one of its own flags for a rendezvous number that nobody will signal.
 // With a short limit it must come back with FT_ERR_TIMEOUT in the status block.
@@ -440,6 +637,28 @@ cudaError_t launch_nvls(int pol, const CommDev& c, const NvlsArgs& a, int lanes,
     case POL_F32: nvls_allreduce_kernel<POL_F32><<<lanes, kThreads, 0, st>>>(c, a); break;
     case POL_BF16: nvls_allreduce_kernel<POL_BF16><<<lanes, kThreads, 0, st>>>(c, a); break;
     case POL_F16: nvls_allreduce_kernel<POL_F16><<<lanes, kThreads, 0, st>>>(c, a); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+template <int POL> static cudaError_t launch_ll_t(const CommDev& c, const LLArgs& a, cudaStream_t st) {
+  const uint64_t nitems = (a.count * a.elem_size + 15) / 16;
+  const int threads = nitems < 128 ? 128 : (nitems < 256 ? 256 : kThreads);
+  ll_allreduce_kernel<POL><<<(unsigned)((nitems + threads - 1) / threads), threads, 0, st>>>(c, a);
+  return cudaGetLastError();
+}
+cudaError_t launch_ll(int pol, const CommDev& c, const LLArgs& a, cudaStream_t st) {
+  ft_count_launch(1);
+#define CALL(P) launch_ll_t<P>(c, a, st)
+  FT_POL_SWITCH(pol, CALL)
+#undef CALL
+}
+cudaError_t launch_hybrid(int pol, const CommDev& c, const NvlsArgs& a, int lanes, int nvls_lanes, uint64_t nvls_bytes, cudaStream_t st) {
+  ft_count_launch(1);
+  switch (pol) {
+    case POL_F32: hybrid_allreduce_kernel<POL_F32><<<lanes, kThreads, 0, st>>>(c, a, nvls_lanes, nvls_bytes); break;
+    case POL_BF16: hybrid_allreduce_kernel<POL_BF16><<<lanes, kThreads, 0, st>>>(c, a, nvls_lanes, nvls_bytes); break;
+    case POL_F16: hybrid_allreduce_kernel<POL_F16><<<lanes, kThreads, 0, st>>>(c, a, nvls_lanes, nvls_bytes); break;
     default: return cudaErrorInvalidValue;
   }
   return cudaGetLastError();

@@ -31,6 +31,8 @@ namespace ftk {
 cudaError_t launch_staged(int pol, const CommDev& c, const StagedArgs& a, int lanes, cudaStream_t st);
 cudaError_t launch_oneshot(int pol, const CommDev& c, const OneShotArgs& a, uint64_t slot_bytes, int lanes, cudaStream_t st);
 cudaError_t launch_nvls(int pol, const CommDev& c, const NvlsArgs& a, int lanes, cudaStream_t st);
+cudaError_t launch_ll(int pol, const CommDev& c, const LLArgs& a, cudaStream_t st);
+cudaError_t launch_hybrid(int pol, const CommDev& c, const NvlsArgs& a, int lanes, int nvls_lanes, uint64_t nvls_bytes, cudaStream_t st);
 cudaError_t launch_wait_probe(const CommDev& c, int peer, unsigned long long timeout_ns, cudaStream_t st);
 }  // namespace ftk
 
@@ -100,7 +102,7 @@ struct DevPlanEntry {
 
 struct ft_comm {
   int rank = 0, world = 1, device = 0, mem_kind = FT_MEM_VMM;
-  size_t user_bytes = 0, staging_bytes = 0, total_bytes = 0, staging_off = 0, flags_off = 0, bump = 0;
+  size_t user_bytes = 0, staging_bytes = 0, total_bytes = 0, staging_off = 0, ll_off = 0, flags_off = 0, bump = 0;
   // local allocation
   CUmemGenericAllocationHandle handle = 0;
   CUdeviceptr va = 0;
@@ -122,6 +124,8 @@ struct ft_comm {
   double timeout_ms = 10000.0;
   int max_lanes = 0, sms = 148;
   size_t oneshot_max = 64 << 10;
+  double hybrid_fraction = 0.7, hybrid_lane_fraction = 0.5;
+  size_t ll_max = 8 << 10;   // AUTO uses the low-latency protocol up to this size
   std::map<std::string, DevPlanEntry> plans;
   ftk::CommDev dev{};
   bool finalized = false;
@@ -334,6 +338,25 @@ int launch_oneshot_call(ft_comm* c, const Prepared& pr, const void* sendbuf, voi
   return FT_OK;
 }
 
+int launch_ll_call(ft_comm* c, const Prepared& pr, const void* sendbuf, void* recvbuf, size_t count, float scale,
+                   uint32_t phase_mask, bool use_counter, uint64_t emu_call, cudaStream_t st) {
+  if (pr.bytes > ftk::kLLMaxBytes) return fail(c, FT_ERR_TOO_LARGE, "low-latency all-reduce is limited to 32 KiB");
+  ftk::LLArgs a{};
+  a.ll_off = c->ll_off;
+  a.user_in = sendbuf ? sendbuf : recvbuf;
+  a.user_out = recvbuf;
+  a.count = count;
+  a.elem_size = pr.es;
+  a.phase_mask = phase_mask;
+  a.user_vec_ok = (((uintptr_t)a.user_in | (uintptr_t)a.user_out) & 15) == 0;
+  a.use_call_counter = use_counter ? 1 : 0;
+  a.emu_call = emu_call;
+  a.scale = scale;
+  cudaError_t e = ftk::launch_ll(pr.pol, c->dev, a, st);
+  if (e != cudaSuccess) return fail(c, FT_ERR_CUDA, std::string("low-latency launch: ") + cudaGetErrorString(e));
+  return FT_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -349,7 +372,9 @@ int ft_comm_create(int rank, int world, int device, size_t heap_bytes, size_t st
   c->user_bytes = round_up(heap_bytes, 256);
   c->staging_bytes = round_up(staging_bytes ? staging_bytes : 256, 256);
   c->staging_off = c->user_bytes;
-  c->flags_off = round_up(c->staging_off + 2 * c->staging_bytes, 4096);
+  c->ll_off = round_up(c->staging_off + 2 * c->staging_bytes, 4096);
+  const size_t ll_bytes = 2 * (size_t)world * ftk::kLLSrcStride;   // two parities of the low-latency receive area
+  c->flags_off = round_up(c->ll_off + ll_bytes, 4096);
   size_t total = c->flags_off + kFlagBytes;
   if (mem_kind == FT_MEM_VMM) {
     Driver& d = driver();
@@ -377,7 +402,7 @@ int ft_comm_create(int rank, int world, int device, size_t heap_bytes, size_t st
     FT_CUDA(c, cudaMalloc(&c->ipc_ptr, total));
     c->total_bytes = total;
   }
-  FT_CUDA(c, cudaMemset(local_base(c) + c->flags_off, 0, kFlagBytes));
+  FT_CUDA(c, cudaMemset(local_base(c) + c->ll_off, 0, c->flags_off - c->ll_off + kFlagBytes));
   FT_CUDA(c, cudaMalloc(&c->call_count, sizeof(unsigned long long)));
   FT_CUDA(c, cudaMalloc(&c->arrived, sizeof(unsigned int)));
   FT_CUDA(c, cudaMemset(c->call_count, 0, sizeof(unsigned long long)));
@@ -593,6 +618,11 @@ void ft_comm_set_timeout_ms(ft_comm* c, double ms) {
 }
 void ft_comm_set_max_lanes(ft_comm* c, int lanes) { if (c) c->max_lanes = lanes; }
 void ft_comm_set_oneshot_max(ft_comm* c, size_t bytes) { if (c) c->oneshot_max = bytes; }
+void ft_comm_set_hybrid(ft_comm* c, double byte_fraction, double lane_fraction) {
+  if (!c) return;
+  c->hybrid_fraction = byte_fraction < 0 ? 0 : (byte_fraction > 1 ? 1 : byte_fraction);
+  c->hybrid_lane_fraction = lane_fraction < 0 ? 0 : (lane_fraction > 1 ? 1 : lane_fraction);
+}
 
 // ---- collectives -----------------------------------------------------------------------
 int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op, const int* widths,
@@ -612,11 +642,13 @@ int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, i
   }
   if (algo == FT_ALGO_AUTO) {
     if (nw > 0 || ring) algo = FT_ALGO_STAGED;
+    else if (pr.bytes <= c->ll_max) algo = FT_ALGO_LL;
     else if (pr.bytes <= c->oneshot_max && pr.bytes <= c->staging_bytes) algo = FT_ALGO_ONESHOT;
     else algo = FT_ALGO_STAGED;
   }
+  if (algo == FT_ALGO_LL) return launch_ll_call(c, pr, sendbuf, recvbuf, count, scale, 3, true, 0, st);
   if (algo == FT_ALGO_ONESHOT) return launch_oneshot_call(c, pr, sendbuf, recvbuf, count, scale, 7, 0, st);
-  if (algo == FT_ALGO_NVLS) {
+  if (algo == FT_ALGO_NVLS || algo == FT_ALGO_HYBRID) {
     if (!ft_comm_has_nvls(c)) return fail(c, FT_ERR_NOT_AVAILABLE, "NVLS multicast is not bound on this communicator");
     if (!pr.heap_resident) return fail(c, FT_ERR_INVALID_ARG, "NVLS all-reduce needs a tensor in the symmetric heap");
     if (pr.bytes % 16) return fail(c, FT_ERR_INVALID_ARG, "NVLS all-reduce needs a multiple of 16 bytes");
@@ -627,8 +659,19 @@ int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, i
     a.elem_size = pr.es;
     a.block_elems = pick_block_elems(count, c->world, pr.es);
     a.scale = scale;
-    const int lanes = pick_lanes(c, a.block_elems * pr.es, 8192);
-    cudaError_t e = ftk::launch_nvls(pr.pol, c->dev, a, lanes, st);
+    int lanes = pick_lanes(c, a.block_elems * pr.es, 8192);
+    cudaError_t e;
+    if (algo == FT_ALGO_HYBRID && lanes >= 8) {
+      // share of each block that goes through the switch, and the same share of the lanes
+      const double f = c->hybrid_fraction;
+      uint64_t nvls_bytes = (uint64_t)(a.block_elems * pr.es * f) / 16 * 16;
+      int nvls_lanes = (int)(lanes * c->hybrid_lane_fraction + 0.5);
+      if (nvls_lanes < 1) nvls_lanes = 1;
+      if (nvls_lanes > lanes - 1) nvls_lanes = lanes - 1;
+      e = ftk::launch_hybrid(pr.pol, c->dev, a, lanes, nvls_lanes, nvls_bytes, st);
+    } else {
+      e = ftk::launch_nvls(pr.pol, c->dev, a, lanes, st);
+    }
     if (e != cudaSuccess) return fail(c, e == cudaErrorInvalidValue ? FT_ERR_UNSUPPORTED_TYPE : FT_ERR_CUDA, std::string("NVLS launch: ") + cudaGetErrorString(e));
     return FT_OK;
   }
@@ -654,6 +697,16 @@ int ft_allreduce_emulate_oneshot(ft_comm* c, const void* sendbuf, void* recvbuf,
   if (count == 0) return FT_OK;
   return launch_oneshot_call(c, pr, sendbuf, recvbuf, count, scale, (uint32_t)phase & 5u, call, (cudaStream_t)stream);
 }
+
+int ft_allreduce_emulate_ll(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op, float scale,
+                            int phase, uint64_t call, void* stream) {
+  Prepared pr;
+  int rc = prepare(c, sendbuf, recvbuf, count, dtype, op, &pr);
+  if (rc != FT_OK) return rc;
+  if (count == 0) return FT_OK;
+  return launch_ll_call(c, pr, sendbuf, recvbuf, count, scale, (uint32_t)phase & 3u, false, call, (cudaStream_t)stream);
+}
+void ft_comm_set_ll_max(ft_comm* c, size_t bytes) { if (c) c->ll_max = bytes < ftk::kLLMaxBytes ? bytes : ftk::kLLMaxBytes; }
 
 int ft_plan_num_stages_for(ft_comm* c, const int* widths, int nw, int lonely, int ring) {
   DevPlanEntry* pe = nullptr;

@@ -30,7 +30,8 @@ from ..utils import log
 from . import planner
 from .planner import CostParams, Shape
 
-ALGOS = {"auto": 0, "staged": 1, "oneshot": 2, "nvls": 3}
+ALGOS = {"auto": 0, "staged": 1, "oneshot": 2, "nvls": 3, "hybrid": 4, "ll": 5}
+LL_MAX_BYTES = 32 << 10
 MEM_IPC, MEM_VMM = 0, 1
 
 
@@ -74,6 +75,7 @@ class _CommBase:
         self.auto = True
         self.has_nvls = False
         self._choices: dict = {}
+        self.ll_auto_max = int(os.environ.get("FT_LL_MAX_BYTES", 8 << 10))
         self._heap_range = None
 
     # -- errors
@@ -106,6 +108,10 @@ class _CommBase:
 
     def set_oneshot_max(self, nbytes: int):
         lib().ft_comm_set_oneshot_max(self._h, nbytes)
+
+    def set_hybrid(self, byte_fraction: float, lane_fraction: float):
+        """Split used by algo="hybrid": share of each block reduced in the switch, share of the CTAs doing it."""
+        lib().ft_comm_set_hybrid(self._h, byte_fraction, lane_fraction)
 
     # -- symmetric heap
     def alloc(self, shape, dtype=torch.float32) -> torch.Tensor:
@@ -141,11 +147,13 @@ class _CommBase:
         hit = self._choices.get(key)
         if hit is None and self.table:   # measured winners for this world size, nearest size on a log scale
             import math
-            rows = [r for r in self.table.get(str(self.world), []) if (r[1] != "nvls" or nvls_ok) and
-                    (r[1] != "oneshot" or nbytes <= self.staging_bytes)]
+            rows = [r for r in self.table.get(str(self.world), []) if (nvls_ok or not (r[1] == "nvls" or r[1].startswith("hybrid"))) and
+                    (r[1] != "oneshot" or nbytes <= self.staging_bytes) and (r[1] != "ll" or nbytes <= LL_MAX_BYTES)]
             if rows:
                 b = min(rows, key=lambda r: abs(math.log(max(r[0], 1)) - math.log(max(nbytes, 1))))
                 hit = self._choices[key] = (b[1], Shape.parse(b[2]))
+        if hit is None and nbytes <= self.ll_auto_max and self.world > 1:
+            hit = self._choices[key] = ("ll", Shape.flat(self.world))
         if hit is None:   # scoring every shape costs ~0.1 ms of host time: do it once per message size
             algo, shape, _ = planner.pick_algorithm(self.world, nbytes, self.cost, allow_oneshot=nbytes <= self.staging_bytes,
                                                     allow_nvls=nvls_ok)
@@ -177,6 +185,10 @@ class _CommBase:
         resident = self.in_heap(dst)
         if shp is None and a == 0 and self.world > 1:
             name, shp = self.choose(nbytes, resident, tensor.dtype)
+            if name.startswith("hybrid-"):   # "hybrid-<byte fraction>-<lane fraction>" from the calibration table
+                _, bf, lf = name.split("-")
+                self.set_hybrid(float(bf), float(lf))
+                name = "hybrid"
             a = ALGOS[name]
             if name != "staged":
                 shp = None
@@ -416,6 +428,14 @@ class LocalWorld:
 
         if world == 1:
             self.ranks[0].all_reduce(tensors[0], op=op, scale=scale, out=outs[0])
+            return outs
+        if algo == "ll":
+            for phase in (1, 2):
+                for r, c in enumerate(self.ranks):
+                    src, dst = ptrs(r)
+                    c._check(L.ft_allreduce_emulate_ll(c._h, src, dst, tensors[r].numel(), dt, OPS[op], float(scale), phase,
+                                                       self._emu_call, st))
+            self._emu_call += 1
             return outs
         if algo == "oneshot":
             for phase in (1, 4):

@@ -44,7 +44,9 @@ def split_impl(impl: str):
     parts = impl.split("/")
     if parts[0] != "flextree" or "auto->" in impl or len(parts) < 3:
         return None
-    if parts[1] not in ("staged", "oneshot", "nvls"):
+    if parts[1].startswith("hybrid-"):
+        return parts[1], parts[2]   # 'hybrid-<byte fraction>-<lane fraction>'
+    if parts[1] not in ("staged", "oneshot", "nvls", "ll"):
         return None
     return parts[1], parts[2]
 

@@ -88,6 +88,13 @@ def main():
                 fill(loc, rank, it)
                 comm.all_reduce(loc, algo="oneshot")
                 verify(loc, count, dtype, it, f"oneshot {dtype} {count}")
+            if count * loc.element_size() <= (32 << 10):
+                for rep in range(3):   # consecutive calls alternate between the two receive areas
+                    it += 1
+                    loc = torch.empty(count, dtype=dtype, device=dev)
+                    fill(loc, rank, it)
+                    comm.all_reduce(loc, algo="ll")
+                    verify(loc, count, dtype, it, f"ll {dtype} {count}")
             if comm.has_nvls and (count * loc.element_size()) % 16 == 0:
                 it += 1
                 comm.free_all()
@@ -95,6 +102,12 @@ def main():
                 fill(sym, rank, it)
                 comm.all_reduce(sym, algo="nvls")
                 verify(sym, count, dtype, it, f"nvls {dtype} {count}")
+                for bf, lf in ((0.7, 0.5), (0.3, 0.25), (1.0, 0.9), (0.0, 0.1)):
+                    it += 1
+                    fill(sym, rank, it)
+                    comm.set_hybrid(bf, lf)
+                    comm.all_reduce(sym, algo="hybrid")
+                    verify(sym, count, dtype, it, f"hybrid {bf}/{lf} {dtype} {count}")
             it += 1
             comm.free_all()
             sym = comm.alloc(count, dtype)
@@ -114,6 +127,8 @@ def main():
         comm.all_reduce(sym, op="avg", shape=shapes[i % len(shapes)], algo="staged")
         comm.all_reduce(loc, op="avg", shape=shapes[(i + 1) % len(shapes)], algo="staged")
         comm.all_reduce(small, op="avg", algo="oneshot")
+        comm.all_reduce(small, op="avg", algo="ll")
+        comm.all_reduce(small, op="avg")
         if comm.has_nvls:
             comm.all_reduce(sym, op="avg", algo="nvls")
     torch.cuda.synchronize()

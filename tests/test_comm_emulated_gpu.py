@@ -122,6 +122,24 @@ def test_oneshot(world, dtype):
     w.close()
 
 
+@pytest.mark.parametrize("world", [2, 5, 8])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int32])
+def test_low_latency_push(world, dtype):
+    w = LocalWorld(world, heap_bytes=1 << 20, staging_bytes=1 << 20)
+    for it, count in enumerate((1, 3, 9, 1000, 8192 if dtype == torch.float32 else 16384, 77)):
+        host = inputs(world, count, dtype, seed=20 + it)
+        want = torch.stack(host).double().sum(0)
+        dev = [h.to(DEV) for h in host]
+        w.all_reduce(dev, algo="ll")       # successive calls alternate between the two receive areas
+        torch.cuda.synchronize()
+        for r in range(world):
+            assert torch.allclose(dev[r].double().cpu(), want, atol=tol(dtype) * 2), (world, count, r)
+        assert all(torch.equal(d, dev[0]) for d in dev)
+    with pytest.raises(Exception, match="32 KiB"):
+        w.all_reduce([torch.zeros(10_000, device=DEV) for _ in range(world)], algo="ll")
+    w.close()
+
+
 def test_scale_and_out_of_place():
     w = LocalWorld(4, heap_bytes=1 << 20, staging_bytes=1 << 20)
     host = inputs(4, 12_345, torch.bfloat16, seed=9)
