@@ -108,7 +108,7 @@ def sweep(a, comm: FlexTreeComm, rank: int, world: int) -> list[dict]:
                         continue
                     if algo == "oneshot" and nbytes > min(comm.staging_bytes, a.oneshot_cap):
                         continue
-                    if algo == "ll" and nbytes > (32 << 10):
+                    if algo == "ll" and nbytes > (256 << 10):
                         continue
                     if algo in ("nvls", "hybrid") and (not comm.has_nvls or nbytes % 16):
                         continue

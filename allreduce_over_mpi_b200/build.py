@@ -80,9 +80,29 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    build_tools()
     if verbose:
         print("\n".join(logs))
     return LIB
+
+
+def build_tools() -> list[Path]:
+    """Native command-line tools next to the library: ft_bench, planner_dump, cost_model_sweep."""
+    out = []
+    tools = CSRC / "tools"
+    hm = headers_mtime()
+    for src in sorted(tools.glob("*.cpp")):
+        exe = LIB.parent / src.stem
+        if exe.exists() and exe.stat().st_mtime >= max(src.stat().st_mtime, hm, LIB.stat().st_mtime):
+            out.append(exe)
+            continue
+        cmd = [NVCC, *ARCH, "-O2", "-std=c++17", "-I", str(CSRC), str(src), "-o", str(exe), "-Xcompiler", "-fopenmp",
+               "-L", str(LIB.parent), "-lflextree", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN", "-lpthread"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"tool build failed for {src.name}:\n{r.stdout}\n{r.stderr}")
+        out.append(exe)
+    return out
 
 
 def ensure_built() -> Path:

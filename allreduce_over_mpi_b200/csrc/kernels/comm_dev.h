@@ -85,7 +85,7 @@ struct OneShotArgs {
 };
 
 // Low-latency push all-reduce: data travels as 8-byte words {32 data bits, 32-bit tag}.
-constexpr uint64_t kLLMaxBytes = 32 << 10;              // largest message (payload bytes)
+constexpr uint64_t kLLMaxBytes = 256 << 10;             // largest message (payload bytes)
 constexpr uint64_t kLLSrcStride = 2 * kLLMaxBytes;      // wire bytes one source rank may deposit per parity
 struct LLArgs {
   uint64_t ll_off;            // byte offset of the receive area in every heap: [2 parities][world][kLLSrcStride]

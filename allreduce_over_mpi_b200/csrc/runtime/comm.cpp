@@ -126,6 +126,7 @@ struct ft_comm {
   size_t oneshot_max = 64 << 10;
   double hybrid_fraction = 0.7, hybrid_lane_fraction = 0.5;
   size_t ll_max = 8 << 10;   // AUTO uses the low-latency protocol up to this size
+  int nvls_ctas_per_sm = 2;
   std::map<std::string, DevPlanEntry> plans;
   ftk::CommDev dev{};
   bool finalized = false;
@@ -250,10 +251,10 @@ uint64_t pick_block_elems(uint64_t count, int world, uint32_t es) {
   return b ? b : per;
 }
 
-int pick_lanes(ft_comm* c, uint64_t region_bytes, uint64_t min_chunk) {
+int pick_lanes(ft_comm* c, uint64_t region_bytes, uint64_t min_chunk, int ctas_per_sm = 1) {
   uint64_t lanes = region_bytes / min_chunk;
   if (lanes < 1) lanes = 1;
-  const int cap = c->max_lanes > 0 ? c->max_lanes : c->sms;
+  const int cap = c->max_lanes > 0 ? c->max_lanes : c->sms * ctas_per_sm;
   if (lanes > (uint64_t)cap) lanes = cap;
   if (lanes > (uint64_t)ftk::kMaxLanes) lanes = ftk::kMaxLanes;
   return (int)lanes;
@@ -340,7 +341,7 @@ int launch_oneshot_call(ft_comm* c, const Prepared& pr, const void* sendbuf, voi
 
 int launch_ll_call(ft_comm* c, const Prepared& pr, const void* sendbuf, void* recvbuf, size_t count, float scale,
                    uint32_t phase_mask, bool use_counter, uint64_t emu_call, cudaStream_t st) {
-  if (pr.bytes > ftk::kLLMaxBytes) return fail(c, FT_ERR_TOO_LARGE, "low-latency all-reduce is limited to 32 KiB");
+  if (pr.bytes > ftk::kLLMaxBytes) return fail(c, FT_ERR_TOO_LARGE, "low-latency all-reduce is limited to 256 KiB");
   ftk::LLArgs a{};
   a.ll_off = c->ll_off;
   a.user_in = sendbuf ? sendbuf : recvbuf;
@@ -659,7 +660,9 @@ int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, i
     a.elem_size = pr.es;
     a.block_elems = pick_block_elems(count, c->world, pr.es);
     a.scale = scale;
-    int lanes = pick_lanes(c, a.block_elems * pr.es, 8192);
+    // the in-switch reduction kernel is light on registers: two CTAs per SM keep loads in flight
+    // while the other CTA stores
+    int lanes = pick_lanes(c, a.block_elems * pr.es, 8192, c->nvls_ctas_per_sm);
     cudaError_t e;
     if (algo == FT_ALGO_HYBRID && lanes >= 8) {
       // share of each block that goes through the switch, and the same share of the lanes
@@ -706,6 +709,7 @@ int ft_allreduce_emulate_ll(ft_comm* c, const void* sendbuf, void* recvbuf, size
   if (count == 0) return FT_OK;
   return launch_ll_call(c, pr, sendbuf, recvbuf, count, scale, (uint32_t)phase & 3u, false, call, (cudaStream_t)stream);
 }
+void ft_comm_set_nvls_ctas_per_sm(ft_comm* c, int n) { if (c && n >= 1 && n <= 3) c->nvls_ctas_per_sm = n; }
 void ft_comm_set_ll_max(ft_comm* c, size_t bytes) { if (c) c->ll_max = bytes < ftk::kLLMaxBytes ? bytes : ftk::kLLMaxBytes; }
 
 int ft_plan_num_stages_for(ft_comm* c, const int* widths, int nw, int lonely, int ring) {

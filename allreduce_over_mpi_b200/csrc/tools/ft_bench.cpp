@@ -1,0 +1,206 @@
+// Standalone all-reduce benchmark with the reference driver's command line
+// (allreduce_over_mpi/benchmark.cpp:69-122):
+//
+//     ft_bench [--size N] [--repeat R] [--to-file] [--comm-type flextree|threads] [--tag T]
+//              [--version] [--check] [--gpus G | --ranks G] [--dtype float|bf16]
+//
+//   --size       elements per rank (default 35, like the reference)
+//   --repeat     number of timed all-reduces (data is NOT re-initialised between repeats)
+//   --comm-type  flextree = GPU ranks over NVLink peer memory, one host thread per GPU in this
+//                process; threads = CPU ranks (thread world, host memory)
+//   --to-file    write one time per line to "<tag.>N.len.<w0-w1-+L>.ar_test.<epoch>.txt"
+//   --check      closed-form check: data[i] = i*0.1 on every rank, so after R in-place sums every
+//                rank must hold i*0.1*N^R (two-sided, relative tolerance)
+// The tree shape comes from FT_TOPO / FT_LONELY exactly as for the library entry point.
+// GPU times are CUDA-event intervals, reported as the maximum over ranks; CPU times are
+// steady-clock intervals on rank 0 like the reference's MPI_Wtime.
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <ctime>
+#include <fstream>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "../api/flextree_mpi.h"
+#include "../planner/config.hpp"
+#include "timer.hpp"
+
+namespace {
+struct Opts {
+  size_t size = 35;
+  int repeat = 1, ranks = 0;
+  bool to_file = false, check = false, bf16 = false;
+  std::string comm = "flextree", tag;
+};
+
+struct SpinBarrier {
+  std::atomic<int> count{0}, gen{0};
+  int n;
+  explicit SpinBarrier(int n_) : n(n_) {}
+  void wait() {
+    const int g = gen.load();
+    if (count.fetch_add(1) == n - 1) { count.store(0); gen.fetch_add(1); }
+    else while (gen.load() == g) std::this_thread::yield();
+  }
+};
+
+unsigned short f2bf(float f) {
+  unsigned u;
+  memcpy(&u, &f, 4);
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return (unsigned short)(u >> 16);
+}
+float bf2f(unsigned short h) {
+  unsigned u = (unsigned)h << 16;
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+}  // namespace
+
+int main(int argc, char** argv) {
+  Opts o;
+  for (int i = 1; i < argc; ++i) {
+    std::string a = argv[i];
+    auto next = [&]() -> const char* { return i + 1 < argc ? argv[++i] : ""; };
+    if (a == "--size") o.size = strtoull(next(), nullptr, 10);
+    else if (a == "--repeat") o.repeat = atoi(next());
+    else if (a == "--to-file") o.to_file = true;
+    else if (a == "--comm-type") o.comm = next();
+    else if (a == "--tag") o.tag = next();
+    else if (a == "--check") o.check = true;
+    else if (a == "--gpus" || a == "--ranks") o.ranks = atoi(next());
+    else if (a == "--dtype") o.bf16 = std::string(next()) == "bf16";
+    else if (a == "--version") { printf("FlexTree Standalone Benchmark\nversion: %s\n", ft_version()); return 0; }
+    else { fprintf(stderr, "unknown parameter: %s\n", a.c_str()); return 1; }
+  }
+  const bool gpu = o.comm == "flextree";
+  if (!gpu && o.comm != "threads") { fprintf(stderr, "unknown comm type: %s\n", o.comm.c_str()); return 1; }
+  int world = o.ranks;
+  if (gpu) {
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) { fprintf(stderr, "no CUDA device; use --comm-type threads\n"); return 1; }
+    if (world <= 0 || world > ndev) world = ndev;
+  } else if (world <= 0) {
+    world = 4;
+  }
+  ft::ShapeConfig cfg = ft::shape_from_env(world);
+  if (!cfg.ok()) { fprintf(stderr, "%s\n", cfg.error.c_str()); return 1; }
+  FT_enabled();
+  printf("configuration:\n  - total_peers: %d\n  - data_size: %zu\n  - repeat: %d\n  - to_file: %s\n  - check_validity: %s\n"
+         "  - communication method: %s\n  - And FlexTree topo is %s\n",
+         world, o.size, o.repeat, o.to_file ? "true" : "false", o.check ? "true" : "false", o.comm.c_str(),
+         cfg.is_auto ? "auto" : cfg.shape.str().c_str());
+
+  const size_t es = o.bf16 ? 2 : 4;
+  const int dtype = o.bf16 ? FT_BFLOAT16 : FT_FLOAT;
+  std::vector<std::vector<double>> times(world, std::vector<double>(o.repeat, 0.0));
+  std::vector<int> bad(world, 0);
+  SpinBarrier bar(world);
+  std::vector<ft_comm*> comms(world, nullptr);
+  ft_cpu_world* cpu_world = nullptr;
+  if (gpu) {
+    const size_t heap = ((o.size * es + (1 << 20)) + 255) / 256 * 256;
+    for (int r = 0; r < world; ++r) {
+      cudaSetDevice(r);
+      if (ft_comm_create(r, world, r, heap, 1 << 20, FT_MEM_IPC, &comms[r]) != FT_OK) {
+        fprintf(stderr, "rank %d: %s\n", r, ft_comm_last_error(comms[r]));
+        return 1;
+      }
+    }
+    if (ft_comm_connect_local(comms.data(), world) != FT_OK) { fprintf(stderr, "connect: %s\n", ft_comm_last_error(comms[0])); return 1; }
+  } else {
+    cpu_world = ft_cpu_world_create(world, 60.0);
+  }
+
+  auto rank_main = [&](int r) {
+    std::vector<float> host(o.size);
+    for (size_t i = 0; i < o.size; ++i) host[i] = (float)i * 0.1f;
+    std::vector<unsigned short> host16;
+    if (o.bf16) { host16.resize(o.size); for (size_t i = 0; i < o.size; ++i) host16[i] = f2bf(host[i]); }
+    void* hostp = o.bf16 ? (void*)host16.data() : (void*)host.data();
+    if (gpu) {
+      cudaSetDevice(r);
+      cudaStream_t st;
+      cudaStreamCreate(&st);
+      void* dev = ft_comm_alloc(comms[r], o.size * es);
+      cudaMemcpy(dev, hostp, o.size * es, cudaMemcpyHostToDevice);
+      FT_Comm mc = ft_mpi_from_comm(comms[r], st);
+      cudaEvent_t a, b;
+      cudaEventCreate(&a); cudaEventCreate(&b);
+      for (int i = 0; i < o.repeat; ++i) {
+        bar.wait();
+        cudaEventRecord(a, st);
+        if (MPI_Allreduce_FT_c(FT_IN_PLACE, dev, o.size, dtype, FT_OP_SUM, mc) != 0) bad[r] = 2;
+        cudaEventRecord(b, st);
+        cudaEventSynchronize(b);
+        float ms = 0;
+        cudaEventElapsedTime(&ms, a, b);
+        times[r][i] = ms * 1e-3;
+      }
+      int status[5];
+      if (ft_comm_status(comms[r], status) != FT_OK) bad[r] = 3;
+      cudaMemcpy(hostp, dev, o.size * es, cudaMemcpyDeviceToHost);
+      ft_mpi_comm_free(mc);
+      cudaStreamDestroy(st);
+    } else {
+      FT_Comm mc = ft_mpi_thread_rank(cpu_world, r);
+      for (int i = 0; i < o.repeat; ++i) {
+        bar.wait();
+        ft::Timer t;
+        t.Start();
+        if (MPI_Allreduce_FT_c(FT_IN_PLACE, hostp, o.size, dtype, FT_OP_SUM, mc) != 0) bad[r] = 2;
+        t.Stop();
+        times[r][i] = t.seconds();
+      }
+      ft_mpi_comm_free(mc);
+    }
+    if (o.check && !bad[r]) {
+      const double scale = std::pow((double)world, o.repeat);
+      for (size_t i = 0; i < o.size; ++i) {
+        const double got = o.bf16 ? bf2f(host16[i]) : host[i];
+        const double want = (o.bf16 ? (double)bf2f(f2bf((float)i * 0.1f)) : (double)((float)i * 0.1f)) * scale;
+        const double tol = (o.bf16 ? 2e-2 * o.repeat : 1e-5 * o.repeat) * std::fabs(want) + 1e-6;
+        if (!(std::fabs(got - want) <= tol)) { bad[r] = 1; fprintf(stderr, "node %d says the result seems not right at %zu: %g vs %g\n", r, i, got, want); break; }
+      }
+    }
+    bar.wait();
+  };
+  std::vector<std::thread> th;
+  for (int r = 0; r < world; ++r) th.emplace_back(rank_main, r);
+  for (auto& t : th) t.join();
+
+  std::vector<double> per_repeat(o.repeat, 0.0);
+  double sum = 0, mn = 1e30;
+  for (int i = 0; i < o.repeat; ++i) {
+    for (int r = 0; r < world; ++r) per_repeat[i] = std::max(per_repeat[i], gpu ? times[r][i] : times[0][i]);
+    sum += per_repeat[i];
+    mn = std::min(mn, per_repeat[i]);
+  }
+  int failed = 0;
+  for (int r = 0; r < world; ++r) failed |= bad[r];
+  if (o.check) printf("%s\n", failed ? "CHECK failed" : "CHECK (test passed)");
+  if (o.to_file) {
+    std::string name;
+    if (!o.tag.empty()) name += o.tag + ".";
+    name += std::to_string(world) + "." + std::to_string(o.size) + ".";
+    if (cfg.shape.ring) name += "ring";
+    else for (int w : cfg.shape.widths) name += std::to_string(w) + "-";
+    name += "+" + std::to_string(cfg.shape.lonely) + ".ar_test." + std::to_string((long long)time(nullptr)) + ".txt";
+    std::ofstream f(name);
+    for (double t : per_repeat) f << t << std::endl;
+    printf("times written to %s\n", name.c_str());
+  }
+  const double bytes = (double)o.size * es;
+  printf("DONE, average time: %g, min time: %g  (busbw at min: %.2f GB/s)\n", sum / o.repeat, mn,
+         bytes / mn / 1e9 * 2.0 * (world - 1) / world);
+  for (auto* c : comms) ft_comm_destroy(c);
+  if (cpu_world) ft_cpu_world_destroy(cpu_world);
+  return failed ? 2 : 0;
+}

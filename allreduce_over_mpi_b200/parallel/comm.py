@@ -31,7 +31,7 @@ from . import planner
 from .planner import CostParams, Shape
 
 ALGOS = {"auto": 0, "staged": 1, "oneshot": 2, "nvls": 3, "hybrid": 4, "ll": 5}
-LL_MAX_BYTES = 32 << 10
+LL_MAX_BYTES = 256 << 10
 MEM_IPC, MEM_VMM = 0, 1
 
 
@@ -98,6 +98,8 @@ class _CommBase:
             self.set_timeout_ms(float(os.environ["FT_TIMEOUT_MS"]))
         if os.environ.get("FT_MAX_LANES"):
             self.set_max_lanes(int(os.environ["FT_MAX_LANES"]))
+        if os.environ.get("FT_NVLS_CTAS_PER_SM"):
+            lib().ft_comm_set_nvls_ctas_per_sm(self._h, int(os.environ["FT_NVLS_CTAS_PER_SM"]))
 
     # -- knobs
     def set_timeout_ms(self, ms: float):

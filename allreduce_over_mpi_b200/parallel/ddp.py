@@ -142,7 +142,7 @@ class HookState:
         self.calls = 0
 
 
-def flextree_allreduce_hook(state: HookState, bucket) -> torch.futures.Future:
+def flextree_allreduce_hook(state, bucket):
     """``ddp.register_comm_hook(HookState(comm), flextree_allreduce_hook)``: average the bucket with
     FlexTree on a side stream and hand DDP a future that is complete in stream order."""
     buf = bucket.buffer()
@@ -154,3 +154,13 @@ def flextree_allreduce_hook(state: HookState, bucket) -> torch.futures.Future:
         fut: torch.futures.Future = torch.futures.Future(devices=[dev])
         fut.set_result(buf)
     return fut
+
+
+# torch validates the hook's signature with real annotation objects (this module postpones
+# annotation evaluation, so they are attached here)
+flextree_allreduce_hook.__annotations__ = {"return": torch.futures.Future[torch.Tensor]}
+try:
+    import torch.distributed as _dist
+    flextree_allreduce_hook.__annotations__["bucket"] = _dist.GradBucket
+except (ImportError, AttributeError):  # torch built without distributed support
+    pass

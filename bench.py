@@ -73,11 +73,12 @@ def bench_nway(a) -> dict:
         for n in FANINS:
             reduce_nway(vecs[:n], out=outs[n])
 
+    sampler = ClockSampler(gpu_index=0).start()   # runs through warm-up, the timed steps and a tail of the same load
+    t_wall = time.time()
     for _ in range(max(a.warmup, 3)):
         step()
     torch.cuda.synchronize()
     per_n = {}
-    sampler = ClockSampler(gpu_index=None).start()
     l0 = launch_count()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(a.steps + 1)]
     torch.cuda.synchronize()
@@ -87,6 +88,10 @@ def bench_nway(a) -> dict:
         ev[i + 1].record()
     torch.cuda.synchronize()
     launches = launch_count() - l0
+    while time.time() - t_wall < 1.0:   # same load, untimed, until the 100 ms clock sampler has seen enough of it
+        for _ in range(20):
+            step()
+        torch.cuda.synchronize()
     clocks = sampler.stop()
     total_ms = ev[0].elapsed_time(ev[-1])
     ms_per_step = total_ms / a.steps
@@ -161,21 +166,30 @@ def main():
     a = parse()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
-    if a.impl == "reference":
-        from baseline.reference_arm import run_reference
-        out = run_reference(a, world, rank)
-        if rank == 0:
-            print(json.dumps(out), flush=True)
-        return 0
-    if a.gpus <= 1 and world <= 1:
-        out = bench_nway(a)
-        print(json.dumps(out), flush=True)
-        return 0
-    from allreduce_over_mpi_b200.bench.allreduce import bench_allreduce_main
-    out = bench_allreduce_main(a)
-    if rank == 0:
+    # Libraries (NCCL's version banner, torch warnings) may write to stdout; the contract is ONE JSON
+    # line there.  Everything else goes to stderr until the result is ready.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        out = run(a, world, rank)
+    finally:
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        os.close(real_stdout)
+    if rank == 0 and out is not None:
         print(json.dumps(out), flush=True)
     return 0
+
+
+def run(a, world, rank):
+    if a.impl == "reference":
+        from baseline.reference_arm import run_reference
+        return run_reference(a, world, rank)
+    if a.gpus <= 1 and world <= 1:
+        return bench_nway(a)
+    from allreduce_over_mpi_b200.bench.allreduce import bench_allreduce_main
+    return bench_allreduce_main(a)
 
 
 if __name__ == "__main__":

@@ -88,7 +88,7 @@ def main():
                 fill(loc, rank, it)
                 comm.all_reduce(loc, algo="oneshot")
                 verify(loc, count, dtype, it, f"oneshot {dtype} {count}")
-            if count * loc.element_size() <= (32 << 10):
+            if count * loc.element_size() <= (256 << 10):
                 for rep in range(3):   # consecutive calls alternate between the two receive areas
                     it += 1
                     loc = torch.empty(count, dtype=dtype, device=dev)

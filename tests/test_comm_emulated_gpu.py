@@ -126,7 +126,7 @@ def test_oneshot(world, dtype):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int32])
 def test_low_latency_push(world, dtype):
     w = LocalWorld(world, heap_bytes=1 << 20, staging_bytes=1 << 20)
-    for it, count in enumerate((1, 3, 9, 1000, 8192 if dtype == torch.float32 else 16384, 77)):
+    for it, count in enumerate((1, 3, 9, 1000, 65536, 77)):
         host = inputs(world, count, dtype, seed=20 + it)
         want = torch.stack(host).double().sum(0)
         dev = [h.to(DEV) for h in host]
@@ -135,8 +135,8 @@ def test_low_latency_push(world, dtype):
         for r in range(world):
             assert torch.allclose(dev[r].double().cpu(), want, atol=tol(dtype) * 2), (world, count, r)
         assert all(torch.equal(d, dev[0]) for d in dev)
-    with pytest.raises(Exception, match="32 KiB"):
-        w.all_reduce([torch.zeros(10_000, device=DEV) for _ in range(world)], algo="ll")
+    with pytest.raises(Exception, match="256 KiB"):
+        w.all_reduce([torch.zeros(100_000, device=DEV) for _ in range(world)], algo="ll")
     w.close()
 
 

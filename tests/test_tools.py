@@ -1,0 +1,58 @@
+"""Native command-line tools built next to the library (CPU-only invocations)."""
+import os
+import subprocess
+
+import pytest
+
+from allreduce_over_mpi_b200.build import LIB, ensure_built
+
+BIN = LIB.parent
+
+
+@pytest.fixture(scope="module", autouse=True)
+def built():
+    ensure_built()
+    for t in ("planner_dump", "cost_model_sweep", "ft_bench"):
+        if not (BIN / t).exists():
+            pytest.skip(f"{t} not built")
+
+
+def run(cmd, env=None, cwd=None):
+    r = subprocess.run(cmd, capture_output=True, text=True, env={**os.environ, **(env or {})}, cwd=cwd, timeout=120)
+    return r.returncode, r.stdout, r.stderr
+
+
+def test_planner_dump_default_is_the_5_rank_lonely_case():
+    rc, out, _ = run([str(BIN / "planner_dump")])
+    assert rc == 0
+    assert "shape 2*2+1, 4 stages, traffic 216 elements (2*(N-1)*count = 216), race check: clean" in out
+    assert "sum b0[0+6] <- 1,4" in out and "get b4[24+3] <- 4" in out
+    rc, _, err = run([str(BIN / "planner_dump"), "7", "2,2", "3"])
+    assert rc == 1 and "invalid FT_TOPO" in err
+
+
+def test_cost_model_sweep_prints_reference_choices(tmp_path):
+    csv = tmp_path / "numofstru.csv"
+    rc, out, _ = run([str(BIN / "cost_model_sweep"), "64", "100", "--csv", str(csv)])
+    assert rc == 0
+    rows = {int(l.split(",")[0]): l.strip().split(",") for l in csv.read_text().splitlines()[1:]}
+    assert rows[8][3] == "1*8" and rows[8][4] == "0.666"
+    assert rows[10][3] == "2*5" and rows[50][3] == "2*5*5" and rows[64][3] == "8*8"
+    assert rows[12][1] == "9"      # nine candidate shapes for 12 ranks
+    assert len(rows) == 64
+
+
+def test_ft_bench_thread_world_check_and_file(tmp_path):
+    exe = str(BIN / "ft_bench")
+    rc, out, err = run([exe, "--comm-type", "threads", "--ranks", "6", "--size", "100000", "--repeat", "2", "--check", "--to-file",
+                        "--tag", "t"], env={"FT_TOPO": "2,3"}, cwd=tmp_path)
+    assert rc == 0, err
+    assert "FlexTree enabled" in out and "CHECK (test passed)" in out and "And FlexTree topo is 2*3" in out
+    files = [f for f in os.listdir(tmp_path) if f.startswith("t.6.100000.2-3-+0.ar_test.")]
+    assert len(files) == 1 and len(open(tmp_path / files[0]).read().split()) == 2
+    rc, out, err = run([exe, "--comm-type", "threads", "--ranks", "4", "--size", "35"], env={"FT_TOPO": "2,3"})
+    assert rc == 1 and "invalid FT_TOPO 2,3" in err
+    rc, out, _ = run([exe, "--version"])
+    assert rc == 0 and "FlexTree Standalone Benchmark" in out
+    rc, _, err = run([exe, "--bogus"])
+    assert rc == 1 and "unknown parameter" in err
