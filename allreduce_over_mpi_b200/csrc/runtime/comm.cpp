@@ -126,7 +126,7 @@ struct ft_comm {
   size_t oneshot_max = 64 << 10;
   double hybrid_fraction = 0.7, hybrid_lane_fraction = 0.5;
   size_t ll_max = 8 << 10;   // AUTO uses the low-latency protocol up to this size
-  int nvls_ctas_per_sm = 2;
+  int nvls_ctas_per_sm = 1;   // measured on 8 GPUs: 2 or 3 CTAs per SM lose 5-15 % at 256 MiB and above
   std::map<std::string, DevPlanEntry> plans;
   ftk::CommDev dev{};
   bool finalized = false;
@@ -660,8 +660,6 @@ int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, i
     a.elem_size = pr.es;
     a.block_elems = pick_block_elems(count, c->world, pr.es);
     a.scale = scale;
-    // the in-switch reduction kernel is light on registers: two CTAs per SM keep loads in flight
-    // while the other CTA stores
     int lanes = pick_lanes(c, a.block_elems * pr.es, 8192, c->nvls_ctas_per_sm);
     cudaError_t e;
     if (algo == FT_ALGO_HYBRID && lanes >= 8) {

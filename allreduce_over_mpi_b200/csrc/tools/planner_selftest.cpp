@@ -1,0 +1,102 @@
+// Self-test of the host-only core, meant to be built with sanitizers:
+//     g++ -std=c++17 -O1 -g -fsanitize=address,undefined planner_selftest.cpp -o t && ./t
+//     g++ -std=c++17 -O1 -g -fsanitize=thread planner_selftest.cpp -o t -lpthread && ./t threads
+// It builds the plan of every executable shape up to 24 ranks, runs the static race check and the
+// snapshot executor against a double-precision sum, exercises the candidate enumerators and the
+// cost models, and (argument "threads") runs the thread-per-rank executor with its flag protocol,
+// including a silent rank that must produce time-outs rather than a hang.
+// The reference has no sanitizer builds (its flags are -Wall -Wextra only, allreduce_over_mpi/CMakeLists.txt:5).
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "../planner/config.hpp"
+#include "../planner/cost_model.hpp"
+#include "../planner/cpu_executor.hpp"
+
+static int fails = 0;
+#define EXPECT(c) do { if (!(c)) { std::printf("FAIL %s:%d %s\n", __FILE__, __LINE__, #c); ++fails; } } while (0)
+
+static void plans_and_snapshot() {
+  int checked = 0;
+  for (int n = 1; n <= 24; ++n)
+    for (const ft::Shape& s : ft::executable_shapes(n)) {
+      ft::Plan p = ft::build_plan(n, s);
+      EXPECT(p.ok());
+      EXPECT(ft::check_hazards(p).empty());
+      for (uint64_t count : {1ull, 29ull, 257ull}) {
+        std::vector<std::vector<double>> data(n, std::vector<double>(count));
+        std::vector<double> want(count, 0.0);
+        for (int r = 0; r < n; ++r)
+          for (uint64_t i = 0; i < count; ++i) { data[r][i] = std::sin(r * 131 + i * 7) ; want[i] += data[r][i]; }
+        std::vector<void*> bufs(n);
+        for (int r = 0; r < n; ++r) bufs[r] = data[r].data();
+        EXPECT(ft::run_plan_snapshot(p, FT_SUM, FT_F64, bufs.data(), count) == FT_OK);
+        for (int r = 0; r < n; ++r)
+          for (uint64_t i = 0; i < count; ++i) EXPECT(std::fabs(data[r][i] - want[i]) < 1e-9);
+        EXPECT(ft::plan_traffic_elems(p, ft::Blocks(count, n)) == 2ull * (n - 1) * count);
+      }
+      ++checked;
+    }
+  EXPECT(checked > 150);
+  EXPECT(!ft::validate_shape(7, ft::Shape{{2, 2}, 3, false}).empty());
+  EXPECT(!ft::parse_topo("2,3", "", 7).ok());
+}
+
+static void enumerators_and_models() {
+  for (int n = 0; n <= 200; ++n) {
+    auto a = ft::candidate_shapes(n);
+    if (n >= 2) EXPECT(a.size() == ft::count_ordered_factorizations(n) + 1);
+    (void)ft::candidate_shapes_legacy(n);
+    (void)ft::choose_width(n);
+    (void)ft::prime_factors(n);
+  }
+  EXPECT(ft::shape_to_string(ft::choose_v0(8).widths) == "1*8");
+  EXPECT(std::fabs(ft::choose_v0(8).cost - 0.666) < 1e-9);
+  ft::V1Params k;
+  k.nvls_gbs = 500;
+  for (int n = 2; n <= 16; ++n)
+    for (uint64_t b : {1024ull, 1ull << 20, 1ull << 30}) EXPECT(std::isfinite(ft::pick_algorithm(n, b, k).us));
+}
+
+static void thread_world(bool with_fault) {
+  for (const char* text : {"2,2", "2,3", "2,2,2"}) {
+    ft::ShapeConfig cfg = ft::parse_topo(text, std::string(text) == "2,3" ? "1" : "", std::string(text) == "2,2" ? 4 : (std::string(text) == "2,3" ? 7 : 8));
+    EXPECT(cfg.ok());
+    const int n = cfg.shape.world();
+    ft::Plan p = ft::build_plan(n, cfg.shape);
+    ft::CpuWorld w(n);
+    w.timeout_s = with_fault ? 0.2 : 20.0;
+    const uint64_t count = 4099;
+    std::vector<std::vector<float>> data(n, std::vector<float>(count));
+    std::vector<ft::RankStatus> st(n);
+    ft::FaultSpec f;
+    f.kind = ft::Fault::NeverSignal; f.rank = 1; f.stage = 1;
+    for (int round = 0; round < 3; ++round) {
+      for (int r = 0; r < n; ++r) for (uint64_t i = 0; i < count; ++i) data[r][i] = (float)(r + 1);
+      std::vector<std::thread> th;
+      for (int r = 0; r < n; ++r)
+        th.emplace_back([&, r] { st[r] = ft::cpu_allreduce(w, r, p, FT_SUM, FT_F32, nullptr, data[r].data(), count, 0, with_fault ? &f : nullptr); });
+      for (auto& t : th) t.join();
+      if (with_fault) {
+        bool any_timeout = false;
+        for (int r = 0; r < n; ++r) any_timeout = any_timeout || st[r].code == FT_ERR_TIMEOUT;
+        EXPECT(any_timeout);
+        break;   // the world is poisoned after a fault
+      }
+      for (int r = 0; r < n; ++r) { EXPECT(st[r].code == FT_OK); EXPECT(data[r][count - 1] == (float)(n * (n + 1) / 2)); }
+    }
+  }
+}
+
+int main(int argc, char** argv) {
+  const bool threads = argc > 1 && !std::strcmp(argv[1], "threads");
+  if (!threads) { plans_and_snapshot(); enumerators_and_models(); }
+  thread_world(false);
+  thread_world(true);
+  std::printf(fails ? "%d FAILURES\n" : "selftest ok\n", fails);
+  return fails ? 1 : 0;
+}

@@ -77,6 +77,7 @@ class _CommBase:
         self._choices: dict = {}
         self.ll_auto_max = int(os.environ.get("FT_LL_MAX_BYTES", 8 << 10))
         self._heap_range = None
+        self._nvtx = os.environ.get("FT_NVTX", "0") == "1"   # NVTX range around every call (for timeline tools)
 
     # -- errors
     def _check(self, code: int):
@@ -151,7 +152,8 @@ class _CommBase:
             import math
             rows = [r for r in self.table.get(str(self.world), []) if (nvls_ok or not (r[1] == "nvls" or r[1].startswith("hybrid"))) and
                     (r[1] != "oneshot" or nbytes <= self.staging_bytes) and (r[1] != "ll" or nbytes <= LL_MAX_BYTES)]
-            if rows:
+            # the table speaks only for the range of sizes that was measured (one octave of slack)
+            if rows and min(r[0] for r in rows) / 2 <= nbytes <= max(r[0] for r in rows) * 2:
                 b = min(rows, key=lambda r: abs(math.log(max(r[0], 1)) - math.log(max(nbytes, 1))))
                 hit = self._choices[key] = (b[1], Shape.parse(b[2]))
         if hit is None and nbytes <= self.ll_auto_max and self.world > 1:
@@ -206,6 +208,9 @@ class _CommBase:
             self._check(lib().ft_allreduce(self._h, src_ptr, dst_ptr, count, dt, OPS[op], arr, nw, lonely, ring, a,
                                            float(scale), C.c_void_p(st)))
 
+        nvtx = self._nvtx
+        if nvtx:
+            torch.cuda.nvtx.range_push(f"flextree.all_reduce {nbytes}B {algo if a else 'auto'}")
         with torch.cuda.device(self.device):
             src_ptr = None if dst.data_ptr() == tensor.data_ptr() else tensor.data_ptr()
             if resident or nbytes <= self.staging_bytes or self.world == 1:
@@ -215,6 +220,8 @@ class _CommBase:
                 for lo in range(0, tensor.numel(), per):
                     n = min(per, tensor.numel() - lo)
                     call((src_ptr + lo * es) if src_ptr else None, dst.data_ptr() + lo * es, n)
+        if nvtx:
+            torch.cuda.nvtx.range_pop()
         return dst
 
     # -- health
@@ -458,6 +465,30 @@ class LocalWorld:
                 c._check(L.ft_allreduce_emulate_stage(c._h, src, dst, tensors[r].numel(), dt, OPS[op], arr, nw, lonely, ring,
                                                       float(scale), max(s, 0), s + 1, st))
         return outs
+
+    def profile_stages(self, tensors: Sequence[torch.Tensor], shape, op: str = "sum", iters: int = 5) -> list[float]:
+        """Per-stage device time (ms, all ranks of the stage together) of a staged plan on an emulated
+        world: CUDA events around each stage's launches.  The counterpart of the reference's SHOW_TIME
+        phase log (allreduce_over_mpi/mpi_mod.hpp:31-35), which times its two phases on the host."""
+        if not self.emulated:
+            raise RuntimeError("per-stage timing needs the single-GPU emulated world")
+        shp = _as_shape(shape, self.world) or Shape.flat(self.world)
+        nstages = planner.plan_num_stages(self.world, shp)
+        arr, nw, lonely, ring = shp.c_args()
+        L, dt = lib(), ft_dtype(tensors[0].dtype)
+        st = C.c_void_p(torch.cuda.current_stream(self.ranks[0].device).cuda_stream)
+        acc = [0.0] * (nstages + 1)
+        for _ in range(iters):
+            for s in range(-1, nstages):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for r, c in enumerate(self.ranks):
+                    c._check(L.ft_allreduce_emulate_stage(c._h, None, tensors[r].data_ptr(), tensors[r].numel(), dt, OPS[op], arr, nw,
+                                                          lonely, ring, 1.0, max(s, 0), s + 1, st))
+                b.record()
+                b.synchronize()
+                acc[s + 1] += a.elapsed_time(b) / iters
+        return acc   # [publish, stage 0, stage 1, ...]
 
     def close(self):
         for c in self.ranks:
