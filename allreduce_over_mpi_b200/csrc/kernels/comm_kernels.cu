@@ -175,7 +175,7 @@ __device__ __forceinline__ LaneSlice lane_slice(uint64_t region_bytes, uint64_t 
 
 // ------------------------------------------------------------------------------- staged
 template <int POL>
-__global__ void __launch_bounds__(kThreads) staged_allreduce_kernel(const __grid_constant__ CommDev c, const __grid_constant__ StagedArgs a) {
+__global__ void __launch_bounds__(kThreads, 2) staged_allreduce_kernel(const __grid_constant__ CommDev c, const __grid_constant__ StagedArgs a) {
   using P = typename PolById<POL>::type;
   __shared__ const unsigned char* ptrs[2][FT_MAX_FANIN];
   __shared__ CopyJob jobs[kMaxGroup];

@@ -126,6 +126,7 @@ struct ft_comm {
   size_t oneshot_max = 64 << 10;
   double hybrid_fraction = 0.7, hybrid_lane_fraction = 0.5;
   size_t ll_max = 8 << 10;   // AUTO uses the low-latency protocol up to this size
+  int staged_ctas_per_sm = 1;
   int nvls_ctas_per_sm = 1;   // measured on 8 GPUs: 2 or 3 CTAs per SM lose 5-15 % at 256 MiB and above
   std::map<std::string, DevPlanEntry> plans;
   ftk::CommDev dev{};
@@ -314,7 +315,7 @@ int launch_staged_call(ft_comm* c, const Prepared& pr, const void* sendbuf, void
     a.end_sync = 0;
     a.user_vec_ok = (((uintptr_t)a.user_in | (uintptr_t)a.user_out) & 15) == 0;
   }
-  const int lanes = pick_lanes(c, a.block_elems * pr.es, 8192);
+  const int lanes = pick_lanes(c, a.block_elems * pr.es, 8192, c->staged_ctas_per_sm);
   cudaError_t e = ftk::launch_staged(pr.pol, c->dev, a, lanes, st);
   if (e != cudaSuccess) return fail(c, FT_ERR_CUDA, std::string("staged launch: ") + cudaGetErrorString(e));
   return FT_OK;
@@ -707,6 +708,7 @@ int ft_allreduce_emulate_ll(ft_comm* c, const void* sendbuf, void* recvbuf, size
   if (count == 0) return FT_OK;
   return launch_ll_call(c, pr, sendbuf, recvbuf, count, scale, (uint32_t)phase & 3u, false, call, (cudaStream_t)stream);
 }
+void ft_comm_set_staged_ctas_per_sm(ft_comm* c, int n) { if (c && n >= 1 && n <= 2) c->staged_ctas_per_sm = n; }
 void ft_comm_set_nvls_ctas_per_sm(ft_comm* c, int n) { if (c && n >= 1 && n <= 3) c->nvls_ctas_per_sm = n; }
 void ft_comm_set_ll_max(ft_comm* c, size_t bytes) { if (c) c->ll_max = bytes < ftk::kLLMaxBytes ? bytes : ftk::kLLMaxBytes; }
 

@@ -99,6 +99,8 @@ class _CommBase:
             self.set_timeout_ms(float(os.environ["FT_TIMEOUT_MS"]))
         if os.environ.get("FT_MAX_LANES"):
             self.set_max_lanes(int(os.environ["FT_MAX_LANES"]))
+        if os.environ.get("FT_STAGED_CTAS_PER_SM"):
+            lib().ft_comm_set_staged_ctas_per_sm(self._h, int(os.environ["FT_STAGED_CTAS_PER_SM"]))
         if os.environ.get("FT_NVLS_CTAS_PER_SM"):
             lib().ft_comm_set_nvls_ctas_per_sm(self._h, int(os.environ["FT_NVLS_CTAS_PER_SM"]))
 
