@@ -100,7 +100,7 @@ int ft_allreduce_emulate_ll(ft_comm* c, const void* sendbuf, void* recvbuf, size
 void ft_comm_set_ll_max(ft_comm* c, size_t bytes);
 /* CTAs per SM of the NVLS kernels (1..3, default 1) */
 void ft_comm_set_nvls_ctas_per_sm(ft_comm* c, int n);
-/* CTAs per SM of the staged (plan-driven) kernel (1 or 2, default 1) */
+/* CTAs per SM of the staged (plan-driven) kernel: pinned to 1 (a second CTA per SM measured slower) */
 void ft_comm_set_staged_ctas_per_sm(ft_comm* c, int n);
 /* one-shot emulation: phase 1 = publish input (all ranks first), phase 4 = reduce */
 int ft_allreduce_emulate_oneshot(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op,

@@ -58,6 +58,26 @@ __device__ __forceinline__ void pull_range(const unsigned char* const* ptrs, int
                                            uint32_t es, bool do_scale, float scale) {
   const uint64_t nvec = (total_bytes + 15) / 16;
   const uint64_t step = (uint64_t)blockDim.x * kUnroll;
+  const unsigned char* s0 = ptrs[0];
+  const unsigned char* s1 = n > 1 ? ptrs[1] : nullptr;
+  // The first two sources of the NEXT step are requested before this step's results are
+  // stored, so loads stay in flight across steps (for fan-in 2 that is all of them).
+  uint4 f0[kUnroll], f1[kUnroll];
+  auto issue_first = [&](uint64_t base) {
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint64_t i = base + (uint64_t)u * blockDim.x + threadIdx.x;
+      f0[u] = i < nvec ? ld_stream(s0 + i * 16) : make_uint4(0, 0, 0, 0);
+    }
+    if (s1) {
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const uint64_t i = base + (uint64_t)u * blockDim.x + threadIdx.x;
+        f1[u] = i < nvec ? ld_stream(s1 + i * 16) : make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+  issue_first(0);
   for (uint64_t base = 0; base < nvec; base += step) {
     uint64_t idx[kUnroll];
     bool ok[kUnroll];
@@ -67,15 +87,13 @@ __device__ __forceinline__ void pull_range(const unsigned char* const* ptrs, int
       idx[u] = base + (uint64_t)u * blockDim.x + threadIdx.x;
       ok[u] = idx[u] < nvec;
     }
-    {
-      uint4 v[kUnroll];
-      const unsigned char* p0 = ptrs[0];
 #pragma unroll
-      for (int u = 0; u < kUnroll; ++u) v[u] = ok[u] ? ld_stream(p0 + idx[u] * 16) : make_uint4(0, 0, 0, 0);
+    for (int u = 0; u < kUnroll; ++u) P::init(acc[u], f0[u]);
+    if (s1) {
 #pragma unroll
-      for (int u = 0; u < kUnroll; ++u) P::init(acc[u], v[u]);
+      for (int u = 0; u < kUnroll; ++u) P::add(acc[u], f1[u]);
     }
-    int k = 1;
+    int k = 2;
     for (; k + 2 <= n; k += 2) {
       uint4 v[2][kUnroll];
       const unsigned char* pa = ptrs[k];
@@ -95,6 +113,7 @@ __device__ __forceinline__ void pull_range(const unsigned char* const* ptrs, int
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u) P::add(acc[u], v[u]);
     }
+    if (base + step < nvec) issue_first(base + step);
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       if (!ok[u]) continue;
@@ -131,34 +150,75 @@ __device__ __forceinline__ void copy_range(const unsigned char* src, bool src_ve
 // large one pulls from every peer's link at once instead of queueing on one peer.
 struct CopyJob { const unsigned char* src; unsigned char* dst_work; unsigned char* dst_user; uint64_t bytes; };
 constexpr int kMaxGroup = FT_MAX_FANIN;
-constexpr int kGroupUnroll = 8;
-__device__ __forceinline__ void copy_group(const CopyJob* jobs, int ng, uint64_t max_bytes, bool user_vec_ok, uint32_t es) {
+constexpr int kGroupLoads = 4;   // loads per step; with the next step issued early, up to 8 are in flight per thread
+
+__device__ __forceinline__ void store_job(const CopyJob& jb, uint64_t off, uint4 v, bool user_vec_ok, uint32_t es) {
+  const uint32_t valid = (uint32_t)(jb.bytes - off < 16 ? jb.bytes - off : 16);
+  if (jb.dst_work) {
+    if (valid == 16) st_vec(jb.dst_work + off, v);
+    else st_partial(jb.dst_work + off, v, valid, es);
+  }
+  if (jb.dst_user) {
+    if (valid == 16 && user_vec_ok) st_vec(jb.dst_user + off, v);
+    else st_partial(jb.dst_user + off, v, valid, es);
+  }
+}
+
+// JOBS jobs x VPT vectors per thread per step = kGroupLoads loads in flight; the loads of the
+// next step are issued before the stores of the current one, so the wire never idles between
+// steps.  `first` is the index of the first job of this batch.
+template <int JOBS, int VPT>
+__device__ __forceinline__ void copy_batch(const CopyJob* jobs, int first, int ng, uint64_t max_bytes, bool user_vec_ok, uint32_t es) {
   const uint64_t max_nvec = (max_bytes + 15) / 16;
-  for (uint64_t base = 0; base < max_nvec; base += blockDim.x) {
-    const uint64_t idx = base + threadIdx.x;
-    const uint64_t off = idx * 16;
-    for (int j0 = 0; j0 < ng; j0 += kGroupUnroll) {
-      uint4 v[kGroupUnroll];
-      bool ok[kGroupUnroll];
+  const uint64_t step = (uint64_t)blockDim.x * VPT;
+  uint4 cur[JOBS][VPT], nxt[JOBS][VPT];
+  auto issue = [&](uint64_t base, uint4 (&buf)[JOBS][VPT]) {
 #pragma unroll
-      for (int u = 0; u < kGroupUnroll; ++u) {
+    for (int j = 0; j < JOBS; ++j)
+#pragma unroll
+      for (int u = 0; u < VPT; ++u) {
+        const uint64_t off = (base + (uint64_t)u * blockDim.x + threadIdx.x) * 16;
+        const bool ok = first + j < ng && off < jobs[first + j < ng ? first + j : first].bytes;
+        buf[j][u] = ok ? ld_stream(jobs[first + j].src + off) : make_uint4(0, 0, 0, 0);
+      }
+  };
+  issue(0, cur);
+  for (uint64_t base = 0; base < max_nvec; base += step) {
+    if (base + step < max_nvec) issue(base + step, nxt);
+#pragma unroll
+    for (int j = 0; j < JOBS; ++j)
+#pragma unroll
+      for (int u = 0; u < VPT; ++u) {
+        const uint64_t off = (base + (uint64_t)u * blockDim.x + threadIdx.x) * 16;
+        if (first + j < ng && off < jobs[first + j].bytes) store_job(jobs[first + j], off, cur[j][u], user_vec_ok, es);
+      }
+#pragma unroll
+    for (int j = 0; j < JOBS; ++j)
+#pragma unroll
+      for (int u = 0; u < VPT; ++u) cur[j][u] = nxt[j][u];
+  }
+}
+
+__device__ __forceinline__ void copy_group(const CopyJob* jobs, int ng, uint64_t max_bytes, bool user_vec_ok, uint32_t es) {
+  if (ng == 1) { copy_batch<1, 4>(jobs, 0, ng, max_bytes, user_vec_ok, es); return; }
+  if (ng == 2) { copy_batch<2, 2>(jobs, 0, ng, max_bytes, user_vec_ok, es); return; }
+  if (ng <= 4) { copy_batch<4, 1>(jobs, 0, ng, max_bytes, user_vec_ok, es); return; }
+  // many sources (flat plans): one pass with a load from every source in flight per thread
+  const uint64_t max_nvec = (max_bytes + 15) / 16;
+  constexpr int kWide = 8;
+  for (uint64_t base = 0; base < max_nvec; base += blockDim.x) {
+    const uint64_t off = (base + threadIdx.x) * 16;
+    for (int j0 = 0; j0 < ng; j0 += kWide) {
+      uint4 v[kWide];
+      bool ok[kWide];
+#pragma unroll
+      for (int u = 0; u < kWide; ++u) {
         ok[u] = j0 + u < ng && off < jobs[j0 + u < ng ? j0 + u : 0].bytes;
         v[u] = ok[u] ? ld_stream(jobs[j0 + u].src + off) : make_uint4(0, 0, 0, 0);
       }
 #pragma unroll
-      for (int u = 0; u < kGroupUnroll; ++u) {
-        if (!ok[u]) continue;
-        const CopyJob& jb = jobs[j0 + u];
-        const uint32_t valid = (uint32_t)(jb.bytes - off < 16 ? jb.bytes - off : 16);
-        if (jb.dst_work) {
-          if (valid == 16) st_vec(jb.dst_work + off, v[u]);
-          else st_partial(jb.dst_work + off, v[u], valid, es);
-        }
-        if (jb.dst_user) {
-          if (valid == 16 && user_vec_ok) st_vec(jb.dst_user + off, v[u]);
-          else st_partial(jb.dst_user + off, v[u], valid, es);
-        }
-      }
+      for (int u = 0; u < kWide; ++u)
+        if (ok[u]) store_job(jobs[j0 + u], off, v[u], user_vec_ok, es);
     }
   }
 }
@@ -175,7 +235,7 @@ __device__ __forceinline__ LaneSlice lane_slice(uint64_t region_bytes, uint64_t 
 
 // ------------------------------------------------------------------------------- staged
 template <int POL>
-__global__ void __launch_bounds__(kThreads, 2) staged_allreduce_kernel(const __grid_constant__ CommDev c, const __grid_constant__ StagedArgs a) {
+__global__ void __launch_bounds__(kThreads, 1) staged_allreduce_kernel(const __grid_constant__ CommDev c, const __grid_constant__ StagedArgs a) {
   using P = typename PolById<POL>::type;
   __shared__ const unsigned char* ptrs[2][FT_MAX_FANIN];
   __shared__ CopyJob jobs[kMaxGroup];
@@ -419,6 +479,42 @@ __device__ __forceinline__ void multimem_st(void* p, uint4 v) {
   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+// Reduce `nvec` 16-byte vectors at multicast address `mc` inside the switch and broadcast the
+// result to every rank.  The in-switch loads of the next step are issued before the stores of
+// the current one: a thread always has kU reductions in flight.
+template <int POL>
+__device__ __forceinline__ void nvls_reduce_broadcast(unsigned char* mc, uint64_t nvec, float scale) {
+  using P = typename PolById<POL>::type;
+  constexpr int kU = 4;
+  const uint64_t step = (uint64_t)blockDim.x * kU;
+  uint4 cur[kU], nxt[kU];
+  auto issue = [&](uint64_t base, uint4 (&buf)[kU]) {
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const uint64_t i = base + (uint64_t)u * blockDim.x + threadIdx.x;
+      buf[u] = i < nvec ? Nvls<POL>::ld(mc + i * 16) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  issue(0, cur);
+  for (uint64_t base = 0; base < nvec; base += step) {
+    if (base + step < nvec) issue(base + step, nxt);
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const uint64_t i = base + (uint64_t)u * blockDim.x + threadIdx.x;
+      if (i >= nvec) continue;
+      uint4 v = cur[u];
+      if (scale != 1.0f) {
+        typename P::Acc t;
+        P::init(t, v);
+        v = P::fins(t, scale);
+      }
+      multimem_st(mc + i * 16, v);
+    }
+#pragma unroll
+    for (int u = 0; u < kU; ++u) cur[u] = nxt[u];
+  }
+}
+
 // In place on the symmetric work buffer: rank r reduces block r (lane-sliced) through the
 // switch and broadcasts the result to every rank.  Requires count*es to be a multiple of 16.
 template <int POL>
@@ -442,28 +538,7 @@ __global__ void __launch_bounds__(kThreads) nvls_allreduce_kernel(const __grid_c
   lane_rendezvous(sync, all, call * kCallStride + 1, 0);   // every rank's input is in place
   if (abort_flag) return;
   unsigned char* mc = c.mc_heap + a.work_off + lo + sl.off;
-  const uint64_t nvec = sl.bytes / 16;
-  constexpr int kU = 4;   // independent in-switch reductions in flight per thread
-  for (uint64_t base = 0; base < nvec; base += (uint64_t)blockDim.x * kU) {
-    uint4 v[kU];
-    uint64_t idx[kU];
-#pragma unroll
-    for (int u = 0; u < kU; ++u) {
-      idx[u] = base + (uint64_t)u * blockDim.x + threadIdx.x;
-      v[u] = idx[u] < nvec ? Nvls<POL>::ld(mc + idx[u] * 16) : make_uint4(0, 0, 0, 0);
-    }
-    if (a.scale != 1.0f) {
-#pragma unroll
-      for (int u = 0; u < kU; ++u) {
-        typename P::Acc t;
-        P::init(t, v[u]);
-        v[u] = P::fins(t, a.scale);
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < kU; ++u)
-      if (idx[u] < nvec) multimem_st(mc + idx[u] * 16, v[u]);
-  }
+  nvls_reduce_broadcast<POL>(mc, sl.bytes / 16, a.scale);
   // all my broadcasts are ordered before my signal; after the rendezvous every rank's
   // slice has landed here too
   __threadfence_system();
@@ -478,7 +553,7 @@ __global__ void __launch_bounds__(kThreads) nvls_allreduce_kernel(const __grid_c
 // [0, nvls_lanes), the remainder through a flat reduce-scatter + gather over peer loads on
 // the other lanes.  The two lane groups never wait for each other.
 template <int POL>
-__global__ void __launch_bounds__(kThreads) hybrid_allreduce_kernel(const __grid_constant__ CommDev c, const __grid_constant__ NvlsArgs a,
+__global__ void __launch_bounds__(kThreads, 1) hybrid_allreduce_kernel(const __grid_constant__ CommDev c, const __grid_constant__ NvlsArgs a,
                                                                      uint32_t nvls_lanes, uint64_t nvls_bytes) {
   using P = typename PolById<POL>::type;
   __shared__ const unsigned char* ptrs[FT_MAX_RANKS];
@@ -518,24 +593,7 @@ __global__ void __launch_bounds__(kThreads) hybrid_allreduce_kernel(const __grid
   if (is_nvls) {
     const LaneSlice sl = my_slice(c.rank);
     unsigned char* mc = c.mc_heap + a.work_off + (uint64_t)c.rank * block_bytes + sl.off;
-    const uint64_t nvec = sl.bytes / 16;
-    constexpr int kU = 4;
-    for (uint64_t base = 0; base < nvec; base += (uint64_t)blockDim.x * kU) {
-      uint4 v[kU];
-      uint64_t idx[kU];
-#pragma unroll
-      for (int u = 0; u < kU; ++u) {
-        idx[u] = base + (uint64_t)u * blockDim.x + threadIdx.x;
-        v[u] = idx[u] < nvec ? Nvls<POL>::ld(mc + idx[u] * 16) : make_uint4(0, 0, 0, 0);
-      }
-      if (a.scale != 1.0f) {
-#pragma unroll
-        for (int u = 0; u < kU; ++u) { typename P::Acc t; P::init(t, v[u]); v[u] = P::fins(t, a.scale); }
-      }
-#pragma unroll
-      for (int u = 0; u < kU; ++u)
-        if (idx[u] < nvec) multimem_st(mc + idx[u] * 16, v[u]);
-    }
+    nvls_reduce_broadcast<POL>(mc, sl.bytes / 16, a.scale);
     __threadfence_system();
     lane_rendezvous(sync, all, call * kCallStride + 2, 1);
     return;

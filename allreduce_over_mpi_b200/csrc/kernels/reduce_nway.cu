@@ -23,6 +23,8 @@
 
 namespace ftk {
 
+static std::atomic<uint64_t> g_launches{0};
+
 struct NwayArgs {
   const void* src[FT_MAX_FANIN];
   void* dst;
@@ -83,6 +85,50 @@ __global__ void __launch_bounds__(512) reduce_nway_vec_kernel(const __grid_const
     for (int u = 0; u < UNROLL; ++u)
       if (ok[u]) st_vec_cs((uint4*)a.dst + idx[u], P::fin(acc[u]));
   }
+}
+
+// ---------------------------------------------------------------------------- narrow-word path
+// One 4- or 8-byte word per thread, one CTA per tile, every source's load issued before the
+// first add: the access pattern of a one-element-per-thread kernel (many more warps in
+// flight, 128-byte requests per warp) with this file's per-type arithmetic.  At high fan-in
+// this keeps HBM busier than 16-byte vectors do.
+template <int POL, int WORDS>   // WORDS = 1 (4 bytes) or 2 (8 bytes) per thread
+__global__ void __launch_bounds__(256) reduce_nway_narrow_kernel(const __grid_constant__ NwayArgs a, unsigned long long nwords) {
+  using P = typename PolById<POL>::type;
+  const unsigned long long i = ((unsigned long long)blockIdx.x * blockDim.x + threadIdx.x) * WORDS;
+  if (i >= nwords) return;
+  typename P::Acc acc;
+  constexpr int G = 8;
+  for (int k = 0; k < a.n; k += G) {
+    uint32_t w[G][2];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+      if (k + g < a.n) {
+        const uint32_t* p = (const uint32_t*)a.src[k + g] + i;
+        if (WORDS == 2) asm volatile("ld.global.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(w[g][0]), "=r"(w[g][1]) : "l"(p) : "memory");
+        else { asm volatile("ld.global.L1::no_allocate.u32 %0, [%1];" : "=r"(w[g][0]) : "l"(p) : "memory"); w[g][1] = 0; }
+      }
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+      if (k + g < a.n) {
+        const uint4 v = make_uint4(w[g][0], w[g][1], 0, 0);
+        if (k + g == 0) P::init(acc, v);
+        else P::add(acc, v);
+      }
+  }
+  const uint4 out = P::fin(acc);
+  uint32_t* d = (uint32_t*)a.dst + i;
+  if (WORDS == 2) asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" ::"l"(d), "r"(out.x), "r"(out.y) : "memory");
+  else asm volatile("st.global.cs.u32 [%0], %1;" ::"l"(d), "r"(out.x) : "memory");
+}
+
+template <int POL, int WORDS>
+static cudaError_t launch_narrow(const NwayArgs& a, cudaStream_t st) {
+  const unsigned long long nwords = a.nvec * 4;   // the aligned part, in 4-byte words (a multiple of 4)
+  const unsigned long long threads = nwords / WORDS;
+  reduce_nway_narrow_kernel<POL, WORDS><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(a, nwords);
+  g_launches++;
+  return cudaGetLastError();
 }
 
 // ---------------------------------------------------------------------------- scalar path
@@ -197,7 +243,6 @@ __global__ void __launch_bounds__(256) reduce_nway_tma_kernel(const __grid_const
 }
 
 // ---------------------------------------------------------------------------- host side
-static std::atomic<uint64_t> g_launches{0};
 static thread_local char g_cuda_err[256] = "";
 
 static int cuda_fail(cudaError_t e, const char* where) {
@@ -303,13 +348,19 @@ static int run_policy(NwayArgs& a, size_t bytes, int variant, cudaStream_t st) {
         case 20: e = launch_vec<POL, 1, 4>(a, 512, 0, st); done = true; break;
         case 21: e = launch_vec<POL, 2, 8>(a, 256, 8, st); done = true; break;
         case 22: e = launch_vec<POL, 1, 8>(a, 512, 4, st); done = true; break;
+        case 23: e = launch_narrow<POL, 1>(a, st); done = true; break;
+        case 24: e = launch_narrow<POL, 2>(a, st); done = true; break;
         default: break;
       }
     }
     // defaults picked from a B200 sweep (fp32 and bf16, 64 Mi elements): low fan-in runs a
     // persistent grid of 2 CTAs x 512 threads per SM with 4 vectors x 2 sources in flight; from
-    // fan-in 6 up one CTA per tile with 1 vector x 4 sources in flight does better
-    if (!done) e = a.n >= 6 ? launch_vec<POL, 1, 4>(a, 512, 0, st) : launch_vec<POL, 4, 2>(a, 512, 2, st);
+    // fan-in 6 up one CTA per tile with 1 vector x 4 sources in flight does better;
+    // fp32 with three or more sources: 8 bytes per thread, one CTA per tile, all loads up front
+    if (!done) {
+      if (POL == POL_F32 && a.n >= 3) e = launch_narrow<POL, 2>(a, st);
+      else e = a.n >= 6 ? launch_vec<POL, 1, 4>(a, 512, 0, st) : launch_vec<POL, 4, 2>(a, 512, 2, st);
+    }
     if (e != cudaSuccess) return cuda_fail(e, "reduce_nway vector launch");
   }
   e = launch_scalar<POL>(a, a.nvec * 16 / unit, st);

@@ -708,7 +708,9 @@ int ft_allreduce_emulate_ll(ft_comm* c, const void* sendbuf, void* recvbuf, size
   if (count == 0) return FT_OK;
   return launch_ll_call(c, pr, sendbuf, recvbuf, count, scale, (uint32_t)phase & 3u, false, call, (cudaStream_t)stream);
 }
-void ft_comm_set_staged_ctas_per_sm(ft_comm* c, int n) { if (c && n >= 1 && n <= 2) c->staged_ctas_per_sm = n; }
+// Measured on 8 GPUs: a second CTA per SM does not help the staged kernel (and it needs more than 64
+// registers since its loops are software pipelined), so the setting is pinned to 1.
+void ft_comm_set_staged_ctas_per_sm(ft_comm* c, int n) { (void)n; if (c) c->staged_ctas_per_sm = 1; }
 void ft_comm_set_nvls_ctas_per_sm(ft_comm* c, int n) { if (c && n >= 1 && n <= 3) c->nvls_ctas_per_sm = n; }
 void ft_comm_set_ll_max(ft_comm* c, size_t bytes) { if (c) c->ll_max = bytes < ftk::kLLMaxBytes ? bytes : ftk::kLLMaxBytes; }
 

@@ -138,6 +138,28 @@ def main():
             ok = False
             print(f"[rank {rank}] back-to-back {name} drifted: {t[:4].tolist()}", flush=True)
 
+    # CUDA graph: calls captured once and replayed (call numbers and slot parity live on the device)
+    sym.fill_(1.0); small.fill_(1.0)
+    side = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    dist.barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        comm.all_reduce(sym, op="avg", shape=shapes[0], algo="staged")
+        comm.all_reduce(small, op="avg", algo="ll")
+        comm.all_reduce(small, op="avg", algo="oneshot")
+        if comm.has_nvls:
+            comm.all_reduce(sym, op="avg", algo="nvls")
+    for _ in range(5):
+        graph.replay()
+    torch.cuda.synchronize()
+    comm.check()
+    for t, name in ((sym, "sym"), (small, "small")):
+        if not torch.allclose(t, torch.ones_like(t), atol=1e-5):
+            ok = False
+            print(f"[rank {rank}] graph replay {name} drifted: {t[:4].tolist()}", flush=True)
+    report["graph_replays"] = 5
+
     # int32 sum and bitwise AND over the wire
     comm.free_all()
     xi = torch.full((10_001,), rank + 1, dtype=torch.int32, device=dev)

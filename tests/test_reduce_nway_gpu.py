@@ -90,7 +90,7 @@ def test_misaligned_bases(offsets):
     assert out_base[:offsets[3]].abs().sum() == 0 and out_base[offsets[3] + n:].abs().sum() == 0
 
 
-@pytest.mark.parametrize("variant", [2, 11, 12, 13, 14, 15, 16, 17, 18, 19, 20, 21, 22])
+@pytest.mark.parametrize("variant", [2, 11, 12, 13, 14, 15, 16, 17, 18, 19, 20, 21, 22, 23, 24])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_variants_agree(variant, dtype):
     for n in (1, 2, 4, 8, 9):
