@@ -41,6 +41,7 @@ def declare(lib) -> None:
         "ft_comm_set_ll_max": (None, [vp, sz]),
         "ft_comm_set_nvls_ctas_per_sm": (None, [vp, i]),
         "ft_comm_set_staged_ctas_per_sm": (None, [vp, i]),
+        "ft_allreduce_emulate_push": (i, [vp, vp, sz, i, i, f32, vp]),
         "ft_allreduce_emulate_ll": (i, [vp, vp, vp, sz, i, i, f32, i, u64, vp]),
         "ft_allreduce": (i, [vp, vp, vp, sz, i, i, *shape, i, f32, vp]),
         "ft_allreduce_emulate_stage": (i, [vp, vp, vp, sz, i, i, *shape, f32, i, i, vp]),

@@ -130,6 +130,8 @@ def sweep(a, comm: FlexTreeComm, rank: int, world: int) -> list[dict]:
                     fn = lambda shape=shape: comm.all_reduce(sym, shape=shape, algo="staged")  # noqa: E731
                 elif algo == "nvls":
                     fn = lambda: comm.all_reduce(sym, algo="nvls")  # noqa: E731
+                elif algo == "push":
+                    fn = lambda: comm.all_reduce(sym, algo="push")  # noqa: E731
                 elif algo == "hybrid":
                     bf, lf = (float(x) for x in shape.split(","))
                     comm.set_hybrid(bf, lf)

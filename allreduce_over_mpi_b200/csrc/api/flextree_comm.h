@@ -31,7 +31,7 @@ extern "C" {
 typedef struct ft_comm ft_comm;
 
 enum { FT_MEM_IPC = 0, FT_MEM_VMM = 1 };
-enum { FT_ALGO_AUTO = 0, FT_ALGO_STAGED = 1, FT_ALGO_ONESHOT = 2, FT_ALGO_NVLS = 3, FT_ALGO_HYBRID = 4, FT_ALGO_LL = 5 };
+enum { FT_ALGO_AUTO = 0, FT_ALGO_STAGED = 1, FT_ALGO_ONESHOT = 2, FT_ALGO_NVLS = 3, FT_ALGO_HYBRID = 4, FT_ALGO_LL = 5, FT_ALGO_PUSH = 6 };
 
 /* heap_bytes: symmetric memory for user tensors (ft_comm_alloc) and internal staging.
  * staging_bytes: size of ONE staging slot (two are carved out of the heap); bounds the
@@ -93,6 +93,8 @@ void ft_comm_set_hybrid(ft_comm* c, double byte_fraction, double lane_fraction);
 int ft_allreduce_emulate_stage(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op,
                                const int* widths, int nw, int lonely, int ring, float scale, int stage_begin,
                                int stage_end, void* stream);
+/* reduce+push emulation: launch rank after rank on one stream (each rank's kernel is self-contained) */
+int ft_allreduce_emulate_push(ft_comm* c, void* recvbuf, size_t count, int dtype, int op, float scale, void* stream);
 /* low-latency push emulation: phase 1 = push (all ranks first), phase 2 = receive and reduce */
 int ft_allreduce_emulate_ll(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op, float scale,
                             int phase, uint64_t call, void* stream);

@@ -12,6 +12,7 @@
 //  * nvls_allreduce_kernel     multimem.ld_reduce / multimem.st through the NVSwitch
 //    multicast mapping (in-switch reduction), where the box exposes it.
 //  * hybrid_allreduce_kernel   both at once on disjoint parts of the message.
+//  * push_allreduce_kernel     flat two-shot in one pass: pull + sum + posted writes to every rank.
 //  * ll_allreduce_kernel       push protocol with the flag inside every 8-byte word, no
 //    rendezvous at all (smallest messages).
 //
@@ -639,6 +640,101 @@ __global__ void __launch_bounds__(kThreads, 1) hybrid_allreduce_kernel(const __g
   lane_rendezvous(sync, all, call * kCallStride + 3, 2);
 }
 
+// ------------------------------------------------------------------------------- flat, reduce + push
+// Flat two-shot in ONE pass for tensors in the symmetric heap: rank r pulls block r from every
+// peer, sums it, and stores the result straight into every rank's buffer (its own and the
+// N-1 peers').  The gather half therefore travels as posted writes instead of read requests
+// and responses, and the kernel needs two rendezvous instead of three.  Only rank r ever
+// writes block r anywhere, and it reads a peer's copy of a vector before overwriting it.
+template <int POL>
+__global__ void __launch_bounds__(kThreads, 1) push_allreduce_kernel(const __grid_constant__ CommDev c, const __grid_constant__ NvlsArgs a,
+                                                                      uint32_t do_sync) {
+  using P = typename PolById<POL>::type;
+  __shared__ unsigned char* bufs[FT_MAX_RANKS];   // every rank's block r, lane-sliced, rotated so that bufs[0] is mine
+  __shared__ int abort_flag;
+  __shared__ unsigned long long call_slot;
+  const int lane = blockIdx.x, nlanes = gridDim.x;
+  if (threadIdx.x == 0) abort_flag = 0;
+  unsigned long long call = 0;
+  if (do_sync) call = begin_call(c, &call_slot);
+  else __syncthreads();
+  LaneSync sync{c.flags, c.flags[c.rank], c.rank, c.world, lane, FT_MAX_RANKS, c.timeout_ns, c.status, &abort_flag};
+  const unsigned long long all = c.world >= 64 ? ~0ull : ((1ull << c.world) - 1);
+  const uint32_t es = a.elem_size;
+  const uint64_t block_bytes = a.block_elems * es, total_bytes = a.count * es;
+  uint64_t chunk = (block_bytes + nlanes - 1) / nlanes;
+  chunk = (chunk + 15) & ~15ull;
+  const uint64_t lo = (uint64_t)c.rank * block_bytes;
+  const uint64_t len = lo >= total_bytes ? 0 : (total_bytes - lo < block_bytes ? total_bytes - lo : block_bytes);
+  const LaneSlice sl = lane_slice(len, chunk, lane);
+  if ((int)threadIdx.x < c.world) bufs[threadIdx.x] = c.heap[(c.rank + threadIdx.x) % c.world] + a.work_off + lo + sl.off;
+  if (do_sync) {
+    lane_rendezvous(sync, all, call * kCallStride + 1, 0);
+    if (abort_flag) return;
+  } else {
+    __syncthreads();
+  }
+  const int n = c.world;
+  const uint64_t nvec = (sl.bytes + 15) / 16;
+  const uint64_t step = (uint64_t)blockDim.x * kUnroll;
+  for (uint64_t base = 0; base < nvec; base += step) {
+    uint64_t idx[kUnroll];
+    bool ok[kUnroll];
+    typename P::Acc acc[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      idx[u] = base + (uint64_t)u * blockDim.x + threadIdx.x;
+      ok[u] = idx[u] < nvec;
+    }
+    {
+      uint4 v[kUnroll];
+      const unsigned char* p0 = bufs[0];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) v[u] = ok[u] ? ld_stream(p0 + idx[u] * 16) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) P::init(acc[u], v[u]);
+    }
+    int k = 1;
+    for (; k + 2 <= n; k += 2) {
+      uint4 v[2][kUnroll];
+      const unsigned char* pa = bufs[k];
+      const unsigned char* pb = bufs[k + 1];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) v[0][u] = ok[u] ? ld_stream(pa + idx[u] * 16) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) v[1][u] = ok[u] ? ld_stream(pb + idx[u] * 16) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) { P::add(acc[u], v[0][u]); P::add(acc[u], v[1][u]); }
+    }
+    if (k < n) {
+      uint4 v[kUnroll];
+      const unsigned char* pa = bufs[k];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) v[u] = ok[u] ? ld_stream(pa + idx[u] * 16) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) P::add(acc[u], v[u]);
+    }
+    uint4 out[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) out[u] = a.scale != 1.0f ? P::fins(acc[u], a.scale) : P::fin(acc[u]);
+    for (int q = 0; q < n; ++q) {   // posted writes to every rank, mine first
+      unsigned char* d = bufs[q];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        if (!ok[u]) continue;
+        const uint64_t off = idx[u] * 16;
+        const uint32_t valid = (uint32_t)(sl.bytes - off < 16 ? sl.bytes - off : 16);
+        if (valid == 16) st_vec(d + off, out[u]);
+        else st_partial(d + off, out[u], valid, es);
+      }
+    }
+  }
+  if (do_sync) {
+    __threadfence_system();   // my stores into the peers' buffers are ordered before my signal
+    lane_rendezvous(sync, all, call * kCallStride + 2, 1);
+  }
+}
+
 // ------------------------------------------------------------------------------- bounded-wait probe
 // One CTA waits on one of its own flags for a rendezvous number that nobody will signal.
 // With a short limit it must come back with FT_ERR_TIMEOUT in the status block.
@@ -720,6 +816,12 @@ cudaError_t launch_hybrid(int pol, const CommDev& c, const NvlsArgs& a, int lane
     default: return cudaErrorInvalidValue;
   }
   return cudaGetLastError();
+}
+cudaError_t launch_push(int pol, const CommDev& c, const NvlsArgs& a, int lanes, bool do_sync, cudaStream_t st) {
+  ft_count_launch(1);
+#define CALL(P) (push_allreduce_kernel<P><<<lanes, kThreads, 0, st>>>(c, a, do_sync ? 1u : 0u), cudaGetLastError())
+  FT_POL_SWITCH(pol, CALL)
+#undef CALL
 }
 cudaError_t launch_wait_probe(const CommDev& c, int peer, unsigned long long timeout_ns, cudaStream_t st) {
   ft_count_launch(1);

@@ -31,6 +31,7 @@ namespace ftk {
 cudaError_t launch_staged(int pol, const CommDev& c, const StagedArgs& a, int lanes, cudaStream_t st);
 cudaError_t launch_oneshot(int pol, const CommDev& c, const OneShotArgs& a, uint64_t slot_bytes, int lanes, cudaStream_t st);
 cudaError_t launch_nvls(int pol, const CommDev& c, const NvlsArgs& a, int lanes, cudaStream_t st);
+cudaError_t launch_push(int pol, const CommDev& c, const NvlsArgs& a, int lanes, bool do_sync, cudaStream_t st);
 cudaError_t launch_ll(int pol, const CommDev& c, const LLArgs& a, cudaStream_t st);
 cudaError_t launch_hybrid(int pol, const CommDev& c, const NvlsArgs& a, int lanes, int nvls_lanes, uint64_t nvls_bytes, cudaStream_t st);
 cudaError_t launch_wait_probe(const CommDev& c, int peer, unsigned long long timeout_ns, cudaStream_t st);
@@ -337,6 +338,22 @@ int launch_oneshot_call(ft_comm* c, const Prepared& pr, const void* sendbuf, voi
   const int lanes = pick_lanes(c, pr.bytes, 4096);
   cudaError_t e = ftk::launch_oneshot(pr.pol, c->dev, a, c->staging_bytes, lanes, st);
   if (e != cudaSuccess) return fail(c, FT_ERR_CUDA, std::string("one-shot launch: ") + cudaGetErrorString(e));
+  return FT_OK;
+}
+
+int launch_push_call(ft_comm* c, const Prepared& pr, const void* sendbuf, void* recvbuf, size_t count, float scale, bool do_sync,
+                     cudaStream_t st) {
+  if (!pr.heap_resident) return fail(c, FT_ERR_INVALID_ARG, "the reduce+push all-reduce needs a tensor in the symmetric heap");
+  if (sendbuf && sendbuf != recvbuf) FT_CUDA(c, cudaMemcpyAsync(recvbuf, sendbuf, pr.bytes, cudaMemcpyDeviceToDevice, st));
+  ftk::NvlsArgs a{};
+  a.work_off = (uint64_t)((unsigned char*)recvbuf - local_base(c));
+  a.count = count;
+  a.elem_size = pr.es;
+  a.block_elems = pick_block_elems(count, c->world, pr.es);
+  a.scale = scale;
+  const int lanes = pick_lanes(c, a.block_elems * pr.es, 8192);
+  cudaError_t e = ftk::launch_push(pr.pol, c->dev, a, lanes, do_sync, st);
+  if (e != cudaSuccess) return fail(c, FT_ERR_CUDA, std::string("push launch: ") + cudaGetErrorString(e));
   return FT_OK;
 }
 
@@ -650,6 +667,7 @@ int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, i
   }
   if (algo == FT_ALGO_LL) return launch_ll_call(c, pr, sendbuf, recvbuf, count, scale, 3, true, 0, st);
   if (algo == FT_ALGO_ONESHOT) return launch_oneshot_call(c, pr, sendbuf, recvbuf, count, scale, 7, 0, st);
+  if (algo == FT_ALGO_PUSH) return launch_push_call(c, pr, sendbuf, recvbuf, count, scale, true, st);
   if (algo == FT_ALGO_NVLS || algo == FT_ALGO_HYBRID) {
     if (!ft_comm_has_nvls(c)) return fail(c, FT_ERR_NOT_AVAILABLE, "NVLS multicast is not bound on this communicator");
     if (!pr.heap_resident) return fail(c, FT_ERR_INVALID_ARG, "NVLS all-reduce needs a tensor in the symmetric heap");
@@ -698,6 +716,14 @@ int ft_allreduce_emulate_oneshot(ft_comm* c, const void* sendbuf, void* recvbuf,
   if (rc != FT_OK) return rc;
   if (count == 0) return FT_OK;
   return launch_oneshot_call(c, pr, sendbuf, recvbuf, count, scale, (uint32_t)phase & 5u, call, (cudaStream_t)stream);
+}
+
+int ft_allreduce_emulate_push(ft_comm* c, void* recvbuf, size_t count, int dtype, int op, float scale, void* stream) {
+  Prepared pr;
+  int rc = prepare(c, nullptr, recvbuf, count, dtype, op, &pr);
+  if (rc != FT_OK) return rc;
+  if (count == 0 || c->world == 1) return FT_OK;
+  return launch_push_call(c, pr, nullptr, recvbuf, count, scale, false, (cudaStream_t)stream);
 }
 
 int ft_allreduce_emulate_ll(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op, float scale,

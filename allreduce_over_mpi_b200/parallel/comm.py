@@ -30,7 +30,7 @@ from ..utils import log
 from . import planner
 from .planner import CostParams, Shape
 
-ALGOS = {"auto": 0, "staged": 1, "oneshot": 2, "nvls": 3, "hybrid": 4, "ll": 5}
+ALGOS = {"auto": 0, "staged": 1, "oneshot": 2, "nvls": 3, "hybrid": 4, "ll": 5, "push": 6}
 LL_MAX_BYTES = 256 << 10
 MEM_IPC, MEM_VMM = 0, 1
 
@@ -152,7 +152,7 @@ class _CommBase:
         hit = self._choices.get(key)
         if hit is None and self.table:   # measured winners for this world size, nearest size on a log scale
             import math
-            rows = [r for r in self.table.get(str(self.world), []) if (nvls_ok or not (r[1] == "nvls" or r[1].startswith("hybrid"))) and
+            rows = [r for r in self.table.get(str(self.world), []) if (nvls_ok or not (r[1] == "nvls" or r[1].startswith("hybrid"))) and (in_heap or r[1] != "push") and
                     (r[1] != "oneshot" or nbytes <= self.staging_bytes) and (r[1] != "ll" or nbytes <= LL_MAX_BYTES)]
             # the table speaks only for the range of sizes that was measured (one octave of slack)
             if rows and min(r[0] for r in rows) / 2 <= nbytes <= max(r[0] for r in rows) * 2:
@@ -439,6 +439,13 @@ class LocalWorld:
 
         if world == 1:
             self.ranks[0].all_reduce(tensors[0], op=op, scale=scale, out=outs[0])
+            return outs
+        if algo == "push":
+            for r, c in enumerate(self.ranks):
+                if outs[r].data_ptr() != tensors[r].data_ptr():
+                    outs[r].copy_(tensors[r])
+            for r, c in enumerate(self.ranks):
+                c._check(L.ft_allreduce_emulate_push(c._h, outs[r].data_ptr(), outs[r].numel(), dt, OPS[op], float(scale), st))
             return outs
         if algo == "ll":
             for phase in (1, 2):

@@ -112,6 +112,12 @@ def main():
             comm.free_all()
             sym = comm.alloc(count, dtype)
             fill(sym, rank, it)
+            comm.all_reduce(sym, algo="push")
+            verify(sym, count, dtype, it, f"push {dtype} {count}")
+            it += 1
+            comm.free_all()
+            sym = comm.alloc(count, dtype)
+            fill(sym, rank, it)
             comm.all_reduce(sym)      # cost model's pick
             verify(sym, count, dtype, it, f"auto {dtype} {count}")
 
@@ -129,6 +135,7 @@ def main():
         comm.all_reduce(small, op="avg", algo="oneshot")
         comm.all_reduce(small, op="avg", algo="ll")
         comm.all_reduce(small, op="avg")
+        comm.all_reduce(sym, op="avg", algo="push")
         if comm.has_nvls:
             comm.all_reduce(sym, op="avg", algo="nvls")
     torch.cuda.synchronize()

@@ -140,6 +140,30 @@ def test_low_latency_push(world, dtype):
     w.close()
 
 
+@pytest.mark.parametrize("world", [2, 3, 8])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int64])
+def test_reduce_and_push(world, dtype):
+    w = LocalWorld(world, heap_bytes=8 << 20, staging_bytes=1 << 16)
+    for it, count in enumerate((1, 35, 4099, 500_001)):
+        host = inputs(world, count, dtype, seed=40 + it)
+        want = torch.stack(host).double().sum(0)
+        dev = []
+        for r, c in enumerate(w.ranks):
+            t = c.alloc(count, dtype)
+            t.copy_(host[r])
+            dev.append(t)
+        w.all_reduce(dev, algo="push")
+        torch.cuda.synchronize()
+        for r in range(world):
+            assert torch.allclose(dev[r].double().cpu(), want, atol=tol(dtype) * 2), (world, count, r)
+        assert all(torch.equal(d, dev[0]) for d in dev)
+        for c in w.ranks:
+            c.free_all()
+    with pytest.raises(Exception, match="symmetric heap"):
+        w.all_reduce([torch.zeros(64, device=DEV) for _ in range(world)], algo="push")
+    w.close()
+
+
 def test_scale_and_out_of_place():
     w = LocalWorld(4, heap_bytes=1 << 20, staging_bytes=1 << 20)
     host = inputs(4, 12_345, torch.bfloat16, seed=9)
