@@ -5,6 +5,8 @@
 
 #include <cstdio>
 #include <cstring>
+#include <map>
+#include <mutex>
 #include <string>
 
 #include "../planner/config.hpp"
@@ -24,6 +26,17 @@ struct ft_mpi_comm {
 
 namespace {
 thread_local std::string g_err;
+// The reference rebuilds its schedule on every call (mpi_mod.hpp:1520-1527); here a plan is built
+// once per (world, shape) and shared by all rank threads.
+const ft::Plan& plan_for(int world, const ft::Shape& shape) {
+  static std::mutex mu;
+  static std::map<std::string, ft::Plan> cache;
+  const std::string key = std::to_string(world) + ":" + shape.str();
+  std::lock_guard<std::mutex> lk(mu);
+  auto it = cache.find(key);
+  if (it == cache.end()) it = cache.emplace(key, ft::build_plan(world, shape)).first;
+  return it->second;
+}
 int fail(int code, const std::string& msg) {
   g_err = msg;
   std::fprintf(stderr, "%s\n", msg.c_str());
@@ -101,7 +114,7 @@ int MPI_Allreduce_FT_c(const void* sendbuf, void* recvbuf, size_t count, FT_Data
       return 0;
     }
     if (cfg.is_auto) shape = ft::Shape::flat(world);  // on shared host memory every shape moves the same bytes
-    ft::Plan plan = ft::build_plan(world, shape);
+    const ft::Plan& plan = plan_for(world, shape);
     ft::RankStatus st = ft::cpu_allreduce(comm->threads->w, comm->rank, plan, (ft_op)op, (ft_dtype)datatype,
                                           in_place ? nullptr : sendbuf, recvbuf, count, 0, nullptr, 1);
     if (st.code != FT_OK)

@@ -83,9 +83,26 @@ def fit_params(rows) -> tuple[CostParams, list]:
             staged.append((r["world"], Shape.parse(k[1]), r["bytes"], r["ms"] * 1e3))
     if not staged:
         return p, []
+    # latency terms from the smallest size: t = launch + sync * (stages + 1)
+    small = min(b for _, _, b, _ in staged)
+    pts = [(planner.plan_num_stages(w, s), us) for w, s, b, us in staged if b == small]
+    n = len(pts)
+    p.stage_floor_us = 0.0
+    if n >= 2:
+        sx = sum(x for x, _ in pts); sy = sum(y for _, y in pts)
+        sxx = sum(x * x for x, _ in pts); sxy = sum(x * y for x, y in pts)
+        den = n * sxx - sx * sx
+        slope = (n * sxy - sx * sy) / den if den else 0.0
+        icpt = (sy - slope * sx) / n
+        p.sync_us = max(0.1, slope)
+        p.launch_us = max(0.0, icpt - p.sync_us)
+
+    def wire_us(w, s, us):   # what is left of a measurement once the fixed costs are taken out
+        return max(us - p.launch_us - p.sync_us * (planner.plan_num_stages(w, s) + 1), 1e-3)
+
     # link bandwidth: the best staged shape at the largest size moves 2(N-1)/N * S per direction
     big = max(b for _, _, b, _ in staged)
-    p.link_gbs = max(2 * (w - 1) / w * b / (us * 1e-6) / 1e9 for w, s, b, us in staged if b == big)
+    p.link_gbs = max(2 * (w - 1) / w * b / (wire_us(w, s, us) * 1e-6) / 1e9 for w, s, b, us in staged if b == big)
     # peer efficiency: for every fan-out k (peers pulled at once), ratio of the bandwidth a shape
     # whose widest stage has k peers reaches at the largest size to the best one
     eff = defaultdict(float)
@@ -93,27 +110,14 @@ def fit_params(rows) -> tuple[CostParams, list]:
         if b != big or s.ring or s.lonely:
             continue
         k = max(s.widths) - 1
-        bw = 2 * (w - 1) / w * b / (us * 1e-6) / 1e9
+        bw = 2 * (w - 1) / w * b / (wire_us(w, s, us) * 1e-6) / 1e9
         eff[k] = max(eff[k], min(1.0, bw / p.link_gbs))
     p.peer_eff = {int(k): round(v, 3) for k, v in eff.items()}
-    # latency terms from the smallest size: t = launch + sync * (stages + 1) + floor * stages
-    small = min(b for _, _, b, _ in staged)
-    pts = [(planner.plan_num_stages(w, s), us) for w, s, b, us in staged if b == small]
-    n = len(pts)
-    if n >= 2:
-        sx = sum(x for x, _ in pts); sy = sum(y for _, y in pts)
-        sxx = sum(x * x for x, _ in pts); sxy = sum(x * y for x, y in pts)
-        den = n * sxx - sx * sx
-        slope = (n * sxy - sx * sy) / den if den else 0.0
-        icpt = (sy - slope * sx) / n
-        p.stage_floor_us = 0.0
-        p.sync_us = max(0.1, slope)
-        p.launch_us = max(0.0, icpt - p.sync_us)
     # NVLS: bytes through each GPU's links are S * (1 + 1/N)
     nv = [(r["world"], r["bytes"], r["ms"] * 1e3) for r in rows if (split_impl(r["impl"]) or ("", ""))[0] == "nvls"]
     if nv:
         w, b, us = max(nv, key=lambda t: t[1])
-        p.nvls_gbs = b * (1 + 1 / w) / (us * 1e-6) / 1e9
+        p.nvls_gbs = b * (1 + 1 / w) / (max(us - p.launch_us - 3 * p.sync_us, 1e-3) * 1e-6) / 1e9
     # one-shot limit: largest size at which one-shot still beats every staged shape
     os_rows = defaultdict(dict)
     for r in rows:

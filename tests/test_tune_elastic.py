@@ -1,0 +1,47 @@
+"""Calibration fit / choice table and re-planning after a lost rank (CPU)."""
+import json
+
+from allreduce_over_mpi_b200.parallel import planner, tune
+from allreduce_over_mpi_b200.parallel.elastic import replan_after_failure
+from allreduce_over_mpi_b200.parallel.planner import CostParams, Shape
+
+
+def synth_rows(world=8, link=600.0, launch=20.0, sync=5.0):
+    k = CostParams(launch_us=launch, sync_us=sync, link_gbs=link, stage_floor_us=0.0)
+    rows = []
+    for b in (1024, 1 << 20, 1 << 28):
+        for shape in ("8", "2*4", "2*2*2"):
+            us = planner.cost_v1(world, Shape.parse(shape), b, k)
+            rows.append({"impl": f"flextree/staged/{shape}", "bytes": b, "world": world, "dtype": "float32", "ms": us / 1e3, "ok": True})
+        rows.append({"impl": "flextree/nvls/auto", "bytes": b, "world": world, "dtype": "float32", "ms": (30 + b * 1.125 / 480e3) / 1e3})
+        rows.append({"impl": "flextree/ll/auto", "bytes": b, "world": world, "dtype": "float32", "ms": (15 + b / 20e3) / 1e3})
+        rows.append({"impl": "flextree/auto->nvls/8", "bytes": b, "world": world, "dtype": "float32", "ms": 1.0})
+        rows.append({"impl": "nccl", "bytes": b, "world": world, "dtype": "float32", "ms": 1.0})
+    return rows
+
+
+def test_fit_recovers_the_generating_constants(tmp_path):
+    rows = synth_rows()
+    p, fit = tune.fit_params(rows)
+    assert abs(p.link_gbs - 600) / 600 < 0.02
+    assert abs(p.sync_us - 5.0) < 0.3 and abs(p.launch_us - 20.0) < 1.5
+    assert 470 < p.nvls_gbs < 490
+    assert max(abs(f["rel_err"]) for f in fit) < 0.05
+    table = tune.best_table(rows)
+    assert [r[1] for r in table["8"]] == ["ll", "nvls", "nvls"]
+    # end to end through the command line, and the communicator-side loader
+    src = tmp_path / "sweep.jsonl"
+    src.write_text("\n".join(json.dumps(r) for r in rows))
+    out = tmp_path / "cal.json"
+    assert tune.main([str(src), "--out", str(out)]) == 0
+    assert planner.load_choice_table(out)["8"][0][1] == "ll"
+    assert abs(CostParams.load(out).link_gbs - 600) < 15
+
+
+def test_replan_after_failure_uses_lonely_layouts():
+    r = replan_after_failure(8, {3}, 64 << 20, CostParams(link_gbs=600, sync_us=5, launch_us=20))
+    assert r.world == 7 and r.rank_map == {0: 0, 1: 1, 2: 2, 4: 3, 5: 4, 6: 5, 7: 6}
+    assert {"7", "2*3+1", "3*2+1", "ring7"} <= set(r.candidates)
+    assert planner.validate_shape(7, r.shape) == "" and r.predicted_us > 0
+    r = replan_after_failure(6, [0, 5], 1024)
+    assert r.world == 4 and r.algo in ("oneshot", "staged")
