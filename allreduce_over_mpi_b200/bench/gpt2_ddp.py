@@ -30,8 +30,8 @@ def run(impl: str, a, rank: int, world: int, dev, comm) -> dict:
     torch.manual_seed(1234)
     cfg = GPT2Config.small() if not a.tiny else GPT2Config.tiny()
     model = GPT2(cfg).to(dev).to(torch.bfloat16)
+    comm.free_all()   # every implementation starts from an empty symmetric heap
     if impl == "flextree":
-        comm.free_all()
         ddp = FlexTreeDDP(model, comm, bucket_bytes=a.bucket_mb << 20)
         fwd, zero = ddp, ddp.zero_grad
     else:
@@ -107,7 +107,7 @@ def main(argv=None):
     a = ap.parse_args(argv)
     rank, world, local = init_dist()
     dev = torch.device("cuda", local)
-    comm = FlexTreeComm(heap_bytes=512 << 20, staging_bytes=64 << 20)
+    comm = FlexTreeComm(heap_bytes=1 << 30, staging_bytes=64 << 20)
     if a.lanes:
         comm.set_max_lanes(a.lanes)
     rows = []

@@ -136,10 +136,27 @@ class FlexTreeDDP(nn.Module):
 
 # ---- torch DDP communication hook ----------------------------------------------------------
 class HookState:
-    def __init__(self, comm, shape=None, algo: str = "auto"):
-        self.comm, self.shape, self.algo = comm, shape, algo
+    """State of :func:`flextree_allreduce_hook`.  With ``mirror=True`` (default) every DDP bucket gets
+    a twin in the symmetric heap: the bucket is copied there, reduced in place with the fastest
+    algorithm for heap tensors (NVLS where available) and copied back - two local copies at HBM
+    speed instead of a slower all-reduce through the staging slots."""
+
+    def __init__(self, comm, shape=None, algo: str = "auto", mirror: bool = True):
+        self.comm, self.shape, self.algo, self.mirror = comm, shape, algo, mirror
         self.stream = torch.cuda.Stream(device=comm.device)
         self.calls = 0
+        self.twins: dict = {}
+
+    def twin(self, bucket, buf: torch.Tensor):
+        key = (bucket.index(), buf.numel(), buf.dtype)
+        t = self.twins.get(key)
+        if t is None:
+            try:
+                t = self.comm.alloc(buf.numel(), buf.dtype)
+            except MemoryError:
+                t = False   # heap exhausted: this bucket goes through the staging slots
+            self.twins[key] = t
+        return t
 
 
 def flextree_allreduce_hook(state, bucket):
@@ -150,7 +167,13 @@ def flextree_allreduce_hook(state, bucket):
     state.calls += 1
     state.stream.wait_stream(torch.cuda.current_stream(dev))
     with torch.cuda.stream(state.stream):
-        state.comm.all_reduce(buf, op="avg", shape=state.shape, algo=state.algo)
+        twin = state.twin(bucket, buf) if state.mirror else False
+        if twin is not False:
+            twin.copy_(buf)
+            state.comm.all_reduce(twin, op="avg", shape=state.shape, algo=state.algo)
+            buf.copy_(twin)
+        else:
+            state.comm.all_reduce(buf, op="avg", shape=state.shape, algo=state.algo)
         fut: torch.futures.Future = torch.futures.Future(devices=[dev])
         fut.set_result(buf)
     return fut
