@@ -439,14 +439,14 @@ int ft_comm_destroy(ft_comm* c) {
   cudaSetDevice(c->device);
   cudaDeviceSynchronize();
   Driver& d = driver();
-  if (c->mc_bound || c->mc_joined || c->mc_have) {
+  if (d.ok && (c->mc_bound || c->mc_joined || c->mc_have)) {
     if (c->mc_va) { d.p_cuMemUnmap(c->mc_va, c->total_bytes); d.p_cuMemAddressFree(c->mc_va, c->total_bytes); }
     if (c->mc_bound && d.p_cuMulticastUnbind) d.p_cuMulticastUnbind(c->mc_handle, c->device, 0, c->total_bytes);
     if (c->mc_handle) d.p_cuMemRelease(c->mc_handle);
   }
   for (int r = 0; r < c->world; ++r) {
     if (r == c->rank || !c->peer_base[r]) continue;
-    if (c->peer_is_vmm[r]) {
+    if (c->peer_is_vmm[r] && d.ok) {
       d.p_cuMemUnmap((CUdeviceptr)c->peer_base[r], c->total_bytes);
       d.p_cuMemAddressFree((CUdeviceptr)c->peer_base[r], c->total_bytes);
       d.p_cuMemRelease(c->peer_handle[r]);
@@ -454,7 +454,7 @@ int ft_comm_destroy(ft_comm* c) {
       cudaIpcCloseMemHandle(c->peer_base[r]);
     }
   }
-  if (c->mem_kind == FT_MEM_VMM && c->va) {
+  if (c->mem_kind == FT_MEM_VMM && c->va && d.ok) {
     d.p_cuMemUnmap(c->va, c->total_bytes);
     d.p_cuMemAddressFree(c->va, c->total_bytes);
     d.p_cuMemRelease(c->handle);

@@ -254,7 +254,7 @@ class _CommBase:
 
     def __del__(self):
         try:
-            self.close()
+            self.close(False) if isinstance(self, FlexTreeComm) else self.close()
         except Exception:
             pass
 
@@ -374,7 +374,18 @@ class FlexTreeComm(_CommBase):
             log.warn("multicast bind failed: " + L.ft_comm_last_error(self._h).decode(), rank)
         return agree(ok)
 
-    def close(self):
+    def close(self, collective: bool = True):
+        """Collective by default: every rank drains its GPU and meets the others before any memory is
+        unmapped, so no peer kernel can still be reading (or multicasting into) a heap that goes away.
+        (Garbage collection calls it with collective=False: ranks are not collected in step.)"""
+        if self._h and collective:
+            try:
+                import torch.distributed as dist
+                torch.cuda.synchronize(self.device)
+                if dist.is_initialized():
+                    dist.barrier(group=self.group)
+            except Exception as e:  # noqa: BLE001 - e.g. the process group is already gone at interpreter exit
+                log.debug(f"close(): no rendezvous before teardown ({e})", self.rank)
         sock = getattr(self, "_sock", -1)
         if sock is not None and sock >= 0:
             lib().ft_fd_close(sock)
