@@ -34,7 +34,8 @@ class FlexTreeError(RuntimeError):
 class V1Params(C.Structure):
     _fields_ = [("launch_us", C.c_double), ("sync_us", C.c_double), ("link_gbs", C.c_double),
                 ("hbm_gbs", C.c_double), ("stage_floor_us", C.c_double), ("nvls_gbs", C.c_double),
-                ("oneshot_max_bytes", C.c_double), ("peer_eff", C.c_double * (FT_MAX_RANKS + 1))]
+                ("oneshot_max_bytes", C.c_double), ("ll_us", C.c_double), ("ll_max_bytes", C.c_double),
+                ("push_gain", C.c_double), ("peer_eff", C.c_double * (FT_MAX_RANKS + 1))]
 
 
 _lib = None

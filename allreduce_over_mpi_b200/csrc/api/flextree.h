@@ -40,13 +40,14 @@ int ft_choose_v0(int n, double chunk, int* widths, int cap, double* cost, uint64
 
 typedef struct ft_v1_params {
   double launch_us, sync_us, link_gbs, hbm_gbs, stage_floor_us, nvls_gbs, oneshot_max_bytes;
+  double ll_us, ll_max_bytes, push_gain;
   double peer_eff[FT_MAX_RANKS + 1];
 } ft_v1_params;
 void ft_v1_defaults(ft_v1_params* p);
 double ft_cost_v1(int world, const int* widths, int nw, int lonely, int ring, uint64_t bytes, const ft_v1_params* p);
 double ft_cost_v1_oneshot(int world, uint64_t bytes, const ft_v1_params* p);
 double ft_cost_v1_nvls(int world, uint64_t bytes, const ft_v1_params* p);
-/* writes the winning shape; algo_out receives "staged", "oneshot" or "nvls" */
+/* writes the winning shape; algo_out receives "staged", "oneshot", "nvls", "ll" or "push" */
 int ft_pick_algorithm(int world, uint64_t bytes, const ft_v1_params* p, int allow_oneshot, int allow_nvls,
                       int* widths, int cap, int* lonely, int* ring, char* algo_out, size_t algo_cap, double* us);
 /* every executable shape for `world`, one per line ("2*4", "2*2+1", "ring8") */

@@ -49,6 +49,7 @@ ft::V1Params to_params(const ft_v1_params* p) {
   if (!p) return k;
   k.launch_us = p->launch_us; k.sync_us = p->sync_us; k.link_gbs = p->link_gbs; k.hbm_gbs = p->hbm_gbs;
   k.stage_floor_us = p->stage_floor_us; k.nvls_gbs = p->nvls_gbs; k.oneshot_max_bytes = p->oneshot_max_bytes;
+  k.ll_us = p->ll_us; k.ll_max_bytes = p->ll_max_bytes; k.push_gain = p->push_gain;
   k.peer_eff.assign(p->peer_eff, p->peer_eff + FT_MAX_RANKS + 1);
   return k;
 }
@@ -96,6 +97,7 @@ void ft_v1_defaults(ft_v1_params* p) {
   ft::V1Params k;
   p->launch_us = k.launch_us; p->sync_us = k.sync_us; p->link_gbs = k.link_gbs; p->hbm_gbs = k.hbm_gbs;
   p->stage_floor_us = k.stage_floor_us; p->nvls_gbs = k.nvls_gbs; p->oneshot_max_bytes = k.oneshot_max_bytes;
+  p->ll_us = k.ll_us; p->ll_max_bytes = k.ll_max_bytes; p->push_gain = k.push_gain;
   for (int i = 0; i <= FT_MAX_RANKS; ++i) p->peer_eff[i] = 1.0;
 }
 double ft_cost_v1(int world, const int* widths, int nw, int lonely, int ring, uint64_t bytes, const ft_v1_params* p) {

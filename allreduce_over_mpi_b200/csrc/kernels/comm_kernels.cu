@@ -481,38 +481,33 @@ __device__ __forceinline__ void multimem_st(void* p, uint4 v) {
 }
 
 // Reduce `nvec` 16-byte vectors at multicast address `mc` inside the switch and broadcast the
-// result to every rank.  The in-switch loads of the next step are issued before the stores of
-// the current one: a thread always has kU reductions in flight.
+// result to every rank: kU in-switch reductions per thread, then their kU broadcasts.  Issuing
+// the next step's reductions before the current stores (as the peer-load loops do) was measured
+// 4 % SLOWER at 64 MiB and above on 4 and 8 GPUs, as was a second CTA per SM: the switch, not
+// the number of requests in flight, is the limit.
 template <int POL>
 __device__ __forceinline__ void nvls_reduce_broadcast(unsigned char* mc, uint64_t nvec, float scale) {
   using P = typename PolById<POL>::type;
   constexpr int kU = 4;
-  const uint64_t step = (uint64_t)blockDim.x * kU;
-  uint4 cur[kU], nxt[kU];
-  auto issue = [&](uint64_t base, uint4 (&buf)[kU]) {
+  for (uint64_t base = 0; base < nvec; base += (uint64_t)blockDim.x * kU) {
+    uint4 v[kU];
+    uint64_t idx[kU];
 #pragma unroll
     for (int u = 0; u < kU; ++u) {
-      const uint64_t i = base + (uint64_t)u * blockDim.x + threadIdx.x;
-      buf[u] = i < nvec ? Nvls<POL>::ld(mc + i * 16) : make_uint4(0, 0, 0, 0);
+      idx[u] = base + (uint64_t)u * blockDim.x + threadIdx.x;
+      v[u] = idx[u] < nvec ? Nvls<POL>::ld(mc + idx[u] * 16) : make_uint4(0, 0, 0, 0);
     }
-  };
-  issue(0, cur);
-  for (uint64_t base = 0; base < nvec; base += step) {
-    if (base + step < nvec) issue(base + step, nxt);
+    if (scale != 1.0f) {
 #pragma unroll
-    for (int u = 0; u < kU; ++u) {
-      const uint64_t i = base + (uint64_t)u * blockDim.x + threadIdx.x;
-      if (i >= nvec) continue;
-      uint4 v = cur[u];
-      if (scale != 1.0f) {
+      for (int u = 0; u < kU; ++u) {
         typename P::Acc t;
-        P::init(t, v);
-        v = P::fins(t, scale);
+        P::init(t, v[u]);
+        v[u] = P::fins(t, scale);
       }
-      multimem_st(mc + i * 16, v);
     }
 #pragma unroll
-    for (int u = 0; u < kU; ++u) cur[u] = nxt[u];
+    for (int u = 0; u < kU; ++u)
+      if (idx[u] < nvec) multimem_st(mc + idx[u] * 16, v[u]);
   }
 }
 

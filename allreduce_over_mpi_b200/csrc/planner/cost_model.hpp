@@ -81,6 +81,9 @@ struct V1Params {
   double stage_floor_us = 0.5; // fixed cost per stage besides the rendezvous
   double nvls_gbs = 0.0;       // in-switch reduce/broadcast bandwidth per GPU; 0 = not available
   double oneshot_max_bytes = 1 << 20;
+  double ll_us = 0.0;          // fixed cost of the low-latency push protocol; 0 = not available
+  double ll_max_bytes = 256 << 10;
+  double push_gain = 0.0;      // > 0: the reduce+push kernel exists; link efficiency of its write half relative to reads
   // link efficiency when a stage pulls from k distinct peers at once (index k, 0 unused)
   std::vector<double> peer_eff = std::vector<double>(FT_MAX_RANKS + 1, 1.0);
 };
@@ -124,6 +127,19 @@ inline double cost_v1_nvls(int world, uint64_t bytes, const V1Params& k) {
   return k.launch_us + 3 * k.sync_us + (double)bytes * (1.0 + 1.0 / world) / k.nvls_gbs * 1e-3;
 }
 
+// Low-latency push: no rendezvous; every rank writes 2x its payload (data + tags) to each of N-1 peers.
+inline double cost_v1_ll(int world, uint64_t bytes, const V1Params& k) {
+  if (k.ll_us <= 0 || (double)bytes > k.ll_max_bytes) return std::numeric_limits<double>::infinity();
+  return k.ll_us + 2.0 * (double)bytes * (world - 1) / k.link_gbs * 1e-3;
+}
+// Flat reduce + push: two rendezvous; (N-1)/N*S in by reads and the same again by posted writes.
+inline double cost_v1_push(int world, uint64_t bytes, const V1Params& k) {
+  if (k.push_gain <= 0 || world < 2) return std::numeric_limits<double>::infinity();
+  const double eff = k.peer_eff[std::min<int>(world - 1, (int)k.peer_eff.size() - 1)];
+  const double half = (double)bytes * (world - 1) / world;
+  return k.launch_us + 2 * k.sync_us + (half / (k.link_gbs * eff) + half / (k.link_gbs * eff * k.push_gain)) * 1e-3;
+}
+
 // Shapes that can be executed for `world`: flat, every ordered factorisation with >= 2
 // levels, the ring, and every schedulable lonely layout.
 inline std::vector<Shape> executable_shapes(int world, int max_lonely = 4) {
@@ -144,11 +160,12 @@ inline std::vector<Shape> executable_shapes(int world, int max_lonely = 4) {
 }
 
 struct V1Choice {
-  std::string algo;  // "staged", "oneshot", "nvls"
+  std::string algo;  // "staged", "oneshot", "nvls", "ll", "push"
   Shape shape;
   double us = std::numeric_limits<double>::infinity();
 };
 
+// allow_nvls also stands for "the tensor lives in the symmetric heap": NVLS and reduce+push work in place only.
 inline V1Choice pick_algorithm(int world, uint64_t bytes, const V1Params& k, bool allow_oneshot = true,
                                bool allow_nvls = true) {
   V1Choice best;
@@ -164,6 +181,12 @@ inline V1Choice pick_algorithm(int world, uint64_t bytes, const V1Params& k, boo
   if (allow_nvls) {
     double c = cost_v1_nvls(world, bytes, k);
     if (c < best.us) { best.us = c; best.shape = Shape::flat(world); best.algo = "nvls"; }
+    c = cost_v1_push(world, bytes, k);
+    if (c < best.us) { best.us = c; best.shape = Shape::flat(world); best.algo = "push"; }
+  }
+  if (allow_oneshot) {
+    double c = cost_v1_ll(world, bytes, k);
+    if (c < best.us) { best.us = c; best.shape = Shape::flat(world); best.algo = "ll"; }
   }
   return best;
 }

@@ -123,12 +123,16 @@ class CostParams:
     stage_floor_us: float = 0.5
     nvls_gbs: float = 0.0
     oneshot_max_bytes: float = float(1 << 20)
+    ll_us: float = 0.0            # fixed cost of the low-latency push protocol (0: not available)
+    ll_max_bytes: float = float(256 << 10)
+    push_gain: float = 0.0        # > 0: reduce+push kernel available; efficiency of posted writes relative to reads
     peer_eff: dict[int, float] = field(default_factory=dict)
 
     def to_c(self) -> V1Params:
         p = V1Params()
         lib().ft_v1_defaults(C.byref(p))
-        for k in ("launch_us", "sync_us", "link_gbs", "hbm_gbs", "stage_floor_us", "nvls_gbs", "oneshot_max_bytes"):
+        for k in ("launch_us", "sync_us", "link_gbs", "hbm_gbs", "stage_floor_us", "nvls_gbs", "oneshot_max_bytes", "ll_us",
+                  "ll_max_bytes", "push_gain"):
             setattr(p, k, float(getattr(self, k)))
         for k, v in self.peer_eff.items():
             p.peer_eff[int(k)] = float(v)

@@ -118,6 +118,19 @@ def fit_params(rows) -> tuple[CostParams, list]:
     if nv:
         w, b, us = max(nv, key=lambda t: t[1])
         p.nvls_gbs = b * (1 + 1 / w) / (max(us - p.launch_us - 3 * p.sync_us, 1e-3) * 1e-6) / 1e9
+    # low-latency protocol: its fixed cost is the fastest time at the smallest size
+    ll = [r["ms"] * 1e3 for r in rows if (split_impl(r["impl"]) or ("", ""))[0] == "ll" and r["bytes"] <= 4096]
+    if ll:
+        p.ll_us = min(ll)
+    # reduce+push: how much faster its write half runs than the read half, from the largest size
+    pu = [(r["world"], r["bytes"], r["ms"] * 1e3) for r in rows if (split_impl(r["impl"]) or ("", ""))[0] == "push"]
+    if pu:
+        w, b, us = max(pu, key=lambda t: t[1])
+        half = b * (w - 1) / w
+        eff = p.peer_eff.get(w - 1, 1.0)
+        t_read = half / (p.link_gbs * eff) * 1e-3
+        t_write = max(us - p.launch_us - 2 * p.sync_us - t_read, 1e-3)
+        p.push_gain = round(max(0.5, min(2.0, t_read / t_write)), 3)
     # one-shot limit: largest size at which one-shot still beats every staged shape
     os_rows = defaultdict(dict)
     for r in rows:
