@@ -56,7 +56,8 @@ __device__ __forceinline__ unsigned long long begin_call(const CommDev& c, unsig
 template <class P>
 __device__ __forceinline__ void pull_range(const unsigned char* const* ptrs, int n, unsigned char* dst_work,
                                            unsigned char* dst_user, bool user_vec_ok, uint64_t total_bytes,
-                                           uint32_t es, bool do_scale, float scale) {
+                                           uint32_t es, bool do_scale, float scale,
+                                           unsigned char* const* push_dsts = nullptr, int n_push = 0) {
   const uint64_t nvec = (total_bytes + 15) / 16;
   const uint64_t step = (uint64_t)blockDim.x * kUnroll;
   const unsigned char* s0 = ptrs[0];
@@ -128,6 +129,10 @@ __device__ __forceinline__ void pull_range(const unsigned char* const* ptrs, int
       if (dst_user) {
         if (valid == 16 && user_vec_ok) st_vec(dst_user + off, out);
         else st_partial(dst_user + off, out, valid, es);
+      }
+      for (int q = 0; q < n_push; ++q) {   // posted writes of the result into other ranks' buffers
+        if (valid == 16) st_vec(push_dsts[q] + off, out);
+        else st_partial(push_dsts[q] + off, out, valid, es);
       }
     }
   }
@@ -669,61 +674,10 @@ __global__ void __launch_bounds__(kThreads, 1) push_allreduce_kernel(const __gri
   } else {
     __syncthreads();
   }
-  const int n = c.world;
-  const uint64_t nvec = (sl.bytes + 15) / 16;
-  const uint64_t step = (uint64_t)blockDim.x * kUnroll;
-  for (uint64_t base = 0; base < nvec; base += step) {
-    uint64_t idx[kUnroll];
-    bool ok[kUnroll];
-    typename P::Acc acc[kUnroll];
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      idx[u] = base + (uint64_t)u * blockDim.x + threadIdx.x;
-      ok[u] = idx[u] < nvec;
-    }
-    {
-      uint4 v[kUnroll];
-      const unsigned char* p0 = bufs[0];
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) v[u] = ok[u] ? ld_stream(p0 + idx[u] * 16) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) P::init(acc[u], v[u]);
-    }
-    int k = 1;
-    for (; k + 2 <= n; k += 2) {
-      uint4 v[2][kUnroll];
-      const unsigned char* pa = bufs[k];
-      const unsigned char* pb = bufs[k + 1];
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) v[0][u] = ok[u] ? ld_stream(pa + idx[u] * 16) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) v[1][u] = ok[u] ? ld_stream(pb + idx[u] * 16) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) { P::add(acc[u], v[0][u]); P::add(acc[u], v[1][u]); }
-    }
-    if (k < n) {
-      uint4 v[kUnroll];
-      const unsigned char* pa = bufs[k];
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) v[u] = ok[u] ? ld_stream(pa + idx[u] * 16) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) P::add(acc[u], v[u]);
-    }
-    uint4 out[kUnroll];
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) out[u] = a.scale != 1.0f ? P::fins(acc[u], a.scale) : P::fin(acc[u]);
-    for (int q = 0; q < n; ++q) {   // posted writes to every rank, mine first
-      unsigned char* d = bufs[q];
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        if (!ok[u]) continue;
-        const uint64_t off = idx[u] * 16;
-        const uint32_t valid = (uint32_t)(sl.bytes - off < 16 ? sl.bytes - off : 16);
-        if (valid == 16) st_vec(d + off, out[u]);
-        else st_partial(d + off, out[u], valid, es);
-      }
-    }
-  }
+  // sources: mine first, then the peers in rotated order; destinations: mine (dst_work) and every peer's
+  if (sl.bytes)
+    pull_range<P>((const unsigned char* const*)bufs, c.world, bufs[0], nullptr, true, sl.bytes, es, a.scale != 1.0f, a.scale,
+                  bufs + 1, c.world - 1);
   if (do_sync) {
     __threadfence_system();   // my stores into the peers' buffers are ordered before my signal
     lane_rendezvous(sync, all, call * kCallStride + 2, 1);

@@ -1,6 +1,6 @@
 """Calibration of the NVSwitch cost model from measured all-reduce sweeps.
 
-    python -m allreduce_over_mpi_b200.parallel.tune gpurun_out/ar8.jsonl gpurun_out/ar4.jsonl ... \
+    python -m allreduce_over_mpi_b200.parallel.tune sweep_8gpu.jsonl sweep_4gpu.jsonl ... \
         --out allreduce_over_mpi_b200/parallel/calibration_b200.json
 
 Input: JSON lines written by ``bench/allreduce.py`` (one per size x implementation).

@@ -1,8 +1,8 @@
 """Build the UNMODIFIED reference (DictXiong/AllReduce-Over-MPI) for the benchmark's reference arm.
 
-The reference is C++/CUDA with no Python packaging, so the prescribed
-``pip install --target baseline/_ref /root/reference`` cannot work ("neither setup.py nor
-pyproject.toml found"); its outcome is recorded in baseline/_ref/INSTALL_LOG.txt.  Instead the
+The reference is C++/CUDA with no Python packaging, so ``pip install --target baseline/_ref
+<reference checkout>`` cannot work ("neither setup.py nor pyproject.toml found"); its outcome is
+recorded in baseline/_ref/INSTALL_LOG.txt.  The checkout is taken from $FT_REFERENCE_SRC.  Instead the
 sources are copied verbatim to baseline/_ref/src and compiled as they are:
 
   * baseline/_ref/ref_nway       nvcc, sm_100a: ref_nway_driver.cu + the reference's
@@ -22,7 +22,7 @@ import sys
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-REF = Path(os.environ.get("FT_REFERENCE_SRC", "/root/reference"))
+REF = Path(os.environ.get("FT_REFERENCE_SRC", str(Path.home() / "reference")))
 OUT = HERE / "_ref"
 
 
