@@ -44,4 +44,4 @@ def test_replan_after_failure_uses_lonely_layouts():
     assert {"7", "2*3+1", "3*2+1", "ring7"} <= set(r.candidates)
     assert planner.validate_shape(7, r.shape) == "" and r.predicted_us > 0
     r = replan_after_failure(6, [0, 5], 1024)
-    assert r.world == 4 and r.algo in ("oneshot", "staged")
+    assert r.world == 4 and r.algo in ("oneshot", "staged", "ll")
