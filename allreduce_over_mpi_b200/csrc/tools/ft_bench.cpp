@@ -1,13 +1,15 @@
 // Standalone all-reduce benchmark with the reference driver's command line
 // (allreduce_over_mpi/benchmark.cpp:69-122):
 //
-//     ft_bench [--size N] [--repeat R] [--to-file] [--comm-type flextree|threads] [--tag T]
+//     ft_bench [--size N] [--repeat R] [--to-file] [--comm-type flextree|threads|nccl] [--tag T]
 //              [--version] [--check] [--gpus G | --ranks G] [--dtype float|bf16]
 //
 //   --size       elements per rank (default 35, like the reference)
 //   --repeat     number of timed all-reduces (data is NOT re-initialised between repeats)
 //   --comm-type  flextree = GPU ranks over NVLink peer memory, one host thread per GPU in this
-//                process; threads = CPU ranks (thread world, host memory)
+//                process; threads = CPU ranks (thread world, host memory); nccl = the vendor
+//                library's own all-reduce on the same GPUs (the comparison arm, like the reference's
+//                "--comm-type mpi"); libnccl is opened at run time, nothing links against it
 //   --to-file    write one time per line to "<tag.>N.len.<w0-w1-+L>.ar_test.<epoch>.txt"
 //   --check      closed-form check: data[i] = i*0.1 on every rank, so after R in-place sums every
 //                rank must hold i*0.1*N^R (two-sided, relative tolerance)
@@ -15,6 +17,7 @@
 // GPU times are CUDA-event intervals, reported as the maximum over ranks; CPU times are
 // steady-clock intervals on rank 0 like the reference's MPI_Wtime.
 #include <cuda_runtime.h>
+#include <dlfcn.h>
 
 #include <atomic>
 #include <cmath>
@@ -50,6 +53,29 @@ struct SpinBarrier {
   }
 };
 
+// The five NCCL entry points the comparison arm needs, resolved from libnccl.so.2 at run time.
+struct Nccl {
+  typedef void* comm_t;
+  int (*CommInitAll)(comm_t*, int, const int*) = nullptr;
+  int (*AllReduce)(const void*, void*, size_t, int, int, comm_t, cudaStream_t) = nullptr;
+  int (*GroupStart)() = nullptr;
+  int (*GroupEnd)() = nullptr;
+  int (*CommDestroy)(comm_t) = nullptr;
+  bool load() {
+    void* h = nullptr;
+    for (const char* name : {"libnccl.so.2", "libnccl.so"})
+      if ((h = dlopen(name, RTLD_NOW | RTLD_GLOBAL))) break;
+    if (!h) return false;
+    CommInitAll = (decltype(CommInitAll))dlsym(h, "ncclCommInitAll");
+    AllReduce = (decltype(AllReduce))dlsym(h, "ncclAllReduce");
+    GroupStart = (decltype(GroupStart))dlsym(h, "ncclGroupStart");
+    GroupEnd = (decltype(GroupEnd))dlsym(h, "ncclGroupEnd");
+    CommDestroy = (decltype(CommDestroy))dlsym(h, "ncclCommDestroy");
+    return CommInitAll && AllReduce && GroupStart && GroupEnd && CommDestroy;
+  }
+};
+constexpr int kNcclFloat32 = 7, kNcclBfloat16 = 9, kNcclSum = 0;   // ncclDataType_t / ncclRedOp_t values
+
 unsigned short f2bf(float f) {
   unsigned u;
   memcpy(&u, &f, 4);
@@ -80,8 +106,11 @@ int main(int argc, char** argv) {
     else if (a == "--version") { printf("FlexTree Standalone Benchmark\nversion: %s\n", ft_version()); return 0; }
     else { fprintf(stderr, "unknown parameter: %s\n", a.c_str()); return 1; }
   }
-  const bool gpu = o.comm == "flextree";
+  const bool use_nccl = o.comm == "nccl";
+  const bool gpu = o.comm == "flextree" || use_nccl;
   if (!gpu && o.comm != "threads") { fprintf(stderr, "unknown comm type: %s\n", o.comm.c_str()); return 1; }
+  Nccl nccl;
+  if (use_nccl && !nccl.load()) { fprintf(stderr, "libnccl.so.2 not found or incomplete\n"); return 1; }
   int world = o.ranks;
   if (gpu) {
     int ndev = 0;
@@ -105,7 +134,12 @@ int main(int argc, char** argv) {
   SpinBarrier bar(world);
   std::vector<ft_comm*> comms(world, nullptr);
   ft_cpu_world* cpu_world = nullptr;
-  if (gpu) {
+  std::vector<Nccl::comm_t> ncomms(world, nullptr);
+  if (use_nccl) {
+    std::vector<int> devs(world);
+    for (int r = 0; r < world; ++r) devs[r] = r;
+    if (nccl.CommInitAll(ncomms.data(), world, devs.data()) != 0) { fprintf(stderr, "ncclCommInitAll failed\n"); return 1; }
+  } else if (gpu) {
     const size_t heap = ((o.size * es + (1 << 20)) + 255) / 256 * 256;
     for (int r = 0; r < world; ++r) {
       cudaSetDevice(r);
@@ -129,15 +163,21 @@ int main(int argc, char** argv) {
       cudaSetDevice(r);
       cudaStream_t st;
       cudaStreamCreate(&st);
-      void* dev = ft_comm_alloc(comms[r], o.size * es);
+      void* dev = nullptr;
+      if (use_nccl) cudaMalloc(&dev, o.size * es);
+      else dev = ft_comm_alloc(comms[r], o.size * es);
       cudaMemcpy(dev, hostp, o.size * es, cudaMemcpyHostToDevice);
-      FT_Comm mc = ft_mpi_from_comm(comms[r], st);
+      FT_Comm mc = use_nccl ? nullptr : ft_mpi_from_comm(comms[r], st);
       cudaEvent_t a, b;
       cudaEventCreate(&a); cudaEventCreate(&b);
       for (int i = 0; i < o.repeat; ++i) {
         bar.wait();
         cudaEventRecord(a, st);
-        if (MPI_Allreduce_FT_c(FT_IN_PLACE, dev, o.size, dtype, FT_OP_SUM, mc) != 0) bad[r] = 2;
+        if (use_nccl) {
+          if (nccl.AllReduce(dev, dev, o.size, o.bf16 ? kNcclBfloat16 : kNcclFloat32, kNcclSum, ncomms[r], st) != 0) bad[r] = 2;
+        } else if (MPI_Allreduce_FT_c(FT_IN_PLACE, dev, o.size, dtype, FT_OP_SUM, mc) != 0) {
+          bad[r] = 2;
+        }
         cudaEventRecord(b, st);
         cudaEventSynchronize(b);
         float ms = 0;
@@ -145,9 +185,10 @@ int main(int argc, char** argv) {
         times[r][i] = ms * 1e-3;
       }
       int status[5];
-      if (ft_comm_status(comms[r], status) != FT_OK) bad[r] = 3;
+      if (!use_nccl && ft_comm_status(comms[r], status) != FT_OK) bad[r] = 3;
       cudaMemcpy(hostp, dev, o.size * es, cudaMemcpyDeviceToHost);
-      ft_mpi_comm_free(mc);
+      if (use_nccl) cudaFree(dev);
+      else ft_mpi_comm_free(mc);
       cudaStreamDestroy(st);
     } else {
       FT_Comm mc = ft_mpi_thread_rank(cpu_world, r);
@@ -200,7 +241,8 @@ int main(int argc, char** argv) {
   const double bytes = (double)o.size * es;
   printf("DONE, average time: %g, min time: %g  (busbw at min: %.2f GB/s)\n", sum / o.repeat, mn,
          bytes / mn / 1e9 * 2.0 * (world - 1) / world);
-  for (auto* c : comms) ft_comm_destroy(c);
+  for (auto c : ncomms) if (c) nccl.CommDestroy(c);
+  for (auto* c : comms) if (c) ft_comm_destroy(c);
   if (cpu_world) ft_cpu_world_destroy(cpu_world);
   return failed ? 2 : 0;
 }
