@@ -77,6 +77,7 @@ class _CommBase:
         self._choices: dict = {}
         self.ll_auto_max = int(os.environ.get("FT_LL_MAX_BYTES", 8 << 10))
         self._heap_range = None
+        self._poisoned = False
         self._nvtx = os.environ.get("FT_NVTX", "0") == "1"   # NVTX range around every call (for timeline tools)
 
     # -- errors
@@ -178,6 +179,9 @@ class _CommBase:
         split when larger than one slot)."""
         if not tensor.is_cuda or not tensor.is_contiguous():
             raise ValueError("all_reduce needs a contiguous CUDA tensor")
+        if self._poisoned:
+            raise FlexTreeError(5, "a device-side wait timed out earlier: the ranks' call counters no longer agree, "
+                                   "rebuild the communicator (see parallel/elastic.py for a smaller world)")
         if op == "avg":
             op, scale = "sum", scale / self.world
         dst = tensor if out is None else out
@@ -240,6 +244,7 @@ class _CommBase:
         s = self.status()
         if s["code"]:
             lib().ft_comm_clear_status(self._h)
+            self._poisoned = self.world > 1
             raise FlexTreeError(s["code"], f"rank {self.rank}: wait on rank {s['peer']} at rendezvous {s['rendezvous']} (lane {s['lane']})")
 
     def wait_probe(self, peer: int, timeout_ms: float = 1.0):

@@ -105,5 +105,10 @@ def _mpi(a, world: int, rank: int) -> dict:
                               "FT_TOPO": topo, "FT_LONELY": os.environ.get("FT_LONELY", "0")},
                    "gpu_launches": 0}
     dist.barrier()
+    if rank == 0:   # a run that died before MPI_Finalize leaves its shared segment behind
+        try:
+            os.unlink(f"/dev/shm/ftshim-{session}")
+        except OSError:
+            pass
     dist.destroy_process_group()
     return out
