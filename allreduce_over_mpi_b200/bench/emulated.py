@@ -29,17 +29,18 @@ def main(argv=None):
     ap.add_argument("--bytes", type=int, default=256 << 20)
     ap.add_argument("--dtype", default="float32")
     ap.add_argument("--shape", default=None)
-    ap.add_argument("--algo", default="staged", choices=["staged", "oneshot", "ll"])
+    ap.add_argument("--algo", default="staged", choices=["staged", "oneshot", "ll", "push"])
     ap.add_argument("--iters", type=int, default=3)
     a = ap.parse_args(argv)
     dtype = getattr(torch, a.dtype)
     es = torch.empty((), dtype=dtype).element_size()
     count = a.bytes // es
     shape = Shape.parse(a.shape) if a.shape else Shape.flat(a.world)
-    heap = a.bytes + (1 << 20) if a.algo == "staged" else 1 << 20
-    w = LocalWorld(a.world, heap_bytes=heap, staging_bytes=max(a.bytes, 1 << 20) if a.algo != "staged" else 1 << 20)
+    in_heap = a.algo in ("staged", "push")
+    heap = a.bytes + (1 << 20) if in_heap else 1 << 20
+    w = LocalWorld(a.world, heap_bytes=heap, staging_bytes=max(a.bytes, 1 << 20) if not in_heap else 1 << 20)
     g = torch.Generator(device="cuda").manual_seed(7)
-    if a.algo == "staged":
+    if in_heap:
         bufs = [c.alloc(count, dtype) for c in w.ranks]
     else:
         bufs = [torch.empty(count, dtype=dtype, device="cuda") for _ in range(a.world)]
