@@ -56,3 +56,19 @@ def test_ft_bench_thread_world_check_and_file(tmp_path):
     assert rc == 0 and "FlexTree Standalone Benchmark" in out
     rc, _, err = run([exe, "--bogus"])
     assert rc == 1 and "unknown parameter" in err
+
+
+def test_mpi_style_example_builds_and_runs(tmp_path):
+    """A program that spells the call MPI_Allreduce compiles against flextree_mpi.h and reduces correctly."""
+    import shutil
+    if shutil.which("g++") is None:
+        pytest.skip("no g++")
+    root = BIN.parent.parent
+    exe = tmp_path / "mpi_style"
+    r = subprocess.run(["g++", "-std=c++17", "-I", str(BIN.parent / "csrc"), str(root / "examples" / "mpi_style.cpp"), "-L", str(BIN),
+                        "-lflextree", f"-Wl,-rpath,{BIN}", "-lpthread", "-o", str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-2000:]
+    rc, out, err = run([str(exe), "7"], env={"FT_TOPO": "2,3", "FT_LONELY": "1"})
+    assert rc == 0 and "7 ranks, every element = 28 (expected 28): ok" in out, (out, err)
+    rc, out, err = run([str(exe), "4"], env={"FT_TOPO": "3,2"})
+    assert rc == 1 and "invalid FT_TOPO" in err
