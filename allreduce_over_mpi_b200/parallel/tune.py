@@ -156,11 +156,14 @@ def main(argv=None):
     ap.add_argument("sweeps", nargs="+")
     ap.add_argument("--out", default=planner.calibration_path())
     ap.add_argument("--dtype", default=None, help="only rows of this dtype (default: all)")
+    ap.add_argument("--hbm-gbs", type=float, default=None, help="measured local copy bandwidth (read+write GB/s) for the model's HBM term")
     a = ap.parse_args(argv)
     rows = parse_rows(a.sweeps)
     if a.dtype:
         rows = [r for r in rows if r.get("dtype") == a.dtype]
     params, fit = fit_params(rows)
+    if a.hbm_gbs:
+        params.hbm_gbs = a.hbm_gbs
     table = best_table(rows)
     errs = [abs(f["rel_err"]) for f in fit]
     doc = {"params": json.loads(params.to_json()), "table": table,
