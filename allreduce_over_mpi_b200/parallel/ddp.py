@@ -17,6 +17,7 @@ a training step.
 """
 from __future__ import annotations
 
+import contextlib
 from dataclasses import dataclass, field
 from typing import Iterable, Sequence
 
@@ -67,6 +68,7 @@ class FlexTreeDDP(nn.Module):
         on_gpu = torch.cuda.is_available() and getattr(comm, "device", torch.device("cpu")).type == "cuda"
         self.stream = stream or (torch.cuda.Stream(device=comm.device) if on_gpu else None)
         self._callback_queued = False
+        self._sync = True
         self.launched = 0
         for b in self.buckets:
             b.flat = comm.alloc(b.numel, b.dtype)
@@ -94,6 +96,16 @@ class FlexTreeDDP(nn.Module):
     def forward(self, *args, **kwargs):
         return self.module(*args, **kwargs)
 
+    @contextlib.contextmanager
+    def no_sync(self):
+        """Backward passes inside this context only accumulate into the buckets (gradient accumulation);
+        the first backward after it reduces the accumulated sums.  Every rank must use it alike."""
+        prev, self._sync = self._sync, False
+        try:
+            yield
+        finally:
+            self._sync = prev
+
     # -- backward-time machinery
     def _on_grad(self, p: nn.Parameter):
         b, off = self._bucket_of[id(p)]
@@ -102,6 +114,8 @@ class FlexTreeDDP(nn.Module):
             view = b.flat[off:off + p.numel()].view_as(p)
             view.copy_(p.grad)
             p.grad = view
+        if not self._sync:
+            return
         if not self._callback_queued:
             self._callback_queued = True
             torch.autograd.Variable._execution_engine.queue_callback(self._finish)

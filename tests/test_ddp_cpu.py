@@ -74,3 +74,23 @@ def test_unused_parameters_still_flush():
     assert len(comm.calls) == 1      # the single bucket is flushed at the end of backward
     ddp(torch.rand(4, 8)).backward()
     assert len(comm.calls) == 2
+
+
+def test_no_sync_accumulates_then_reduces_once():
+    torch.manual_seed(1)
+    ref = nn.Sequential(nn.Linear(16, 16), nn.Tanh(), nn.Linear(16, 4))
+    mod = nn.Sequential(nn.Linear(16, 16), nn.Tanh(), nn.Linear(16, 4))
+    mod.load_state_dict(ref.state_dict())
+    comm = FakeComm()
+    ddp = FlexTreeDDP(mod, comm, bucket_bytes=1 << 20)
+    xs = [torch.rand(3, 16) for _ in range(3)]
+    with ddp.no_sync():
+        for x in xs[:2]:
+            ddp(x).sum().backward()
+    assert comm.calls == []                      # nothing was sent while accumulating
+    ddp(xs[2]).sum().backward()
+    assert len(comm.calls) == len(ddp.buckets)   # the accumulated sums go out once
+    for x in xs:
+        ref(x).sum().backward()
+    for p1, p2 in zip(ref.parameters(), mod.parameters()):
+        assert torch.allclose(p1.grad, p2.grad, atol=1e-6)
