@@ -58,6 +58,21 @@ def test_ft_bench_thread_world_check_and_file(tmp_path):
     assert rc == 1 and "unknown parameter" in err
 
 
+def test_reduce_bench_host_side(tmp_path):
+    exe = str(BIN / "reduce_bench")
+    rc, out, err = run([exe, "--elements", "50000", "--rounds", "2", "--max-width", "5", "--cpu-only"])
+    assert rc == 0, err
+    lines = out.strip().splitlines()
+    assert all(l.startswith("n=") for l in lines[:5])
+    assert len(lines[-1].split()) == 5          # closing line: one average per fan-in
+    rc, out, _ = run([exe, "--elements", "1000", "--rounds", "1", "--min-width", "2", "--max-width", "3", "--cpu-only", "--json"])
+    import json
+    rows = [json.loads(l) for l in out.strip().splitlines()]
+    assert [r["n"] for r in rows] == [2, 3] and all(r["cpu_ms"] > 0 for r in rows)
+    rc, _, err = run([exe, "--max-width", "33"])
+    assert rc == 2 and "max-width" in err
+
+
 def test_mpi_style_example_builds_and_runs(tmp_path):
     """A program that spells the call MPI_Allreduce compiles against flextree_mpi.h and reduces correctly."""
     import shutil
