@@ -10,8 +10,11 @@ sources are copied verbatim to baseline/_ref/src and compiled as they are:
   * baseline/_ref/ref_mpi_bench  g++: the reference's allreduce_over_mpi/benchmark.cpp + mpi_mod.hpp
                                  against baseline/mpi_shim (shared-memory MPI subset) and
                                  baseline/glog_stub (the image has neither MPI nor glog)
+  * baseline/_ref/ref_config1    g++: config1_driver.cpp -DCONFIG1_REFERENCE + the reference's mpi_mod.hpp
+                                 over the same shim (seeded uniform data, fp64 check; see config1.py)
+  * baseline/_ref/ft_config1     g++: the same driver against this repository's libflextree.so (thread world)
 
-Nothing of this repository's library is linked into either binary.
+Nothing of this repository's library is linked into the three reference binaries.
 """
 from __future__ import annotations
 
@@ -51,7 +54,14 @@ def main() -> int:
                    "-I", str(HERE / "mpi_shim"), "-I", str(HERE / "glog_stub"), "-I", str(src / "allreduce_over_mpi"),
                    str(src / "allreduce_over_mpi" / "benchmark.cpp"), str(HERE / "mpi_shim" / "mpi_shim.cpp"),
                    "-o", str(OUT / "ref_mpi_bench"), "-lrt", "-lpthread"], log)
-        log.write(f"ref_nway build rc={rc1}; ref_mpi_bench build rc={rc2}\n")
+        ref_flags = ["g++", "-std=c++11", "-O2", "-fPIC", "-fopenmp", "-mavx2", "-fpermissive", "-w"]
+        rc3 = run([*ref_flags, "-DCONFIG1_REFERENCE", "-I", str(HERE / "mpi_shim"), "-I", str(HERE / "glog_stub"),
+                   "-I", str(src / "allreduce_over_mpi"), str(HERE / "config1_driver.cpp"), str(HERE / "mpi_shim" / "mpi_shim.cpp"),
+                   "-o", str(OUT / "ref_config1"), "-lrt", "-lpthread"], log)
+        pkg = HERE.parent / "allreduce_over_mpi_b200"
+        rc4 = run(["g++", "-std=c++17", "-O2", "-I", str(pkg / "csrc"), str(HERE / "config1_driver.cpp"), "-L", str(pkg / "lib"),
+                   "-lflextree", f"-Wl,-rpath,{pkg / 'lib'}", "-lpthread", "-o", str(OUT / "ft_config1")], log)
+        log.write(f"ref_nway build rc={rc1}; ref_mpi_bench build rc={rc2}; ref_config1 build rc={rc3}; ft_config1 build rc={rc4}\n")
     print(open(OUT / "INSTALL_LOG.txt").read()[-1500:])
     return 0 if rc1 == 0 and rc2 == 0 else 1
 
