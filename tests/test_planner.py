@@ -5,7 +5,6 @@ lonely layout) is run through the single-thread snapshot executor and checked ag
 fp64 sum, for traffic optimality, fan-in bound and the static race check.  Invalid
 layouts must be rejected with a message, never asserted or mis-scheduled.
 """
-import itertools
 
 import pytest
 import torch
