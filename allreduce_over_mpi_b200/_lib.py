@@ -71,6 +71,8 @@ def _declare(lib):
         "ft_plan_json": (sz, [i, *shape, cp, sz]),
         "ft_cpu_reduce": (i, [i, i, C.POINTER(vp), vp, i, sz, i]),
         "ft_run_plan_snapshot": (i, [i, *shape, i, i, C.POINTER(vp), u64, u64]),
+        "ft_run_plan_snapshot_range": (i, [i, *shape, i, i, C.POINTER(vp), u64, u64, i, i]),
+        "ft_plan_rs_holders": (i, [i, *shape, C.POINTER(u64)]),
         "ft_cpu_world_create": (vp, [i, dbl]),
         "ft_cpu_world_destroy": (None, [vp]),
         "ft_cpu_allreduce": (i, [vp, i, *shape, i, i, vp, vp, u64, u64, i, i, i, ip]),

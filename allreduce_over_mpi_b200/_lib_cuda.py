@@ -44,6 +44,9 @@ def declare(lib) -> None:
         "ft_allreduce_emulate_push": (i, [vp, vp, sz, i, i, f32, vp]),
         "ft_allreduce_emulate_ll": (i, [vp, vp, vp, sz, i, i, f32, i, u64, vp]),
         "ft_allreduce": (i, [vp, vp, vp, sz, i, i, *shape, i, f32, vp]),
+        "ft_reduce_scatter": (i, [vp, vp, sz, i, i, *shape, f32, vp]),
+        "ft_all_gather": (i, [vp, vp, sz, i, *shape, vp]),
+        "ft_comm_block_elems": (u64, [vp, sz, i]),
         "ft_allreduce_emulate_stage": (i, [vp, vp, vp, sz, i, i, *shape, f32, i, i, vp]),
         "ft_allreduce_emulate_oneshot": (i, [vp, vp, vp, sz, i, i, f32, i, u64, vp]),
         "ft_comm_status": (i, [vp, ip]),

@@ -77,6 +77,13 @@ int ft_cpu_reduce(int op, int dtype, const void* const* src, void* dst, int n, s
 /* all ranks in the calling thread, in place on bufs[rank] */
 int ft_run_plan_snapshot(int world, const int* widths, int nw, int lonely, int ring, int op, int dtype,
                          void* const* bufs, uint64_t count, uint64_t block_elems);
+/* one phase alone: stages [stage_begin, stage_end) of the plan (stage_end < 0: to the end);
+ * [0, S/2) is the reduce-scatter half, [S/2, S) the all-gather half, S = ft_plan_num_stages */
+int ft_run_plan_snapshot_range(int world, const int* widths, int nw, int lonely, int ring, int op, int dtype,
+                               void* const* bufs, uint64_t count, uint64_t block_elems, int stage_begin, int stage_end);
+/* holders[b] (b < world) = bit mask of the ranks whose block b is complete after the
+ * reduce-scatter half alone; world <= 64 */
+int ft_plan_rs_holders(int world, const int* widths, int nw, int lonely, int ring, uint64_t* holders);
 
 /* thread-per-rank world: every rank thread calls ft_cpu_allreduce with the same shape */
 typedef struct ft_cpu_world ft_cpu_world;

@@ -84,6 +84,23 @@ void ft_comm_set_max_lanes(ft_comm* c, int lanes);              /* CTAs per coll
 int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op, const int* widths,
                  int nw, int lonely, int ring, int algo, float scale, void* stream);
 void ft_comm_set_oneshot_max(ft_comm* c, size_t bytes);
+/* The two halves of the staged all-reduce as collectives of their own (the reference runs them
+ * only back to back inside tree_allreduce, mpi_mod.hpp:1550-1599 and :1620-1647).  Both work in
+ * place on a buffer inside the symmetric heap, cut into `world` blocks of
+ * B = ft_comm_block_elems(c, count, dtype) elements: block b = [b*B, min((b+1)*B, count)).
+ *   ft_reduce_scatter  runs the reduce-scatter stages of the shape's plan: afterwards block b is
+ *                      complete (and scaled) on the rank ft_plan_rs_holders names for it; every
+ *                      other part of the buffer holds inputs or partial sums.
+ *   ft_all_gather      runs the all-gather stages: it takes each rank's own blocks as final and
+ *                      leaves every rank with every block.
+ * ft_reduce_scatter followed by ft_all_gather on the same buffer and shape equals ft_allreduce
+ * with FT_ALGO_STAGED.  Each call closes with a rendezvous of all ranks, so the buffer may be
+ * rewritten as soon as the call has completed on the caller's stream. */
+int ft_reduce_scatter(ft_comm* c, void* buf, size_t count, int dtype, int op, const int* widths, int nw, int lonely,
+                      int ring, float scale, void* stream);
+int ft_all_gather(ft_comm* c, void* buf, size_t count, int dtype, const int* widths, int nw, int lonely, int ring,
+                  void* stream);
+uint64_t ft_comm_block_elems(ft_comm* c, size_t count, int dtype);
 /* FT_ALGO_HYBRID: fraction of every block reduced inside the switch (the rest goes over peer
  * loads at the same time) and fraction of the kernel's CTAs given to that part */
 void ft_comm_set_hybrid(ft_comm* c, double byte_fraction, double lane_fraction);

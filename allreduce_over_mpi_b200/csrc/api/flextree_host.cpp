@@ -208,6 +208,19 @@ int ft_run_plan_snapshot(int world, const int* widths, int nw, int lonely, int r
                                bufs, count, block_elems);
 }
 
+int ft_run_plan_snapshot_range(int world, const int* widths, int nw, int lonely, int ring, int op, int dtype,
+                               void* const* bufs, uint64_t count, uint64_t block_elems, int stage_begin, int stage_end) {
+  return ft::run_plan_snapshot(cached_plan(world, make_shape(widths, nw, lonely, ring)), (ft_op)op, (ft_dtype)dtype,
+                               bufs, count, block_elems, stage_begin, stage_end);
+}
+int ft_plan_rs_holders(int world, const int* widths, int nw, int lonely, int ring, uint64_t* holders) {
+  const auto& p = cached_plan(world, make_shape(widths, nw, lonely, ring));
+  if (!p.ok() || !holders || world > 64) return FT_ERR_INVALID_TOPO;
+  const std::vector<uint64_t> h = ft::rs_holders(p);
+  for (int b = 0; b < world; ++b) holders[b] = h[b];
+  return FT_OK;
+}
+
 ft_cpu_world* ft_cpu_world_create(int world, double timeout_s) {
   if (world < 1 || world > 4096) return nullptr;
   auto* w = new ft_cpu_world{ft::CpuWorld(world)};

@@ -67,7 +67,7 @@ struct StagedArgs {
   uint32_t elem_size;
   uint32_t stage_begin, stage_end;   // [begin, end) — the full plan unless emulating
   uint32_t do_sync;           // 0: no rendezvous at all (single-GPU emulation, one stage per launch)
-  uint32_t end_sync;          // closing rendezvous wanted
+  uint32_t end_sync;          // closing rendezvous: 0 none, 1 the plan's set after the last stage, 2 every rank (a phase run alone)
   uint32_t user_vec_ok;       // user_in / user_out are 16-byte aligned
   float scale;                // applied when a block's reduction completes (float types)
 };

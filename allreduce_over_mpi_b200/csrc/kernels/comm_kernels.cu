@@ -332,8 +332,13 @@ __global__ void __launch_bounds__(kThreads, 1) staged_allreduce_kernel(const __g
       __syncthreads();
     }
   }
-  if (a.do_sync && a.end_sync && !abort_flag && a.stage_end == a.plan->nstages)
-    lane_rendezvous(sync, a.plan->end_sync_mask, call * kCallStride + a.plan->nstages + 1, (int)a.plan->nstages);
+  // closing rendezvous: the plan's own set after the last stage; every rank (end_sync == 2) when a
+  // phase runs alone, since then the caller may rewrite any part of the buffer once the call returns
+  if (a.do_sync && a.end_sync && !abort_flag && (a.end_sync == 2 || a.stage_end == a.plan->nstages)) {
+    const unsigned long long everyone = c.world >= 64 ? ~0ull : ((1ull << c.world) - 1);
+    lane_rendezvous(sync, a.end_sync == 2 ? everyone : a.plan->end_sync_mask, call * kCallStride + a.plan->nstages + 1,
+                    (int)a.plan->nstages);
+  }
 }
 
 // ------------------------------------------------------------------------------- one-shot

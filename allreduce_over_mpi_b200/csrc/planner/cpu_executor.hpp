@@ -28,15 +28,18 @@
 
 namespace ft {
 
-// In-place execution over bufs[rank] (each `count` elements of dtype).
+// In-place execution over bufs[rank] (each `count` elements of dtype).  A stage range runs one
+// phase alone: [0, num_stages/2) is the reduce-scatter, [num_stages/2, num_stages) the all-gather
+// (stage_end < 0: to the end).
 inline ft_status run_plan_snapshot(const Plan& p, ft_op op, ft_dtype dt, void* const* bufs, uint64_t count,
-                                   uint64_t block_elems = 0) {
+                                   uint64_t block_elems = 0, int stage_begin = 0, int stage_end = -1) {
   if (!p.ok()) return FT_ERR_INVALID_TOPO;
   if (!ft_op_supported(op, dt)) return ((int)op < 0 || op >= FT_OP_COUNT) ? FT_ERR_UNSUPPORTED_OP : FT_ERR_UNSUPPORTED_TYPE;
   const size_t es = ft_dtype_size(dt);
   Blocks g(count, p.world, block_elems);
   struct Pending { int rank; uint64_t off; std::vector<char> bytes; };
-  for (int s = 0; s < p.num_stages; ++s) {
+  if (stage_end < 0 || stage_end > p.num_stages) stage_end = p.num_stages;
+  for (int s = stage_begin < 0 ? 0 : stage_begin; s < stage_end; ++s) {
     std::vector<Pending> pend;
     for (int r = 0; r < p.world; ++r)
       for (const Pull& pl : p.stages[r][s].pulls) {

@@ -381,6 +381,34 @@ inline uint64_t plan_traffic_elems(const Plan& p, const Blocks& g) {
   return t;
 }
 
+// Who holds what after the reduce-scatter half (stages [0, num_stages/2)) alone: holders[b]
+// is the set of ranks, as a bit mask, whose copy of block b then contains every rank's
+// contribution.  Found by pushing "set of contributors" masks through the plan with the same
+// read-before-write semantics as the executors.  These are the blocks a caller of the
+// reduce-scatter phase may read, and the blocks the all-gather phase takes as final.
+inline std::vector<uint64_t> rs_holders(const Plan& p) {
+  std::vector<uint64_t> holders(p.world > 0 ? p.world : 0, 0);
+  if (!p.ok() || p.world > 64) return holders;
+  const uint64_t all = p.world >= 64 ? ~0ull : ((1ull << p.world) - 1);
+  std::vector<std::vector<uint64_t>> have(p.world, std::vector<uint64_t>(p.world, 0));  // [rank][block]
+  for (int r = 0; r < p.world; ++r)
+    for (int b = 0; b < p.world; ++b) have[r][b] = 1ull << r;
+  for (int s = 0; s < p.num_stages / 2; ++s) {
+    auto next = have;
+    for (int r = 0; r < p.world; ++r)
+      for (const Pull& pl : p.stages[r][s].pulls) {
+        uint64_t m = pl.reduce ? have[r][pl.block] : 0;
+        for (int q : pl.srcs) m |= have[q][pl.block];
+        next[r][pl.block] = m;
+      }
+    have.swap(next);
+  }
+  for (int b = 0; b < p.world; ++b)
+    for (int r = 0; r < p.world; ++r)
+      if (have[r][b] == all) holders[b] |= 1ull << r;
+  return holders;
+}
+
 // Human-readable dump of one rank's schedule (the counterpart of the reference's
 // coloured print(), mpi_mod.hpp:159-199 and :585-624).  With count > 0 the element
 // ranges "offset+len" are printed next to the block ids.

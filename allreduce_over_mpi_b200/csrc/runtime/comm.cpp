@@ -283,7 +283,8 @@ int prepare(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dt
 }
 
 int launch_staged_call(ft_comm* c, const Prepared& pr, const void* sendbuf, void* recvbuf, size_t count,
-                       const ft::Shape& shape, float scale, int stage_begin, int stage_end, bool do_sync, cudaStream_t st) {
+                       const ft::Shape& shape, float scale, int stage_begin, int stage_end, bool do_sync, cudaStream_t st,
+                       bool phase_alone = false) {
   DevPlanEntry* pe = nullptr;
   int rc = get_plan(c, shape, &pe);
   if (rc != FT_OK) return rc;
@@ -303,9 +304,10 @@ int launch_staged_call(ft_comm* c, const Prepared& pr, const void* sendbuf, void
     }
     a.work_off = (uint64_t)((unsigned char*)recvbuf - local_base(c));
     a.alt_stride = 0;
-    a.end_sync = 1;
+    a.end_sync = phase_alone ? 2 : 1;
     a.user_vec_ok = 1;
   } else {
+    if (phase_alone) return fail(c, FT_ERR_INVALID_ARG, "reduce-scatter / all-gather work in place on a tensor in the symmetric heap");
     if (pr.bytes > c->staging_bytes)
       return fail(c, FT_ERR_TOO_LARGE, "message of " + std::to_string(pr.bytes) + " bytes exceeds the staging slot (" +
                                            std::to_string(c->staging_bytes) + "); allocate the tensor in the symmetric heap or split it");
@@ -696,6 +698,43 @@ int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, i
     return FT_OK;
   }
   return launch_staged_call(c, pr, sendbuf, recvbuf, count, make_shape(c->world, widths, nw, lonely, ring), scale, -1, -1, true, st);
+}
+
+// The two halves of the staged plan as collectives of their own (in place, symmetric heap only).
+static int phase_call(ft_comm* c, void* buf, size_t count, int dtype, int op, const int* widths, int nw, int lonely, int ring,
+                      float scale, bool gather, void* stream) {
+  Prepared pr;
+  int rc = prepare(c, nullptr, buf, count, dtype, op, &pr);
+  if (rc != FT_OK) return rc;
+  if (count == 0) return FT_OK;
+  if (c->world == 1) {
+    if (!gather && scale != 1.0f && (dtype == FT_F32 || dtype == FT_BF16)) {
+      const void* src[1] = {buf};
+      return ft_reduce_nway_scaled(dtype, dtype, src, buf, 1, count, scale, stream);
+    }
+    return FT_OK;
+  }
+  DevPlanEntry* pe = nullptr;
+  const ft::Shape shape = make_shape(c->world, widths, nw, lonely, ring);
+  rc = get_plan(c, shape, &pe);
+  if (rc != FT_OK) return rc;
+  const int half = pe->nstages / 2;
+  return launch_staged_call(c, pr, nullptr, buf, count, shape, scale, gather ? half : 0, gather ? pe->nstages : half, true,
+                            (cudaStream_t)stream, true);
+}
+int ft_reduce_scatter(ft_comm* c, void* buf, size_t count, int dtype, int op, const int* widths, int nw, int lonely, int ring,
+                      float scale, void* stream) {
+  return phase_call(c, buf, count, dtype, op, widths, nw, lonely, ring, scale, false, stream);
+}
+int ft_all_gather(ft_comm* c, void* buf, size_t count, int dtype, const int* widths, int nw, int lonely, int ring, void* stream) {
+  // gathers move bytes; any operator the type supports selects a kernel instantiation
+  const int op = ftk::policy_id(FT_SUM, dtype) >= 0 ? FT_SUM : FT_BAND;
+  return phase_call(c, buf, count, dtype, op, widths, nw, lonely, ring, 1.0f, true, stream);
+}
+uint64_t ft_comm_block_elems(ft_comm* c, size_t count, int dtype) {
+  const size_t es = ft_dtype_size((ft_dtype)dtype);
+  if (!c || !es) return 0;
+  return pick_block_elems(count, c->world, (uint32_t)es);
 }
 
 int ft_allreduce_emulate_stage(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op,

@@ -2,7 +2,7 @@
 // (allreduce_over_mpi/benchmark.cpp:69-122):
 //
 //     ft_bench [--size N] [--repeat R] [--to-file] [--comm-type flextree|threads|nccl] [--tag T]
-//              [--version] [--check] [--gpus G | --ranks G] [--dtype float|bf16]
+//              [--version] [--check] [--gpus G | --ranks G] [--dtype float|bf16] [--phases]
 //
 //   --size       elements per rank (default 35, like the reference)
 //   --repeat     number of timed all-reduces (data is NOT re-initialised between repeats)
@@ -13,6 +13,9 @@
 //   --to-file    write one time per line to "<tag.>N.len.<w0-w1-+L>.ar_test.<epoch>.txt"
 //   --check      closed-form check: data[i] = i*0.1 on every rank, so after R in-place sums every
 //                rank must hold i*0.1*N^R (two-sided, relative tolerance)
+//   --phases     (flextree) every all-reduce is issued as its two halves, ft_reduce_scatter then
+//                ft_all_gather; with --check everything a rank does not own is overwritten with NaN
+//                bit patterns between the two, so the gather has to rebuild it from the owners
 // The tree shape comes from FT_TOPO / FT_LONELY exactly as for the library entry point.
 // GPU times are CUDA-event intervals, reported as the maximum over ranks; CPU times are
 // steady-clock intervals on rank 0 like the reference's MPI_Wtime.
@@ -38,7 +41,7 @@ namespace {
 struct Opts {
   size_t size = 35;
   int repeat = 1, ranks = 0;
-  bool to_file = false, check = false, bf16 = false;
+  bool to_file = false, check = false, bf16 = false, phases = false;
   std::string comm = "flextree", tag;
 };
 
@@ -103,6 +106,7 @@ int main(int argc, char** argv) {
     else if (a == "--check") o.check = true;
     else if (a == "--gpus" || a == "--ranks") o.ranks = atoi(next());
     else if (a == "--dtype") o.bf16 = std::string(next()) == "bf16";
+    else if (a == "--phases") o.phases = true;
     else if (a == "--version") { printf("FlexTree Standalone Benchmark\nversion: %s\n", ft_version()); return 0; }
     else { fprintf(stderr, "unknown parameter: %s\n", a.c_str()); return 1; }
   }
@@ -153,6 +157,16 @@ int main(int argc, char** argv) {
     cpu_world = ft_cpu_world_create(world, 60.0);
   }
 
+  std::vector<uint64_t> holders(world, 0);
+  if (o.phases) {
+    if (o.comm != "flextree") { fprintf(stderr, "--phases needs --comm-type flextree\n"); return 1; }
+    const ft::Shape& sh = cfg.shape;
+    if (ft_plan_rs_holders(world, sh.widths.data(), (int)sh.widths.size(), sh.lonely, sh.ring, holders.data()) != FT_OK) {
+      fprintf(stderr, "no plan for %s\n", sh.str().c_str());
+      return 1;
+    }
+  }
+
   auto rank_main = [&](int r) {
     std::vector<float> host(o.size);
     for (size_t i = 0; i < o.size; ++i) host[i] = (float)i * 0.1f;
@@ -175,6 +189,21 @@ int main(int argc, char** argv) {
         cudaEventRecord(a, st);
         if (use_nccl) {
           if (nccl.AllReduce(dev, dev, o.size, o.bf16 ? kNcclBfloat16 : kNcclFloat32, kNcclSum, ncomms[r], st) != 0) bad[r] = 2;
+        } else if (o.phases) {
+          // the two halves as calls of their own; with --check everything this rank does not own is
+          // overwritten with NaN bit patterns in between, so the gather must rebuild it from the owners
+          const ft::Shape& sh = cfg.shape;
+          const int nw = (int)sh.widths.size();
+          if (ft_reduce_scatter(comms[r], dev, o.size, dtype, FT_SUM, sh.widths.data(), nw, sh.lonely, sh.ring, 1.0f, st) != FT_OK) bad[r] = 2;
+          if (o.check && world > 1) {
+            const uint64_t B = ft_comm_block_elems(comms[r], o.size, dtype);
+            uint64_t lo = o.size, hi = o.size;
+            for (int b = 0; b < world; ++b)
+              if (holders[b] >> r & 1) { lo = std::min<uint64_t>(o.size, b * B); hi = std::min<uint64_t>(o.size, (b + 1) * B); }
+            if (lo) cudaMemsetAsync(dev, 0xFF, lo * es, st);
+            if (hi < o.size) cudaMemsetAsync((char*)dev + hi * es, 0xFF, (o.size - hi) * es, st);
+          }
+          if (ft_all_gather(comms[r], dev, o.size, dtype, sh.widths.data(), nw, sh.lonely, sh.ring, st) != FT_OK) bad[r] = 2;
         } else if (MPI_Allreduce_FT_c(FT_IN_PLACE, dev, o.size, dtype, FT_OP_SUM, mc) != 0) {
           bad[r] = 2;
         }

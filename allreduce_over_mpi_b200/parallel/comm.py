@@ -230,6 +230,60 @@ class _CommBase:
             torch.cuda.nvtx.range_pop()
         return dst
 
+    # -- the two halves of the staged plan as collectives of their own
+    def _phase_shape(self, shape) -> Shape:
+        shp = _as_shape(shape, self.world)
+        if shp is None:
+            shp = self.default_shape if not self.auto and self.default_shape is not None else Shape.flat(self.world)
+        return shp
+
+    def block_range(self, tensor: torch.Tensor, block: int) -> tuple[int, int]:
+        """Element range [lo, hi) of ``block`` when ``tensor`` is cut for a collective (``world`` blocks of
+        whole 16-byte vectors; trailing blocks may be short or empty)."""
+        n = tensor.numel()
+        B = planner.block_elems_for(n, self.world, tensor.element_size())
+        return min(n, block * B), min(n, (block + 1) * B)
+
+    def owned_blocks(self, shape=None) -> list[int]:
+        """Blocks this rank holds complete after :meth:`reduce_scatter` with ``shape`` (block = rank for
+        trees, rank + 1 for the ring)."""
+        return planner.owned_blocks(self.world, self._phase_shape(shape), self.rank)
+
+    def _phase(self, tensor: torch.Tensor, gather: bool, op: str, shape, scale: float, stream):
+        if not tensor.is_cuda or not tensor.is_contiguous():
+            raise ValueError("needs a contiguous CUDA tensor")
+        if self.world > 1 and not self.in_heap(tensor):
+            raise ValueError("reduce_scatter / all_gather work in place on a tensor from comm.alloc()")
+        if self._poisoned:
+            raise FlexTreeError(5, "a device-side wait timed out earlier: rebuild the communicator")
+        shp = self._phase_shape(shape)
+        arr, nw, lonely, ring = shp.c_args()
+        st = C.c_void_p((stream or torch.cuda.current_stream(self.device)).cuda_stream)
+        with torch.cuda.device(self.device):
+            if gather:
+                self._check(lib().ft_all_gather(self._h, tensor.data_ptr(), tensor.numel(), ft_dtype(tensor.dtype), arr, nw, lonely,
+                                                ring, st))
+            else:
+                self._check(lib().ft_reduce_scatter(self._h, tensor.data_ptr(), tensor.numel(), ft_dtype(tensor.dtype), OPS[op], arr,
+                                                    nw, lonely, ring, float(scale), st))
+        return shp
+
+    def reduce_scatter(self, tensor: torch.Tensor, op: str = "sum", shape=None, scale: float = 1.0,
+                       stream: torch.cuda.Stream | None = None) -> list[torch.Tensor]:
+        """Reduce-scatter half of the staged all-reduce, in place on a heap tensor.  Returns views of the
+        blocks this rank now holds complete (one block; the rest of ``tensor`` holds partial sums)."""
+        if op == "avg":
+            op, scale = "sum", scale / self.world
+        shp = self._phase(tensor, False, op, shape, scale, stream)
+        flat = tensor.view(-1)
+        return [flat[slice(*self.block_range(tensor, b))] for b in planner.owned_blocks(self.world, shp, self.rank)]
+
+    def all_gather(self, tensor: torch.Tensor, shape=None, stream: torch.cuda.Stream | None = None) -> torch.Tensor:
+        """All-gather half: every rank's own blocks (:meth:`owned_blocks`) are taken as final and copied to
+        every other rank, in place on a heap tensor."""
+        self._phase(tensor, True, "sum", shape, 1.0, stream)
+        return tensor
+
     # -- health
     def status(self) -> dict:
         """Status block written by device-side bounded waits (call after synchronising)."""
@@ -490,6 +544,47 @@ class LocalWorld:
                 c._check(L.ft_allreduce_emulate_stage(c._h, src, dst, tensors[r].numel(), dt, OPS[op], arr, nw, lonely, ring,
                                                       float(scale), max(s, 0), s + 1, st))
         return outs
+
+    def _phase(self, tensors: Sequence[torch.Tensor], gather: bool, op: str, shape, scale: float):
+        world = self.world
+        shp = _as_shape(shape, world) or Shape.flat(world)
+        if op == "avg":
+            op, scale = "sum", scale / world
+        if not self.emulated or world == 1:
+            for r, c in enumerate(self.ranks):
+                with torch.cuda.device(c.device):
+                    if gather:
+                        c.all_gather(tensors[r], shape=shp)
+                    else:
+                        c.reduce_scatter(tensors[r], op=op, shape=shp, scale=scale)
+            return shp
+        nstages = planner.plan_num_stages(world, shp)
+        if nstages < 0:
+            raise FlexTreeError(4, f"invalid FT_TOPO {shp} ({planner.validate_shape(world, shp)})")
+        arr, nw, lonely, ring = shp.c_args()
+        L, dt = lib(), ft_dtype(tensors[0].dtype)
+        st = C.c_void_p(torch.cuda.current_stream(self.ranks[0].device).cuda_stream)
+        for s in (range(nstages // 2, nstages) if gather else range(nstages // 2)):
+            for r, c in enumerate(self.ranks):
+                if not c.in_heap(tensors[r]):
+                    raise ValueError("reduce_scatter / all_gather work in place on a tensor from alloc()")
+                c._check(L.ft_allreduce_emulate_stage(c._h, None, tensors[r].data_ptr(), tensors[r].numel(), dt, OPS[op], arr, nw,
+                                                      lonely, ring, float(scale), s, s + 1, st))
+        return shp
+
+    def reduce_scatter(self, tensors: Sequence[torch.Tensor], op: str = "sum", shape=None, scale: float = 1.0):
+        """Reduce-scatter half alone; returns, per rank, the views of the blocks it holds complete."""
+        shp = self._phase(tensors, False, op, shape, scale)
+        out = []
+        for r, c in enumerate(self.ranks):
+            flat = tensors[r].view(-1)
+            out.append([flat[slice(*c.block_range(tensors[r], b))] for b in planner.owned_blocks(self.world, shp, r)])
+        return out
+
+    def all_gather(self, tensors: Sequence[torch.Tensor], shape=None):
+        """All-gather half alone, in place."""
+        self._phase(tensors, True, "sum", shape, 1.0)
+        return tensors
 
     def profile_stages(self, tensors: Sequence[torch.Tensor], shape, op: str = "sum", iters: int = 5) -> list[float]:
         """Per-stage device time (ms, all ranks of the stage together) of a staged plan on an emulated

@@ -252,12 +252,38 @@ def plan_json(world: int, shape: Shape) -> dict:
 
 
 # ---- CPU executors ----------------------------------------------------------------------
-def run_plan_snapshot(shape: Shape, bufs: Sequence[torch.Tensor], op: str = "sum", block_elems: int = 0) -> None:
-    """All ranks in this thread, in place on ``bufs[rank]`` (CPU tensors)."""
+def run_plan_snapshot(shape: Shape, bufs: Sequence[torch.Tensor], op: str = "sum", block_elems: int = 0,
+                      phase: str = "all") -> None:
+    """All ranks in this thread, in place on ``bufs[rank]`` (CPU tensors).  ``phase`` runs one half of
+    the plan alone: "reduce_scatter" (afterwards :func:`rs_holders` says who holds which block) or
+    "all_gather"."""
     world = len(bufs)
     ptrs = (C.c_void_p * world)(*[b.data_ptr() for b in bufs])
-    check(lib().ft_run_plan_snapshot(world, *shape.c_args(), OPS[op], ft_dtype(bufs[0].dtype), ptrs, bufs[0].numel(),
-                                     block_elems), f"shape {shape} for world {world}")
+    half = plan_num_stages(world, shape) // 2
+    begin, end = {"all": (0, -1), "reduce_scatter": (0, half), "all_gather": (half, -1)}[phase]
+    check(lib().ft_run_plan_snapshot_range(world, *shape.c_args(), OPS[op], ft_dtype(bufs[0].dtype), ptrs, bufs[0].numel(),
+                                           block_elems, begin, end), f"shape {shape} for world {world}")
+
+
+def rs_holders(world: int, shape: Shape) -> list[list[int]]:
+    """``holders[b]`` = ranks whose block ``b`` is complete after the reduce-scatter half alone.  In a
+    plain tree every block has one holder; with lonely ranks a lonely rank shares its holder's blocks."""
+    masks = (C.c_uint64 * world)()
+    check(lib().ft_plan_rs_holders(world, *shape.c_args(), masks), f"shape {shape} for world {world}")
+    return [[r for r in range(world) if masks[b] >> r & 1] for b in range(world)]
+
+
+def owned_blocks(world: int, shape: Shape, rank: int) -> list[int]:
+    """Blocks that ``rank`` holds complete after a reduce-scatter, and must hold valid before an all-gather."""
+    return [b for b, hs in enumerate(rs_holders(world, shape)) if rank in hs]
+
+
+def block_elems_for(count: int, world: int, elem_size: int) -> int:
+    """Elements per block as the GPU communicator cuts a tensor: ceil(count / world) rounded up to whole
+    16-byte vectors; block b covers [b * B, min((b + 1) * B, count))."""
+    per = max(1, 16 // elem_size)
+    b = -(-count // world)
+    return max(per, -(-b // per) * per)
 
 
 class CpuWorld:

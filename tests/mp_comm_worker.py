@@ -43,6 +43,59 @@ def main():
         dist.destroy_process_group()
         return 0
 
+    if mode == "phases":
+        # reduce-scatter and all-gather as calls of their own: the owned block is complete after the
+        # first, everything else is then overwritten with NaN, and the second alone rebuilds the result
+        good = True
+        it = 0
+        for dtype in (torch.float32, torch.bfloat16):
+            for count in (3, 4099, (3 << 20) + 5):
+                for shape in [str(s) for s in planner.executable_shapes(world)]:
+                    it += 1
+                    comm.free_all()
+                    sym = comm.alloc(count, dtype)
+                    fill(sym, rank, it)
+                    want = expected(count, dtype, world, dev, it)
+                    tol = 1e-4 if dtype == torch.float32 else 0.3
+                    owned = comm.reduce_scatter(sym, shape=shape)
+                    torch.cuda.synchronize()
+                    comm.check()
+                    blocks = comm.owned_blocks(shape)
+                    for b, view in zip(blocks, owned):
+                        lo, hi = comm.block_range(sym, b)
+                        if hi > lo and not (view.double() - want[lo:hi]).abs().max().item() <= tol:
+                            good = False
+                            print(f"[rank {rank}] reduce_scatter {shape} {dtype} {count}: block {b} is wrong", flush=True)
+                    keep = [v.clone() for v in owned]
+                    sym.fill_(float("nan"))
+                    for v, k in zip(owned, keep):
+                        v.copy_(k)
+                    comm.all_gather(sym, shape=shape)
+                    torch.cuda.synchronize()
+                    comm.check()
+                    if not (sym.double() - want).abs().max().item() <= tol:
+                        good = False
+                        print(f"[rank {rank}] all_gather {shape} {dtype} {count} is wrong", flush=True)
+                    report["cases"] += 1
+        # back to back without host synchronisation, the buffer rewritten between the calls
+        comm.free_all()
+        sym = comm.alloc(200_000, torch.float32)
+        for i in range(8):
+            sym.fill_(1.0)
+            comm.reduce_scatter(sym, op="avg")
+            comm.all_gather(sym)
+        torch.cuda.synchronize()
+        comm.check()
+        good = good and bool(torch.allclose(sym, torch.ones_like(sym), atol=1e-5))
+        flags = [None] * world
+        dist.all_gather_object(flags, good)
+        if rank == 0:
+            print("RESULT " + json.dumps({"ok": all(flags), **report}), flush=True)
+        comm.close()
+        dist.barrier()
+        dist.destroy_process_group()
+        return 0 if all(flags) else 1
+
     ok = True
 
     def verify(t, count, dtype, it, what):

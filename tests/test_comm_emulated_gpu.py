@@ -217,3 +217,52 @@ def test_world_of_one_and_bounded_wait():
     c.all_reduce(y)
     torch.cuda.synchronize()
     w.close()
+
+
+@pytest.mark.parametrize("text", ["2", "4", "2*2+1", "2*4", "2*2*2", "ring5", "3*2+1", "8"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_reduce_scatter_and_all_gather_alone(text, dtype):
+    """The two halves of the staged plan as collectives of their own: after reduce_scatter a rank's
+    own block is complete (everything it does not own is then overwritten with NaN), and all_gather
+    alone rebuilds the full result from the owned blocks."""
+    shape = Shape.parse(text)
+    n = shape.world
+    w = LocalWorld(n, heap_bytes=8 << 20, staging_bytes=1 << 16)
+    for count in (5, 4099, 300_001):
+        host = inputs(n, count, dtype, seed=11)
+        want = torch.stack(host).double().sum(0) / n
+        dev = []
+        for r, c in enumerate(w.ranks):
+            t = c.alloc(count, dtype)
+            t.copy_(host[r])
+            dev.append(t)
+        owned = w.reduce_scatter(dev, op="avg", shape=shape)
+        torch.cuda.synchronize()
+        covered = torch.zeros(count, dtype=torch.bool)
+        for r, c in enumerate(w.ranks):
+            blocks = P.owned_blocks(n, shape, r)
+            assert len(blocks) == 1 and len(owned[r]) == 1
+            lo, hi = c.block_range(dev[r], blocks[0])
+            assert owned[r][0].numel() == hi - lo and (hi == lo or owned[r][0].data_ptr() == dev[r][lo:hi].data_ptr())
+            assert torch.allclose(dev[r][lo:hi].double().cpu(), want[lo:hi], atol=tol(dtype)), (text, count, r)
+            covered[lo:hi] = True
+            keep = dev[r][lo:hi].clone()
+            dev[r].fill_(float("nan"))
+            dev[r][lo:hi] = keep
+        assert bool(covered.all())
+        w.all_gather(dev, shape=shape)
+        torch.cuda.synchronize()
+        for r in range(n):
+            assert torch.allclose(dev[r].double().cpu(), want, atol=tol(dtype)), (text, count, r)
+        assert all(torch.equal(d, dev[0]) for d in dev)
+        for c in w.ranks:
+            c.free_all()
+    w.close()
+
+
+def test_phases_refuse_tensors_outside_the_heap():
+    w = LocalWorld(2, heap_bytes=1 << 20, staging_bytes=1 << 16)
+    outside = [torch.zeros(64, device=DEV) for _ in range(2)]
+    with pytest.raises(ValueError):
+        w.reduce_scatter(outside)
+    w.close()

@@ -51,3 +51,11 @@ def test_absent_rank_times_out_instead_of_hanging():
         pytest.skip("needs 2 GPUs")
     res = run_worker(n, "timeout", {"FT_NVLS": "0", "NCCL_NVLS_ENABLE": "0"}, port=29571)
     assert res["ok"], res
+
+
+def test_reduce_scatter_and_all_gather_as_calls_of_their_own():
+    n = min(ngpu(), 8)
+    if n < 2:
+        pytest.skip("needs 2 GPUs")
+    res = run_worker(n, "phases", port=29581)
+    assert res["ok"] and res["cases"] > 10, res

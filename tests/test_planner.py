@@ -55,6 +55,38 @@ def test_every_shape_up_to_32(count):
     assert checked > 300
 
 
+def test_phases_alone_reduce_scatter_then_all_gather():
+    """The two halves of every plan stand on their own: after the reduce-scatter half each block is
+    complete on exactly the ranks rs_holders names (one per block), and the all-gather half reads
+    nothing but those copies (every other block is poisoned before it runs)."""
+    count = 53
+    for n, s in all_shapes(16):
+        holders = P.rs_holders(n, s)
+        assert all(len(h) == 1 for h in holders), (n, str(s), holders)
+        assert sorted(h[0] for h in holders) == list(range(n))       # every rank owns exactly one block
+        bufs = make_bufs(n, count, torch.float64)
+        want = torch.stack(bufs).sum(0)
+        P.run_plan_snapshot(s, bufs, phase="reduce_scatter")
+        B = -(-count // n)
+        for b, (owner,) in enumerate(holders):
+            lo, hi = min(count, b * B), min(count, (b + 1) * B)
+            assert torch.allclose(bufs[owner][lo:hi], want[lo:hi], rtol=0, atol=1e-12), (n, str(s), b)
+            assert P.owned_blocks(n, s, owner) == [b]
+            for r in range(n):
+                if r != owner:
+                    bufs[r][lo:hi] = float("nan")
+        P.run_plan_snapshot(s, bufs, phase="all_gather")
+        for r in range(n):
+            assert torch.allclose(bufs[r], want, rtol=0, atol=1e-12), (n, str(s), r)
+
+
+def test_block_elems_matches_the_16_byte_rule():
+    assert P.block_elems_for(1000, 8, 4) == 128          # ceil(1000/8) = 125 -> whole 16-byte vectors
+    assert P.block_elems_for(1000, 8, 2) == 128
+    assert P.block_elems_for(3, 8, 4) == 4
+    assert P.block_elems_for(1 << 20, 7, 1) == 149808
+
+
 def test_lonely_validity_rule_is_exact():
     """L <= w0 and L*w0 <= M (with >= 2 levels) are accepted and correct; everything else is refused."""
     ok = bad = 0

@@ -56,6 +56,8 @@ def test_ft_bench_thread_world_check_and_file(tmp_path):
     assert rc == 0 and "FlexTree Standalone Benchmark" in out
     rc, _, err = run([exe, "--bogus"])
     assert rc == 1 and "unknown parameter" in err
+    rc, _, err = run([exe, "--comm-type", "threads", "--ranks", "2", "--phases"])
+    assert rc == 1 and "--phases needs --comm-type flextree" in err
 
 
 def test_reduce_bench_host_side(tmp_path):
