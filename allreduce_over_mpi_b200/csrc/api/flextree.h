@@ -69,6 +69,10 @@ uint64_t ft_plan_traffic(int world, const int* widths, int nw, int lonely, int r
                          uint64_t block_elems);
 size_t ft_plan_describe(int world, const int* widths, int nw, int lonely, int ring, int rank, uint64_t count,
                         uint64_t block_elems, char* buf, size_t cap);
+/* builds `rank`'s device table for the shape and checks every descriptor the kernels will follow
+ * (indices, block ids, fan-in, source ranks, rendezvous coverage); the communicator runs the same
+ * check before it uploads a plan.  FT_OK, or FT_ERR_INVALID_TOPO with the reason in err */
+int ft_dev_plan_check(int world, const int* widths, int nw, int lonely, int ring, int rank, char* err, size_t err_cap);
 /* machine-readable plan: JSON {"world":..,"stages":..,"ranks":[[{"rs":1,"sync":[..],"pulls":[[block,reduce,[srcs]],..]},..],..]} */
 size_t ft_plan_json(int world, const int* widths, int nw, int lonely, int ring, char* buf, size_t cap);
 

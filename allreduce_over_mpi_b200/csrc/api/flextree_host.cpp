@@ -13,6 +13,7 @@
 #include "../planner/factorize.hpp"
 #include "../planner/plan.hpp"
 #include "flextree.h"
+#include "../runtime/dev_plan.hpp"
 
 namespace {
 
@@ -219,6 +220,15 @@ int ft_plan_rs_holders(int world, const int* widths, int nw, int lonely, int rin
   const std::vector<uint64_t> h = ft::rs_holders(p);
   for (int b = 0; b < world; ++b) holders[b] = h[b];
   return FT_OK;
+}
+
+int ft_dev_plan_check(int world, const int* widths, int nw, int lonely, int ring, int rank, char* err, size_t err_cap) {
+  const auto& p = cached_plan(world, make_shape(widths, nw, lonely, ring));
+  if (!p.ok()) { put(p.error, err, err_cap); return FT_ERR_INVALID_TOPO; }
+  if (rank < 0 || rank >= world) { put("invalid rank", err, err_cap); return FT_ERR_INVALID_ARG; }
+  const std::string e = ft::check_dev_plan(ft::build_dev_plan(p, rank), world, rank);
+  put(e, err, err_cap);
+  return e.empty() ? FT_OK : FT_ERR_INVALID_TOPO;
 }
 
 ft_cpu_world* ft_cpu_world_create(int world, double timeout_s) {

@@ -25,6 +25,7 @@
 #include "../kernels/comm_dev.h"
 #include "../kernels/pol_ids.h"
 #include "../planner/plan.hpp"
+#include "dev_plan.hpp"
 #include <unistd.h>
 
 namespace ftk {
@@ -194,40 +195,11 @@ int get_plan(ft_comm* c, const ft::Shape& shape, DevPlanEntry** out) {
   ft::Plan p = ft::build_plan(c->world, shape);
   if (!p.ok()) return fail(c, FT_ERR_INVALID_TOPO, "invalid FT_TOPO " + key + " (" + p.error + ")");
   if (p.num_stages > ftk::kMaxStages) return fail(c, FT_ERR_TOO_LARGE, "plan has too many stages");
-  std::vector<ftk::DevPull> pulls;
-  ftk::DevPlan hp{};
-  hp.nstages = (uint32_t)p.num_stages;
-  auto mask_of = [](const std::vector<int>& v) {
-    uint64_t m = 0;
-    for (int q : v) m |= 1ull << q;
-    return m;
-  };
-  const int last_rs = p.num_stages / 2 - 1;
-  for (int s = 0; s < p.num_stages; ++s) {
-    ftk::DevStage& ds = hp.stages[s];
-    ds.pull_begin = (uint32_t)pulls.size();
-    std::vector<ft::Pull> ordered = p.stages[c->rank][s].pulls;
-    // gathers start at the next rank up and wrap around, so that at any moment the ranks of a
-    // stage read from different peers instead of all queueing on the lowest-numbered one
-    if (std::none_of(ordered.begin(), ordered.end(), [](const ft::Pull& x) { return x.reduce; }))
-      std::stable_sort(ordered.begin(), ordered.end(), [&](const ft::Pull& x, const ft::Pull& y) {
-        return (x.srcs[0] - c->rank + c->world) % c->world < (y.srcs[0] - c->rank + c->world) % c->world;
-      });
-    for (const ft::Pull& pl : ordered) {
-      ftk::DevPull dp{};
-      dp.block = (uint16_t)pl.block;
-      dp.nsrc = (uint8_t)pl.srcs.size();
-      dp.reduce = pl.reduce ? 1 : 0;
-      for (size_t i = 0; i < pl.srcs.size() && i < FT_MAX_FANIN; ++i) dp.src[i] = (uint8_t)pl.srcs[i];
-      pulls.push_back(dp);
-    }
-    ds.pull_end = (uint32_t)pulls.size();
-    ds.sync_mask = mask_of(p.sync[s][c->rank]);
-    ds.last_rs = (s == last_rs);
-    ds.is_ag = !p.stages[c->rank][s].reduce_scatter || s > last_rs;
-  }
-  hp.npulls = (uint32_t)pulls.size();
-  hp.end_sync_mask = mask_of(p.sync[p.num_stages][c->rank]);
+  ft::HostDevPlan hd = ft::build_dev_plan(p, c->rank);
+  const std::string flaw = ft::check_dev_plan(hd, c->world, c->rank);
+  if (!flaw.empty()) return fail(c, FT_ERR_INVALID_TOPO, "plan " + key + " failed its descriptor check (" + flaw + ")");
+  const ftk::DevPlan& hp = hd.plan;
+  const std::vector<ftk::DevPull>& pulls = hd.pulls;
   DevPlanEntry e;
   e.nstages = p.num_stages;
   FT_CUDA(c, cudaMalloc(&e.plan, sizeof(ftk::DevPlan)));

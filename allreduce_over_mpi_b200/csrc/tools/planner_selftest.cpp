@@ -3,7 +3,7 @@
 //     g++ -std=c++17 -O1 -g -fsanitize=thread planner_selftest.cpp -o t -lpthread && ./t threads
 // It builds the plan of every executable shape up to 24 ranks, runs the static race check and the
 // snapshot executor against a double-precision sum, exercises the candidate enumerators and the
-// cost models, and (argument "threads") runs the thread-per-rank executor with its flag protocol,
+// cost models, checks the device tables (and that damaged ones are refused), and (argument "threads") runs the thread-per-rank executor with its flag protocol,
 // including a silent rank that must produce time-outs rather than a hang.
 // The reference has no sanitizer builds (its flags are -Wall -Wextra only, allreduce_over_mpi/CMakeLists.txt:5).
 #include <cmath>
@@ -16,6 +16,7 @@
 #include "../planner/config.hpp"
 #include "../planner/cost_model.hpp"
 #include "../planner/cpu_executor.hpp"
+#include "../runtime/dev_plan.hpp"
 
 static int fails = 0;
 #define EXPECT(c) do { if (!(c)) { std::printf("FAIL %s:%d %s\n", __FILE__, __LINE__, #c); ++fails; } } while (0)
@@ -44,6 +45,42 @@ static void plans_and_snapshot() {
   EXPECT(checked > 150);
   EXPECT(!ft::validate_shape(7, ft::Shape{{2, 2}, 3, false}).empty());
   EXPECT(!ft::parse_topo("2,3", "", 7).ok());
+}
+
+// Device tables: every rank of every shape passes the descriptor check, the reduce-scatter half
+// leaves each block complete on exactly one rank, and a table damaged in any of the ways the check
+// guards against is refused.
+static void device_tables() {
+  for (int n = 1; n <= 24; ++n)
+    for (const ft::Shape& s : ft::executable_shapes(n)) {
+      ft::Plan p = ft::build_plan(n, s);
+      for (int r = 0; r < n; ++r) EXPECT(ft::check_dev_plan(ft::build_dev_plan(p, r), n, r).empty());
+      uint64_t owners = 0;
+      for (uint64_t h : ft::rs_holders(p)) { EXPECT(h && !(h & (h - 1))); owners |= h; }
+      EXPECT(n == 1 || owners == (1ull << n) - 1);
+    }
+  const ft::Plan p = ft::build_plan(7, ft::Shape{{2, 3}, 1, false});
+  const ft::HostDevPlan good = ft::build_dev_plan(p, 2);
+  EXPECT(ft::check_dev_plan(good, 7, 2).empty());
+  EXPECT(!good.pulls.empty());
+  auto broken = [&](auto&& damage) {
+    ft::HostDevPlan d = good;
+    damage(d);
+    return !ft::check_dev_plan(d, 7, 2).empty();
+  };
+  EXPECT(broken([](ft::HostDevPlan& d) { d.pulls[0].block = 7; }));
+  EXPECT(broken([](ft::HostDevPlan& d) { d.pulls[0].src[0] = 9; }));
+  EXPECT(broken([](ft::HostDevPlan& d) { d.pulls[0].src[0] = 2; }));
+  EXPECT(broken([](ft::HostDevPlan& d) { d.pulls[0].nsrc = 0; }));
+  EXPECT(broken([](ft::HostDevPlan& d) { d.pulls[0].nsrc = FT_MAX_FANIN; d.pulls[0].reduce = 1; }));
+  EXPECT(broken([](ft::HostDevPlan& d) { d.plan.stages[0].sync_mask = 0; }));
+  EXPECT(broken([](ft::HostDevPlan& d) { d.plan.stages[0].sync_mask |= 1ull << 7; }));
+  EXPECT(broken([](ft::HostDevPlan& d) { d.plan.stages[1].pull_begin += 1; }));
+  EXPECT(broken([](ft::HostDevPlan& d) { d.plan.stages[d.plan.nstages - 1].pull_end += 1; }));
+  EXPECT(broken([](ft::HostDevPlan& d) { d.plan.nstages += 1; }));
+  EXPECT(broken([](ft::HostDevPlan& d) { d.plan.stages[0].last_rs = 1; }));
+  EXPECT(broken([](ft::HostDevPlan& d) { d.plan.end_sync_mask = ~0ull; }));
+  EXPECT(!ft::check_dev_plan(good, 7, 7).empty());
 }
 
 static void enumerators_and_models() {
@@ -94,7 +131,7 @@ static void thread_world(bool with_fault) {
 
 int main(int argc, char** argv) {
   const bool threads = argc > 1 && !std::strcmp(argv[1], "threads");
-  if (!threads) { plans_and_snapshot(); enumerators_and_models(); }
+  if (!threads) { plans_and_snapshot(); device_tables(); enumerators_and_models(); }
   thread_world(false);
   thread_world(true);
   std::printf(fails ? "%d FAILURES\n" : "selftest ok\n", fails);

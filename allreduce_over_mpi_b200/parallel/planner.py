@@ -231,6 +231,14 @@ def plan_check(world: int, shape: Shape) -> str:
     return err.value.decode()
 
 
+def dev_plan_check(world: int, shape: Shape, rank: int) -> str:
+    """Descriptor check of ``rank``'s device table (what the communicator verifies before upload):
+    empty string when every index, block id, fan-in, source rank and rendezvous mask is in range."""
+    err = C.create_string_buffer(1024)
+    lib().ft_dev_plan_check(world, *shape.c_args(), rank, err, 1024)
+    return err.value.decode()
+
+
 def plan_num_stages(world: int, shape: Shape) -> int:
     return lib().ft_plan_num_stages(world, *shape.c_args())
 

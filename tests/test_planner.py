@@ -80,6 +80,19 @@ def test_phases_alone_reduce_scatter_then_all_gather():
             assert torch.allclose(bufs[r], want, rtol=0, atol=1e-12), (n, str(s), r)
 
 
+def test_device_tables_pass_the_descriptor_check():
+    """What the communicator verifies before it uploads a plan: every rank's table of every shape is
+    in range (indices, block ids, fan-in, sources, and each stage reads only from ranks it has met)."""
+    checked = 0
+    for n, s in all_shapes(32):
+        for r in range(n):
+            assert P.dev_plan_check(n, s, r) == "", (n, str(s), r)
+            checked += 1
+    assert checked > 5000
+    assert "rank" in P.dev_plan_check(4, Shape.flat(4), 9)
+    assert P.dev_plan_check(7, Shape([2, 2], lonely=3), 0) != ""
+
+
 def test_block_elems_matches_the_16_byte_rule():
     assert P.block_elems_for(1000, 8, 4) == 128          # ceil(1000/8) = 125 -> whole 16-byte vectors
     assert P.block_elems_for(1000, 8, 2) == 128
