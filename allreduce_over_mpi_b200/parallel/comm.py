@@ -32,6 +32,7 @@ from .planner import CostParams, Shape
 
 ALGOS = {"auto": 0, "staged": 1, "oneshot": 2, "nvls": 3, "hybrid": 4, "ll": 5, "push": 6}
 LL_MAX_BYTES = 256 << 10
+CANARY_BYTES, CANARY_BYTE = 256, 0xA5
 MEM_IPC, MEM_VMM = 0, 1
 
 
@@ -79,6 +80,8 @@ class _CommBase:
         self._heap_range = None
         self._poisoned = False
         self._nvtx = os.environ.get("FT_NVTX", "0") == "1"   # NVTX range around every call (for timeline tools)
+        # guard words behind every alloc() (debugging aid, FT_CANARY=1 or enable_canaries())
+        self._canaries: list | None = [] if os.environ.get("FT_CANARY", "0") == "1" else None
 
     # -- errors
     def _check(self, code: int):
@@ -132,11 +135,40 @@ class _CommBase:
         ptr = lib().ft_comm_alloc(self._h, nbytes)
         if not ptr:
             raise MemoryError(f"symmetric heap exhausted ({self.heap_bytes} bytes); pass a larger heap_bytes")
-        return tensor_from_ptr(ptr, shape, dtype, self.device, owner=self)
+        t = tensor_from_ptr(ptr, shape, dtype, self.device, owner=self)
+        if self._canaries is not None:
+            gptr = lib().ft_comm_alloc(self._h, CANARY_BYTES)
+            if not gptr:
+                raise MemoryError("symmetric heap exhausted while placing a guard block")
+            guard = tensor_from_ptr(gptr, (CANARY_BYTES,), torch.uint8, self.device, owner=self)
+            guard.fill_(CANARY_BYTE)
+            self._canaries.append((guard, f"{tuple(shape)} {dtype} at heap offset {ptr - (lib().ft_comm_heap_base(self._h) or 0)}"))
+        return t
 
     def free_all(self):
         """Forget every alloc() (tensors handed out before must no longer be used)."""
         lib().ft_comm_alloc_reset(self._h)
+        if self._canaries is not None:
+            self._canaries = []
+
+    def enable_canaries(self, on: bool = True):
+        """Place a 256-byte guard block of a known pattern behind every later alloc().  Kernels address a
+        heap tensor by block and lane offsets computed from its length; a wrong offset that runs past the
+        tensor lands in the guard, and :meth:`check_canaries` reports it.  (compute-sanitizer's memcheck does
+        the same job where it is available; this works everywhere and across ranks, since peers write into
+        this heap too.)"""
+        self._canaries = [] if on else None
+
+    def check_canaries(self, synchronize: bool = True) -> int:
+        """Raise if any guard block was overwritten; returns the number of guards checked."""
+        if self._canaries is None:
+            return 0
+        if synchronize:
+            torch.cuda.synchronize(self.device)
+        hit = [what for guard, what in self._canaries if not bool((guard == CANARY_BYTE).all())]
+        if hit:
+            raise FlexTreeError(8, f"rank {self.rank}: memory behind these heap tensors was overwritten: " + "; ".join(hit))
+        return len(self._canaries)
 
     def in_heap(self, t: torch.Tensor) -> bool:
         if self._heap_range is None:
