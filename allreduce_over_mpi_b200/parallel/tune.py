@@ -11,7 +11,8 @@ Output: a calibration file with
     once, one-shot limit and NVLS bandwidth;
   * ``table``   - per world size, the measured winner (algorithm, shape) per message size,
     which the communicator consults before falling back to the model;
-  * ``fit``     - predicted vs measured time per row, so the model's error is on record.
+  * ``fit``     - predicted vs measured time per row, so the model's error is on record
+    (``python -m allreduce_over_mpi_b200.parallel.tune --report [calibration.json]`` prints a summary).
 
 This is the re-derivation, on measured B200 numbers, of the reference's constants lo / co /
 bo / o (cost_model/CostModel.h:3-4, :24, :37), which were fitted to a 16-host Ethernet cluster.
@@ -150,7 +151,49 @@ def fit_params(rows) -> tuple[CostParams, list]:
     return p, fit
 
 
+def report(path: str) -> str:
+    """Predicted against measured, from the ``fit`` section of a calibration file: per world size the
+    median and worst relative error of the model over the staged shapes, and how often the shape the
+    model ranks first is the one that measured fastest (or within 3 % of it)."""
+    with open(path) as f:
+        doc = json.load(f)
+    detail = doc.get("fit", {}).get("detail", [])
+    out = [f"cost model v1 fit: {len(detail)} measured staged runs, median |error| {doc.get('fit', {}).get('median_abs_rel_err')}",
+           "", "| world | runs | median abs err | worst err | sizes | model's first choice fastest (within 3 %) |", "|---|---|---|---|---|---|"]
+    by_world = defaultdict(list)
+    for d in detail:
+        by_world[d["world"]].append(d)
+    for world in sorted(by_world):
+        rows = by_world[world]
+        errs = sorted(abs(d["rel_err"]) for d in rows)
+        worst = max(rows, key=lambda d: abs(d["rel_err"]))
+        by_size = defaultdict(dict)
+        for d in rows:   # a shape measured twice: keep the faster run
+            t = by_size[d["bytes"]].get(d["shape"])
+            if t is None or d["measured_us"] < t[0]:
+                by_size[d["bytes"]][d["shape"]] = (d["measured_us"], d["predicted_us"])
+        sizes = [b for b, shapes in by_size.items() if len(shapes) > 1]
+        right = 0
+        for b in sizes:
+            shapes = by_size[b]
+            pick = min(shapes, key=lambda k: shapes[k][1])
+            best = min(v[0] for v in shapes.values())
+            right += shapes[pick][0] <= best * 1.03
+        out.append(f"| {world} | {len(rows)} | {errs[len(errs) // 2]:.3f} | {worst['rel_err']:+.3f} ({worst['shape']}, {worst['bytes']} B) | "
+                   f"{len(sizes)} | {right} of {len(sizes)} |" if sizes else
+                   f"| {world} | {len(rows)} | {errs[len(errs) // 2]:.3f} | {worst['rel_err']:+.3f} ({worst['shape']}, {worst['bytes']} B) | 0 | one shape only |")
+    p = doc.get("params", {})
+    out += ["", "fitted constants: " + ", ".join(f"{k} = {p[k]:.4g}" for k in ("launch_us", "sync_us", "stage_floor_us", "link_gbs", "nvls_gbs",
+                                                                              "ll_us", "push_gain", "hbm_gbs") if k in p),
+            "link efficiency by number of peers read at once: " + ", ".join(f"{k}: {v}" for k, v in sorted(p.get("peer_eff", {}).items(), key=lambda kv: int(kv[0])))]
+    return "\n".join(out)
+
+
 def main(argv=None):
+    argv = sys.argv[1:] if argv is None else list(argv)
+    if argv and argv[0] == "--report":
+        print(report(argv[1] if len(argv) > 1 else planner.calibration_path()))
+        return 0
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("sweeps", nargs="+")
     ap.add_argument("--out", default=planner.calibration_path())
