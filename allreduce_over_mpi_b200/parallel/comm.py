@@ -316,6 +316,26 @@ class _CommBase:
         self._phase(tensor, True, "sum", shape, 1.0, stream)
         return tensor
 
+    def profile_phases(self, tensor: torch.Tensor, shape=None, op: str = "sum", iters: int = 5) -> dict:
+        """Device time (ms, this rank) of the two halves of the staged all-reduce on a heap tensor, each
+        issued as a call of its own between CUDA events: what the reference's SHOW_TIME switch logs with
+        MPI_Wtime around its reduce-scatter and all-gather loops (allreduce_over_mpi/mpi_mod.hpp:31-35,
+        :1597-1599, :1645-1647).  The tensor's contents are reduced ``iters + 1`` times."""
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        acc = [0.0, 0.0]
+        self.reduce_scatter(tensor, op=op, shape=shape)     # warm-up: plan upload, first touch
+        self.all_gather(tensor, shape=shape)
+        for _ in range(iters):
+            ev[0].record()
+            self.reduce_scatter(tensor, op=op, shape=shape)
+            ev[1].record()
+            self.all_gather(tensor, shape=shape)
+            ev[2].record()
+            ev[2].synchronize()
+            acc[0] += ev[0].elapsed_time(ev[1]) / iters
+            acc[1] += ev[1].elapsed_time(ev[2]) / iters
+        return {"reduce_scatter_ms": acc[0], "all_gather_ms": acc[1], "shape": str(self._phase_shape(shape))}
+
     # -- health
     def status(self) -> dict:
         """Status block written by device-side bounded waits (call after synchronising)."""

@@ -87,6 +87,11 @@ def main():
         torch.cuda.synchronize()
         comm.check()
         good = good and bool(torch.allclose(sym, torch.ones_like(sym), atol=1e-5))
+        sym.zero_()
+        times = comm.profile_phases(sym, iters=3)
+        comm.check()
+        good = good and times["reduce_scatter_ms"] > 0 and times["all_gather_ms"] > 0
+        report["phase_ms"] = times
         flags = [None] * world
         dist.all_gather_object(flags, good)
         if rank == 0:
