@@ -9,7 +9,8 @@
 //   --comm-type  flextree = GPU ranks over NVLink peer memory, one host thread per GPU in this
 //                process; threads = CPU ranks (thread world, host memory); nccl = the vendor
 //                library's own all-reduce on the same GPUs (the comparison arm, like the reference's
-//                "--comm-type mpi"); libnccl is opened at run time, nothing links against it
+//                "--comm-type mpi", which is accepted as another name for it); libnccl is opened at run
+//                time, nothing links against it
 //   --to-file    write one time per line to "<tag.>N.len.<w0-w1-+L>.ar_test.<epoch>.txt"
 //   --check      closed-form check: data[i] = i*0.1 on every rank, so after R in-place sums every
 //                rank must hold i*0.1*N^R (two-sided, relative tolerance)
@@ -110,6 +111,7 @@ int main(int argc, char** argv) {
     else if (a == "--version") { printf("FlexTree Standalone Benchmark\nversion: %s\n", ft_version()); return 0; }
     else { fprintf(stderr, "unknown parameter: %s\n", a.c_str()); return 1; }
   }
+  if (o.comm == "mpi") o.comm = "nccl";   // the reference's name for "the library's own all-reduce"
   const bool use_nccl = o.comm == "nccl";
   const bool gpu = o.comm == "flextree" || use_nccl;
   if (!gpu && o.comm != "threads") { fprintf(stderr, "unknown comm type: %s\n", o.comm.c_str()); return 1; }
