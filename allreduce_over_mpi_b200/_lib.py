@@ -74,6 +74,7 @@ def _declare(lib):
         "ft_run_plan_snapshot_range": (i, [i, *shape, i, i, C.POINTER(vp), u64, u64, i, i]),
         "ft_plan_rs_holders": (i, [i, *shape, C.POINTER(u64)]),
         "ft_dev_plan_check": (i, [i, *shape, i, C.c_char_p, sz]),
+        "ft_context_describe": (sz, [i, i, i, u64, i, C.c_char_p, sz]),
         "ft_cpu_world_create": (vp, [i, dbl]),
         "ft_cpu_world_destroy": (None, [vp]),
         "ft_cpu_allreduce": (i, [vp, i, *shape, i, i, vp, vp, u64, u64, i, i, i, ip]),

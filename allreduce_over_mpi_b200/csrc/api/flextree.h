@@ -76,6 +76,12 @@ int ft_dev_plan_check(int world, const int* widths, int nw, int lonely, int ring
 /* machine-readable plan: JSON {"world":..,"stages":..,"ranks":[[{"rs":1,"sync":[..],"pulls":[[block,reduce,[srcs]],..]},..],..]} */
 size_t ft_plan_json(int world, const int* widths, int nw, int lonely, int ring, char* buf, size_t cap);
 
+/* one line with the per-call quantities the reference keeps in FlexTree_Context and prints with
+ * show_context() (mpi_mod.hpp:776-801): "num_nodes=.., node_label=.., num_lonely=.., data_size=..,
+ * num_split=.., split_size=.., data_size_aligned=.., type_size=.., has_lonely=..".
+ * MPI_Allreduce_FT prints it to stderr on every call when FT_DEBUG=1 is set. */
+size_t ft_context_describe(int world, int rank, int lonely, uint64_t count, int dtype, char* buf, size_t cap);
+
 /* ---- CPU reductions and executors ---- */
 int ft_cpu_reduce(int op, int dtype, const void* const* src, void* dst, int n, size_t len, int threads);
 /* all ranks in the calling thread, in place on bufs[rank] */

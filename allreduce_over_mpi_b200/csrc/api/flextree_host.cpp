@@ -209,6 +209,16 @@ int ft_run_plan_snapshot(int world, const int* widths, int nw, int lonely, int r
                                bufs, count, block_elems);
 }
 
+size_t ft_context_describe(int world, int rank, int lonely, uint64_t count, int dtype, char* buf, size_t cap) {
+  // the fields of the reference's per-call context, in its order and spelling (mpi_mod.hpp:776-801)
+  const uint64_t split = world > 0 ? (count + world - 1) / (uint64_t)world : 0;
+  std::ostringstream os;
+  os << "num_nodes=" << world << ", node_label=" << rank << ", num_lonely=" << lonely << ", data_size=" << count
+     << ", num_split=" << world - lonely << ", split_size=" << split << ", data_size_aligned=" << split * (uint64_t)world
+     << ", type_size=" << ft_dtype_size((ft_dtype)dtype) << ", has_lonely=" << (lonely > 0 ? 1 : 0) << "\n";
+  return put(os.str(), buf, cap);
+}
+
 int ft_run_plan_snapshot_range(int world, const int* widths, int nw, int lonely, int ring, int op, int dtype,
                                void* const* bufs, uint64_t count, uint64_t block_elems, int stage_begin, int stage_end) {
   return ft::run_plan_snapshot(cached_plan(world, make_shape(widths, nw, lonely, ring)), (ft_op)op, (ft_dtype)dtype,

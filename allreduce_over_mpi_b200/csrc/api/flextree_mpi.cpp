@@ -107,6 +107,13 @@ int MPI_Allreduce_FT_c(const void* sendbuf, void* recvbuf, size_t count, FT_Data
   ft::ShapeConfig cfg = ft::shape_from_env(world);
   if (!cfg.ok()) return fail(FT_ERR_INVALID_TOPO, cfg.error);
   ft::Shape shape = cfg.shape;
+  if (const char* dbg = std::getenv("FT_DEBUG"); dbg && dbg[0] == '1') {
+    int rank = 0;
+    FT_Comm_rank(comm, &rank);
+    char line[256];
+    ft_context_describe(world, rank, shape.lonely, count, datatype, line, sizeof line);
+    std::fprintf(stderr, "%s", line);
+  }
 
   if (comm->threads) {
     if (world <= 1) {

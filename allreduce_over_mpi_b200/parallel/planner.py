@@ -255,6 +255,13 @@ def describe(world: int, shape: Shape, rank: int, count: int = 0, block_elems: i
     return text_call(lib().ft_plan_describe, world, *shape.c_args(), rank, count, block_elems)
 
 
+def context(world: int, rank: int, count: int, dtype: torch.dtype = torch.float32, lonely: int = 0) -> dict:
+    """The per-call quantities of the reference's FlexTree_Context (mpi_mod.hpp:776-801) as a dict:
+    num_nodes, node_label, num_lonely, data_size, num_split, split_size, data_size_aligned, type_size, has_lonely."""
+    line = text_call(lib().ft_context_describe, world, rank, lonely, count, ft_dtype(dtype))
+    return {k: int(v) for k, v in (kv.split("=") for kv in line.strip().split(", "))}
+
+
 def plan_json(world: int, shape: Shape) -> dict:
     return json.loads(text_call(lib().ft_plan_json, world, *shape.c_args(), cap=1 << 20))
 

@@ -126,3 +126,22 @@ def test_errors_are_returned_not_fatal(env, capfd):
     assert run_world(2, bad_type) == [(2, 3, 2)] * 2
     err = capfd.readouterr().err
     assert "is not supported in MPI mode." in err and "Unsupported op 100" in err
+
+
+def test_call_context_record_and_debug_print(env, capfd):
+    """The per-call quantities the reference keeps in FlexTree_Context (mpi_mod.hpp:776-801): split size
+    is ceil(count / N) whatever the tree, the aligned size is N splits; FT_DEBUG=1 prints them per call."""
+    from allreduce_over_mpi_b200.parallel import planner as P
+    c = P.context(7, 3, 27, torch.float32, lonely=1)
+    assert c == {"num_nodes": 7, "node_label": 3, "num_lonely": 1, "data_size": 27, "num_split": 6, "split_size": 4,
+                 "data_size_aligned": 28, "type_size": 4, "has_lonely": 1}
+    assert P.context(10, 0, 1, torch.float64)["data_size_aligned"] == 10     # ten ranks, one element: nine empty blocks
+    env["FT_TOPO"], env["FT_LONELY"], env["FT_DEBUG"] = "2,2", "1", "1"
+    try:
+        def rank_fn(r, comm):
+            return M.MPI_Allreduce_FT(M.IN_PLACE, torch.ones(27), 27, M.MPI_FLOAT, M.MPI_SUM, comm)
+        assert run_world(5, rank_fn) == [0] * 5
+    finally:
+        env.pop("FT_DEBUG", None)
+    err = capfd.readouterr().err
+    assert "num_nodes=5, node_label=4, num_lonely=1, data_size=27, num_split=4, split_size=6, data_size_aligned=30, type_size=4, has_lonely=1" in err
