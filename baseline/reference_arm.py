@@ -93,9 +93,10 @@ def _mpi(a, world: int, rank: int) -> dict:
         else:
             times = [float(x) for x in open(files[0]).read().split()][-a.steps:]
             sec = sum(times) / len(times)
-            value = a.bytes / sec / 1e9 * (2 * (world - 1) / world)
+            per_rank = a.bytes / sec / 1e9 * (2 * (world - 1) / world)
             topo = env["FT_TOPO"]
-            out = {"metric": "all-reduce bus bandwidth GB/s (bytes/t * 2(N-1)/N), t = max over ranks", "value": round(value, 3),
+            out = {"metric": "all-reduce bus bandwidth GB/s, whole job = N x per-GPU busbw; busbw = bytes/t * 2(N-1)/N, t = max over ranks",
+                   "value": round(per_rank * world, 3), "per_gpu_busbw_GBps": round(per_rank, 3),
                    "unit": "GB/s", "n_gpus": world, "steps": a.steps, "warmup": warm, "ms_per_step": round(sec * 1e3, 3),
                    "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "float32",
                    "data": "reference benchmark's own fill (i * 0.1 on every rank)", "impl": "reference",

@@ -7,8 +7,9 @@
 
   python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N --steps K --warmup W
       FlexTree all-reduce over NVLink peer memory on N B200s: a step is one in-place all-reduce of
-      --bytes (default 256 MiB) fp32; value = bus bandwidth (bytes/t) * 2(N-1)/N in GB/s,
-      t = max over ranks of CUDA-event time.  The NCCL number for the same buffer rides along.
+      --bytes (default 256 MiB) fp32 per GPU; per-GPU bus bandwidth = (bytes/t) * 2(N-1)/N in GB/s,
+      t = max over ranks of CUDA-event time; value = N x that (the whole job), the per-GPU figure
+      and the NCCL number for the same buffer ride along.
 
   --impl reference runs the unmodified reference code for the same metric (its CUDA reduce_sum_gpu
   launcher at N = 1, its MPI_Allreduce_FT over a shared-memory MPI shim at N > 1).
