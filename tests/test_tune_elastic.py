@@ -1,6 +1,8 @@
 """Calibration fit / choice table and re-planning after a lost rank (CPU)."""
 import json
 
+import torch
+
 from allreduce_over_mpi_b200.parallel import planner, tune
 from allreduce_over_mpi_b200.parallel.elastic import replan_after_failure
 from allreduce_over_mpi_b200.parallel.planner import CostParams, Shape
@@ -45,3 +47,37 @@ def test_replan_after_failure_uses_lonely_layouts():
     assert planner.validate_shape(7, r.shape) == "" and r.predicted_us > 0
     r = replan_after_failure(6, [0, 5], 1024)
     assert r.world == 4 and r.algo in ("oneshot", "staged", "ll")
+
+
+def test_selection_from_the_committed_calibration():
+    """What the communicator picks per message size on an 8-GPU box, from the committed table and model
+    (pure host logic: no GPU is touched)."""
+    from allreduce_over_mpi_b200.parallel.comm import _CommBase
+
+    def comm(world, nvls):
+        c = _CommBase()
+        c.world, c.has_nvls, c.staging_bytes = world, nvls, 64 << 20
+        return c
+
+    c8 = comm(8, True)
+    assert c8.choose(1024, True, torch.float32)[0] == "ll"
+    assert c8.choose(1 << 30, True, torch.float32)[0] == "nvls"
+    assert c8.choose(256 << 20, True, torch.bfloat16)[0] == "nvls"
+    # integers, tensors outside the heap and boxes without multicast never get the switch reduction
+    for args in ((1 << 30, True, torch.int32), (32 << 20, False, torch.float32)):
+        assert c8.choose(*args)[0] not in ("nvls", "hybrid")
+    name, shape = comm(8, False).choose(1 << 30, True, torch.float32)
+    assert name in ("staged", "push") and planner.validate_shape(8, shape) == ""
+    # outside the heap the in-place-only algorithms are out, and one-shot needs the message to fit a slot
+    name, shape = c8.choose(32 << 20, False, torch.float32)
+    assert name in ("staged", "oneshot") and planner.validate_shape(8, shape) == ""
+    assert c8.choose(128 << 20, False, torch.float32)[0] == "staged"
+    # every world size from 2 to 8 gets a valid answer at every size, cached on the second ask
+    for world in range(2, 9):
+        c = comm(world, True)
+        for nbytes in (16, 4096, 1 << 20, 48 << 20, 3 << 30):
+            for in_heap in (True, False):
+                name, shape = c.choose(nbytes, in_heap, torch.float32)
+                assert name.split("-")[0] in ("ll", "oneshot", "staged", "push", "nvls", "hybrid")
+                assert planner.validate_shape(world, shape) == ""
+                assert c.choose(nbytes, in_heap, torch.float32) == (name, shape)
