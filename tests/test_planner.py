@@ -287,3 +287,31 @@ def test_fault_injection_on_host():
         assert all(x[2] == 2 or x[0] == 5 for x in bad)  # the culprit is named (or a knock-on timeout)
         assert any(x[2] == 2 for x in bad)
         w.close()
+
+
+def test_env_syntax_fuzz_never_yields_an_unusable_shape():
+    """Whatever FT_TOPO / FT_LONELY hold, the parser either refuses with a message or returns a shape
+    whose plan is race-free and sums correctly (the reference exits, asserts or mis-schedules on
+    several of these, mpi_mod.hpp:1447-1475)."""
+    from hypothesis import given, settings, strategies as st
+
+    part = st.one_of(st.integers(-2, 12).map(str), st.sampled_from(["", " ", "a", "2x", "+1", "99999999999", "auto", "0"]))
+    topo = st.lists(part, max_size=5).map(",".join)
+    lonely = st.one_of(st.none(), st.integers(-3, 9).map(str), st.sampled_from(["", "x", "1.5", " 2"]))
+
+    @settings(max_examples=400, deadline=None)
+    @given(topo, lonely, st.integers(1, 24))
+    def run(t, l, world):
+        try:
+            shape, is_auto = P.parse_topo(t, l, world)
+        except Exception as e:  # noqa: BLE001
+            assert "invalid FT_" in str(e), (t, l, world, str(e))
+            return
+        assert P.validate_shape(world, shape) == "", (t, l, world, str(shape))
+        assert P.plan_check(world, shape) == ""
+        bufs = make_bufs(world, 17, torch.float64)
+        want = torch.stack(bufs).sum(0)
+        P.run_plan_snapshot(shape, bufs)
+        assert all(torch.allclose(b, want, rtol=0, atol=1e-12) for b in bufs), (t, l, world, str(shape))
+
+    run()
