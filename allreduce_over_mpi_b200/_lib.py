@@ -78,6 +78,7 @@ def _declare(lib):
         "ft_cpu_world_create": (vp, [i, dbl]),
         "ft_cpu_world_destroy": (None, [vp]),
         "ft_cpu_allreduce": (i, [vp, i, *shape, i, i, vp, vp, u64, u64, i, i, i, ip]),
+        "ft_cpu_phase": (i, [vp, i, *shape, i, i, vp, u64, u64, i, ip]),
         "ft_mpi_thread_rank": (vp, [vp, i]),
         "ft_mpi_from_comm": (vp, [vp, vp]),
         "ft_mpi_comm_free": (None, [vp]),

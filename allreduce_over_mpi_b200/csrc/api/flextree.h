@@ -104,6 +104,11 @@ void ft_cpu_world_destroy(ft_cpu_world* w);
 int ft_cpu_allreduce(ft_cpu_world* w, int rank, const int* widths, int nw, int lonely, int ring, int op, int dtype,
                      const void* sendbuf, void* recvbuf, uint64_t count, uint64_t block_elems, int fault_kind,
                      int fault_rank, int fault_stage, int* status_out);
+/* one half of the plan as a call of its own, in place on buf: phase 1 = reduce-scatter stages,
+ * 2 = all-gather stages; closes with a rendezvous of all ranks (the host twin of
+ * ft_reduce_scatter / ft_all_gather in flextree_comm.h, same rendezvous numbering) */
+int ft_cpu_phase(ft_cpu_world* w, int rank, const int* widths, int nw, int lonely, int ring, int op, int dtype, void* buf,
+                 uint64_t count, uint64_t block_elems, int phase, int* status_out);
 
 /* ---- single-GPU n-way reduction (reference: vector_add/reduce_sum_gpu.h) ---- */
 /* dst[i] = src[0][i] (op) ... (op) src[n-1][i], n in [1, FT_MAX_FANIN]; src/dst are device

@@ -262,5 +262,13 @@ int ft_cpu_allreduce(ft_cpu_world* w, int rank, const int* widths, int nw, int l
   if (status_out) { status_out[0] = st.code; status_out[1] = st.stage; status_out[2] = st.peer; }
   return st.code;
 }
+int ft_cpu_phase(ft_cpu_world* w, int rank, const int* widths, int nw, int lonely, int ring, int op, int dtype, void* buf,
+                 uint64_t count, uint64_t block_elems, int phase, int* status_out) {
+  if (!w || rank < 0 || rank >= w->w.n || (phase != 1 && phase != 2)) return FT_ERR_INVALID_ARG;
+  const auto& p = cached_plan(w->w.n, make_shape(widths, nw, lonely, ring));
+  ft::RankStatus st = ft::cpu_allreduce(w->w, rank, p, (ft_op)op, (ft_dtype)dtype, nullptr, buf, count, block_elems, nullptr, 1, phase);
+  if (status_out) { status_out[0] = st.code; status_out[1] = st.stage; status_out[2] = st.peer; }
+  return st.code;
+}
 
 }  // extern "C"

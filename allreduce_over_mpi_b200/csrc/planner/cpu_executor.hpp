@@ -125,9 +125,13 @@ inline RankStatus rendezvous(CpuWorld& w, int rank, const std::vector<int>& peer
 
 // One rank's part of an all-reduce; call from n threads with the same arguments
 // (sendbuf == nullptr or == recvbuf means in place).  Returns the rank's status.
+// `phase` runs one half of the plan as a call of its own, the way the device entry points
+// ft_reduce_scatter / ft_all_gather do: 1 = stages [0, S/2), 2 = stages [S/2, S); each stage keeps
+// its rendezvous number inside the call, and the call closes with a rendezvous of ALL ranks (the
+// caller may rewrite any part of its buffer afterwards).
 inline RankStatus cpu_allreduce(CpuWorld& w, int rank, const Plan& p, ft_op op, ft_dtype dt, const void* sendbuf,
                                 void* recvbuf, uint64_t count, uint64_t block_elems = 0,
-                                const FaultSpec* fault = nullptr, int threads = 1) {
+                                const FaultSpec* fault = nullptr, int threads = 1, int phase = 0) {
   RankStatus st;
   if (!p.ok() || p.world != w.n) { st.code = FT_ERR_INVALID_TOPO; return st; }
   if (!ft_op_supported(op, dt)) {
@@ -141,11 +145,20 @@ inline RankStatus cpu_allreduce(CpuWorld& w, int rank, const Plan& p, ft_op op, 
   const uint32_t base = w.epoch[rank];
   w.epoch[rank] = base + (uint32_t)p.num_stages + 1;
   w.bufs[rank].store(recvbuf, std::memory_order_release);
-  for (int s = 0; s <= p.num_stages; ++s) {
-    if (fault && fault->rank == rank && fault->kind == Fault::LeaveEarly && fault->stage == s) return st;
-    st = detail::rendezvous(w, rank, p.sync[s][rank], base + (uint32_t)s + 1, s, p.num_stages + 1, fault);
+  const int first = phase == 2 ? p.num_stages / 2 : 0;
+  const int last = phase == 1 ? p.num_stages / 2 : p.num_stages;   // one past the last stage that runs
+  std::vector<int> everyone;
+  if (phase)
+    for (int q = 0; q < w.n; ++q)
+      if (q != rank) everyone.push_back(q);
+  for (int s = first; s <= last; ++s) {
+    const bool closing = s == last;
+    const int index = closing ? p.num_stages : s;
+    if (fault && fault->rank == rank && fault->kind == Fault::LeaveEarly && fault->stage == index) return st;
+    st = detail::rendezvous(w, rank, closing && phase ? everyone : p.sync[index][rank], base + (uint32_t)index + 1, index,
+                            p.num_stages + 1, fault);
     if (st.code != FT_OK) return st;
-    if (s == p.num_stages) break;
+    if (closing) break;
     for (const Pull& pl : p.stages[rank][s].pulls) {
       const uint64_t off = g.offset(pl.block), len = g.length(pl.block);
       if (!len) continue;

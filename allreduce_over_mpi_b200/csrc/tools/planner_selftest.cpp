@@ -129,10 +129,48 @@ static void thread_world(bool with_fault) {
   }
 }
 
+// Reduce-scatter and all-gather as calls of their own, three rounds without any host barrier in
+// between, with a whole all-reduce after each pair: rendezvous numbers keep growing across the three
+// kinds of call and the closing all-rank rendezvous lets every rank overwrite its buffer right away.
+static void thread_world_phases() {
+  for (const char* text : {"2,2", "2,3", "2,2,2", "1"}) {
+    const std::string t = text;
+    const int n = t == "2,2" ? 4 : (t == "2,3" ? 7 : (t == "1" ? 5 : 8));
+    ft::ShapeConfig cfg = ft::parse_topo(text, t == "2,3" ? "1" : "", n);
+    EXPECT(cfg.ok());
+    ft::Plan p = ft::build_plan(n, cfg.shape);
+    const std::vector<uint64_t> holders = ft::rs_holders(p);
+    ft::CpuWorld w(n);
+    w.timeout_s = 20.0;
+    const uint64_t count = 1031;
+    const ft::Blocks g(count, n);
+    std::vector<std::vector<double>> data(n, std::vector<double>(count));
+    std::vector<int> bad(n, 0);
+    std::vector<std::thread> th;
+    for (int r = 0; r < n; ++r)
+      th.emplace_back([&, r] {
+        for (int round = 0; round < 3; ++round) {
+          for (uint64_t i = 0; i < count; ++i) data[r][i] = (double)(r + 1 + round);
+          bad[r] |= ft::cpu_allreduce(w, r, p, FT_SUM, FT_F64, nullptr, data[r].data(), count, 0, nullptr, 1, 1).code != FT_OK;
+          for (int b = 0; b < n; ++b)   // wipe everything this rank does not own
+            if (!(holders[b] >> r & 1))
+              for (uint64_t i = g.offset(b); i < g.offset(b) + g.length(b); ++i) data[r][i] = -1e300;
+          bad[r] |= ft::cpu_allreduce(w, r, p, FT_SUM, FT_F64, nullptr, data[r].data(), count, 0, nullptr, 1, 2).code != FT_OK;
+          bad[r] |= ft::cpu_allreduce(w, r, p, FT_SUM, FT_F64, nullptr, data[r].data(), count).code != FT_OK;
+          const double want = (double)n * (n * (n + 1) / 2 + n * round);
+          for (uint64_t i = 0; i < count; ++i) bad[r] |= data[r][i] != want;
+        }
+      });
+    for (auto& x : th) x.join();
+    for (int r = 0; r < n; ++r) EXPECT(!bad[r]);
+  }
+}
+
 int main(int argc, char** argv) {
   const bool threads = argc > 1 && !std::strcmp(argv[1], "threads");
   if (!threads) { plans_and_snapshot(); device_tables(); enumerators_and_models(); }
   thread_world(false);
+  thread_world_phases();
   thread_world(true);
   std::printf(fails ? "%d FAILURES\n" : "selftest ok\n", fails);
   return fails ? 1 : 0;

@@ -327,6 +327,14 @@ class CpuWorld:
                                block_elems, fault[0], fault[1], fault[2], st)
         return st[0], st[1], st[2]
 
+    def phase_rank(self, rank: int, shape: Shape, buf: torch.Tensor, phase: str, op: str = "sum",
+                   block_elems: int = 0) -> tuple[int, int, int]:
+        """One rank's call of one half of the plan, in place: ``phase`` "reduce_scatter" or "all_gather"."""
+        st = (C.c_int * 3)()
+        lib().ft_cpu_phase(self._h, rank, *shape.c_args(), OPS[op], ft_dtype(buf.dtype), buf.data_ptr(), buf.numel(),
+                           block_elems, {"reduce_scatter": 1, "all_gather": 2}[phase], st)
+        return st[0], st[1], st[2]
+
     def allreduce(self, shape: Shape, bufs: Sequence[torch.Tensor], op: str = "sum", block_elems: int = 0,
                   fault=(0, -1, 0)) -> list[tuple[int, int, int]]:
         """Run every rank on its own thread, in place on ``bufs``; returns per-rank status."""

@@ -274,6 +274,41 @@ def test_threaded_world_matches_oracle():
         w.close()
 
 
+def test_threaded_world_phases_as_calls_of_their_own():
+    """Thread-per-rank world with the device protocol: reduce-scatter and all-gather as separate calls,
+    each closed by an all-rank rendezvous, interleaved with whole all-reduces; the ranks poison what they
+    do not own between the two halves, which is only safe because the closing rendezvous is global."""
+    import threading
+    for text in ["2", "ring3", "4", "2*2+1", "2*3+1", "2*2*2", "ring5", "2*4"]:
+        s = Shape.parse(text)
+        n, count = s.world, 4001
+        w = P.CpuWorld(n, timeout_s=20)
+        holders = P.rs_holders(n, s)
+        B = -(-count // n)
+        results, status = [None] * n, [[] for _ in range(n)]
+
+        def rank_main(r):
+            mine = [b for b, hs in enumerate(holders) if r in hs]
+            for it in range(3):
+                buf = make_bufs(n, count, torch.float64, seed=it)[r]
+                status[r].append(w.phase_rank(r, s, buf, "reduce_scatter"))
+                keep = {b: buf[min(count, b * B):min(count, (b + 1) * B)].clone() for b in mine}
+                buf.fill_(float("nan"))
+                for b, v in keep.items():
+                    buf[min(count, b * B):min(count, (b + 1) * B)] = v
+                status[r].append(w.phase_rank(r, s, buf, "all_gather"))
+                status[r].append(w.allreduce_rank(r, s, buf))          # a whole call in between keeps the numbering honest
+                results[r] = buf
+        ts = [threading.Thread(target=rank_main, args=(r,)) for r in range(n)]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+        want = torch.stack(make_bufs(n, count, torch.float64, seed=2)).sum(0) * n
+        for r in range(n):
+            assert all(x[0] == 0 for x in status[r]), (text, r, status[r])
+            assert torch.allclose(results[r], want, rtol=0, atol=1e-9), (text, r)
+        w.close()
+
+
 def test_fault_injection_on_host():
     """A rank that never signals / leaves early makes its peers time out; a wrong epoch is a protocol error."""
     s = Shape.parse("2*2")
