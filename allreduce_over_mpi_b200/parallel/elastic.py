@@ -36,3 +36,55 @@ def replan_after_failure(world: int, failed: set[int] | list[int], nbytes: int, 
     algo, shape, us = planner.pick_algorithm(n, nbytes, params or CostParams.load(), allow_oneshot=True, allow_nvls=nvls)
     return Replan(n, {old: new for new, old in enumerate(survivors)}, algo, shape, us,
                   [str(s) for s in planner.executable_shapes(n)])
+
+
+class RankLost(RuntimeError):
+    """Raised on the host, between steps, when peers stopped reporting."""
+
+    def __init__(self, lost):
+        self.lost = set(lost)
+        super().__init__(f"ranks {sorted(self.lost)} stopped reporting")
+
+
+class Liveness:
+    """Host-side liveness over a ``torch.distributed`` store (TCPStore, FileStore, HashStore).
+
+    Every rank calls :meth:`beat` once per step (it bumps a counter under its own key) and
+    :meth:`guard` before it launches the next collective.  A peer whose counter has not moved for
+    ``timeout_s`` of this rank's own clock is reported lost, so the survivors learn of it on the
+    host and never launch a kernel that would wait for it (the device-side wait limit remains the
+    second line of defence).  No clocks are compared between ranks.  The store should live in a
+    process that outlasts the ranks (the launcher's), or on a rank that is not expected to leave.
+    """
+
+    def __init__(self, store, rank: int, world: int, timeout_s: float = 5.0, prefix: str = "ft/alive/"):
+        import time
+        self._now = time.monotonic
+        self.store, self.rank, self.world, self.timeout_s, self.prefix = store, rank, world, timeout_s, prefix
+        self._count = 0
+        t = self._now()
+        self._seen = {r: (None, t) for r in range(world) if r != rank}
+        self.beat()
+
+    def beat(self):
+        self._count += 1
+        self.store.set(f"{self.prefix}{self.rank}", str(self._count))
+
+    def poll(self) -> set[int]:
+        """Ranks that have been silent for longer than the timeout."""
+        now, lost = self._now(), set()
+        for r, (last, since) in self._seen.items():
+            key = f"{self.prefix}{r}"
+            val = bytes(self.store.get(key)) if self.store.check([key]) else None
+            if val != last:
+                self._seen[r] = (val, now)
+            elif now - since > self.timeout_s:
+                lost.add(r)
+        return lost
+
+    def guard(self):
+        """Call between steps: beat, then raise :class:`RankLost` if a peer has gone silent."""
+        self.beat()
+        lost = self.poll()
+        if lost:
+            raise RankLost(lost)

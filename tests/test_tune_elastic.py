@@ -81,3 +81,66 @@ def test_selection_from_the_committed_calibration():
                 assert name.split("-")[0] in ("ll", "oneshot", "staged", "push", "nvls", "hybrid")
                 assert planner.validate_shape(world, shape) == ""
                 assert c.choose(nbytes, in_heap, torch.float32) == (name, shape)
+
+
+def _liveness_worker(rank, world, port, leave_after, q):
+    import time
+    import torch.distributed as dist
+    from datetime import timedelta
+    from allreduce_over_mpi_b200.parallel.elastic import Liveness, RankLost
+    store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=timedelta(seconds=20))
+    live = Liveness(store, rank, world, timeout_s=0.6)
+    step = 0
+    try:
+        for step in range(200):
+            if rank == leave_after[0] and step == leave_after[1]:
+                q.put((rank, "left", step))
+                time.sleep(3.0)      # stays quiet (keeps the process, and rank 0's store, alive) while the others notice
+                return
+            live.guard()              # between steps, before the next launch
+            time.sleep(0.02)          # the step
+        q.put((rank, "finished", step))
+    except RankLost as e:
+        plan = replan_after_failure(world, e.lost, 64 << 20, CostParams(link_gbs=600, sync_us=5, launch_us=20))
+        q.put((rank, "lost", sorted(e.lost), plan.world, plan.rank_map[rank], str(plan.shape)))
+        time.sleep(1.0)
+
+
+def test_lost_rank_is_noticed_on_the_host_between_steps():
+    """Three CPU processes around a TCP store; rank 2 stops stepping after step 10.  The other two learn
+    of it from the store before a later step, agree on who is gone and on the plan for the smaller world."""
+    import multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29611
+    procs = [ctx.Process(target=_liveness_worker, args=(r, 3, port, (2, 10), q)) for r in range(3)]
+    [p.start() for p in procs]
+    got = [q.get(timeout=60) for _ in range(3)]
+    [p.join(timeout=30) for p in procs]
+    by_rank = {g[0]: g for g in got}
+    assert by_rank[2][1] == "left"
+    for r in (0, 1):
+        assert by_rank[r][1] == "lost" and by_rank[r][2] == [2], by_rank
+        assert by_rank[r][3] == 2 and by_rank[r][4] == r and by_rank[r][5] in ("2", "ring2")
+    assert all(p.exitcode == 0 for p in procs)
+
+
+def test_liveness_in_one_process():
+    import time
+    import torch.distributed as dist
+    from allreduce_over_mpi_b200.parallel.elastic import Liveness, RankLost
+    store = dist.HashStore()
+    a, b = Liveness(store, 0, 2, timeout_s=0.2), Liveness(store, 1, 2, timeout_s=0.2)
+    for _ in range(5):
+        a.guard(); b.guard()
+        time.sleep(0.05)
+    assert a.poll() == set()       # picks up b's last beat
+    time.sleep(0.3)
+    a.beat()                       # a keeps stepping, b has stopped
+    assert a.poll() == {1}
+    try:
+        a.guard()
+        raise AssertionError("expected RankLost")
+    except RankLost as e:
+        assert e.lost == {1}
+    assert b.poll() == set()       # b still sees a's counter moving
