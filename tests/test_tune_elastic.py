@@ -112,7 +112,10 @@ def test_lost_rank_is_noticed_on_the_host_between_steps():
     import multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29611
+    import socket
+    with socket.socket() as sk:      # a port that is free right now
+        sk.bind(("127.0.0.1", 0))
+        port = sk.getsockname()[1]
     procs = [ctx.Process(target=_liveness_worker, args=(r, 3, port, (2, 10), q)) for r in range(3)]
     [p.start() for p in procs]
     got = [q.get(timeout=60) for _ in range(3)]
