@@ -14,8 +14,8 @@
 //   --to-file    write one time per line to "<tag.>N.len.<w0-w1-+L>.ar_test.<epoch>.txt"
 //   --check      closed-form check: data[i] = i*0.1 on every rank, so after R in-place sums every
 //                rank must hold i*0.1*N^R (two-sided, relative tolerance)
-//   --phases     (flextree) every all-reduce is issued as its two halves, ft_reduce_scatter then
-//                ft_all_gather; with --check everything a rank does not own is overwritten with NaN
+//   --phases     (flextree, threads) every all-reduce is issued as its two halves, reduce-scatter then
+//                all-gather (ft_reduce_scatter / ft_all_gather on GPUs, ft_cpu_phase on threads); with --check everything a rank does not own is overwritten with NaN
 //                bit patterns between the two, so the gather has to rebuild it from the owners
 // The tree shape comes from FT_TOPO / FT_LONELY exactly as for the library entry point.
 // GPU times are CUDA-event intervals, reported as the maximum over ranks; CPU times are
@@ -161,7 +161,7 @@ int main(int argc, char** argv) {
 
   std::vector<uint64_t> holders(world, 0);
   if (o.phases) {
-    if (o.comm != "flextree") { fprintf(stderr, "--phases needs --comm-type flextree\n"); return 1; }
+    if (use_nccl) { fprintf(stderr, "--phases needs --comm-type flextree or threads\n"); return 1; }
     const ft::Shape& sh = cfg.shape;
     if (ft_plan_rs_holders(world, sh.widths.data(), (int)sh.widths.size(), sh.lonely, sh.ring, holders.data()) != FT_OK) {
       fprintf(stderr, "no plan for %s\n", sh.str().c_str());
@@ -227,7 +227,23 @@ int main(int argc, char** argv) {
         bar.wait();
         ft::Timer t;
         t.Start();
-        if (MPI_Allreduce_FT_c(FT_IN_PLACE, hostp, o.size, dtype, FT_OP_SUM, mc) != 0) bad[r] = 2;
+        if (o.phases) {
+          const ft::Shape& sh = cfg.shape;
+          const int nw = (int)sh.widths.size();
+          int st3[3];
+          if (ft_cpu_phase(cpu_world, r, sh.widths.data(), nw, sh.lonely, sh.ring, FT_SUM, dtype, hostp, o.size, 0, 1, st3) != FT_OK) bad[r] = 2;
+          if (o.check && world > 1) {   // wipe what this rank does not own (host blocks are ceil(size / world) elements)
+            const uint64_t B = (o.size + world - 1) / world;
+            for (int b = 0; b < world; ++b)
+              if (!(holders[b] >> r & 1)) {
+                const uint64_t lo = std::min<uint64_t>(o.size, b * B), hi = std::min<uint64_t>(o.size, (b + 1) * B);
+                std::memset((char*)hostp + lo * es, 0xFF, (hi - lo) * es);
+              }
+          }
+          if (ft_cpu_phase(cpu_world, r, sh.widths.data(), nw, sh.lonely, sh.ring, FT_SUM, dtype, hostp, o.size, 0, 2, st3) != FT_OK) bad[r] = 2;
+        } else if (MPI_Allreduce_FT_c(FT_IN_PLACE, hostp, o.size, dtype, FT_OP_SUM, mc) != 0) {
+          bad[r] = 2;
+        }
         t.Stop();
         times[r][i] = t.seconds();
       }

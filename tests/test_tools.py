@@ -56,8 +56,10 @@ def test_ft_bench_thread_world_check_and_file(tmp_path):
     assert rc == 0 and "FlexTree Standalone Benchmark" in out
     rc, _, err = run([exe, "--bogus"])
     assert rc == 1 and "unknown parameter" in err
-    rc, _, err = run([exe, "--comm-type", "threads", "--ranks", "2", "--phases"])
-    assert rc == 1 and "--phases needs --comm-type flextree" in err
+    # the two halves as calls of their own, everything a rank does not own wiped in between
+    rc, out, err = run([exe, "--comm-type", "threads", "--ranks", "7", "--size", "10007", "--repeat", "2", "--check", "--phases"],
+                       env={"FT_TOPO": "2,3", "FT_LONELY": "1"})
+    assert rc == 0 and "CHECK (test passed)" in out, err
 
 
 def test_reduce_bench_host_side(tmp_path):
