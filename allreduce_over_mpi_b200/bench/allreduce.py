@@ -63,6 +63,12 @@ def time_collective(fn, iters: int, warmup: int, flush: bool = True) -> float:
     return statistics.median(ms.tolist())
 
 
+# Roofline of an all-reduce on NVSwitch: each GPU must take in 2(N-1)/N * S bytes over its links, so the
+# bus bandwidth cannot exceed the per-direction link bandwidth; 770 GB/s is the measured peer-copy rate of this
+# pool's B200s (900 GB/s nominal).  The HBM side (at most ~3 S bytes per GPU) is an order of magnitude below its roof.
+LINK_GBPS = 770.0
+
+
 def busbw(nbytes: int, ms: float, world: int) -> float:
     return nbytes / (ms * 1e-3) / 1e9 * (2 * (world - 1) / world)
 
@@ -154,7 +160,8 @@ def sweep(a, comm: FlexTreeComm, rank: int, world: int) -> list[dict]:
                     comm.check()
                 ms = time_collective(fn, iters, a.warmup, flush=not a.no_flush)
                 comm.check()
-                row.update(ms=round(ms, 5), algbw_GBps=round(nbytes / ms / 1e6, 2), busbw_GBps=round(busbw(nbytes, ms, world), 2))
+                row.update(ms=round(ms, 5), algbw_GBps=round(nbytes / ms / 1e6, 2), busbw_GBps=round(busbw(nbytes, ms, world), 2),
+                           frac_of_link_roofline=round(busbw(nbytes, ms, world) / LINK_GBPS, 3))
                 rows.append(row)
                 if rank == 0:
                     print(json.dumps(row), flush=True)
@@ -169,7 +176,8 @@ def sweep(a, comm: FlexTreeComm, rank: int, world: int) -> list[dict]:
             if a.nccl:
                 ms = time_collective(lambda: dist.all_reduce(loc), iters, a.warmup, flush=not a.no_flush)
                 row = {"bench": "allreduce", "impl": "nccl", "bytes": nbytes, "dtype": dt_name, "world": world,
-                       "ms": round(ms, 5), "algbw_GBps": round(nbytes / ms / 1e6, 2), "busbw_GBps": round(busbw(nbytes, ms, world), 2)}
+                       "ms": round(ms, 5), "algbw_GBps": round(nbytes / ms / 1e6, 2), "busbw_GBps": round(busbw(nbytes, ms, world), 2),
+                       "frac_of_link_roofline": round(busbw(nbytes, ms, world) / LINK_GBPS, 3)}
                 rows.append(row)
                 if rank == 0:
                     print(json.dumps(row), flush=True)
