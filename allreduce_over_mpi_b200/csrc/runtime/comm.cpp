@@ -210,10 +210,13 @@ int get_plan(ft_comm* c, const ft::Shape& shape, DevPlanEntry** out) {
   return FT_OK;
 }
 
+// In the heap AND on a 16-byte boundary: only then may the kernels address the tensor in place with
+// vector loads.  A slice of a heap tensor that starts at an odd element is treated like any other
+// user tensor (staged through the slots, where alignment is handled element by element).
 bool in_heap(ft_comm* c, const void* p, size_t bytes) {
   const unsigned char* b = local_base(c);
   const unsigned char* q = (const unsigned char*)p;
-  return b && q >= b && q + bytes <= b + c->user_bytes;
+  return b && q >= b && q + bytes <= b + c->user_bytes && ((uintptr_t)q & 15) == 0;
 }
 
 // Elements per block: ceil(count/world) rounded up so that a block is a whole number of
@@ -317,7 +320,7 @@ int launch_oneshot_call(ft_comm* c, const Prepared& pr, const void* sendbuf, voi
 
 int launch_push_call(ft_comm* c, const Prepared& pr, const void* sendbuf, void* recvbuf, size_t count, float scale, bool do_sync,
                      cudaStream_t st) {
-  if (!pr.heap_resident) return fail(c, FT_ERR_INVALID_ARG, "the reduce+push all-reduce needs a tensor in the symmetric heap");
+  if (!pr.heap_resident) return fail(c, FT_ERR_INVALID_ARG, "the reduce+push all-reduce needs a 16-byte aligned tensor in the symmetric heap");
   if (sendbuf && sendbuf != recvbuf) FT_CUDA(c, cudaMemcpyAsync(recvbuf, sendbuf, pr.bytes, cudaMemcpyDeviceToDevice, st));
   ftk::NvlsArgs a{};
   a.work_off = (uint64_t)((unsigned char*)recvbuf - local_base(c));
@@ -644,7 +647,7 @@ int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, i
   if (algo == FT_ALGO_PUSH) return launch_push_call(c, pr, sendbuf, recvbuf, count, scale, true, st);
   if (algo == FT_ALGO_NVLS || algo == FT_ALGO_HYBRID) {
     if (!ft_comm_has_nvls(c)) return fail(c, FT_ERR_NOT_AVAILABLE, "NVLS multicast is not bound on this communicator");
-    if (!pr.heap_resident) return fail(c, FT_ERR_INVALID_ARG, "NVLS all-reduce needs a tensor in the symmetric heap");
+    if (!pr.heap_resident) return fail(c, FT_ERR_INVALID_ARG, "NVLS all-reduce needs a 16-byte aligned tensor in the symmetric heap");
     if (pr.bytes % 16) return fail(c, FT_ERR_INVALID_ARG, "NVLS all-reduce needs a multiple of 16 bytes");
     if (sendbuf && sendbuf != recvbuf) FT_CUDA(c, cudaMemcpyAsync(recvbuf, sendbuf, pr.bytes, cudaMemcpyDeviceToDevice, st));
     ftk::NvlsArgs a{};

@@ -174,8 +174,8 @@ class _CommBase:
         if self._heap_range is None:
             base = lib().ft_comm_heap_base(self._h) or 0
             self._heap_range = (base, base + lib().ft_comm_heap_bytes(self._h))
-        p = t.data_ptr()
-        return self._heap_range[0] <= p and p + t.numel() * t.element_size() <= self._heap_range[1]
+        p = t.data_ptr()   # in place only from a 16-byte boundary (the kernels use vector loads there)
+        return self._heap_range[0] <= p and p + t.numel() * t.element_size() <= self._heap_range[1] and p % 16 == 0
 
     # -- selection
     def choose(self, nbytes: int, in_heap: bool, dtype: torch.dtype) -> tuple[str, Shape]:

@@ -297,3 +297,31 @@ def test_guard_blocks_behind_heap_tensors_stay_intact():
     with pytest.raises(Exception, match="overwritten"):
         w.ranks[2].check_canaries()
     w.close()
+
+
+def test_unaligned_slice_of_a_heap_tensor_goes_through_the_slots():
+    """A view that starts at an odd element of a heap tensor is not on a 16-byte boundary: it must not be
+    addressed in place with vector loads.  It is reduced like any user tensor, and the elements around it
+    stay as they were."""
+    w = LocalWorld(4, heap_bytes=1 << 20, staging_bytes=1 << 20)
+    host = inputs(4, 3001, torch.float32, seed=21)
+    want = torch.stack(host).double().sum(0)
+    base, views = [], []
+    for r, c in enumerate(w.ranks):
+        b = c.alloc(3010, torch.float32)
+        b.fill_(-7.0)
+        v = b[3:3 + 3001]
+        assert c.in_heap(b) and not c.in_heap(v)
+        v.copy_(host[r])
+        base.append(b); views.append(v)
+    for shape in ("4", "2*2"):
+        w.all_reduce(views, shape=shape)
+        torch.cuda.synchronize()
+        for r in range(4):
+            assert torch.allclose(views[r].double().cpu(), want, atol=1e-5), (shape, r)
+            assert bool((base[r][:3] == -7).all()) and bool((base[r][3 + 3001:] == -7).all())
+        for v, h in zip(views, host):
+            v.copy_(h)
+    with pytest.raises(Exception, match="symmetric heap"):
+        w.all_reduce(views, algo="push")
+    w.close()
