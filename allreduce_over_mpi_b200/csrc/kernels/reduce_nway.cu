@@ -454,7 +454,11 @@ int ft_reduce_nway_scaled(int in_dtype, int out_dtype, const void* const* src, v
   if (!src || !dst) return FT_ERR_INVALID_ARG;
   NwayArgs a{};
   bool aligned = ((uintptr_t)dst & 15) == 0;
-  for (int k = 0; k < n; ++k) { a.src[k] = src[k]; aligned = aligned && (((uintptr_t)src[k] & 15) == 0); }
+  for (int k = 0; k < n; ++k) {
+    if (!src[k]) return FT_ERR_INVALID_ARG;
+    a.src[k] = src[k];
+    aligned = aligned && (((uintptr_t)src[k] & 15) == 0);
+  }
   a.dst = dst;
   a.n = n;
   unsigned long long want = (len / 8 + 511) / 512 + 1, cap = (unsigned long long)dev_info().sms * 4;

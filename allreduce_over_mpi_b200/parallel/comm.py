@@ -211,6 +211,8 @@ class _CommBase:
         split when larger than one slot)."""
         if not tensor.is_cuda or not tensor.is_contiguous():
             raise ValueError("all_reduce needs a contiguous CUDA tensor")
+        if tensor.device != self.device or (out is not None and out.device != self.device):
+            raise ValueError(f"tensor on {tensor.device}, communicator on {self.device}")
         if self._poisoned:
             raise FlexTreeError(5, "a device-side wait timed out earlier: the ranks' call counters no longer agree, "
                                    "rebuild the communicator (see parallel/elastic.py for a smaller world)")
@@ -284,6 +286,8 @@ class _CommBase:
     def _phase(self, tensor: torch.Tensor, gather: bool, op: str, shape, scale: float, stream):
         if not tensor.is_cuda or not tensor.is_contiguous():
             raise ValueError("needs a contiguous CUDA tensor")
+        if tensor.device != self.device:
+            raise ValueError(f"tensor on {tensor.device}, communicator on {self.device}")
         if self.world > 1 and not self.in_heap(tensor):
             raise ValueError("reduce_scatter / all_gather work in place on a tensor from comm.alloc()")
         if self._poisoned:
