@@ -363,7 +363,10 @@ class _CommBase:
         self._check(lib().ft_comm_wait_probe(self._h, peer, timeout_ms, C.c_void_p(st)))
 
     def close(self):
+        """Unmap the heaps and free the communicator.  Tensors handed out by :meth:`alloc` point into the
+        heap: they must not be touched afterwards (drop them first)."""
         if self._h:
+            self._canaries = None if self._canaries is None else []
             lib().ft_comm_destroy(self._h)
             self._h = C.c_void_p()
 
