@@ -147,3 +147,11 @@ def test_liveness_in_one_process():
     except RankLost as e:
         assert e.lost == {1}
     assert b.poll() == set()       # b still sees a's counter moving
+
+
+def test_fit_report_reads_the_committed_calibration():
+    text = tune.report(planner.calibration_path())
+    lines = text.splitlines()
+    assert lines[0].startswith("cost model v1 fit:") and "| 8 |" in text and "fitted constants:" in text
+    # every world size with several measured shapes reports how often the model's first choice was the fastest
+    assert sum(" of " in l for l in lines if l.startswith("| ")) >= 5
