@@ -387,6 +387,7 @@ class FlexTreeComm(_CommBase):
         if not dist.is_initialized():
             raise RuntimeError("init torch.distributed first (it only carries the memory handles)")
         self.group = group
+        self._check_symmetric = os.environ.get("FT_CHECK_SYMMETRIC", "0") == "1"
         rank, world = dist.get_rank(group), dist.get_world_size(group)
         dev = device if device is not None else int(os.environ.get("LOCAL_RANK", rank % max(1, torch.cuda.device_count())))
         torch.cuda.set_device(dev)
@@ -412,6 +413,20 @@ class FlexTreeComm(_CommBase):
         self._check(lib().ft_comm_finalize(self._h))
         self._configure_from_env()
         dist.barrier(group=group)
+
+    def alloc(self, shape, dtype=torch.float32) -> torch.Tensor:
+        """As :meth:`_CommBase.alloc`.  With ``FT_CHECK_SYMMETRIC=1`` the call is collective and verifies that
+        every rank got the same heap offset and size: in-place collectives read a peer's heap at THIS rank's
+        offset, so ranks that allocate in different orders would silently reduce unrelated memory."""
+        t = super().alloc(shape, dtype)
+        if self._check_symmetric and self.world > 1:
+            import torch.distributed as dist
+            mine = (t.data_ptr() - (lib().ft_comm_heap_base(self._h) or 0), t.numel() * t.element_size())
+            every = [None] * self.world
+            dist.all_gather_object(every, mine, group=self.group)
+            if any(e != mine for e in every):
+                raise FlexTreeError(1, f"asymmetric heap allocation: (offset, bytes) per rank = {every}")
+        return t
 
     # handles travel as pickled bytes (IPC) or as descriptors over unix sockets (VMM)
     def _exchange(self, kind: int) -> bool:
