@@ -57,5 +57,6 @@ def test_reduce_scatter_and_all_gather_as_calls_of_their_own():
     n = min(ngpu(), 8)
     if n < 2:
         pytest.skip("needs 2 GPUs")
-    res = run_worker(n, "phases", port=29581)
-    assert res["ok"] and res["cases"] > 10, res
+    # with the two debugging aids on: guard blocks behind every heap tensor, collective symmetry check of alloc()
+    res = run_worker(n, "phases", {"FT_CANARY": "1", "FT_CHECK_SYMMETRIC": "1"}, port=29581)
+    assert res["ok"] and res["cases"] > 10 and res["guards_checked"] >= 1, res
