@@ -73,6 +73,10 @@ def main(argv=None):
     ap.add_argument("--cpu", action="store_true", help="also time the CPU kernel")
     ap.add_argument("--out", default=None, help="append JSON lines to this file")
     a = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        print("this benchmark times the GPU kernels and needs a CUDA device; for the host reduction alone run "
+              "allreduce_over_mpi_b200/lib/reduce_bench --cpu-only", file=sys.stderr)
+        return 2
     rows = []
     for dt in a.dtypes:
         for n in a.fanin:
