@@ -156,7 +156,6 @@ __device__ __forceinline__ void copy_range(const unsigned char* src, bool src_ve
 // large one pulls from every peer's link at once instead of queueing on one peer.
 struct CopyJob { const unsigned char* src; unsigned char* dst_work; unsigned char* dst_user; uint64_t bytes; };
 constexpr int kMaxGroup = FT_MAX_FANIN;
-constexpr int kGroupLoads = 4;   // loads per step; with the next step issued early, up to 8 are in flight per thread
 
 __device__ __forceinline__ void store_job(const CopyJob& jb, uint64_t off, uint4 v, bool user_vec_ok, uint32_t es) {
   const uint32_t valid = (uint32_t)(jb.bytes - off < 16 ? jb.bytes - off : 16);
@@ -170,9 +169,9 @@ __device__ __forceinline__ void store_job(const CopyJob& jb, uint64_t off, uint4
   }
 }
 
-// JOBS jobs x VPT vectors per thread per step = kGroupLoads loads in flight; the loads of the
-// next step are issued before the stores of the current one, so the wire never idles between
-// steps.  `first` is the index of the first job of this batch.
+// JOBS jobs x VPT vectors per thread per step = 4 loads per step; the loads of the next step are
+// issued before the stores of the current one (up to 8 in flight), so the wire never idles
+// between steps.  `first` is the index of the first job of this batch.
 template <int JOBS, int VPT>
 __device__ __forceinline__ void copy_batch(const CopyJob* jobs, int first, int ng, uint64_t max_bytes, bool user_vec_ok, uint32_t es) {
   const uint64_t max_nvec = (max_bytes + 15) / 16;
@@ -693,9 +692,7 @@ __global__ void __launch_bounds__(kThreads, 1) push_allreduce_kernel(const __gri
 // One CTA waits on one of its own flags for a rendezvous number that nobody will signal.
 // With a short limit it must come back with FT_ERR_TIMEOUT in the status block.
 __global__ void wait_probe_kernel(const __grid_constant__ CommDev c, int peer, unsigned long long timeout_ns) {
-  __shared__ int abort_flag;
   if (threadIdx.x == 0) {
-    abort_flag = 0;
     const flag_t never = ~0ull - 1;
     if (!wait_flag(c.flags[c.rank] + (size_t)(kMaxLanes - 1) * FT_MAX_RANKS + peer, never, timeout_ns))
       report(c.status, FT_ERR_TIMEOUT, 0, peer, kMaxLanes - 1);
