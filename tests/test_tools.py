@@ -91,3 +91,24 @@ def test_mpi_style_example_builds_and_runs(tmp_path):
     assert rc == 0 and "7 ranks, every element = 28 (expected 28): ok" in out, (out, err)
     rc, out, err = run([str(exe), "4"], env={"FT_TOPO": "3,2"})
     assert rc == 1 and "invalid FT_TOPO" in err
+
+
+def test_cmake_build_of_the_native_library(tmp_path):
+    """The CMake route for C/C++ users: configure, build libflextree.so and the tools for sm_100a, run two of them."""
+    import shutil
+    cmake, gxx = shutil.which("cmake"), shutil.which("g++")
+    if not cmake or not gxx or not shutil.which("nvcc"):
+        pytest.skip("needs cmake, g++ and nvcc")
+    src = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "allreduce_over_mpi_b200", "csrc")
+    r = subprocess.run([cmake, "-S", src, "-B", str(tmp_path), f"-DCMAKE_CXX_COMPILER={gxx}", f"-DCMAKE_CUDA_HOST_COMPILER={gxx}"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    r = subprocess.run([cmake, "--build", str(tmp_path), "-j", str(min(8, os.cpu_count() or 2))], capture_output=True, text=True, timeout=1200)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    flags = open(tmp_path / "CMakeFiles" / "flextree.dir" / "flags.make").read()
+    assert "compute_100a" in flags and "sm_100a" in flags
+    rc, out, _ = run([str(tmp_path / "planner_selftest")])
+    assert rc == 0 and "selftest ok" in out
+    rc, out, err = run([str(tmp_path / "ft_bench"), "--comm-type", "threads", "--ranks", "5", "--size", "1000", "--check"],
+                       env={"FT_TOPO": "2,2", "FT_LONELY": "1"})
+    assert rc == 0 and "CHECK (test passed)" in out, err
