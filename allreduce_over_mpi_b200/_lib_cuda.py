@@ -31,6 +31,8 @@ def declare(lib) -> None:
         "ft_comm_heap_bytes": (sz, [vp]),
         "ft_comm_alloc": (vp, [vp, sz]),
         "ft_comm_alloc_reset": (None, [vp]),
+        "ft_comm_free": (i, [vp, vp]),
+        "ft_comm_heap_free_bytes": (sz, [vp]),
         "ft_comm_rank": (i, [vp]),
         "ft_comm_world": (i, [vp]),
         "ft_comm_mem_kind": (i, [vp]),

@@ -61,10 +61,14 @@ int ft_comm_has_nvls(ft_comm* c);
 /* symmetric heap */
 void* ft_comm_heap_base(ft_comm* c);
 size_t ft_comm_heap_bytes(ft_comm* c);       /* bytes available to ft_comm_alloc */
-/* bump allocation of `bytes` (256-byte aligned) at the same offset on every rank, provided
- * every rank issues the same sequence of calls; returns NULL when the heap is exhausted */
+/* `bytes` of the heap, 256-byte aligned: first fit at the lowest free offset, so every rank gets the
+ * same offset provided every rank issues the same sequence of ft_comm_alloc / ft_comm_free calls (a run
+ * of allocations alone comes out back to back from offset 0); NULL when no free block is large enough */
 void* ft_comm_alloc(ft_comm* c, size_t bytes);
-void ft_comm_alloc_reset(ft_comm* c);
+/* give a block back (p as returned by ft_comm_alloc); neighbouring free blocks merge */
+int ft_comm_free(ft_comm* c, void* p);
+void ft_comm_alloc_reset(ft_comm* c);          /* forget every allocation */
+size_t ft_comm_heap_free_bytes(ft_comm* c);    /* largest block ft_comm_alloc could return now */
 int ft_comm_rank(ft_comm* c);
 int ft_comm_world(ft_comm* c);
 int ft_comm_mem_kind(ft_comm* c);

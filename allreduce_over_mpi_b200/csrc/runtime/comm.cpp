@@ -26,6 +26,7 @@
 #include "../kernels/pol_ids.h"
 #include "../planner/plan.hpp"
 #include "dev_plan.hpp"
+#include "heap_alloc.hpp"
 #include <unistd.h>
 
 namespace ftk {
@@ -104,7 +105,8 @@ struct DevPlanEntry {
 
 struct ft_comm {
   int rank = 0, world = 1, device = 0, mem_kind = FT_MEM_VMM;
-  size_t user_bytes = 0, staging_bytes = 0, total_bytes = 0, staging_off = 0, ll_off = 0, flags_off = 0, bump = 0;
+  size_t user_bytes = 0, staging_bytes = 0, total_bytes = 0, staging_off = 0, ll_off = 0, flags_off = 0;
+  ft::HeapAllocator heap_alloc;   // offsets of the tensors handed out from the user part of the heap
   // local allocation
   CUmemGenericAllocationHandle handle = 0;
   CUdeviceptr va = 0;
@@ -366,6 +368,7 @@ int ft_comm_create(int rank, int world, int device, size_t heap_bytes, size_t st
   FT_CUDA(c, cudaFree(nullptr));
   cudaDeviceGetAttribute(&c->sms, cudaDevAttrMultiProcessorCount, device);
   c->user_bytes = round_up(heap_bytes, 256);
+  c->heap_alloc.reset(c->user_bytes);
   c->staging_bytes = round_up(staging_bytes ? staging_bytes : 256, 256);
   c->staging_off = c->user_bytes;
   c->ll_off = round_up(c->staging_off + 2 * c->staging_bytes, 4096);
@@ -596,14 +599,20 @@ int ft_comm_has_nvls(ft_comm* c) { return c && c->mc_bound && c->mc_va; }
 void* ft_comm_heap_base(ft_comm* c) { return c ? local_base(c) : nullptr; }
 size_t ft_comm_heap_bytes(ft_comm* c) { return c ? c->user_bytes : 0; }
 void* ft_comm_alloc(ft_comm* c, size_t bytes) {
-  if (!c) return nullptr;
-  const size_t need = round_up(bytes ? bytes : 1, 256);
-  if (c->bump + need > c->user_bytes) return nullptr;
-  void* p = local_base(c) + c->bump;
-  c->bump += need;
-  return p;
+  if (!c || !local_base(c)) return nullptr;
+  const size_t off = c->heap_alloc.alloc(bytes);
+  return off == ft::HeapAllocator::kNone ? nullptr : local_base(c) + off;
 }
-void ft_comm_alloc_reset(ft_comm* c) { if (c) c->bump = 0; }
+int ft_comm_free(ft_comm* c, void* p) {
+  if (!c || !p) return FT_ERR_INVALID_ARG;
+  const unsigned char* b = local_base(c);
+  const unsigned char* q = (const unsigned char*)p;
+  if (!b || q < b || q >= b + c->user_bytes || !c->heap_alloc.free((size_t)(q - b)))
+    return fail(c, FT_ERR_INVALID_ARG, "ft_comm_free: not the start of a block from ft_comm_alloc");
+  return FT_OK;
+}
+void ft_comm_alloc_reset(ft_comm* c) { if (c) c->heap_alloc.reset(); }
+size_t ft_comm_heap_free_bytes(ft_comm* c) { return c ? c->heap_alloc.largest_free() : 0; }
 int ft_comm_rank(ft_comm* c) { return c ? c->rank : -1; }
 int ft_comm_world(ft_comm* c) { return c ? c->world : 0; }
 int ft_comm_mem_kind(ft_comm* c) { return c ? c->mem_kind : -1; }

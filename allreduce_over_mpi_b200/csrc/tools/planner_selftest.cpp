@@ -3,7 +3,7 @@
 //     g++ -std=c++17 -O1 -g -fsanitize=thread planner_selftest.cpp -o t -lpthread && ./t threads
 // It builds the plan of every executable shape up to 24 ranks, runs the static race check and the
 // snapshot executor against a double-precision sum, exercises the candidate enumerators and the
-// cost models, checks the device tables (and that damaged ones are refused), and (argument "threads") runs the thread-per-rank executor with its flag protocol,
+// cost models, checks the device tables (and that damaged ones are refused) and the heap allocator, and (argument "threads") runs the thread-per-rank executor with its flag protocol,
 // including a silent rank that must produce time-outs rather than a hang.
 // The reference has no sanitizer builds (its flags are -Wall -Wextra only, allreduce_over_mpi/CMakeLists.txt:5).
 #include <cmath>
@@ -17,6 +17,7 @@
 #include "../planner/cost_model.hpp"
 #include "../planner/cpu_executor.hpp"
 #include "../runtime/dev_plan.hpp"
+#include "../runtime/heap_alloc.hpp"
 
 static int fails = 0;
 #define EXPECT(c) do { if (!(c)) { std::printf("FAIL %s:%d %s\n", __FILE__, __LINE__, #c); ++fails; } } while (0)
@@ -81,6 +82,46 @@ static void device_tables() {
   EXPECT(broken([](ft::HostDevPlan& d) { d.plan.stages[0].last_rs = 1; }));
   EXPECT(broken([](ft::HostDevPlan& d) { d.plan.end_sync_mask = ~0ull; }));
   EXPECT(!ft::check_dev_plan(good, 7, 7).empty());
+}
+
+// Heap offsets: allocations alone are consecutive from zero; live blocks never overlap and stay inside the
+// heap under a random mix of alloc and free; everything merges back into one block; two allocators fed the
+// same sequence agree (that is what keeps the ranks' heaps symmetric).
+static void heap_offsets() {
+  ft::HeapAllocator h(1 << 20);
+  EXPECT(h.alloc(1) == 0 && h.alloc(256) == 256 && h.alloc(257) == 512 && h.alloc(0) == 1024);
+  EXPECT(h.used_bytes() == 256 + 256 + 512 + 256 && h.live_blocks() == 4);
+  EXPECT(h.alloc((size_t)1 << 20) == ft::HeapAllocator::kNone);
+  EXPECT(h.alloc(~(size_t)0) == ft::HeapAllocator::kNone);
+  EXPECT(!h.free(128) && !h.free(4096));
+  EXPECT(h.free(256) && !h.free(256));
+  EXPECT(h.alloc(300) == 1280);          // the 256-byte hole is too small: first fit moves on
+  EXPECT(h.alloc(200) == 256);           // and takes it for something that fits
+  h.reset();
+  EXPECT(h.largest_free() == (size_t)1 << 20 && h.live_blocks() == 0);
+
+  ft::HeapAllocator a(1 << 22), b(1 << 22);
+  std::vector<std::pair<size_t, size_t>> live;   // offset, requested bytes
+  uint64_t rng = 12345;
+  auto next = [&] { rng = rng * 6364136223846793005ull + 1442695040888963407ull; return (uint32_t)(rng >> 33); };
+  for (int step = 0; step < 20000; ++step) {
+    if (live.empty() || next() % 3) {
+      const size_t want = 1 + next() % 60000;
+      const size_t off = a.alloc(want);
+      EXPECT(off == b.alloc(want));
+      if (off == ft::HeapAllocator::kNone) { EXPECT(a.largest_free() < ((want + 255) / 256) * 256); continue; }
+      EXPECT(off % 256 == 0 && off + want <= a.size());
+      for (const auto& l : live) EXPECT(off + want <= l.first || l.first + ((l.second + 255) / 256) * 256 <= off);
+      live.push_back({off, want});
+    } else {
+      const size_t k = next() % live.size();
+      EXPECT(a.free(live[k].first) && b.free(live[k].first));
+      live[k] = live.back();
+      live.pop_back();
+    }
+  }
+  for (const auto& l : live) EXPECT(a.free(l.first));
+  EXPECT(a.live_blocks() == 0 && a.free_blocks() == 1 && a.largest_free() == a.size());
 }
 
 static void enumerators_and_models() {
@@ -168,7 +209,7 @@ static void thread_world_phases() {
 
 int main(int argc, char** argv) {
   const bool threads = argc > 1 && !std::strcmp(argv[1], "threads");
-  if (!threads) { plans_and_snapshot(); device_tables(); enumerators_and_models(); }
+  if (!threads) { plans_and_snapshot(); device_tables(); heap_offsets(); enumerators_and_models(); }
   thread_world(false);
   thread_world_phases();
   thread_world(true);

@@ -142,8 +142,25 @@ class _CommBase:
                 raise MemoryError("symmetric heap exhausted while placing a guard block")
             guard = tensor_from_ptr(gptr, (CANARY_BYTES,), torch.uint8, self.device, owner=self)
             guard.fill_(CANARY_BYTE)
-            self._canaries.append((guard, f"{tuple(shape)} {dtype} at heap offset {ptr - (lib().ft_comm_heap_base(self._h) or 0)}"))
+            self._canaries.append((guard, f"{tuple(shape)} {dtype} at heap offset {ptr - (lib().ft_comm_heap_base(self._h) or 0)}", ptr))
         return t
+
+    def free(self, tensor: torch.Tensor):
+        """Give a tensor from :meth:`alloc` back to the heap (it must no longer be used).  Like alloc(), every
+        rank has to do this in the same order for later allocations to stay symmetric."""
+        ptr = tensor.data_ptr()
+        self._check(lib().ft_comm_free(self._h, ptr))
+        if self._canaries:   # the guard block behind it goes too
+            for k, (guard, what, owner_ptr) in enumerate(self._canaries):
+                if owner_ptr == ptr:
+                    lib().ft_comm_free(self._h, guard.data_ptr())
+                    del self._canaries[k]
+                    break
+
+    @property
+    def heap_free_bytes(self) -> int:
+        """Largest tensor :meth:`alloc` could hand out right now."""
+        return int(lib().ft_comm_heap_free_bytes(self._h))
 
     def free_all(self):
         """Forget every alloc() (tensors handed out before must no longer be used)."""
@@ -165,7 +182,7 @@ class _CommBase:
             return 0
         if synchronize:
             torch.cuda.synchronize(self.device)
-        hit = [what for guard, what in self._canaries if not bool((guard == CANARY_BYTE).all())]
+        hit = [what for guard, what, _ in self._canaries if not bool((guard == CANARY_BYTE).all())]
         if hit:
             raise FlexTreeError(8, f"rank {self.rank}: memory behind these heap tensors was overwritten: " + "; ".join(hit))
         return len(self._canaries)

@@ -292,7 +292,7 @@ def test_guard_blocks_behind_heap_tensors_stay_intact():
             for r, c in enumerate(w.ranks):
                 assert c.check_canaries() >= 1
     # a write that does run past a tensor is caught (done here with an ordinary torch copy into the guard)
-    guard, _ = w.ranks[2]._canaries[-1]
+    guard = w.ranks[2]._canaries[-1][0]
     guard[:4] = 0
     with pytest.raises(Exception, match="overwritten"):
         w.ranks[2].check_canaries()
@@ -324,4 +324,33 @@ def test_unaligned_slice_of_a_heap_tensor_goes_through_the_slots():
             v.copy_(h)
     with pytest.raises(Exception, match="symmetric heap"):
         w.all_reduce(views, algo="push")
+    w.close()
+
+
+def test_heap_free_and_reuse():
+    """alloc / free: a freed block is handed out again (first fit at the lowest offset, the same on every
+    rank), freed neighbours merge, and a collective on the reused block works."""
+    w = LocalWorld(3, heap_bytes=1 << 20, staging_bytes=1 << 16)
+    ptrs = []
+    for c in w.ranks:
+        a, b, d = c.alloc(1000), c.alloc(5000), c.alloc(1000)
+        hole = b.data_ptr() - a.data_ptr()
+        assert hole == 4096 and d.data_ptr() - b.data_ptr() == 20224      # 4000 B -> 4096, 20000 B -> 20224
+        before = c.heap_free_bytes
+        c.free(b)
+        e = c.alloc(4000)
+        assert e.data_ptr() == b.data_ptr() and c.heap_free_bytes == before
+        with pytest.raises(Exception, match="ft_comm_free"):
+            c.free(e[1:])                      # not the start of a block
+        c.free(a); c.free(e)                   # neighbours merge: one block of 4096 + 20224 bytes at the start
+        f = c.alloc(6000)
+        assert f.data_ptr() == a.data_ptr()
+        ptrs.append(f)
+    host = inputs(3, 6000, torch.float32, seed=31)
+    for t, h in zip(ptrs, host):
+        t.copy_(h)
+    w.all_reduce(ptrs, shape="3")
+    torch.cuda.synchronize()
+    want = torch.stack(host).double().sum(0)
+    assert all(torch.allclose(t.double().cpu(), want, atol=1e-5) for t in ptrs)
     w.close()
