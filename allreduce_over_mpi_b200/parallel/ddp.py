@@ -69,6 +69,7 @@ class FlexTreeDDP(nn.Module):
         self.stream = stream or (torch.cuda.Stream(device=comm.device) if on_gpu else None)
         self._callback_queued = False
         self._sync = True
+        self._hooks: list = []
         self.launched = 0
         for b in self.buckets:
             b.flat = comm.alloc(b.numel, b.dtype)
@@ -76,7 +77,7 @@ class FlexTreeDDP(nn.Module):
             for p, off in zip(b.params, b.offsets):
                 p.grad = b.flat[off:off + p.numel()].view_as(p)
                 self._bucket_of[id(p)] = (b, off)
-                p.register_post_accumulate_grad_hook(self._on_grad)
+                self._hooks.append(p.register_post_accumulate_grad_hook(self._on_grad))
             b.pending = len(b.params)
         if broadcast_from is not None and comm.world > 1:
             self._sync_parameters(broadcast_from)
@@ -141,6 +142,25 @@ class FlexTreeDDP(nn.Module):
         if self.stream is not None:
             torch.cuda.current_stream(self.comm.device).wait_stream(self.stream)
         self._callback_queued = False
+
+    def release(self):
+        """Detach the gradients from the symmetric heap and give the buckets back to the communicator (when it
+        has ``free``).  The wrapper must not be used afterwards; every rank has to call this at the same point."""
+        if self.stream is not None:
+            torch.cuda.current_stream(self.comm.device).wait_stream(self.stream)
+            torch.cuda.synchronize(self.comm.device)
+        for h in self._hooks:
+            h.remove()
+        self._hooks = []
+        for b in self.buckets:
+            for p in b.params:
+                p.grad = None
+        free = getattr(self.comm, "free", None)
+        for b in reversed(self.buckets):
+            if free is not None and b.flat is not None:
+                free(b.flat)
+            b.flat = None
+        self.buckets = []
 
     def zero_grad(self, set_to_none: bool = False):
         """Gradients are views of the symmetric buckets; they are zeroed in place, never released."""

@@ -94,3 +94,28 @@ def test_no_sync_accumulates_then_reduces_once():
         ref(x).sum().backward()
     for p1, p2 in zip(ref.parameters(), mod.parameters()):
         assert torch.allclose(p1.grad, p2.grad, atol=1e-6)
+
+
+def test_release_returns_the_buckets():
+    class Comm(FakeComm):
+        def __init__(self):
+            super().__init__()
+            self.live = []
+
+        def alloc(self, shape, dtype=torch.float32):
+            t = super().alloc(shape, dtype)
+            self.live.append(t.data_ptr())
+            return t
+
+        def free(self, t):
+            self.live.remove(t.data_ptr())
+
+    comm = Comm()
+    model = nn.Sequential(nn.Linear(8, 8), nn.Linear(8, 2))
+    ddp = FlexTreeDDP(model, comm, bucket_bytes=128)
+    assert len(comm.live) == len(ddp.buckets) > 1
+    ddp(torch.rand(3, 8)).sum().backward()
+    ddp.release()
+    assert comm.live == [] and all(p.grad is None for p in model.parameters()) and ddp.buckets == []
+    model(torch.rand(3, 8)).sum().backward()      # the bare module trains on with ordinary gradients
+    assert all(p.grad is not None for p in model.parameters())
