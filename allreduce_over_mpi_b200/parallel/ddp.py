@@ -193,6 +193,15 @@ class HookState:
         return t
 
 
+    def release(self):
+        """Give the heap twins back (after the last backward has finished; same point on every rank)."""
+        torch.cuda.synchronize(self.comm.device)
+        for t in reversed(list(self.twins.values())):
+            if t is not False:
+                self.comm.free(t)
+        self.twins = {}
+
+
 def flextree_allreduce_hook(state, bucket):
     """``ddp.register_comm_hook(HookState(comm), flextree_allreduce_hook)``: average the bucket with
     FlexTree on a side stream and hand DDP a future that is complete in stream order."""
