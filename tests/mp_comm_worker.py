@@ -43,6 +43,52 @@ def main():
         dist.destroy_process_group()
         return 0
 
+    if mode == "ddp":
+        # one backward of a small fp32 GPT-2 with rank-specific tokens: the gradients that FlexTreeDDP and the
+        # FlexTree comm hook leave behind must equal those of torch DDP over NCCL (summation order aside)
+        from torch.nn.parallel import DistributedDataParallel as DDP
+        from allreduce_over_mpi_b200.models.gpt2 import GPT2, GPT2Config
+        from allreduce_over_mpi_b200.parallel.ddp import FlexTreeDDP, HookState, flextree_allreduce_hook
+        cfg = GPT2Config.tiny()
+        gen = torch.Generator().manual_seed(500 + rank)
+        tok = torch.randint(0, cfg.vocab_size, (4, 33), generator=gen).to(dev)
+
+        def grads(kind):
+            torch.manual_seed(77)                      # same weights on every rank and in every arm
+            model = GPT2(cfg).to(dev)
+            comm.free_all()
+            if kind == "flextree":
+                wrap = FlexTreeDDP(model, comm, bucket_bytes=64 << 10)
+            else:
+                wrap = DDP(model, device_ids=[dev.index], bucket_cap_mb=1)
+                if kind == "hook":
+                    wrap.register_comm_hook(HookState(comm), flextree_allreduce_hook)
+            loss = wrap(tok[:, :-1], tok[:, 1:])
+            loss.backward()
+            torch.cuda.synchronize()
+            comm.check()
+            flat = torch.cat([p.grad.detach().float().reshape(-1) for p in model.parameters()]).clone()
+            return flat, float(loss.item())
+
+        ref, loss_ref = grads("nccl")
+        good = True
+        for kind in ("flextree", "hook"):
+            got, loss = grads(kind)
+            err = (got - ref).abs().max().item()
+            report[f"{kind}_max_abs_err"] = err
+            if not err <= 1e-5 * max(1.0, ref.abs().max().item()) or abs(loss - loss_ref) > 1e-5:
+                good = False
+                print(f"[rank {rank}] {kind}: gradients differ from NCCL DDP by {err}, loss {loss} vs {loss_ref}", flush=True)
+        report["cases"] = 2
+        flags = [None] * world
+        dist.all_gather_object(flags, good)
+        if rank == 0:
+            print("RESULT " + json.dumps({"ok": all(flags), **report}), flush=True)
+        comm.close()
+        dist.barrier()
+        dist.destroy_process_group()
+        return 0 if all(flags) else 1
+
     if mode == "phases":
         # reduce-scatter and all-gather as calls of their own: the owned block is complete after the
         # first, everything else is then overwritten with NaN, and the second alone rebuilds the result
