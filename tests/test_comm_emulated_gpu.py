@@ -217,140 +217,3 @@ def test_world_of_one_and_bounded_wait():
     c.all_reduce(y)
     torch.cuda.synchronize()
     w.close()
-
-
-@pytest.mark.parametrize("text", ["2", "4", "2*2+1", "2*4", "2*2*2", "ring5", "3*2+1", "8"])
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_reduce_scatter_and_all_gather_alone(text, dtype):
-    """The two halves of the staged plan as collectives of their own: after reduce_scatter a rank's
-    own block is complete (everything it does not own is then overwritten with NaN), and all_gather
-    alone rebuilds the full result from the owned blocks."""
-    shape = Shape.parse(text)
-    n = shape.world
-    w = LocalWorld(n, heap_bytes=8 << 20, staging_bytes=1 << 16)
-    for count in (5, 4099, 300_001):
-        host = inputs(n, count, dtype, seed=11)
-        want = torch.stack(host).double().sum(0) / n
-        dev = []
-        for r, c in enumerate(w.ranks):
-            t = c.alloc(count, dtype)
-            t.copy_(host[r])
-            dev.append(t)
-        owned = w.reduce_scatter(dev, op="avg", shape=shape)
-        torch.cuda.synchronize()
-        covered = torch.zeros(count, dtype=torch.bool)
-        for r, c in enumerate(w.ranks):
-            blocks = P.owned_blocks(n, shape, r)
-            assert len(blocks) == 1 and len(owned[r]) == 1
-            lo, hi = c.block_range(dev[r], blocks[0])
-            assert owned[r][0].numel() == hi - lo and (hi == lo or owned[r][0].data_ptr() == dev[r][lo:hi].data_ptr())
-            assert torch.allclose(dev[r][lo:hi].double().cpu(), want[lo:hi], atol=tol(dtype)), (text, count, r)
-            covered[lo:hi] = True
-            keep = dev[r][lo:hi].clone()
-            dev[r].fill_(float("nan"))
-            dev[r][lo:hi] = keep
-        assert bool(covered.all())
-        w.all_gather(dev, shape=shape)
-        torch.cuda.synchronize()
-        for r in range(n):
-            assert torch.allclose(dev[r].double().cpu(), want, atol=tol(dtype)), (text, count, r)
-        assert all(torch.equal(d, dev[0]) for d in dev)
-        for c in w.ranks:
-            c.free_all()
-    w.close()
-
-
-def test_phases_refuse_tensors_outside_the_heap():
-    w = LocalWorld(2, heap_bytes=1 << 20, staging_bytes=1 << 16)
-    outside = [torch.zeros(64, device=DEV) for _ in range(2)]
-    with pytest.raises(ValueError):
-        w.reduce_scatter(outside)
-    w.close()
-
-
-def test_guard_blocks_behind_heap_tensors_stay_intact():
-    """Opt-in canaries: a 256-byte guard of a known pattern behind every heap tensor.  No collective
-    kernel may touch them, whatever the length (odd sizes put the tensor's end in the middle of a
-    16-byte vector and of a lane's slice); a write into a guard is reported."""
-    n = 5
-    w = LocalWorld(n, heap_bytes=8 << 20, staging_bytes=1 << 20)
-    for c in w.ranks:
-        c.enable_canaries()
-    for count in (1, 333, 4099, 250_001):
-        for dtype in (torch.float32, torch.bfloat16):
-            dev = []
-            for r, c in enumerate(w.ranks):
-                t = c.alloc(count, dtype)
-                t.fill_(1.0)
-                dev.append(t)
-            for shape in ("5", "2*2+1", "ring5"):
-                w.all_reduce(dev, op="avg", shape=shape)
-                w.reduce_scatter(dev, shape=shape, op="avg")
-                w.all_gather(dev, shape=shape)
-            w.all_reduce(dev, op="avg", algo="push")
-            torch.cuda.synchronize()
-            for r, c in enumerate(w.ranks):
-                assert c.check_canaries() >= 1
-    # a write that does run past a tensor is caught (done here with an ordinary torch copy into the guard)
-    guard = w.ranks[2]._canaries[-1][0]
-    guard[:4] = 0
-    with pytest.raises(Exception, match="overwritten"):
-        w.ranks[2].check_canaries()
-    w.close()
-
-
-def test_unaligned_slice_of_a_heap_tensor_goes_through_the_slots():
-    """A view that starts at an odd element of a heap tensor is not on a 16-byte boundary: it must not be
-    addressed in place with vector loads.  It is reduced like any user tensor, and the elements around it
-    stay as they were."""
-    w = LocalWorld(4, heap_bytes=1 << 20, staging_bytes=1 << 20)
-    host = inputs(4, 3001, torch.float32, seed=21)
-    want = torch.stack(host).double().sum(0)
-    base, views = [], []
-    for r, c in enumerate(w.ranks):
-        b = c.alloc(3010, torch.float32)
-        b.fill_(-7.0)
-        v = b[3:3 + 3001]
-        assert c.in_heap(b) and not c.in_heap(v)
-        v.copy_(host[r])
-        base.append(b); views.append(v)
-    for shape in ("4", "2*2"):
-        w.all_reduce(views, shape=shape)
-        torch.cuda.synchronize()
-        for r in range(4):
-            assert torch.allclose(views[r].double().cpu(), want, atol=1e-5), (shape, r)
-            assert bool((base[r][:3] == -7).all()) and bool((base[r][3 + 3001:] == -7).all())
-        for v, h in zip(views, host):
-            v.copy_(h)
-    with pytest.raises(Exception, match="symmetric heap"):
-        w.all_reduce(views, algo="push")
-    w.close()
-
-
-def test_heap_free_and_reuse():
-    """alloc / free: a freed block is handed out again (first fit at the lowest offset, the same on every
-    rank), freed neighbours merge, and a collective on the reused block works."""
-    w = LocalWorld(3, heap_bytes=1 << 20, staging_bytes=1 << 16)
-    ptrs = []
-    for c in w.ranks:
-        a, b, d = c.alloc(1000), c.alloc(5000), c.alloc(1000)
-        hole = b.data_ptr() - a.data_ptr()
-        assert hole == 4096 and d.data_ptr() - b.data_ptr() == 20224      # 4000 B -> 4096, 20000 B -> 20224
-        before = c.heap_free_bytes
-        c.free(b)
-        e = c.alloc(4000)
-        assert e.data_ptr() == b.data_ptr() and c.heap_free_bytes == before
-        with pytest.raises(Exception, match="ft_comm_free"):
-            c.free(e[1:])                      # not the start of a block
-        c.free(a); c.free(e)                   # neighbours merge: one block of 4096 + 20224 bytes at the start
-        f = c.alloc(6000)
-        assert f.data_ptr() == a.data_ptr()
-        ptrs.append(f)
-    host = inputs(3, 6000, torch.float32, seed=31)
-    for t, h in zip(ptrs, host):
-        t.copy_(h)
-    w.all_reduce(ptrs, shape="3")
-    torch.cuda.synchronize()
-    want = torch.stack(host).double().sum(0)
-    assert all(torch.allclose(t.double().cpu(), want, atol=1e-5) for t in ptrs)
-    w.close()

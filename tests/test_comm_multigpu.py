@@ -51,23 +51,3 @@ def test_absent_rank_times_out_instead_of_hanging():
         pytest.skip("needs 2 GPUs")
     res = run_worker(n, "timeout", {"FT_NVLS": "0", "NCCL_NVLS_ENABLE": "0"}, port=29571)
     assert res["ok"], res
-
-
-def test_reduce_scatter_and_all_gather_as_calls_of_their_own():
-    n = min(ngpu(), 8)
-    if n < 2:
-        pytest.skip("needs 2 GPUs")
-    # with the two debugging aids on: guard blocks behind every heap tensor, collective symmetry check of alloc()
-    res = run_worker(n, "phases", {"FT_CANARY": "1", "FT_CHECK_SYMMETRIC": "1"}, port=29581)
-    assert res["ok"] and res["cases"] > 10 and res["guards_checked"] >= 1, res
-
-
-def test_ddp_gradients_equal_nccl_ddp():
-    """One backward of a small GPT-2: FlexTreeDDP and the comm hook on torch DDP leave the same averaged
-    gradients as torch DDP over NCCL."""
-    n = min(ngpu(), 4)
-    if n < 2:
-        pytest.skip("needs 2 GPUs")
-    res = run_worker(n, "ddp", port=29591)
-    assert res["ok"], res
-    assert res["flextree_max_abs_err"] < 1e-4 and res["hook_max_abs_err"] < 1e-4
