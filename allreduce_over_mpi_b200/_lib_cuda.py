@@ -52,6 +52,7 @@ def declare(lib) -> None:
         "ft_allreduce_emulate_stage": (i, [vp, vp, vp, sz, i, i, *shape, f32, i, i, vp]),
         "ft_allreduce_emulate_oneshot": (i, [vp, vp, vp, sz, i, i, f32, i, u64, vp]),
         "ft_comm_status": (i, [vp, ip]),
+        "ft_comm_stats": (i, [vp, C.POINTER(u64), C.POINTER(u64)]),
         "ft_comm_clear_status": (None, [vp]),
         "ft_comm_wait_probe": (i, [vp, i, dbl, vp]),
         "ft_fd_listen": (i, [cp]),

@@ -133,6 +133,9 @@ int ft_allreduce_emulate_oneshot(ft_comm* c, const void* sendbuf, void* recvbuf,
  * {ft_status, rendezvous index, peer, lane, calls completed}.  Synchronises nothing: call
  * after the stream is idle.  ft_comm_clear_status resets it. */
 int ft_comm_status(ft_comm* c, int* out5);
+/* usage so far, counted on the host at launch: calls and message bytes per algorithm, index FT_ALGO_STAGED ..
+ * FT_ALGO_PUSH as resolved (index 0 stays empty), 7 = ft_reduce_scatter, 8 = ft_all_gather */
+int ft_comm_stats(ft_comm* c, uint64_t* calls9, uint64_t* bytes9);
 void ft_comm_clear_status(ft_comm* c);
 /* launches a kernel that waits `timeout_ms` for a signal from `peer` that never comes */
 int ft_comm_wait_probe(ft_comm* c, int peer, double timeout_ms, void* stream);

@@ -107,6 +107,8 @@ struct ft_comm {
   int rank = 0, world = 1, device = 0, mem_kind = FT_MEM_VMM;
   size_t user_bytes = 0, staging_bytes = 0, total_bytes = 0, staging_off = 0, ll_off = 0, flags_off = 0;
   ft::HeapAllocator heap_alloc;   // offsets of the tensors handed out from the user part of the heap
+  // host-side usage counters per algorithm (FT_ALGO_* index; 7 = reduce-scatter alone, 8 = all-gather alone)
+  uint64_t stat_calls[9] = {}, stat_bytes[9] = {};
   // local allocation
   CUmemGenericAllocationHandle handle = 0;
   CUdeviceptr va = 0;
@@ -651,6 +653,7 @@ int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, i
     else if (pr.bytes <= c->oneshot_max && pr.bytes <= c->staging_bytes) algo = FT_ALGO_ONESHOT;
     else algo = FT_ALGO_STAGED;
   }
+  if (algo >= 0 && algo < 7) { c->stat_calls[algo]++; c->stat_bytes[algo] += pr.bytes; }
   if (algo == FT_ALGO_LL) return launch_ll_call(c, pr, sendbuf, recvbuf, count, scale, 3, true, 0, st);
   if (algo == FT_ALGO_ONESHOT) return launch_oneshot_call(c, pr, sendbuf, recvbuf, count, scale, 7, 0, st);
   if (algo == FT_ALGO_PUSH) return launch_push_call(c, pr, sendbuf, recvbuf, count, scale, true, st);
@@ -703,6 +706,8 @@ static int phase_call(ft_comm* c, void* buf, size_t count, int dtype, int op, co
   rc = get_plan(c, shape, &pe);
   if (rc != FT_OK) return rc;
   const int half = pe->nstages / 2;
+  c->stat_calls[gather ? 8 : 7]++;
+  c->stat_bytes[gather ? 8 : 7] += pr.bytes;
   return launch_staged_call(c, pr, nullptr, buf, count, shape, scale, gather ? half : 0, gather ? pe->nstages : half, true,
                             (cudaStream_t)stream, true);
 }
@@ -774,6 +779,11 @@ int ft_comm_status(ft_comm* c, int* out5) {
   out5[0] = c->status_host->code; out5[1] = c->status_host->index; out5[2] = c->status_host->peer;
   out5[3] = c->status_host->lane; out5[4] = (int)c->status_host->calls;
   return c->status_host->code;
+}
+int ft_comm_stats(ft_comm* c, uint64_t* calls9, uint64_t* bytes9) {
+  if (!c || !calls9 || !bytes9) return FT_ERR_INVALID_ARG;
+  for (int i = 0; i < 9; ++i) { calls9[i] = c->stat_calls[i]; bytes9[i] = c->stat_bytes[i]; }
+  return FT_OK;
 }
 void ft_comm_clear_status(ft_comm* c) {
   if (c) { c->status_host->code = 0; c->status_host->index = c->status_host->peer = c->status_host->lane = 0; }

@@ -364,6 +364,15 @@ class _CommBase:
         lib().ft_comm_status(self._h, out)
         return {"code": out[0], "rendezvous": out[1], "peer": out[2], "lane": out[3], "calls": out[4]}
 
+    def stats(self) -> dict:
+        """Calls and message bytes so far per algorithm as resolved at launch (host-side counters), e.g.
+        ``{"nvls": {"calls": 12, "bytes": 3221225472}, "ll": {...}, "reduce_scatter": {...}}``."""
+        calls, nbytes = (C.c_uint64 * 9)(), (C.c_uint64 * 9)()
+        self._check(lib().ft_comm_stats(self._h, calls, nbytes))
+        names = {v: k for k, v in ALGOS.items()}
+        names.update({7: "reduce_scatter", 8: "all_gather"})
+        return {names[k]: {"calls": int(calls[k]), "bytes": int(nbytes[k])} for k in range(1, 9) if calls[k]}
+
     def check(self, synchronize: bool = True):
         """Raise if a device-side wait timed out (a peer never arrived)."""
         if synchronize:

@@ -139,6 +139,7 @@ def main():
         good = good and times["reduce_scatter_ms"] > 0 and times["all_gather_ms"] > 0
         report["phase_ms"] = times
         report["guards_checked"] = comm.check_canaries()     # > 0 when the test runs with FT_CANARY=1
+        report["stats"] = comm.stats()
         flags = [None] * world
         dist.all_gather_object(flags, good)
         if rank == 0:

@@ -14,6 +14,9 @@ def test_reduce_scatter_and_all_gather_as_calls_of_their_own():
     # with the two debugging aids on: guard blocks behind every heap tensor, collective symmetry check of alloc()
     res = run_worker(n, "phases", {"FT_CANARY": "1", "FT_CHECK_SYMMETRIC": "1"}, port=29581)
     assert res["ok"] and res["cases"] > 10 and res["guards_checked"] >= 1, res
+    st = res["stats"]                     # every case is one reduce-scatter and one all-gather of the same bytes
+    assert st["reduce_scatter"]["calls"] == st["all_gather"]["calls"] >= res["cases"]
+    assert st["reduce_scatter"]["bytes"] == st["all_gather"]["bytes"] > 0
 
 
 def test_ddp_gradients_equal_nccl_ddp():
