@@ -392,6 +392,10 @@ class _CommBase:
         """Unmap the heaps and free the communicator.  Tensors handed out by :meth:`alloc` point into the
         heap: they must not be touched afterwards (drop them first)."""
         if self._h:
+            try:
+                log.debug(f"closing; usage {self.stats()}", self.rank)
+            except Exception:  # noqa: BLE001 - a summary line must never get in the way of teardown
+                pass
             self._canaries = None if self._canaries is None else []
             lib().ft_comm_destroy(self._h)
             self._h = C.c_void_p()
@@ -438,6 +442,9 @@ class FlexTreeComm(_CommBase):
             self.has_nvls = self._setup_multicast()
         self._check(lib().ft_comm_finalize(self._h))
         self._configure_from_env()
+        log.info(f"communicator up: world {world}, device {dev}, heap {heap_bytes >> 20} MiB + 2 x {staging_bytes >> 20} MiB slots, "
+                 f"memory {'vmm' if self.mem_kind == MEM_VMM else 'ipc'}, nvls {'on' if self.has_nvls else 'off'}, "
+                 f"shape {'auto' if self.auto else self.default_shape}", rank)
         dist.barrier(group=group)
 
     def alloc(self, shape, dtype=torch.float32) -> torch.Tensor:
