@@ -347,3 +347,4 @@ class CpuWorld:
         [t.start() for t in ts]
         [t.join() for t in ts]
         return out
+

@@ -106,3 +106,24 @@ def test_v1_model_behaviour():
     # round trip of the calibration table
     k2 = P.CostParams.from_json(k.to_json())
     assert k2 == k
+
+
+def test_command_line_of_the_small_tools(capsys):
+    """factor count, candidate printer, +1/-1 printer, model picks and schedule printer from one command line."""
+    from allreduce_over_mpi_b200.parallel.__main__ import main
+    assert main(["factor-count", "0", "1", "12", "64"]) == 0
+    assert capsys.readouterr().out.split() == ["0", "1", "8", "32"]
+    assert main(["candidates", "8"]) == 0
+    assert capsys.readouterr().out.split() == ["2*2*2", "2*4", "4*2", "1*8", "8*1"]
+    assert main(["choose-width", "7"]) == 0
+    out = capsys.readouterr().out.split()
+    assert "2*3+1" in out and "2*4-1" in out
+    assert main(["choose", "10"]) == 0 and capsys.readouterr().out.startswith("2*5 0.688")
+    assert main(["pick", "8", str(1 << 30)]) == 0 and capsys.readouterr().out.split()[0] in ("nvls", "staged", "push")
+    assert main(["owners", "4", "1"]) == 0
+    assert capsys.readouterr().out.splitlines() == ["block 0: rank 3", "block 1: rank 0", "block 2: rank 1", "block 3: rank 2"]
+    assert main(["describe", "5", "2,2", "1"]) == 0
+    out = capsys.readouterr().out
+    assert "rank 4 of 5, shape 2*2+1, 4 stages" in out and out.count("stage 0 RS") == 5
+    assert main(["describe", "7", "2,2", "3"]) == 1 and "invalid FT_TOPO" in capsys.readouterr().err
+    assert main(["pick", "8"]) == 2
