@@ -18,7 +18,7 @@ def test_two_senders_one_listener():
     name = f"ft-test-{os.getpid()}"
     s = L.ft_fd_listen(name.encode())
     assert s >= 0
-    ctx = mp.get_context("fork")
+    ctx = mp.get_context("spawn")   # fork in a process that already runs OpenMP threads can deadlock the child
     ps = [ctx.Process(target=_child, args=(name, t)) for t in (3, 7)]
     [p.start() for p in ps]
     got = {}

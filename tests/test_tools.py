@@ -49,7 +49,7 @@ def test_ft_bench_thread_world_check_and_file(tmp_path):
     assert rc == 0, err
     assert "FlexTree enabled" in out and "CHECK (test passed)" in out and "And FlexTree topo is 2*3" in out
     files = [f for f in os.listdir(tmp_path) if f.startswith("t.6.100000.2-3-+0.ar_test.")]
-    assert len(files) == 1 and len(open(tmp_path / files[0]).read().split()) == 2
+    assert len(files) == 1 and len((tmp_path / files[0]).read_text().split()) == 2
     rc, out, err = run([exe, "--comm-type", "threads", "--ranks", "4", "--size", "35"], env={"FT_TOPO": "2,3"})
     assert rc == 1 and "invalid FT_TOPO 2,3" in err
     rc, out, _ = run([exe, "--version"])
@@ -105,7 +105,7 @@ def test_cmake_build_of_the_native_library(tmp_path):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     r = subprocess.run([cmake, "--build", str(tmp_path), "-j", str(min(8, os.cpu_count() or 2))], capture_output=True, text=True, timeout=1200)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-    flags = open(tmp_path / "CMakeFiles" / "flextree.dir" / "flags.make").read()
+    flags = (tmp_path / "CMakeFiles" / "flextree.dir" / "flags.make").read_text()
     assert "compute_100a" in flags and "sm_100a" in flags
     rc, out, _ = run([str(tmp_path / "planner_selftest")])
     assert rc == 0 and "selftest ok" in out
