@@ -123,6 +123,8 @@ def bench_nway(a) -> dict:
         "impl": "flextree", "per_fanin": per_n, "frac_of_hbm_copy_peak": round(value / pk["hbm_gbs"], 3),
         "peak_source": f"of {how} ({pk['hbm_gbs']} GB/s copy)", "max_abs_err": err,
         "gpu_launches": int(launches), "clocks": clocks,
+        "scaling_note": "one GPU has no link to measure: this run times the n-way reduce kernel (HBM-bound), the runs at "
+                        "N > 1 time the all-reduce (NVLink-bound); the two values are different quantities",
     }
     if not a.no_e2e:
         res["e2e"] = e2e_nway(a, vecs, outs, step_bytes)
