@@ -20,6 +20,7 @@
 #include <chrono>
 #include <cstring>
 #include <memory>
+#include <mutex>
 #include <thread>
 #include <vector>
 
@@ -82,10 +83,27 @@ struct CpuWorld {
   std::unique_ptr<std::atomic<uint32_t>[]> flags;  // flags[dst * n + src]
   std::unique_ptr<std::atomic<void*>[]> bufs;      // buffer each rank exposes for the current call
   std::vector<uint32_t> epoch;                     // per-rank local rendezvous counter
+  std::vector<uint64_t> calls;                     // per-rank count of collective calls (slot parity, low-latency tag)
   double timeout_s = 5.0;
-  explicit CpuWorld(int n_) : n(n_), flags(new std::atomic<uint32_t>[(size_t)n_ * n_]), bufs(new std::atomic<void*>[n_]), epoch(n_, 0) {
+  // Host twins of the device's staging slots and low-latency receive area (allocated on first use):
+  // slots[rank] = two slots of kSlotBytes; ll[((dst * 2 + parity) * n + src) * kLLWords + i] = {data32, tag32}.
+  static constexpr size_t kSlotBytes = 1 << 18;
+  static constexpr size_t kLLWords = 2048;
+  std::vector<std::vector<char>> slots;
+  std::unique_ptr<std::atomic<uint64_t>[]> ll;
+  std::once_flag twins_once;
+  void (*mid_call_hook)(int rank) = nullptr;       // tests: called by the twins between publishing and waiting
+  explicit CpuWorld(int n_) : n(n_), flags(new std::atomic<uint32_t>[(size_t)n_ * n_]), bufs(new std::atomic<void*>[n_]), epoch(n_, 0), calls(n_, 0) {
     for (int i = 0; i < n * n; ++i) flags[i].store(0);
     for (int i = 0; i < n; ++i) bufs[i].store(nullptr);
+  }
+  void ensure_twins() {
+    std::call_once(twins_once, [this] {
+      slots.assign(n, std::vector<char>(2 * kSlotBytes));
+      const size_t words = (size_t)n * 2 * n * kLLWords;
+      ll.reset(new std::atomic<uint64_t>[words]);
+      for (size_t i = 0; i < words; ++i) ll[i].store(0, std::memory_order_relaxed);
+    });
   }
 };
 
@@ -144,6 +162,7 @@ inline RankStatus cpu_allreduce(CpuWorld& w, int rank, const Plan& p, ft_op op, 
   Blocks g(count, p.world, block_elems);
   const uint32_t base = w.epoch[rank];
   w.epoch[rank] = base + (uint32_t)p.num_stages + 1;
+  ++w.calls[rank];
   w.bufs[rank].store(recvbuf, std::memory_order_release);
   const int first = phase == 2 ? p.num_stages / 2 : 0;
   const int last = phase == 1 ? p.num_stages / 2 : p.num_stages;   // one past the last stage that runs
@@ -175,6 +194,87 @@ inline RankStatus cpu_allreduce(CpuWorld& w, int rank, const Plan& p, ft_op op, 
       }
     }
   }
+  return st;
+}
+
+// ---- host twins of the two small-message protocols -------------------------------------------
+// They exist to check the protocols' reuse rules under real concurrency (thread sanitizer, jittered
+// ranks): neither closes with a rendezvous, so a slot or receive area is safe to rewrite only because
+// of what finishing the call in between implies about the peers.
+
+// One-shot: publish the input in staging slot (call mod 2), one rendezvous of all ranks, every rank sums
+// all slots in rank order.  Device form: oneshot_allreduce_kernel.
+inline RankStatus cpu_allreduce_oneshot(CpuWorld& w, int rank, ft_op op, ft_dtype dt, const void* sendbuf, void* recvbuf,
+                                        uint64_t count) {
+  RankStatus st;
+  if (!ft_op_supported(op, dt)) { st.code = FT_ERR_UNSUPPORTED_TYPE; return st; }
+  const size_t es = ft_dtype_size(dt), bytes = count * es;
+  if (bytes > CpuWorld::kSlotBytes || w.n > FT_MAX_FANIN) { st.code = FT_ERR_TOO_LARGE; return st; }
+  if (sendbuf && sendbuf != recvbuf) std::memcpy(recvbuf, sendbuf, bytes);
+  if (w.n == 1 || count == 0) return st;
+  w.ensure_twins();
+  const uint64_t call = w.calls[rank]++;
+  const uint32_t base = w.epoch[rank];
+  w.epoch[rank] = base + 1;
+  const size_t slot = (call & 1) * CpuWorld::kSlotBytes;
+  std::memcpy(w.slots[rank].data() + slot, recvbuf, bytes);
+  if (w.mid_call_hook) w.mid_call_hook(rank);
+  std::vector<int> everyone;
+  for (int q = 0; q < w.n; ++q)
+    if (q != rank) everyone.push_back(q);
+  st = detail::rendezvous(w, rank, everyone, base + 1, 0, 1 << 20, nullptr);
+  if (st.code != FT_OK) return st;
+  if (w.mid_call_hook) w.mid_call_hook(rank);
+  const void* src[FT_MAX_FANIN];
+  for (int q = 0; q < w.n; ++q) src[q] = w.slots[q].data() + slot;
+  st.code = reduce_nway_cpu_dispatch(op, dt, src, recvbuf, w.n, count, 1);
+  return st;
+}
+
+// Low-latency push: no rendezvous at all.  Every rank writes its input as 8-byte words {32 bits of data,
+// 32-bit tag of the call} into receive area (call mod 2) of every rank, then polls its own area until
+// every word carries the tag, and sums in rank order.  Device form: ll_allreduce_kernel.
+inline RankStatus cpu_allreduce_ll(CpuWorld& w, int rank, ft_op op, ft_dtype dt, const void* sendbuf, void* recvbuf,
+                                   uint64_t count) {
+  RankStatus st;
+  if (!ft_op_supported(op, dt)) { st.code = FT_ERR_UNSUPPORTED_TYPE; return st; }
+  const size_t es = ft_dtype_size(dt), bytes = count * es, words = (bytes + 3) / 4;
+  if (words > CpuWorld::kLLWords || w.n > FT_MAX_FANIN) { st.code = FT_ERR_TOO_LARGE; return st; }
+  if (sendbuf && sendbuf != recvbuf) std::memcpy(recvbuf, sendbuf, bytes);
+  if (w.n == 1 || count == 0) return st;
+  w.ensure_twins();
+  const uint64_t call = w.calls[rank]++;
+  const uint32_t tag = (uint32_t)(call + 1);   // never 0, the value of untouched memory
+  const size_t parity = call & 1;
+  auto area = [&](int dst, int src) { return w.ll.get() + (((size_t)dst * 2 + parity) * w.n + src) * CpuWorld::kLLWords; };
+  std::vector<uint32_t> mine(words, 0);
+  std::memcpy(mine.data(), recvbuf, bytes);
+  for (int dst = 0; dst < w.n; ++dst) {
+    std::atomic<uint64_t>* a = area(dst, rank);
+    for (size_t i = 0; i < words; ++i) a[i].store(((uint64_t)tag << 32) | mine[i], std::memory_order_relaxed);
+  }
+  if (w.mid_call_hook) w.mid_call_hook(rank);
+  std::vector<std::vector<uint32_t>> got(w.n, std::vector<uint32_t>(words));
+  const auto t0 = std::chrono::steady_clock::now();
+  for (int src = 0; src < w.n; ++src) {
+    std::atomic<uint64_t>* a = area(rank, src);
+    for (size_t i = 0; i < words; ++i) {
+      for (;;) {
+        const uint64_t v = a[i].load(std::memory_order_relaxed);
+        if ((uint32_t)(v >> 32) == tag) { got[src][i] = (uint32_t)v; break; }
+        if (std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() > w.timeout_s) {
+          st = {FT_ERR_TIMEOUT, 0, src};
+          return st;
+        }
+        std::this_thread::yield();
+      }
+    }
+  }
+  const void* src[FT_MAX_FANIN];
+  for (int q = 0; q < w.n; ++q) src[q] = got[q].data();
+  std::vector<uint32_t> out(words);
+  st.code = reduce_nway_cpu_dispatch(op, dt, src, out.data(), w.n, count, 1);
+  std::memcpy(recvbuf, out.data(), bytes);
   return st;
 }
 

@@ -207,11 +207,66 @@ static void thread_world_phases() {
   }
 }
 
+// Host twins of the small-message protocols, mixed with staged calls and single phases, with every rank
+// delayed at random before each call.  Neither protocol closes with a rendezvous; what keeps a slow rank's
+// reads apart from a fast rank's next write into the same slot (two calls later) is only the argument
+// that finishing the call in between needs every rank's contribution.  Under the thread sanitizer a hole
+// in that argument is a reported race; in any build it is a wrong sum or a timeout.
+static void random_pause(int rank) {
+  thread_local uint64_t rng = 0;
+  if (!rng) rng = 7777 + 13 * (uint64_t)rank;
+  rng = rng * 6364136223846793005ull + 1442695040888963407ull;
+  if ((rng >> 60) < 5) std::this_thread::sleep_for(std::chrono::microseconds((rng >> 40) % 400));
+}
+
+static void thread_world_small_message_twins() {
+  for (int n : {2, 3, 5, 8}) {
+    ft::CpuWorld w(n);
+    w.timeout_s = 30.0;
+    w.mid_call_hook = random_pause;   // ranks also stall in the middle of a call, between publishing and reading
+    const ft::Plan flat = ft::build_plan(n, ft::Shape::flat(n));
+    const ft::Plan ring = ft::build_plan(n, ft::Shape::make_ring(n));
+    const uint64_t count = 777;
+    std::vector<int> bad(n, 0);
+    std::vector<std::thread> th;
+    for (int r = 0; r < n; ++r)
+      th.emplace_back([&, r] {
+        uint64_t rng = 99 + r;
+        auto jitter = [&] {
+          rng = rng * 6364136223846793005ull + 1442695040888963407ull;
+          std::this_thread::sleep_for(std::chrono::microseconds((rng >> 40) % 300));
+        };
+        std::vector<float> buf(count);
+        for (int round = 0; round < 96; ++round) {
+          for (uint64_t i = 0; i < count; ++i) buf[i] = (float)(r + 1) + (float)(i % 7) + (float)round;
+          jitter();
+          ft::RankStatus st;
+          switch (round % 8) {   // back-to-back calls of the same kind are the ones that lean on the parity rule
+            case 0: case 1: case 6: st = ft::cpu_allreduce_ll(w, r, FT_SUM, FT_F32, nullptr, buf.data(), count); break;
+            case 2: case 3: case 5: st = ft::cpu_allreduce_oneshot(w, r, FT_SUM, FT_F32, nullptr, buf.data(), count); break;
+            case 4: st = ft::cpu_allreduce(w, r, round % 16 == 4 ? flat : ring, FT_SUM, FT_F32, nullptr, buf.data(), count); break;
+            default:
+              st = ft::cpu_allreduce(w, r, flat, FT_SUM, FT_F32, nullptr, buf.data(), count, 0, nullptr, 1, 1);
+              if (st.code == FT_OK) st = ft::cpu_allreduce(w, r, flat, FT_SUM, FT_F32, nullptr, buf.data(), count, 0, nullptr, 1, 2);
+          }
+          bad[r] |= st.code != FT_OK;
+          for (uint64_t i = 0; i < count; ++i) {
+            const float want = (float)(n * (n + 1) / 2) + (float)n * ((float)(i % 7) + (float)round);
+            bad[r] |= buf[i] != want;
+          }
+        }
+      });
+    for (auto& x : th) x.join();
+    for (int r = 0; r < n; ++r) EXPECT(!bad[r]);
+  }
+}
+
 int main(int argc, char** argv) {
   const bool threads = argc > 1 && !std::strcmp(argv[1], "threads");
   if (!threads) { plans_and_snapshot(); device_tables(); heap_offsets(); enumerators_and_models(); }
   thread_world(false);
   thread_world_phases();
+  thread_world_small_message_twins();
   thread_world(true);
   std::printf(fails ? "%d FAILURES\n" : "selftest ok\n", fails);
   return fails ? 1 : 0;
