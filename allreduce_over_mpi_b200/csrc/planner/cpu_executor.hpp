@@ -197,6 +197,59 @@ inline RankStatus cpu_allreduce(CpuWorld& w, int rank, const Plan& p, ft_op op, 
   return st;
 }
 
+// Staged plan through the staging slots: the device's path for tensors that do not live in the symmetric
+// heap (staged_allreduce_kernel with user_in / user_out).  The input is copied into work slot (call mod 2),
+// the stages run on the ranks' work slots, every finished block is written to recvbuf, the last stage
+// skips the work slot, and there is NO closing rendezvous.
+inline RankStatus cpu_allreduce_slots(CpuWorld& w, int rank, const Plan& p, ft_op op, ft_dtype dt, const void* sendbuf,
+                                      void* recvbuf, uint64_t count) {
+  RankStatus st;
+  if (!p.ok() || p.world != w.n) { st.code = FT_ERR_INVALID_TOPO; return st; }
+  if (!ft_op_supported(op, dt)) { st.code = FT_ERR_UNSUPPORTED_TYPE; return st; }
+  const size_t es = ft_dtype_size(dt), bytes = count * es;
+  if (bytes > CpuWorld::kSlotBytes) { st.code = FT_ERR_TOO_LARGE; return st; }
+  const void* input = sendbuf ? sendbuf : recvbuf;
+  if (w.n == 1 || count == 0) {
+    if (input != recvbuf) std::memcpy(recvbuf, input, bytes);
+    return st;
+  }
+  w.ensure_twins();
+  Blocks g(count, p.world);
+  const uint64_t call = w.calls[rank]++;
+  const uint32_t base = w.epoch[rank];
+  w.epoch[rank] = base + (uint32_t)p.num_stages + 1;
+  auto work = [&](int q) { return w.slots[q].data() + (call & 1) * CpuWorld::kSlotBytes; };
+  std::memcpy(work(rank), input, bytes);
+  const int last_rs = p.num_stages / 2 - 1;
+  for (int s = 0; s < p.num_stages; ++s) {
+    st = detail::rendezvous(w, rank, p.sync[s][rank], base + (uint32_t)s + 1, s, 1 << 20, nullptr);
+    if (st.code != FT_OK) return st;
+    if (w.mid_call_hook) w.mid_call_hook(rank);
+    const bool need_work = s + 1 != p.num_stages;
+    for (const Pull& pl : p.stages[rank][s].pulls) {
+      const uint64_t off = g.offset(pl.block), len = g.length(pl.block);
+      if (!len) continue;
+      char* mine = work(rank) + off * es;
+      char* user = (char*)recvbuf + off * es;
+      if (pl.reduce) {
+        const void* src[FT_MAX_FANIN];
+        int n = 0;
+        src[n++] = mine;
+        for (int q : pl.srcs) src[n++] = work(q) + off * es;
+        char* dst = s == last_rs ? user : mine;     // a block's last reduction lands in the caller's tensor
+        st.code = reduce_nway_cpu_dispatch(op, dt, src, dst, n, len, 1);
+        if (st.code != FT_OK) return st;
+        if (s == last_rs && need_work) std::memcpy(mine, user, len * es);
+      } else {
+        const char* from = work(pl.srcs[0]) + off * es;
+        if (need_work) std::memcpy(mine, from, len * es);
+        std::memcpy(user, from, len * es);
+      }
+    }
+  }
+  return st;
+}
+
 // ---- host twins of the two small-message protocols -------------------------------------------
 // They exist to check the protocols' reuse rules under real concurrency (thread sanitizer, jittered
 // ranks): neither closes with a rendezvous, so a slot or receive area is safe to rewrite only because
@@ -251,7 +304,10 @@ inline RankStatus cpu_allreduce_ll(CpuWorld& w, int rank, ft_op op, ft_dtype dt,
   std::memcpy(mine.data(), recvbuf, bytes);
   for (int dst = 0; dst < w.n; ++dst) {
     std::atomic<uint64_t>* a = area(dst, rank);
-    for (size_t i = 0; i < words; ++i) a[i].store(((uint64_t)tag << 32) | mine[i], std::memory_order_relaxed);
+    // release / acquire on the words stands for the kernel boundaries of the device: a rank's earlier calls
+    // have completed (their loads have returned) before this call's stores are issued, and its later calls
+    // start only after this call's polls have returned
+    for (size_t i = 0; i < words; ++i) a[i].store(((uint64_t)tag << 32) | mine[i], std::memory_order_release);
   }
   if (w.mid_call_hook) w.mid_call_hook(rank);
   std::vector<std::vector<uint32_t>> got(w.n, std::vector<uint32_t>(words));
@@ -260,7 +316,7 @@ inline RankStatus cpu_allreduce_ll(CpuWorld& w, int rank, ft_op op, ft_dtype dt,
     std::atomic<uint64_t>* a = area(rank, src);
     for (size_t i = 0; i < words; ++i) {
       for (;;) {
-        const uint64_t v = a[i].load(std::memory_order_relaxed);
+        const uint64_t v = a[i].load(std::memory_order_acquire);
         if ((uint32_t)(v >> 32) == tag) { got[src][i] = (uint32_t)v; break; }
         if (std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() > w.timeout_s) {
           st = {FT_ERR_TIMEOUT, 0, src};

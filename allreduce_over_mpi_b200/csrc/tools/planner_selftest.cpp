@@ -226,6 +226,7 @@ static void thread_world_small_message_twins() {
     w.mid_call_hook = random_pause;   // ranks also stall in the middle of a call, between publishing and reading
     const ft::Plan flat = ft::build_plan(n, ft::Shape::flat(n));
     const ft::Plan ring = ft::build_plan(n, ft::Shape::make_ring(n));
+    const ft::Plan tree = ft::build_plan(n, n == 8 ? ft::Shape{{2, 4}, 0, false} : (n == 5 ? ft::Shape{{2, 2}, 1, false} : ft::Shape::flat(n)));
     const uint64_t count = 777;
     std::vector<int> bad(n, 0);
     std::vector<std::thread> th;
@@ -237,14 +238,21 @@ static void thread_world_small_message_twins() {
           std::this_thread::sleep_for(std::chrono::microseconds((rng >> 40) % 300));
         };
         std::vector<float> buf(count);
-        for (int round = 0; round < 96; ++round) {
+        for (int round = 0; round < 108; ++round) {
           for (uint64_t i = 0; i < count; ++i) buf[i] = (float)(r + 1) + (float)(i % 7) + (float)round;
           jitter();
           ft::RankStatus st;
-          switch (round % 8) {   // back-to-back calls of the same kind are the ones that lean on the parity rule
+          switch (round % 9) {   // back-to-back calls of the same kind are the ones that lean on the parity rule
             case 0: case 1: case 6: st = ft::cpu_allreduce_ll(w, r, FT_SUM, FT_F32, nullptr, buf.data(), count); break;
             case 2: case 3: case 5: st = ft::cpu_allreduce_oneshot(w, r, FT_SUM, FT_F32, nullptr, buf.data(), count); break;
             case 4: st = ft::cpu_allreduce(w, r, round % 16 == 4 ? flat : ring, FT_SUM, FT_F32, nullptr, buf.data(), count); break;
+            case 7:   // through the slots, twice in a row, with different shapes (no closing rendezvous in this mode)
+              st = ft::cpu_allreduce_slots(w, r, round % 16 == 7 ? tree : ring, FT_SUM, FT_F32, nullptr, buf.data(), count);
+              if (st.code == FT_OK) {
+                for (uint64_t i = 0; i < count; ++i) buf[i] = (float)(r + 1) + (float)(i % 7) + (float)round;
+                st = ft::cpu_allreduce_slots(w, r, flat, FT_SUM, FT_F32, nullptr, buf.data(), count);
+              }
+              break;
             default:
               st = ft::cpu_allreduce(w, r, flat, FT_SUM, FT_F32, nullptr, buf.data(), count, 0, nullptr, 1, 1);
               if (st.code == FT_OK) st = ft::cpu_allreduce(w, r, flat, FT_SUM, FT_F32, nullptr, buf.data(), count, 0, nullptr, 1, 2);
