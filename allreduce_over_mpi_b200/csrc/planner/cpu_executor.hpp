@@ -178,6 +178,7 @@ inline RankStatus cpu_allreduce(CpuWorld& w, int rank, const Plan& p, ft_op op, 
                             p.num_stages + 1, fault);
     if (st.code != FT_OK) return st;
     if (closing) break;
+    if (w.mid_call_hook) w.mid_call_hook(rank);
     for (const Pull& pl : p.stages[rank][s].pulls) {
       const uint64_t off = g.offset(pl.block), len = g.length(pl.block);
       if (!len) continue;
