@@ -220,7 +220,7 @@ static void random_pause(int rank) {
 }
 
 // Every executable shape up to 9 ranks on real threads that stall at random between a stage's rendezvous and
-// its pulls, three calls back to back, in place and through the slots.  The per-stage rendezvous sets are the
+// its pulls, six calls back to back: in place, through the slots, and as two single phases.  The per-stage rendezvous sets are the
 // only thing that orders one rank's writes against another's reads; a set that misses a dependency shows up
 // as a race under the thread sanitizer (and usually as a wrong sum).
 static void thread_world_all_shapes() {
@@ -232,15 +232,27 @@ static void thread_world_all_shapes() {
       w.timeout_s = 30.0;
       w.mid_call_hook = random_pause;
       const uint64_t count = 97;
+      const std::vector<uint64_t> holders = ft::rs_holders(p);
+      const ft::Blocks g(count, n);
       std::vector<int> bad(n, 0);
       std::vector<std::thread> th;
       for (int r = 0; r < n; ++r)
         th.emplace_back([&, r] {
           std::vector<double> buf(count);
-          for (int round = 0; round < 4; ++round) {
+          for (int round = 0; round < 6; ++round) {
             for (uint64_t i = 0; i < count; ++i) buf[i] = (double)(r + 1) * (double)(i + 1) + round;
-            const ft::RankStatus st = round % 2 ? ft::cpu_allreduce_slots(w, r, p, FT_SUM, FT_F64, nullptr, buf.data(), count)
-                                                : ft::cpu_allreduce(w, r, p, FT_SUM, FT_F64, nullptr, buf.data(), count);
+            ft::RankStatus st;
+            if (round % 3 == 0) {
+              st = ft::cpu_allreduce(w, r, p, FT_SUM, FT_F64, nullptr, buf.data(), count);
+            } else if (round % 3 == 1) {
+              st = ft::cpu_allreduce_slots(w, r, p, FT_SUM, FT_F64, nullptr, buf.data(), count);
+            } else {   // the two halves as calls of their own, everything not owned wiped in between
+              st = ft::cpu_allreduce(w, r, p, FT_SUM, FT_F64, nullptr, buf.data(), count, 0, nullptr, 1, 1);
+              for (int b = 0; b < n; ++b)
+                if (!(holders[b] >> r & 1))
+                  for (uint64_t i = g.offset(b); i < g.offset(b) + g.length(b); ++i) buf[i] = -1e300;
+              if (st.code == FT_OK) st = ft::cpu_allreduce(w, r, p, FT_SUM, FT_F64, nullptr, buf.data(), count, 0, nullptr, 1, 2);
+            }
             bad[r] |= st.code != FT_OK;
             for (uint64_t i = 0; i < count; ++i) bad[r] |= buf[i] != (double)(n * (n + 1) / 2) * (double)(i + 1) + (double)n * round;
           }
