@@ -3,8 +3,9 @@ lonely rank, 1 048 576 floats per rank drawn uniform[-1,1) from seed = rank, res
 an fp64 sum.  Both arms run config1_driver.cpp (built by install_reference.py):
 
   reference   unmodified mpi_mod.hpp (MPI_Allreduce_FT) over the shared-memory MPI shim, one
-              process per rank; its OpenMP reduction is tried with 1, 2 and 4 threads per rank and
-              the fastest is reported
+              process per rank.  Its reduction loops ask for 14 OpenMP threads in the source
+              (PARALLEL_THREAD, mpi_mod.hpp:820), which oversubscribes a small machine, so it is
+              run both as it is and with OMP_THREAD_LIMIT=1 and the faster run is reported
   flextree    this repository's MPI-compatible entry over the thread world (one thread per rank)
 
     python baseline/config1.py [--count 1048576] [--repeat 20] [--warmup 3]
@@ -42,12 +43,14 @@ def run_flextree(world, topo, lonely, count, repeat, warmup):
     return json.loads(r.stdout.strip().splitlines()[-1])
 
 
-def run_reference(world, topo, lonely, count, repeat, warmup, omp_threads):
+def run_reference(world, topo, lonely, count, repeat, warmup, thread_limit):
     session = "c1-" + uuid.uuid4().hex[:10]
     procs = []
     for rank in range(world):
-        env = _env(topo, lonely, FTSHIM_RANK=str(rank), FTSHIM_SIZE=str(world), FTSHIM_SESSION=session,
-                   OMP_NUM_THREADS=str(omp_threads))
+        env = _env(topo, lonely, FTSHIM_RANK=str(rank), FTSHIM_SIZE=str(world), FTSHIM_SESSION=session)
+        env.pop("OMP_THREAD_LIMIT", None)
+        if thread_limit:   # 0 = the reference as it is (14 threads per reduction loop)
+            env["OMP_THREAD_LIMIT"] = str(thread_limit)
         procs.append(subprocess.Popen([os.path.join(REF, "ref_config1"), str(world), str(count), str(repeat), str(warmup)],
                                       stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, env=env))
     outs = []
@@ -65,7 +68,7 @@ def run_reference(world, topo, lonely, count, repeat, warmup, omp_threads):
     if any(p.returncode for p in procs):
         return {"impl": "reference", "world": world, "error": f"exit codes {[p.returncode for p in procs]}"}
     d = json.loads(outs[0].strip().splitlines()[-1])
-    d["omp_threads_per_rank"] = omp_threads
+    d["omp_thread_limit"] = thread_limit or "unset (14 threads per loop)"
     return d
 
 
@@ -74,7 +77,7 @@ def main(argv=None) -> int:
     ap.add_argument("--count", type=int, default=1 << 20)
     ap.add_argument("--repeat", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--omp", type=int, nargs="+", default=[1, 2, 4])
+    ap.add_argument("--omp", type=int, nargs="+", default=[0, 1], help="OMP_THREAD_LIMIT values tried for the reference (0 = unset)")
     a = ap.parse_args(argv)
     for exe in ("ref_config1", "ft_config1"):
         if not os.path.exists(os.path.join(REF, exe)):
