@@ -71,30 +71,54 @@ def _mpi(a, world: int, rank: int) -> dict:
     os.environ.setdefault("MASTER_PORT", "29533")
     if not dist.is_initialized():
         dist.init_process_group("gloo", rank=rank, world_size=world)
-    box = [f"{uuid.uuid4().hex[:12]}" if rank == 0 else None, tempfile.mkdtemp(prefix="ftref-") if rank == 0 else None]
-    dist.broadcast_object_list(box, src=0)
-    session, workdir = box
     count = a.bytes // 4
     warm = max(a.warmup, 3)
     repeat = a.steps + warm
-    env = dict(os.environ, FTSHIM_RANK=str(rank), FTSHIM_SIZE=str(world), FTSHIM_SESSION=session, OMP_NUM_THREADS="14")
-    # With FT_TOPO unset the reference's own validity check rejects every world > 1 (its width
-    # product stays 1, allreduce_over_mpi/mpi_mod.hpp:1447-1475), so the flat tree is named explicitly.
-    env.setdefault("FT_TOPO", str(world))
-    cmd = [exe, "--size", str(count), "--repeat", str(repeat), "--to-file", "--tag", "bench"]
-    r = subprocess.run(cmd, capture_output=True, text=True, cwd=workdir, env=env, timeout=3000)
-    codes = [None] * world
-    dist.all_gather_object(codes, r.returncode)
+    # The reference's reduction loops ask for 14 OpenMP threads each (PARALLEL_THREAD, mpi_mod.hpp:820).  That is its
+    # stock behaviour and the first run; on a host with fewer than 14 cores per rank it oversubscribes, so a second run
+    # caps the threads through the environment (the code stays untouched) and the faster of the two is reported.
+    cores = os.cpu_count() or 1
+    limits = [0] + ([max(1, cores // world)] if cores < 14 * world else [])
+    best = None
+    for limit in limits:
+        box = [f"{uuid.uuid4().hex[:12]}" if rank == 0 else None, tempfile.mkdtemp(prefix="ftref-") if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        session, workdir = box
+        env = dict(os.environ, FTSHIM_RANK=str(rank), FTSHIM_SIZE=str(world), FTSHIM_SESSION=session)
+        env.pop("OMP_THREAD_LIMIT", None)
+        if limit:
+            env["OMP_THREAD_LIMIT"] = str(limit)
+        # With FT_TOPO unset the reference's own validity check rejects every world > 1 (its width
+        # product stays 1, allreduce_over_mpi/mpi_mod.hpp:1447-1475), so the flat tree is named explicitly.
+        if not env.get("FT_TOPO"):
+            env["FT_TOPO"] = str(world)
+        cmd = [exe, "--size", str(count), "--repeat", str(repeat), "--to-file", "--tag", "bench"]
+        r = subprocess.run(cmd, capture_output=True, text=True, cwd=workdir, env=env, timeout=3000)
+        codes = [None] * world
+        dist.all_gather_object(codes, r.returncode)
+        if rank == 0:
+            files = glob.glob(os.path.join(workdir, "bench.*.txt"))
+            if any(codes) or not files:
+                if best is None:
+                    best = unavailable(f"ref_mpi_bench failed: rc={codes} {r.stderr[-200:]}")
+            else:
+                times = [float(x) for x in open(files[0]).read().split()][-a.steps:]
+                sec = sum(times) / len(times)
+                if best is None or "unavailable" in best or sec < best["_sec"]:
+                    best = {"_sec": sec, "_limit": limit, "_topo": env["FT_TOPO"]}
+        dist.barrier()
+        if rank == 0:   # a run that died before MPI_Finalize leaves its shared segment behind
+            try:
+                os.unlink(f"/dev/shm/ftshim-{session}")
+            except OSError:
+                pass
     out = None
     if rank == 0:
-        files = glob.glob(os.path.join(workdir, "bench.*.txt"))
-        if any(codes) or not files:
-            out = unavailable(f"ref_mpi_bench failed: rc={codes} {r.stderr[-200:]}")
+        if best is None or "unavailable" in best:
+            out = best or unavailable("ref_mpi_bench produced no result")
         else:
-            times = [float(x) for x in open(files[0]).read().split()][-a.steps:]
-            sec = sum(times) / len(times)
+            sec = best["_sec"]
             per_rank = a.bytes / sec / 1e9 * (2 * (world - 1) / world)
-            topo = env["FT_TOPO"]
             out = {"metric": "all-reduce bus bandwidth GB/s, whole job = N x per-GPU busbw; busbw = bytes/t * 2(N-1)/N, t = max over ranks",
                    "value": round(per_rank * world, 3), "per_gpu_busbw_GBps": round(per_rank, 3),
                    "unit": "GB/s", "n_gpus": world, "steps": a.steps, "warmup": warm, "ms_per_step": round(sec * 1e3, 3),
@@ -103,13 +127,9 @@ def _mpi(a, world: int, rank: int) -> dict:
                    "config": {"model": "all-reduce", "message_bytes": a.bytes, "parallelism": f"dp{world}",
                               "path": "reference MPI_Allreduce_FT (benchmark.cpp --size --repeat --to-file), CPU ranks in host "
                                       "memory over a shared-memory MPI shim; time is the reference's own host MPI_Wtime on rank 0",
-                              "FT_TOPO": topo, "FT_LONELY": os.environ.get("FT_LONELY", "0")},
+                              "FT_TOPO": best["_topo"], "FT_LONELY": os.environ.get("FT_LONELY", "0"),
+                              "openmp": "stock (14 threads per reduction loop)" if not best["_limit"] else
+                                        f"OMP_THREAD_LIMIT={best['_limit']} (faster than stock on {cores} cores); settings tried: {limits}"},
                    "gpu_launches": 0}
-    dist.barrier()
-    if rank == 0:   # a run that died before MPI_Finalize leaves its shared segment behind
-        try:
-            os.unlink(f"/dev/shm/ftshim-{session}")
-        except OSError:
-            pass
     dist.destroy_process_group()
     return out
