@@ -200,8 +200,8 @@ int main(int argc, char** argv) {
           if (o.check && world > 1) {
             const uint64_t B = ft_comm_block_elems(comms[r], o.size, dtype);
             uint64_t lo = o.size, hi = o.size;
-            for (int b = 0; b < world; ++b)
-              if (holders[b] >> r & 1) { lo = std::min<uint64_t>(o.size, b * B); hi = std::min<uint64_t>(o.size, (b + 1) * B); }
+            for (int blk = 0; blk < world; ++blk)
+              if (holders[blk] >> r & 1) { lo = std::min<uint64_t>(o.size, blk * B); hi = std::min<uint64_t>(o.size, (blk + 1) * B); }
             if (lo) cudaMemsetAsync(dev, 0xFF, lo * es, st);
             if (hi < o.size) cudaMemsetAsync((char*)dev + hi * es, 0xFF, (o.size - hi) * es, st);
           }
