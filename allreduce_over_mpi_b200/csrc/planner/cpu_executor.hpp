@@ -285,6 +285,39 @@ inline RankStatus cpu_allreduce_oneshot(CpuWorld& w, int rank, ft_op op, ft_dtyp
   return st;
 }
 
+// Reduce + push (flat two-shot in one pass), in place on the ranks' own buffers: a rendezvous of all ranks
+// (inputs are in place), then rank r sums block r over all ranks and writes the result into block r of EVERY
+// rank's buffer, then a second rendezvous (results have landed, nobody reads inputs any more).  Device form:
+// push_allreduce_kernel; the switch-reduced variant (nvls_allreduce_kernel) has the same two brackets.
+inline RankStatus cpu_allreduce_push(CpuWorld& w, int rank, ft_op op, ft_dtype dt, void* buf, uint64_t count) {
+  RankStatus st;
+  if (!ft_op_supported(op, dt)) { st.code = FT_ERR_UNSUPPORTED_TYPE; return st; }
+  if (w.n > FT_MAX_FANIN) { st.code = FT_ERR_TOO_LARGE; return st; }
+  if (w.n == 1 || count == 0) return st;
+  const size_t es = ft_dtype_size(dt);
+  ++w.calls[rank];
+  const uint32_t base = w.epoch[rank];
+  w.epoch[rank] = base + 2;
+  w.bufs[rank].store(buf, std::memory_order_release);
+  std::vector<int> everyone;
+  for (int q = 0; q < w.n; ++q)
+    if (q != rank) everyone.push_back(q);
+  st = detail::rendezvous(w, rank, everyone, base + 1, 0, 1 << 20, nullptr);
+  if (st.code != FT_OK) return st;
+  if (w.mid_call_hook) w.mid_call_hook(rank);
+  Blocks g(count, w.n);
+  const uint64_t off = g.offset(rank), len = g.length(rank);
+  if (len) {
+    const void* src[FT_MAX_FANIN];
+    for (int q = 0; q < w.n; ++q) src[q] = (const char*)w.bufs[q].load(std::memory_order_acquire) + off * es;
+    std::vector<char> sum(len * es);
+    st.code = reduce_nway_cpu_dispatch(op, dt, src, sum.data(), w.n, len, 1);
+    if (st.code != FT_OK) return st;
+    for (int q = 0; q < w.n; ++q) std::memcpy((char*)w.bufs[q].load(std::memory_order_acquire) + off * es, sum.data(), len * es);
+  }
+  return detail::rendezvous(w, rank, everyone, base + 2, 1, 1 << 20, nullptr);
+}
+
 // Low-latency push: no rendezvous at all.  Every rank writes its input as 8-byte words {32 bits of data,
 // 32-bit tag of the call} into receive area (call mod 2) of every rank, then polls its own area until
 // every word carries the tag, and sums in rank order.  Device form: ll_allreduce_kernel.

@@ -283,14 +283,15 @@ static void thread_world_small_message_twins() {
           std::this_thread::sleep_for(std::chrono::microseconds((rng >> 40) % 300));
         };
         std::vector<float> buf(count);
-        for (int round = 0; round < 108; ++round) {
+        for (int round = 0; round < 120; ++round) {
           for (uint64_t i = 0; i < count; ++i) buf[i] = (float)(r + 1) + (float)(i % 7) + (float)round;
           jitter();
           ft::RankStatus st;
-          switch (round % 9) {   // back-to-back calls of the same kind are the ones that lean on the parity rule
+          switch (round % 10) {   // back-to-back calls of the same kind are the ones that lean on the parity rule
             case 0: case 1: case 6: st = ft::cpu_allreduce_ll(w, r, FT_SUM, FT_F32, nullptr, buf.data(), count); break;
             case 2: case 3: case 5: st = ft::cpu_allreduce_oneshot(w, r, FT_SUM, FT_F32, nullptr, buf.data(), count); break;
             case 4: st = ft::cpu_allreduce(w, r, round % 16 == 4 ? flat : ring, FT_SUM, FT_F32, nullptr, buf.data(), count); break;
+            case 9: st = ft::cpu_allreduce_push(w, r, FT_SUM, FT_F32, buf.data(), count); break;
             case 7:   // through the slots, twice in a row, with different shapes (no closing rendezvous in this mode)
               st = ft::cpu_allreduce_slots(w, r, round % 16 == 7 ? tree : ring, FT_SUM, FT_F32, nullptr, buf.data(), count);
               if (st.code == FT_OK) {
