@@ -79,6 +79,13 @@ def _declare(lib):
         "ft_cpu_world_destroy": (None, [vp]),
         "ft_cpu_allreduce": (i, [vp, i, *shape, i, i, vp, vp, u64, u64, i, i, i, ip]),
         "ft_cpu_phase": (i, [vp, i, *shape, i, i, vp, u64, u64, i, ip]),
+        "ft_proc_world_join": (vp, [C.c_char_p, i, i, C.c_double, C.c_char_p, sz]),
+        "ft_proc_world_leave": (None, [vp]),
+        "ft_proc_world_rank": (i, [vp]),
+        "ft_proc_world_size": (i, [vp]),
+        "ft_proc_barrier": (i, [vp]),
+        "ft_proc_last_error": (C.c_char_p, [vp]),
+        "ft_proc_allreduce": (i, [vp, *shape, i, i, vp, vp, u64, ip]),
         "ft_mpi_thread_rank": (vp, [vp, i]),
         "ft_mpi_from_comm": (vp, [vp, vp]),
         "ft_mpi_comm_free": (None, [vp]),

@@ -110,6 +110,23 @@ int ft_cpu_allreduce(ft_cpu_world* w, int rank, const int* widths, int nw, int l
 int ft_cpu_phase(ft_cpu_world* w, int rank, const int* widths, int nw, int lonely, int ring, int op, int dtype, void* buf,
                  uint64_t count, uint64_t block_elems, int phase, int* status_out);
 
+/* ---- process-per-rank world: the ranks are ordinary processes of one host (launched like an MPI job), they
+ * meet in a POSIX shared-memory segment named after `session` (unique per job) that carries control state
+ * only, and pull blocks straight out of each other's buffers with process_vm_readv.  Same plans, same
+ * rendezvous protocol and the same bounded waits as the thread world. */
+typedef struct ft_proc_world ft_proc_world;
+/* collective over the `world` processes; NULL (reason in err) if the others do not arrive within timeout_s */
+ft_proc_world* ft_proc_world_join(const char* session, int rank, int world, double timeout_s, char* err, size_t err_cap);
+void ft_proc_world_leave(ft_proc_world* w);
+int ft_proc_world_rank(ft_proc_world* w);
+int ft_proc_world_size(ft_proc_world* w);
+int ft_proc_barrier(ft_proc_world* w);
+const char* ft_proc_last_error(ft_proc_world* w);
+/* every rank calls it with the same shape and count; in place when sendbuf is NULL or == recvbuf.
+ * status_out[0..2] = {ft_status, rendezvous index, peer} */
+int ft_proc_allreduce(ft_proc_world* w, const int* widths, int nw, int lonely, int ring, int op, int dtype,
+                      const void* sendbuf, void* recvbuf, uint64_t count, int* status_out);
+
 /* ---- single-GPU n-way reduction (reference: vector_add/reduce_sum_gpu.h) ---- */
 /* dst[i] = src[0][i] (op) ... (op) src[n-1][i], n in [1, FT_MAX_FANIN]; src/dst are device
  * pointers, `stream` a cudaStream_t.  variant: 0 auto, 1 vector loads, 2 TMA bulk pipeline.

@@ -12,6 +12,7 @@
 #include "../planner/cpu_executor.hpp"
 #include "../planner/factorize.hpp"
 #include "../planner/plan.hpp"
+#include "../planner/proc_world.hpp"
 #include "flextree.h"
 #include "../runtime/dev_plan.hpp"
 
@@ -207,6 +208,33 @@ int ft_run_plan_snapshot(int world, const int* widths, int nw, int lonely, int r
                          void* const* bufs, uint64_t count, uint64_t block_elems) {
   return ft::run_plan_snapshot(cached_plan(world, make_shape(widths, nw, lonely, ring)), (ft_op)op, (ft_dtype)dtype,
                                bufs, count, block_elems);
+}
+
+// ---- process-per-rank world (one host, ranks are processes) ------------------------------------
+struct ft_proc_world { ft::ProcWorld w; };
+
+ft_proc_world* ft_proc_world_join(const char* session, int rank, int world, double timeout_s, char* err, size_t err_cap) {
+  auto* h = new ft_proc_world;
+  if (!session || !h->w.join(session, rank, world, timeout_s)) {
+    put(session ? h->w.error : "no session name", err, err_cap);
+    delete h;
+    return nullptr;
+  }
+  put("", err, err_cap);
+  return h;
+}
+void ft_proc_world_leave(ft_proc_world* h) { delete h; }
+int ft_proc_world_rank(ft_proc_world* h) { return h ? h->w.rank : -1; }
+int ft_proc_world_size(ft_proc_world* h) { return h ? h->w.n : 0; }
+int ft_proc_barrier(ft_proc_world* h) { return h ? h->w.barrier().code : FT_ERR_INVALID_ARG; }
+const char* ft_proc_last_error(ft_proc_world* h) { return h ? h->w.error.c_str() : "null world"; }
+int ft_proc_allreduce(ft_proc_world* h, const int* widths, int nw, int lonely, int ring, int op, int dtype,
+                      const void* sendbuf, void* recvbuf, uint64_t count, int* status_out) {
+  if (!h) return FT_ERR_INVALID_ARG;
+  const auto& p = cached_plan(h->w.n, make_shape(widths, nw, lonely, ring));
+  ft::RankStatus st = h->w.allreduce(p, (ft_op)op, (ft_dtype)dtype, sendbuf, recvbuf, count);
+  if (status_out) { status_out[0] = st.code; status_out[1] = st.stage; status_out[2] = st.peer; }
+  return st.code;
 }
 
 size_t ft_context_describe(int world, int rank, int lonely, uint64_t count, int dtype, char* buf, size_t cap) {

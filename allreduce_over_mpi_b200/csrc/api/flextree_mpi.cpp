@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -18,6 +19,7 @@ struct ft_cpu_world { ft::CpuWorld w; };  // layout shared with flextree_host.cp
 struct ft_mpi_comm {
   ft_cpu_world* threads = nullptr;  // thread world ...
   int rank = 0;
+  ft_proc_world* procs = nullptr;   // ... or process world ...
   ft_comm* gpu = nullptr;           // ... or GPU communicator
   void* stream = nullptr;
   void* bounce = nullptr;           // symmetric-heap region for host buffers (GPU communicator)
@@ -69,11 +71,46 @@ FT_Comm ft_mpi_from_comm(ft_comm* comm, void* stream) {
   c->stream = stream;
   return c;
 }
+FT_Comm ft_mpi_proc_rank(ft_proc_world* world) {
+  if (!world) return nullptr;
+  auto* c = new ft_mpi_comm;
+  c->procs = world;
+  c->rank = ft_proc_world_rank(world);
+  return c;
+}
+FT_Comm ft_mpi_proc_init_env(double timeout_s) {
+  auto env = [](const char* a, const char* b) -> const char* {
+    const char* v = std::getenv(a);
+    return v && *v ? v : std::getenv(b);
+  };
+  const char* r = env("FT_RANK", "RANK");
+  const char* n = env("FT_WORLD", "WORLD_SIZE");
+  const char* s = env("FT_SESSION", "MASTER_PORT");
+  if (!r || !n || !s) { fail(FT_ERR_INVALID_ARG, "ft_mpi_proc_init_env: need FT_RANK/FT_WORLD/FT_SESSION (or RANK/WORLD_SIZE/MASTER_PORT)"); return nullptr; }
+  char err[256];
+  ft_proc_world* w = ft_proc_world_join(s, std::atoi(r), std::atoi(n), timeout_s, err, sizeof err);
+  if (!w) { fail(FT_ERR_NOT_AVAILABLE, std::string("ft_mpi_proc_init_env: ") + err); return nullptr; }
+  return ft_mpi_proc_rank(w);
+}
+void ft_mpi_proc_finalize(FT_Comm c) {
+  if (!c) return;
+  if (c->procs) ft_proc_world_leave(c->procs);
+  delete c;
+}
+int FT_Barrier(FT_Comm c) {
+  if (!c) return FT_ERR_INVALID_ARG;
+  if (c->procs) return ft_proc_barrier(c->procs);
+  if (c->threads) {   // an all-reduce of one byte over the flat plan is a barrier
+    unsigned char b = 0;
+    return MPI_Allreduce_FT_c(FT_IN_PLACE, &b, 1, FT_UINT8_T, FT_OP_SUM, c);
+  }
+  return FT_ERR_NOT_AVAILABLE;
+}
 void ft_mpi_comm_free(FT_Comm c) { delete c; }
 
 int FT_Comm_size(FT_Comm c, int* size) {
   if (!c || !size) return FT_ERR_INVALID_ARG;
-  *size = c->threads ? c->threads->w.n : ft_comm_world(c->gpu);
+  *size = c->threads ? c->threads->w.n : (c->procs ? ft_proc_world_size(c->procs) : ft_comm_world(c->gpu));
   return 0;
 }
 int FT_Comm_rank(FT_Comm c, int* rank) {
@@ -127,6 +164,18 @@ int MPI_Allreduce_FT_c(const void* sendbuf, void* recvbuf, size_t count, FT_Data
     if (st.code != FT_OK)
       return fail(st.code, std::string("MPI_Allreduce_FT: ") + ft_status_name(st.code) + " at rendezvous " +
                                std::to_string(st.stage) + " (peer " + std::to_string(st.peer) + ")");
+    return 0;
+  }
+
+  if (comm->procs) {
+    if (cfg.is_auto) shape = ft::Shape::flat(world);
+    int st3[3] = {0, 0, 0};
+    const int nw = (int)shape.widths.size();
+    const int rc = ft_proc_allreduce(comm->procs, shape.widths.data(), nw, shape.lonely, shape.ring, op, datatype,
+                                     in_place ? nullptr : sendbuf, recvbuf, count, st3);
+    if (rc != FT_OK)
+      return fail(rc, std::string("MPI_Allreduce_FT: ") + ft_status_name((ft_status)rc) + " at rendezvous " + std::to_string(st3[1]) +
+                          " (peer " + std::to_string(st3[2]) + ") " + ft_proc_last_error(comm->procs));
     return 0;
   }
 

@@ -59,6 +59,14 @@ typedef int FT_Op;
 /* communicators */
 FT_Comm ft_mpi_thread_rank(ft_cpu_world* world, int rank);     /* rank of a thread world */
 FT_Comm ft_mpi_from_comm(ft_comm* comm, void* stream);         /* GPU communicator on a CUDA stream */
+FT_Comm ft_mpi_proc_rank(ft_proc_world* world);                /* this process as a rank of a process world */
+/* Process world from the launcher's environment: rank / size from FT_RANK / FT_WORLD (else RANK / WORLD_SIZE,
+ * what torch.distributed.run sets), session from FT_SESSION (else MASTER_PORT).  NULL on failure
+ * (ft_mpi_last_error).  The counterpart of MPI_Init + MPI_COMM_WORLD for a job started as N processes. */
+FT_Comm ft_mpi_proc_init_env(double timeout_s);
+/* leaves the process world of a communicator made by ft_mpi_proc_init_env (MPI_Finalize) and frees it */
+void ft_mpi_proc_finalize(FT_Comm c);
+int FT_Barrier(FT_Comm c);                                      /* thread and process worlds */
 void ft_mpi_comm_free(FT_Comm c);
 int FT_Comm_size(FT_Comm c, int* size);
 int FT_Comm_rank(FT_Comm c, int* rank);
@@ -99,6 +107,7 @@ typedef FT_Op MPI_Op;
 #define MPI_Type_size FT_Type_size
 #define MPI_Type_get_name FT_Type_get_name
 #define MPI_Allreduce MPI_Allreduce_FT
+#define MPI_Barrier FT_Barrier
 #endif
 
 #endif /* FLEXTREE_MPI_H_ */

@@ -348,3 +348,45 @@ class CpuWorld:
         [t.join() for t in ts]
         return out
 
+
+class ProcWorld:
+    """This process as one rank of a world of ordinary processes on one host (launched like an MPI job, no MPI
+    library): control state in a POSIX shared-memory segment named after ``session`` (unique per job), data
+    pulled straight out of the peers' buffers with ``process_vm_readv`` (messages up to 16 KiB through the
+    segment).  ``join`` is collective; rank / world / session default to FT_RANK / FT_WORLD / FT_SESSION,
+    else RANK / WORLD_SIZE / MASTER_PORT (what ``torch.distributed.run`` sets)."""
+
+    def __init__(self, session: str | None = None, rank: int | None = None, world: int | None = None, timeout_s: float = 30.0):
+        env = os.environ
+        rank = int(env.get("FT_RANK") or env["RANK"]) if rank is None else rank
+        world = int(env.get("FT_WORLD") or env["WORLD_SIZE"]) if world is None else world
+        session = session or env.get("FT_SESSION") or env["MASTER_PORT"]
+        err = C.create_string_buffer(256)
+        self._h = lib().ft_proc_world_join(str(session).encode(), rank, world, timeout_s, err, 256)
+        if not self._h:
+            raise FlexTreeError(9, err.value.decode())
+        self.rank, self.world = rank, world
+
+    def all_reduce(self, tensor: torch.Tensor, shape: Shape | None = None, op: str = "sum", out: torch.Tensor | None = None) -> torch.Tensor:
+        """All-reduce a contiguous CPU tensor across the processes (in place unless ``out`` is given)."""
+        dst = tensor if out is None else out
+        if tensor.is_cuda or not tensor.is_contiguous() or not dst.is_contiguous() or dst.numel() != tensor.numel():
+            raise ValueError("needs contiguous CPU tensors of equal size")
+        shp = shape or shape_from_env(self.world)[0]
+        st = (C.c_int * 3)()
+        code = lib().ft_proc_allreduce(self._h, *shp.c_args(), OPS[op], ft_dtype(tensor.dtype),
+                                       None if dst is tensor else tensor.data_ptr(), dst.data_ptr(), tensor.numel(), st)
+        if code:
+            raise FlexTreeError(code, f"rendezvous {st[1]}, peer {st[2]}: {lib().ft_proc_last_error(self._h).decode()}")
+        return dst
+
+    def barrier(self):
+        check(lib().ft_proc_barrier(self._h), "barrier")
+
+    def close(self):
+        if self._h:
+            lib().ft_proc_world_leave(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()

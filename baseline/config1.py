@@ -6,7 +6,8 @@ an fp64 sum.  Both arms run config1_driver.cpp (built by install_reference.py):
               process per rank.  Its reduction loops ask for 14 OpenMP threads in the source
               (PARALLEL_THREAD, mpi_mod.hpp:820), which oversubscribes a small machine, so it is
               run both as it is and with OMP_THREAD_LIMIT=1 and the faster run is reported
-  flextree    this repository's MPI-compatible entry over the thread world (one thread per rank)
+  flextree    this repository's MPI-compatible entry over the thread world (one thread per rank) and over the
+              process world (one process per rank, launched like the reference arm; no MPI library underneath)
 
     python baseline/config1.py [--count 1048576] [--repeat 20] [--warmup 3]
 
@@ -41,6 +42,30 @@ def run_flextree(world, topo, lonely, count, repeat, warmup):
     if r.returncode != 0:
         return {"impl": "flextree-threads", "world": world, "error": r.stderr[-300:]}
     return json.loads(r.stdout.strip().splitlines()[-1])
+
+
+def run_flextree_procs(world, topo, lonely, count, repeat, warmup):
+    session = "c1p-" + uuid.uuid4().hex[:10]
+    procs = []
+    for rank in range(world):
+        env = _env(topo, lonely, FT_RANK=str(rank), FT_WORLD=str(world), FT_SESSION=session)
+        procs.append(subprocess.Popen([os.path.join(REF, "ft_config1_procs"), str(world), str(count), str(repeat), str(warmup)],
+                                      stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, env=env))
+    outs = []
+    try:
+        for p in procs:
+            outs.append(p.communicate(timeout=600)[0])
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+        try:
+            os.unlink(f"/dev/shm/ftpw-{session}")
+        except OSError:
+            pass
+    if any(p.returncode for p in procs):
+        return {"impl": "flextree-procs", "world": world, "error": f"exit codes {[p.returncode for p in procs]}"}
+    return json.loads(outs[0].strip().splitlines()[-1])
 
 
 def run_reference(world, topo, lonely, count, repeat, warmup, thread_limit):
@@ -89,9 +114,13 @@ def main(argv=None) -> int:
         good = [r for r in refs if "error" not in r]
         ref = min(good, key=lambda r: r["ms_min"]) if good else refs[0]
         ours = run_flextree(world, topo, lonely, a.count, a.repeat, a.warmup)
-        if "error" not in ref and "error" not in ours:
-            ours["speedup_vs_reference_at_min"] = round(ref["ms_min"] / ours["ms_min"], 2)
-        for d in (ref, ours):
+        rows = [ref, ours]
+        if os.path.exists(os.path.join(REF, "ft_config1_procs")):
+            rows.append(run_flextree_procs(world, topo, lonely, a.count, a.repeat, a.warmup))
+        for d in rows[1:]:
+            if "error" not in ref and "error" not in d:
+                d["speedup_vs_reference_at_min"] = round(ref["ms_min"] / d["ms_min"], 2)
+        for d in rows:
             bad += "error" in d or d.get("check") != "passed"
             print(json.dumps(d))
     return 1 if bad else 0

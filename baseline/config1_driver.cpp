@@ -4,6 +4,8 @@
 //                         over baseline/mpi_shim; ranks are processes (FTSHIM_RANK / FTSHIM_SIZE)
 //   (default)             this repository's MPI-compatible entry (csrc/api/flextree_mpi.h) over the
 //                         thread world of libflextree.so; ranks are threads of this process
+//   -DCONFIG1_PROCS       the same entry over the process world: ranks are processes (FT_RANK / FT_WORLD /
+//                         FT_SESSION), exactly like the reference arm, with no MPI library underneath
 //
 //   config1_driver <world> <count> <repeat> [warmup]         (world is ignored by the reference build)
 //
@@ -102,6 +104,38 @@ int main(int argc, char** argv) {
   if (rank == 0) report("reference", world, count, repeat, sec, bad_all > 0 ? 1.0 : err);
   MPI_Finalize();
   return bad_all > 0 ? 1 : 0;
+}
+
+#elif defined(CONFIG1_PROCS)
+
+int main(int argc, char** argv) {
+  if (argc < 4) { fprintf(stderr, "usage: %s <world> <count> <repeat> [warmup]\n", argv[0]); return 2; }
+  const size_t count = strtoull(argv[2], nullptr, 10);
+  const int repeat = atoi(argv[3]), warmup = argc > 4 ? atoi(argv[4]) : 1;
+  FT_Comm comm = ft_mpi_proc_init_env(60.0);
+  if (!comm) { fprintf(stderr, "%s\n", ft_mpi_last_error()); return 2; }
+  int world = 0, rank = 0;
+  FT_Comm_size(comm, &world);
+  FT_Comm_rank(comm, &rank);
+  std::vector<float> input(count), work(count);
+  fill(input, rank);
+  std::vector<double> sec;
+  int rc = 0;
+  for (int i = 0; i < warmup + repeat; ++i) {
+    work = input;
+    FT_Barrier(comm);
+    const auto t0 = std::chrono::steady_clock::now();
+    rc |= MPI_Allreduce_FT(FT_IN_PLACE, work.data(), (int)count, FT_FLOAT, FT_OP_SUM, comm);
+    FT_Barrier(comm);
+    const auto t1 = std::chrono::steady_clock::now();
+    if (i >= warmup) sec.push_back(std::chrono::duration<double>(t1 - t0).count());
+  }
+  const double err = max_err(work, oracle(world, count));
+  float bad = (rc != 0 || err > 4e-7 * world * 4) ? 1.f : 0.f;
+  MPI_Allreduce_FT(FT_IN_PLACE, &bad, 1, FT_FLOAT, FT_OP_SUM, comm);   // every rank's verdict reaches rank 0
+  if (rank == 0) report("flextree-procs", world, count, repeat, sec, bad > 0 ? 1.0 : err);
+  ft_mpi_proc_finalize(comm);
+  return bad > 0 ? 1 : 0;
 }
 
 #else

@@ -13,6 +13,7 @@ sources are copied verbatim to baseline/_ref/src and compiled as they are:
   * baseline/_ref/ref_config1    g++: config1_driver.cpp -DCONFIG1_REFERENCE + the reference's mpi_mod.hpp
                                  over the same shim (seeded uniform data, fp64 check; see config1.py)
   * baseline/_ref/ft_config1     g++: the same driver against this repository's libflextree.so (thread world)
+  * baseline/_ref/ft_config1_procs  g++ -DCONFIG1_PROCS: the same driver over the process world (ranks are processes)
 
 Nothing of this repository's library is linked into the three reference binaries.
 """
@@ -61,7 +62,10 @@ def main() -> int:
         pkg = HERE.parent / "allreduce_over_mpi_b200"
         rc4 = run(["g++", "-std=c++17", "-O2", "-I", str(pkg / "csrc"), str(HERE / "config1_driver.cpp"), "-L", str(pkg / "lib"),
                    "-lflextree", f"-Wl,-rpath,{pkg / 'lib'}", "-lpthread", "-o", str(OUT / "ft_config1")], log)
-        log.write(f"ref_nway build rc={rc1}; ref_mpi_bench build rc={rc2}; ref_config1 build rc={rc3}; ft_config1 build rc={rc4}\n")
+        rc5 = run(["g++", "-std=c++17", "-O2", "-DCONFIG1_PROCS", "-I", str(pkg / "csrc"), str(HERE / "config1_driver.cpp"), "-L", str(pkg / "lib"),
+                   "-lflextree", f"-Wl,-rpath,{pkg / 'lib'}", "-lpthread", "-o", str(OUT / "ft_config1_procs")], log)
+        log.write(f"ref_nway build rc={rc1}; ref_mpi_bench build rc={rc2}; ref_config1 build rc={rc3}; ft_config1 build rc={rc4}; "
+                  f"ft_config1_procs build rc={rc5}\n")
     print(open(OUT / "INSTALL_LOG.txt").read()[-1500:])
     return 0 if rc1 == 0 and rc2 == 0 else 1
 

@@ -45,12 +45,13 @@ def test_reference_arm_single_gpu_reports_unavailable_without_cuda():
                     reason="reference not built (python baseline/install_reference.py)")
 def test_seeded_fp64_checked_comparison_on_6_and_7_ranks():
     """World 6 (2*3) and 7 (2*3 + 1 lonely), uniform[-1,1) data from seed = rank, fp64 oracle:
-    the unmodified reference and the thread world both pass and report a time."""
+    the unmodified reference, the thread world and the process world (ranks launched as processes, like the
+    reference's) all pass and report a time."""
     r = subprocess.run([sys.executable, os.path.join(ROOT, "baseline", "config1.py"), "--count", "20000", "--repeat", "3",
                         "--warmup", "1", "--omp", "1"], capture_output=True, text=True, timeout=300, cwd=ROOT)
     rows = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
-    assert r.returncode == 0 and len(rows) == 4, (r.stdout[-1500:], r.stderr[-1500:])
-    assert [(d["impl"], d["world"]) for d in rows] == [("reference", 6), ("flextree-threads", 6), ("reference", 7),
-                                                       ("flextree-threads", 7)]
+    assert r.returncode == 0 and len(rows) == 6, (r.stdout[-1500:], r.stderr[-1500:])
+    assert [(d["impl"], d["world"]) for d in rows] == [("reference", 6), ("flextree-threads", 6), ("flextree-procs", 6),
+                                                       ("reference", 7), ("flextree-threads", 7), ("flextree-procs", 7)]
     assert all(d["check"] == "passed" and d["ms_min"] > 0 for d in rows)
-    assert rows[3]["FT_LONELY"] == "1" and rows[1]["FT_TOPO"] == "2,3"
+    assert rows[5]["FT_LONELY"] == "1" and rows[1]["FT_TOPO"] == "2,3"
