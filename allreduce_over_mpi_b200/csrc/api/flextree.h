@@ -122,6 +122,14 @@ int ft_proc_world_rank(ft_proc_world* w);
 int ft_proc_world_size(ft_proc_world* w);
 int ft_proc_barrier(ft_proc_world* w);
 const char* ft_proc_last_error(ft_proc_world* w);
+/* Symmetric heap of the process world (the host twin of the GPU communicator's): ft_proc_heap_create is
+ * collective and gives every rank one shared segment of `bytes` that all the others map; a buffer from
+ * ft_proc_alloc is reduced in place with plain loads from the peers' mappings - no system call, no copy -
+ * provided every rank allocates in the same order (ft_proc_heap_symmetric checks one pointer, collectively). */
+int ft_proc_heap_create(ft_proc_world* w, size_t bytes);
+void* ft_proc_alloc(ft_proc_world* w, size_t bytes);
+int ft_proc_free(ft_proc_world* w, void* p);
+int ft_proc_heap_symmetric(ft_proc_world* w, const void* p);
 /* every rank calls it with the same shape and count; in place when sendbuf is NULL or == recvbuf.
  * status_out[0..2] = {ft_status, rendezvous index, peer} */
 int ft_proc_allreduce(ft_proc_world* w, const int* widths, int nw, int lonely, int ring, int op, int dtype,

@@ -228,6 +228,10 @@ int ft_proc_world_rank(ft_proc_world* h) { return h ? h->w.rank : -1; }
 int ft_proc_world_size(ft_proc_world* h) { return h ? h->w.n : 0; }
 int ft_proc_barrier(ft_proc_world* h) { return h ? h->w.barrier().code : FT_ERR_INVALID_ARG; }
 const char* ft_proc_last_error(ft_proc_world* h) { return h ? h->w.error.c_str() : "null world"; }
+int ft_proc_heap_create(ft_proc_world* h, size_t bytes) { return h && h->w.heap_create(bytes) ? FT_OK : FT_ERR_NOT_AVAILABLE; }
+void* ft_proc_alloc(ft_proc_world* h, size_t bytes) { return h ? h->w.heap_alloc(bytes) : nullptr; }
+int ft_proc_free(ft_proc_world* h, void* p) { return h && h->w.heap_free(p) ? FT_OK : FT_ERR_INVALID_ARG; }
+int ft_proc_heap_symmetric(ft_proc_world* h, const void* p) { return h && h->w.heap_symmetric(p) ? 1 : 0; }
 int ft_proc_allreduce(ft_proc_world* h, const int* widths, int nw, int lonely, int ring, int op, int dtype,
                       const void* sendbuf, void* recvbuf, uint64_t count, int* status_out) {
   if (!h) return FT_ERR_INVALID_ARG;

@@ -97,6 +97,7 @@ void ft_mpi_proc_finalize(FT_Comm c) {
   if (c->procs) ft_proc_world_leave(c->procs);
   delete c;
 }
+ft_proc_world* ft_mpi_proc_world(FT_Comm c) { return c ? c->procs : nullptr; }
 int FT_Barrier(FT_Comm c) {
   if (!c) return FT_ERR_INVALID_ARG;
   if (c->procs) return ft_proc_barrier(c->procs);

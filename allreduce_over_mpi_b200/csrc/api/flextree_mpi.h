@@ -66,6 +66,8 @@ FT_Comm ft_mpi_proc_rank(ft_proc_world* world);                /* this process a
 FT_Comm ft_mpi_proc_init_env(double timeout_s);
 /* leaves the process world of a communicator made by ft_mpi_proc_init_env (MPI_Finalize) and frees it */
 void ft_mpi_proc_finalize(FT_Comm c);
+/* the process world behind a communicator (for ft_proc_heap_create / ft_proc_alloc), or NULL */
+ft_proc_world* ft_mpi_proc_world(FT_Comm c);
 int FT_Barrier(FT_Comm c);                                      /* thread and process worlds */
 void ft_mpi_comm_free(FT_Comm c);
 int FT_Comm_size(FT_Comm c, int* size);

@@ -28,6 +28,7 @@
 #include <thread>
 #include <vector>
 
+#include "../runtime/heap_alloc.hpp"
 #include "cpu_executor.hpp"
 
 namespace ft {
@@ -105,6 +106,10 @@ class ProcWorld {
 
   void leave() {
     if (!sh_) return;
+    for (unsigned char* b : heap_base_)
+      if (b) munmap(b, heap_size_);
+    heap_base_.clear();
+    heap_size_ = 0;
     const bool last = (int)sh_->detached.fetch_add(1, std::memory_order_acq_rel) + 1 == n;
     munmap(sh_, sizeof(ProcShared));
     sh_ = nullptr;
@@ -195,31 +200,16 @@ class ProcWorld {
     Blocks g(count, n);
     const uint32_t base = epoch_;
     epoch_ = base + (uint32_t)p.num_stages + 1;
+    // a tensor in the symmetric heap: every peer has it mapped at the same offset of that peer's heap
+    if (heap_size_ && in_heap(recvbuf, count * es)) {
+      const uint64_t off_in_heap = (uint64_t)(static_cast<unsigned char*>(recvbuf) - heap_base_[rank]);
+      return run_direct(p, op, dt, g, base, es, [&](int q) { return heap_base_[q] + off_in_heap; });
+    }
     if (count * es <= ProcShared::kEagerBytes) {
-      // the whole call runs on the shared working copies, exactly like the thread world
-      unsigned char* work = sh_->eager[rank];
-      std::memcpy(work, recvbuf, count * es);
-      for (int s = 0; s <= p.num_stages; ++s) {
-        st = rendezvous(p.sync[s][rank], base + (uint32_t)s + 1, s);
-        if (st.code != FT_OK) return st;
-        if (s == p.num_stages) break;
-        for (const Pull& pl : p.stages[rank][s].pulls) {
-          const uint64_t off = g.offset(pl.block), len = g.length(pl.block);
-          if (!len) continue;
-          unsigned char* mine = work + off * es;
-          if (pl.reduce) {
-            const void* src[FT_MAX_FANIN];
-            int k = 0;
-            src[k++] = mine;
-            for (int q : pl.srcs) src[k++] = sh_->eager[q] + off * es;
-            st.code = reduce_nway_cpu_dispatch(op, dt, src, mine, k, len, 1);
-            if (st.code != FT_OK) return st;
-          } else {
-            std::memcpy(mine, sh_->eager[pl.srcs[0]] + off * es, len * es);
-          }
-        }
-      }
-      std::memcpy(recvbuf, work, count * es);
+      // the whole call runs on working copies inside the control segment, exactly like the thread world
+      std::memcpy(sh_->eager[rank], recvbuf, count * es);
+      st = run_direct(p, op, dt, g, base, es, [&](int q) { return sh_->eager[q]; });
+      if (st.code == FT_OK) std::memcpy(recvbuf, sh_->eager[rank], count * es);
       return st;
     }
     sh_->buf[rank].store((uint64_t)reinterpret_cast<uintptr_t>(recvbuf), std::memory_order_release);
@@ -313,12 +303,96 @@ class ProcWorld {
     return st;
   }
 
+  // ---- symmetric heap: memory that every rank can address directly -------------------------------------
+  // Each rank owns one shared segment of `bytes` and maps everybody else's.  A tensor allocated from it is
+  // reduced in place with plain loads from the peers' mappings (no system call, no copy), provided every rank
+  // allocates in the same order so that the tensor sits at the same offset everywhere: the design of the GPU
+  // communicator's symmetric heap, on the host.  Collective; call once.
+  bool heap_create(size_t bytes) {
+    if (!sh_ || heap_size_) { error = "heap_create: not joined, or a heap exists already"; return false; }
+    bytes = (bytes + 4095) / 4096 * 4096;
+    auto seg = [&](int q) { return name_ + "-h" + std::to_string(q); };
+    auto map_seg = [&](int q, bool create) -> unsigned char* {
+      const int fd = shm_open(seg(q).c_str(), create ? (O_CREAT | O_EXCL | O_RDWR) : O_RDWR, 0600);
+      if (fd < 0 || (create && ftruncate(fd, (off_t)bytes) != 0)) { error = "heap segment: " + std::string(std::strerror(errno)); if (fd >= 0) close(fd); return nullptr; }
+      void* m = mmap(nullptr, bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+      close(fd);
+      if (m == MAP_FAILED) { error = "heap mmap: " + std::string(std::strerror(errno)); return nullptr; }
+      return static_cast<unsigned char*>(m);
+    };
+    shm_unlink(seg(rank).c_str());
+    heap_base_.assign(n, nullptr);
+    bool ok = (heap_base_[rank] = map_seg(rank, true)) != nullptr;
+    if (barrier().code != FT_OK) return false;          // every segment exists (or its owner failed)
+    for (int q = 0; q < n && ok; ++q)
+      if (q != rank) ok = (heap_base_[q] = map_seg(q, false)) != nullptr;
+    const bool all_here = barrier().code == FT_OK;      // everybody has mapped everything: the names can go
+    shm_unlink(seg(rank).c_str());
+    if (!ok || !all_here) return false;
+    heap_size_ = bytes;
+    heap_alloc_.reset(bytes);
+    return true;
+  }
+  void* heap_alloc(size_t bytes) {
+    if (!heap_size_) return nullptr;
+    const size_t off = heap_alloc_.alloc(bytes);
+    return off == HeapAllocator::kNone ? nullptr : heap_base_[rank] + off;
+  }
+  bool heap_free(void* ptr) {
+    return heap_size_ && in_heap(ptr, 1) && heap_alloc_.free((size_t)(static_cast<unsigned char*>(ptr) - heap_base_[rank]));
+  }
+  // Collective debugging aid: true when `ptr` sits at the same heap offset on every rank (ranks that allocate
+  // in different orders would otherwise reduce unrelated memory without any error).
+  bool heap_symmetric(const void* ptr) {
+    if (!heap_size_ || !in_heap(ptr, 1)) return false;
+    const uint64_t mine = (uint64_t)(static_cast<const unsigned char*>(ptr) - heap_base_[rank]);
+    sh_->buf[rank].store(mine, std::memory_order_release);
+    if (barrier().code != FT_OK) return false;
+    bool same = true;
+    for (int q = 0; q < n; ++q) same = same && sh_->buf[q].load(std::memory_order_acquire) == mine;
+    return barrier().code == FT_OK && same;
+  }
+  bool in_heap(const void* ptr, size_t bytes) const {
+    const unsigned char* q = static_cast<const unsigned char*>(ptr);
+    return heap_size_ && q >= heap_base_[rank] && q + bytes <= heap_base_[rank] + heap_size_;
+  }
+
  private:
+  // The plan on working copies that every rank can address: base_of(q) is rank q's copy as mapped here.
+  template <class BaseOf>
+  RankStatus run_direct(const Plan& p, ft_op op, ft_dtype dt, const Blocks& g, uint32_t base, size_t es, BaseOf base_of) {
+    RankStatus st;
+    unsigned char* work = base_of(rank);
+    for (int s = 0; s <= p.num_stages; ++s) {
+      st = rendezvous(p.sync[s][rank], base + (uint32_t)s + 1, s);
+      if (st.code != FT_OK || s == p.num_stages) return st;
+      for (const Pull& pl : p.stages[rank][s].pulls) {
+        const uint64_t off = g.offset(pl.block), len = g.length(pl.block);
+        if (!len) continue;
+        unsigned char* mine = work + off * es;
+        if (pl.reduce) {
+          const void* src[FT_MAX_FANIN];
+          int k = 0;
+          src[k++] = mine;
+          for (int q : pl.srcs) src[k++] = base_of(q) + off * es;
+          st.code = reduce_nway_cpu_dispatch(op, dt, src, mine, k, len, 1);
+          if (st.code != FT_OK) return st;
+        } else {
+          std::memcpy(mine, base_of(pl.srcs[0]) + off * es, len * es);
+        }
+      }
+    }
+    return st;
+  }
+
   static constexpr size_t kTileBytes = 256 << 10;   // pulled tiles stay in the cache until they are added
   ProcShared* sh_ = nullptr;
   std::string name_;
   uint32_t epoch_ = 0;
   std::vector<char> tmp_;
+  std::vector<unsigned char*> heap_base_;   // heap_base_[q] = rank q's heap segment as mapped in this process
+  size_t heap_size_ = 0;
+  HeapAllocator heap_alloc_;
 };
 
 }  // namespace ft

@@ -380,6 +380,34 @@ class ProcWorld:
             raise FlexTreeError(code, f"rendezvous {st[1]}, peer {st[2]}: {lib().ft_proc_last_error(self._h).decode()}")
         return dst
 
+    def heap_create(self, nbytes: int):
+        """Collective, once: every rank gets a shared segment of ``nbytes`` that all the others map.  Tensors from
+        :meth:`alloc` are then reduced in place with plain loads from the peers' mappings (no system call, no
+        copy), as long as every rank allocates in the same order."""
+        if lib().ft_proc_heap_create(self._h, nbytes):
+            raise FlexTreeError(9, lib().ft_proc_last_error(self._h).decode())
+
+    def alloc(self, shape, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        """CPU tensor inside this rank's shared heap segment (call :meth:`heap_create` first)."""
+        shape = (shape,) if isinstance(shape, int) else tuple(shape)
+        n = 1
+        for d in shape:
+            n *= int(d)
+        nbytes = max(1, n * torch.empty((), dtype=dtype).element_size())
+        ptr = lib().ft_proc_alloc(self._h, nbytes)
+        if not ptr:
+            raise MemoryError("the process world's heap is exhausted (or heap_create was not called)")
+        t = torch.frombuffer((C.c_char * nbytes).from_address(ptr), dtype=dtype, count=n).view(shape)
+        t._ft_owner = self   # the mapping lives as long as the world
+        return t
+
+    def free(self, tensor: torch.Tensor):
+        check(lib().ft_proc_free(self._h, tensor.data_ptr()), "not a tensor from alloc()")
+
+    def symmetric(self, tensor: torch.Tensor) -> bool:
+        """Collective check that ``tensor`` sits at the same heap offset on every rank."""
+        return bool(lib().ft_proc_heap_symmetric(self._h, tensor.data_ptr()))
+
     def barrier(self):
         check(lib().ft_proc_barrier(self._h), "barrier")
 

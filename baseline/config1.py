@@ -7,7 +7,8 @@ an fp64 sum.  Both arms run config1_driver.cpp (built by install_reference.py):
               (PARALLEL_THREAD, mpi_mod.hpp:820), which oversubscribes a small machine, so it is
               run both as it is and with OMP_THREAD_LIMIT=1 and the faster run is reported
   flextree    this repository's MPI-compatible entry over the thread world (one thread per rank) and over the
-              process world (one process per rank, launched like the reference arm; no MPI library underneath)
+              process world (one process per rank, launched like the reference arm; no MPI library underneath),
+              the latter with the tensor in private memory and in the world's symmetric shared heap
 
     python baseline/config1.py [--count 1048576] [--repeat 20] [--warmup 3]
 
@@ -44,11 +45,11 @@ def run_flextree(world, topo, lonely, count, repeat, warmup):
     return json.loads(r.stdout.strip().splitlines()[-1])
 
 
-def run_flextree_procs(world, topo, lonely, count, repeat, warmup):
+def run_flextree_procs(world, topo, lonely, count, repeat, warmup, heap=False):
     session = "c1p-" + uuid.uuid4().hex[:10]
     procs = []
     for rank in range(world):
-        env = _env(topo, lonely, FT_RANK=str(rank), FT_WORLD=str(world), FT_SESSION=session)
+        env = _env(topo, lonely, FT_RANK=str(rank), FT_WORLD=str(world), FT_SESSION=session, CONFIG1_HEAP="1" if heap else "0")
         procs.append(subprocess.Popen([os.path.join(REF, "ft_config1_procs"), str(world), str(count), str(repeat), str(warmup)],
                                       stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, env=env))
     outs = []
@@ -64,7 +65,7 @@ def run_flextree_procs(world, topo, lonely, count, repeat, warmup):
         except OSError:
             pass
     if any(p.returncode for p in procs):
-        return {"impl": "flextree-procs", "world": world, "error": f"exit codes {[p.returncode for p in procs]}"}
+        return {"impl": "flextree-procs-heap" if heap else "flextree-procs", "world": world, "error": f"exit codes {[p.returncode for p in procs]}"}
     return json.loads(outs[0].strip().splitlines()[-1])
 
 
@@ -117,6 +118,7 @@ def main(argv=None) -> int:
         rows = [ref, ours]
         if os.path.exists(os.path.join(REF, "ft_config1_procs")):
             rows.append(run_flextree_procs(world, topo, lonely, a.count, a.repeat, a.warmup))
+            rows.append(run_flextree_procs(world, topo, lonely, a.count, a.repeat, a.warmup, heap=True))
         for d in rows[1:]:
             if "error" not in ref and "error" not in d:
                 d["speedup_vs_reference_at_min"] = round(ref["ms_min"] / d["ms_min"], 2)

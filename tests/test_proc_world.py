@@ -31,6 +31,22 @@ def _rank(rank, world, session, topo, lonely, q):
             src, dst = every[rank].clone(), torch.zeros(count, dtype=dtype)
             w.all_reduce(src, out=dst)             # out of place leaves the source alone
             ok = ok and torch.equal(src, every[rank]) and torch.equal(dst, mine)
+    # tensors in the world's symmetric heap: reduced in place through the peers' shared mappings
+    w.heap_create(4 << 20)
+    a, b = w.alloc(200_003, torch.float32), w.alloc((50, 7), torch.float64)
+    ok = ok and w.symmetric(a) and w.symmetric(b)
+    for rep in range(2):
+        g = torch.Generator().manual_seed(77 + rep)
+        every = [torch.rand(200_003, generator=g) * 2 - 1 for _ in range(world)]
+        a.copy_(every[rank])
+        w.all_reduce(a)
+        ok = ok and torch.allclose(a.double(), torch.stack([e.double() for e in every]).sum(0), atol=1e-4)
+        b.fill_(float(rank + 1))
+        w.all_reduce(b)
+        ok = ok and bool((b == world * (world + 1) / 2).all())
+    w.free(b)
+    c = w.alloc(300, torch.float64)
+    ok = ok and c.data_ptr() == b.data_ptr() and w.symmetric(c)      # first fit: the freed block is handed out again
     w.barrier()
     w.close()
     q.put((rank, ok))

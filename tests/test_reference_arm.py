@@ -50,8 +50,8 @@ def test_seeded_fp64_checked_comparison_on_6_and_7_ranks():
     r = subprocess.run([sys.executable, os.path.join(ROOT, "baseline", "config1.py"), "--count", "20000", "--repeat", "3",
                         "--warmup", "1", "--omp", "1"], capture_output=True, text=True, timeout=300, cwd=ROOT)
     rows = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
-    assert r.returncode == 0 and len(rows) == 6, (r.stdout[-1500:], r.stderr[-1500:])
-    assert [(d["impl"], d["world"]) for d in rows] == [("reference", 6), ("flextree-threads", 6), ("flextree-procs", 6),
-                                                       ("reference", 7), ("flextree-threads", 7), ("flextree-procs", 7)]
+    assert r.returncode == 0 and len(rows) == 8, (r.stdout[-1500:], r.stderr[-1500:])
+    arms = ["reference", "flextree-threads", "flextree-procs", "flextree-procs-heap"]
+    assert [(d["impl"], d["world"]) for d in rows] == [(a, 6) for a in arms] + [(a, 7) for a in arms]
     assert all(d["check"] == "passed" and d["ms_min"] > 0 for d in rows)
-    assert rows[5]["FT_LONELY"] == "1" and rows[1]["FT_TOPO"] == "2,3"
+    assert rows[7]["FT_LONELY"] == "1" and rows[1]["FT_TOPO"] == "2,3"
