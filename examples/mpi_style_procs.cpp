@@ -23,7 +23,17 @@ int main() {
   MPI_Barrier(comm);
   const int rc = MPI_Allreduce(MPI_IN_PLACE, data.data(), count, MPI_DOUBLE, MPI_SUM, comm);
   const double want = size * (size + 1) / 2.0;
-  const bool ok = rc == 0 && data[0] == want && data[count - 1] == want;
+  bool ok = rc == 0 && data[0] == want && data[count - 1] == want;
+  // The same call on a buffer from the world's symmetric heap is reduced in place through shared mappings
+  // (no copy, no system call) - the host twin of a tensor in the GPU communicator's symmetric heap.
+  ft_proc_world* world = ft_mpi_proc_world(comm);
+  if (ft_proc_heap_create(world, 4 << 20) == 0) {
+    double* shared = (double*)ft_proc_alloc(world, count * sizeof(double));
+    for (int i = 0; i < count; ++i) shared[i] = (double)(rank + 1);
+    ok = ok && MPI_Allreduce(MPI_IN_PLACE, shared, count, MPI_DOUBLE, MPI_SUM, comm) == 0 && shared[0] == want && shared[count - 1] == want;
+  } else {
+    ok = false;
+  }
   std::printf("rank %d of %d: every element = %g (expected %g): %s\n", rank, size, data[0], want, ok ? "ok" : "FAILED");
   ft_mpi_proc_finalize(comm);                           // MPI_Finalize
   return ok ? 0 : 1;
