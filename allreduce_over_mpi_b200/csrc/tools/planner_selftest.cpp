@@ -6,6 +6,8 @@
 // cost models, checks the device tables (and that damaged ones are refused) and the heap allocator, and (argument "threads") runs the thread-per-rank executor with its flag protocol,
 // including a silent rank that must produce time-outs rather than a hang.
 // The reference has no sanitizer builds (its flags are -Wall -Wextra only, allreduce_over_mpi/CMakeLists.txt:5).
+#include <sys/wait.h>
+
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -16,6 +18,7 @@
 #include "../planner/config.hpp"
 #include "../planner/cost_model.hpp"
 #include "../planner/cpu_executor.hpp"
+#include "../planner/proc_world.hpp"
 #include "../runtime/dev_plan.hpp"
 #include "../runtime/heap_alloc.hpp"
 
@@ -122,6 +125,50 @@ static void heap_offsets() {
   }
   for (const auto& l : live) EXPECT(a.free(l.first));
   EXPECT(a.live_blocks() == 0 && a.free_blocks() == 1 && a.largest_free() == a.size());
+}
+
+// Process world: five forked children meet in a session, reduce a private buffer (pulled with
+// process_vm_readv), a small one (through the segment) and one in the symmetric heap, for a lonely layout.
+static void proc_world_forked() {
+  const int n = 5;
+  const std::string session = "selftest-" + std::to_string((long)getpid());
+  std::vector<pid_t> kids;
+  for (int r = 0; r < n; ++r) {
+    const pid_t pid = fork();
+    if (pid == 0) {
+      int bad = 0;
+      {
+        ft::ProcWorld w;
+        if (!w.join(session, r, n, 30.0)) _exit(10);
+        const ft::Plan p = ft::build_plan(n, ft::Shape{{2, 2}, 1, false});
+        for (uint64_t count : {9ull, 70001ull}) {
+          std::vector<double> v(count);
+          for (int round = 0; round < 3; ++round) {
+            for (uint64_t i = 0; i < count; ++i) v[i] = (double)(r + 1) + (double)(i % 5) + round;
+            bad |= w.allreduce(p, FT_SUM, FT_F64, nullptr, v.data(), count).code != FT_OK;
+            for (uint64_t i = 0; i < count; ++i) bad |= v[i] != 15.0 + n * ((double)(i % 5) + round);
+          }
+        }
+        bad |= !w.heap_create(1 << 20);
+        double* h = bad ? nullptr : (double*)w.heap_alloc(30000 * sizeof(double));
+        if (h && w.heap_symmetric(h)) {
+          for (int i = 0; i < 30000; ++i) h[i] = (double)(r + 1);
+          bad |= w.allreduce(p, FT_SUM, FT_F64, nullptr, h, 30000).code != FT_OK;
+          bad |= h[0] != 15.0 || h[29999] != 15.0;
+        } else {
+          bad = 1;
+        }
+        bad |= w.barrier().code != FT_OK;
+      }
+      _exit(bad ? 11 : 0);
+    }
+    kids.push_back(pid);
+  }
+  for (pid_t k : kids) {
+    int status = 0;
+    waitpid(k, &status, 0);
+    EXPECT(WIFEXITED(status) && WEXITSTATUS(status) == 0);
+  }
 }
 
 static void enumerators_and_models() {
@@ -317,7 +364,7 @@ static void thread_world_small_message_twins() {
 
 int main(int argc, char** argv) {
   const bool threads = argc > 1 && !std::strcmp(argv[1], "threads");
-  if (!threads) { plans_and_snapshot(); device_tables(); heap_offsets(); enumerators_and_models(); }
+  if (!threads) { proc_world_forked(); plans_and_snapshot(); device_tables(); heap_offsets(); enumerators_and_models(); }
   thread_world(false);
   thread_world_phases();
   thread_world_small_message_twins();
