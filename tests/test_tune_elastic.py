@@ -89,13 +89,13 @@ def _liveness_worker(rank, world, port, leave_after, q):
     from datetime import timedelta
     from allreduce_over_mpi_b200.parallel.elastic import Liveness, RankLost
     store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=timedelta(seconds=20))
-    live = Liveness(store, rank, world, timeout_s=0.6)
+    live = Liveness(store, rank, world, timeout_s=1.5)   # generous: the ranks share a busy machine with other tests
     step = 0
     try:
-        for step in range(200):
+        for step in range(500):
             if rank == leave_after[0] and step == leave_after[1]:
                 q.put((rank, "left", step))
-                time.sleep(3.0)      # stays quiet (keeps the process, and rank 0's store, alive) while the others notice
+                time.sleep(6.0)      # stays quiet (keeps the process, and rank 0's store, alive) while the others notice
                 return
             live.guard()              # between steps, before the next launch
             time.sleep(0.02)          # the step
