@@ -189,6 +189,32 @@ def make_comm(max_bytes: int, staging: int = 64 << 20) -> FlexTreeComm:
     return FlexTreeComm(heap_bytes=max_bytes + (4 << 20), staging_bytes=staging)
 
 
+def phase_times(a, comm: FlexTreeComm, rank: int, world: int) -> list[dict]:
+    """Device time of the two halves of the staged all-reduce, each issued as a call of its own (max over ranks)."""
+    rows = []
+    for dt_name in a.dtypes:
+        dtype = getattr(torch, dt_name)
+        es = torch.empty((), dtype=dtype).element_size()
+        nbytes = a.min_bytes
+        while nbytes <= a.max_bytes:
+            for text in a.shapes:
+                shape = None if text == "auto" else text
+                comm.free_all()
+                t = comm.alloc(max(1, nbytes // es), dtype)
+                fill(t, rank)
+                times = comm.profile_phases(t, shape=shape, iters=a.iters)
+                v = torch.tensor([times["reduce_scatter_ms"], times["all_gather_ms"]], dtype=torch.float64, device="cuda")
+                dist.all_reduce(v, op=dist.ReduceOp.MAX)
+                comm.check()
+                row = {"bench": "allreduce_phases", "bytes": nbytes, "dtype": dt_name, "world": world, "shape": times["shape"],
+                       "reduce_scatter_ms": round(v[0].item(), 5), "all_gather_ms": round(v[1].item(), 5)}
+                rows.append(row)
+                if rank == 0:
+                    print(json.dumps(row), flush=True)
+            nbytes *= a.step
+    return rows
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--min-bytes", type=int, default=1024)
@@ -207,13 +233,15 @@ def main(argv=None):
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--staged-copy", action="store_true", help="also time the path for tensors outside the symmetric heap")
     ap.add_argument("--out", default=None)
+    ap.add_argument("--phases", action="store_true",
+                    help="instead of the sweep: time the reduce-scatter and the all-gather half separately (staged, heap tensors)")
     a = ap.parse_args(argv)
     a.hybrid = [tuple(float(x) for x in h.split(",")) for h in a.hybrid]
     rank, world, _ = init_dist()
     comm = make_comm(a.max_bytes)
     if rank == 0:
         print(json.dumps({"bench": "allreduce", "world": world, "nvls": comm.has_nvls, "mem_kind": comm.mem_kind}), flush=True)
-    rows = sweep(a, comm, rank, world)
+    rows = phase_times(a, comm, rank, world) if a.phases else sweep(a, comm, rank, world)
     if rank == 0 and a.out:
         with open(a.out, "a") as f:
             for r in rows:
