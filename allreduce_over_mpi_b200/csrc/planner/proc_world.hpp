@@ -23,6 +23,7 @@
 #include <atomic>
 #include <cerrno>
 #include <chrono>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <thread>
@@ -93,6 +94,7 @@ class ProcWorld {
       }
       if (sh_->world != world) { error = "ranks disagree on the world size"; return false; }
     }
+    if (const char* kb = std::getenv("FT_PROC_TILE_KB"); kb && std::atoi(kb) >= 4) tile_bytes_ = (size_t)std::atoi(kb) << 10;
     // let the sibling ranks read this process's memory (needed where ptrace is restricted to descendants)
     prctl(PR_SET_PTRACER, PR_SET_PTRACER_ANY, 0, 0, 0);
     sh_->pid[rank].store((int32_t)getpid(), std::memory_order_release);
@@ -213,11 +215,11 @@ class ProcWorld {
       return st;
     }
     sh_->buf[rank].store((uint64_t)reinterpret_cast<uintptr_t>(recvbuf), std::memory_order_release);
-    const size_t tile_elems = kTileBytes / es;
+    const size_t tile_elems = tile_bytes_ / es;
     int max_src = 1;
     for (int s = 0; s < p.num_stages; ++s)
       for (const Pull& pl : p.stages[rank][s].pulls) max_src = std::max<int>(max_src, (int)pl.srcs.size());
-    if (tmp_.size() < (size_t)max_src * kTileBytes) tmp_.resize((size_t)max_src * kTileBytes);
+    if (tmp_.size() < (size_t)max_src * tile_bytes_) tmp_.resize((size_t)max_src * tile_bytes_);
     for (int s = 0; s <= p.num_stages; ++s) {
       st = rendezvous(p.sync[s][rank], base + (uint32_t)s + 1, s);
       if (st.code != FT_OK || s == p.num_stages) return st;
@@ -246,7 +248,7 @@ class ProcWorld {
         // reductions with the same sources whose blocks fit one tile together: one call per source for all of them
         size_t j = i, batch_bytes = 0;
         while (j < pulls.size() && pulls[j].reduce && pulls[j].srcs == pulls[i].srcs &&
-               batch_bytes + g.length(pulls[j].block) * es <= kTileBytes) {
+               batch_bytes + g.length(pulls[j].block) * es <= tile_bytes_) {
           batch_bytes += g.length(pulls[j].block) * es;
           ++j;
         }
@@ -264,7 +266,7 @@ class ProcWorld {
           for (int q : pulls[i].srcs) {
             std::vector<void*> local;
             for (size_t b = i; b < j; ++b)
-              if (g.length(pulls[b].block)) local.push_back(tmp_.data() + (size_t)k * kTileBytes + at[b - i]);
+              if (g.length(pulls[b].block)) local.push_back(tmp_.data() + (size_t)k * tile_bytes_ + at[b - i]);
             if (!ranges.empty() && !read_peer_ranges(q, ranges, local)) { st = {FT_ERR_PROTOCOL, s, q}; return st; }
             ++k;
           }
@@ -275,7 +277,7 @@ class ProcWorld {
             const void* src[FT_MAX_FANIN];
             int m = 0;
             src[m++] = mine;
-            for (size_t q = 0; q < pulls[i].srcs.size(); ++q) src[m++] = tmp_.data() + q * kTileBytes + at[b - i];
+            for (size_t q = 0; q < pulls[i].srcs.size(); ++q) src[m++] = tmp_.data() + q * tile_bytes_ + at[b - i];
             st.code = reduce_nway_cpu_dispatch(op, dt, src, mine, m, len, 1);
             if (st.code != FT_OK) return st;
           }
@@ -291,7 +293,7 @@ class ProcWorld {
           int k = 0;
           src[k++] = mine;
           for (int q : pl.srcs) {
-            char* slot = tmp_.data() + (size_t)(k - 1) * kTileBytes;
+            char* slot = tmp_.data() + (size_t)(k - 1) * tile_bytes_;
             if (!read_peer(q, (off + t) * es, slot, m * es)) { st = {FT_ERR_PROTOCOL, s, q}; return st; }
             src[k++] = slot;
           }
@@ -385,7 +387,7 @@ class ProcWorld {
     return st;
   }
 
-  static constexpr size_t kTileBytes = 256 << 10;   // pulled tiles stay in the cache until they are added
+  size_t tile_bytes_ = 256 << 10;   // pulled tiles stay in the cache until they are added (FT_PROC_TILE_KB overrides)
   ProcShared* sh_ = nullptr;
   std::string name_;
   uint32_t epoch_ = 0;
