@@ -1,13 +1,15 @@
 // Standalone all-reduce benchmark with the reference driver's command line
 // (allreduce_over_mpi/benchmark.cpp:69-122):
 //
-//     ft_bench [--size N] [--repeat R] [--to-file] [--comm-type flextree|threads|nccl] [--tag T]
+//     ft_bench [--size N] [--repeat R] [--to-file] [--comm-type flextree|threads|procs|nccl] [--tag T]
 //              [--version] [--check] [--gpus G | --ranks G] [--dtype float|bf16] [--phases]
 //
 //   --size       elements per rank (default 35, like the reference)
 //   --repeat     number of timed all-reduces (data is NOT re-initialised between repeats)
 //   --comm-type  flextree = GPU ranks over NVLink peer memory, one host thread per GPU in this
-//                process; threads = CPU ranks (thread world, host memory); nccl = the vendor
+//                process; threads = CPU ranks (thread world, host memory); procs = this process is one CPU
+//                rank of a process world, started once per rank like an MPI job (FT_RANK / FT_WORLD /
+//                FT_SESSION in the environment); nccl = the vendor
 //                library's own all-reduce on the same GPUs (the comparison arm, like the reference's
 //                "--comm-type mpi", which is accepted as another name for it); libnccl is opened at run
 //                time, nothing links against it
@@ -94,6 +96,71 @@ float bf2f(unsigned short h) {
 }
 }  // namespace
 
+// --comm-type procs: this process is ONE rank; start as many copies as there are ranks, the way the reference's
+// benchmark is started by mpirun, with FT_RANK / FT_WORLD / FT_SESSION (or RANK / WORLD_SIZE / MASTER_PORT) set.
+// Host buffers, the process world underneath (no MPI library); rank 0 prints the summary and writes the file.
+static int run_as_process_rank(const Opts& o) {
+  FT_Comm comm = ft_mpi_proc_init_env(60.0);
+  if (!comm) { fprintf(stderr, "%s\n", ft_mpi_last_error()); return 1; }
+  int world = 1, rank = 0;
+  FT_Comm_size(comm, &world);
+  FT_Comm_rank(comm, &rank);
+  ft::ShapeConfig cfg = ft::shape_from_env(world);
+  if (!cfg.ok()) { if (rank == 0) fprintf(stderr, "%s\n", cfg.error.c_str()); ft_mpi_proc_finalize(comm); return 1; }
+  if (rank == 0) {
+    FT_enabled();
+    printf("configuration:\n  - total_peers: %d\n  - data_size: %zu\n  - repeat: %d\n  - to_file: %s\n  - check_validity: %s\n"
+           "  - communication method: procs\n  - And FlexTree topo is %s\n",
+           world, o.size, o.repeat, o.to_file ? "true" : "false", o.check ? "true" : "false",
+           cfg.is_auto ? "auto" : cfg.shape.str().c_str());
+  }
+  std::vector<float> data(o.size);
+  for (size_t i = 0; i < o.size; ++i) data[i] = (float)i * 0.1f;
+  std::vector<double> times;
+  int bad = 0;
+  for (int i = 0; i < o.repeat; ++i) {
+    FT_Barrier(comm);
+    ft::Timer t;
+    t.Start();
+    if (MPI_Allreduce_FT_c(FT_IN_PLACE, data.data(), o.size, FT_FLOAT, FT_OP_SUM, comm) != 0) bad = 2;
+    t.Stop();
+    times.push_back(t.seconds());
+  }
+  if (o.check && !bad) {
+    const double scale = std::pow((double)world, o.repeat);
+    for (size_t i = 0; i < o.size; ++i) {
+      const double want = (double)((float)i * 0.1f) * scale;
+      if (!(std::fabs(data[i] - want) <= 1e-5 * o.repeat * std::fabs(want) + 1e-6)) {
+        bad = 1;
+        fprintf(stderr, "node %d says the result seems not right at %zu: %g vs %g\n", rank, i, (double)data[i], want);
+        break;
+      }
+    }
+  }
+  float failed = bad ? 1.f : 0.f;   // every rank's verdict reaches rank 0
+  MPI_Allreduce_FT_c(FT_IN_PLACE, &failed, 1, FT_FLOAT, FT_OP_SUM, comm);
+  if (rank == 0) {
+    double sum = 0, mn = 1e30;
+    for (double t : times) { sum += t; mn = std::min(mn, t); }
+    if (o.check) printf("%s\n", failed > 0 ? "CHECK failed" : "CHECK (test passed)");
+    if (o.to_file) {
+      std::string name;
+      if (!o.tag.empty()) name += o.tag + ".";
+      name += std::to_string(world) + "." + std::to_string(o.size) + ".";
+      if (cfg.shape.ring) name += "ring";
+      else for (int w : cfg.shape.widths) name += std::to_string(w) + "-";
+      name += "+" + std::to_string(cfg.shape.lonely) + ".ar_test." + std::to_string((long long)time(nullptr)) + ".txt";
+      std::ofstream f(name);
+      for (double t : times) f << t << std::endl;
+      printf("times written to %s\n", name.c_str());
+    }
+    printf("DONE, average time: %g, min time: %g  (busbw at min: %.2f GB/s)\n", sum / o.repeat, mn,
+           (double)o.size * 4 / mn / 1e9 * 2.0 * (world - 1) / world);
+  }
+  ft_mpi_proc_finalize(comm);
+  return failed > 0 ? 2 : 0;
+}
+
 int main(int argc, char** argv) {
   Opts o;
   for (int i = 1; i < argc; ++i) {
@@ -111,6 +178,7 @@ int main(int argc, char** argv) {
     else if (a == "--version") { printf("FlexTree Standalone Benchmark\nversion: %s\n", ft_version()); return 0; }
     else { fprintf(stderr, "unknown parameter: %s\n", a.c_str()); return 1; }
   }
+  if (o.comm == "procs") return run_as_process_rank(o);
   if (o.comm == "mpi") o.comm = "nccl";   // the reference's name for "the library's own all-reduce"
   const bool use_nccl = o.comm == "nccl";
   const bool gpu = o.comm == "flextree" || use_nccl;

@@ -62,6 +62,23 @@ def test_ft_bench_thread_world_check_and_file(tmp_path):
     assert rc == 0 and "CHECK (test passed)" in out, err
 
 
+def test_ft_bench_started_once_per_rank_like_an_mpi_job(tmp_path):
+    """--comm-type procs: six copies of the benchmark, one per rank, meet through the process world (no MPI library)."""
+    import uuid
+    exe = str(BIN / "ft_bench")
+    env = {**os.environ, "FT_WORLD": "6", "FT_SESSION": "tb-" + uuid.uuid4().hex[:8], "FT_TOPO": "2,3"}
+    env.pop("FT_LONELY", None)
+    ps = [subprocess.Popen([exe, "--comm-type", "procs", "--size", "50000", "--repeat", "2", "--check", "--to-file", "--tag", "p"],
+                           env={**env, "FT_RANK": str(r)}, cwd=tmp_path, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+          for r in range(6)]
+    outs = [p.communicate(timeout=120) for p in ps]
+    assert all(p.returncode == 0 for p in ps), outs
+    assert "CHECK (test passed)" in outs[0][0] and "And FlexTree topo is 2*3" in outs[0][0]
+    assert all(o[0] == "" for o in outs[1:])                       # only rank 0 talks
+    files = [f for f in os.listdir(tmp_path) if f.startswith("p.6.50000.2-3-+0.ar_test.")]
+    assert len(files) == 1 and len((tmp_path / files[0]).read_text().split()) == 2
+
+
 def test_reduce_bench_host_side(tmp_path):
     exe = str(BIN / "reduce_bench")
     rc, out, err = run([exe, "--elements", "50000", "--rounds", "2", "--max-width", "5", "--cpu-only"])
