@@ -92,3 +92,19 @@ def test_mpi_spelled_program_as_processes(tmp_path):
     outs = [p.communicate(timeout=120)[0] for p in ps]
     assert all(p.returncode == 0 for p in ps), outs
     assert sorted(outs) == [f"rank {k} of 7: every element = 28 (expected 28): ok\n" for k in range(7)]
+
+
+def test_launcher_starts_one_copy_per_rank_and_reports_the_worst_exit_code():
+    """python -m allreduce_over_mpi_b200.parallel.launch: the one-host stand-in for mpirun."""
+    import sys
+    import time
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = str(LIB.parent / "ft_bench")
+    r = subprocess.run([sys.executable, "-m", "allreduce_over_mpi_b200.parallel.launch", "-np", "5", "--topo", "2,2", "--lonely", "1", "--",
+                        exe, "--comm-type", "procs", "--size", "20000", "--repeat", "2", "--check"],
+                       capture_output=True, text=True, timeout=120, cwd=root)
+    assert r.returncode == 0 and "CHECK (test passed)" in r.stdout and "topo is 2*2+1" in r.stdout, (r.stdout, r.stderr)
+    t0 = time.time()   # one rank fails at once: the job ends with its code and the others are stopped, not waited for
+    r = subprocess.run([sys.executable, "-m", "allreduce_over_mpi_b200.parallel.launch", "-np", "3", "--", "sh", "-c",
+                        "test $FT_RANK != 1 || exit 7; sleep 30"], capture_output=True, text=True, timeout=60, cwd=root)
+    assert r.returncode == 7 and time.time() - t0 < 20
