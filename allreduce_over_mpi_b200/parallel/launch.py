@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import argparse
 import os
+import signal
 import subprocess
 import sys
 import time
@@ -26,25 +27,38 @@ def launch(cmd: list[str], nprocs: int, topo: str | None = None, lonely: str | N
         base["FT_TOPO"] = topo
     if lonely is not None:
         base["FT_LONELY"] = lonely
-    procs = [subprocess.Popen(cmd, env={**base, "FT_RANK": str(r), "RANK": str(r), "LOCAL_RANK": str(r)}) for r in range(nprocs)]
+    # every rank leads a process group of its own, so that stopping a rank also stops what it started
+    procs = [subprocess.Popen(cmd, env={**base, "FT_RANK": str(r), "RANK": str(r), "LOCAL_RANK": str(r)}, start_new_session=True)
+             for r in range(nprocs)]
+
+    def stop(p, sig):
+        try:
+            os.killpg(p.pid, sig)      # the group led by the process started above, nothing else
+        except (ProcessLookupError, PermissionError):
+            pass
     t0 = time.monotonic()
     worst = 0
     try:
-        while any(p.poll() is None for p in procs):
-            failed = [p.returncode for p in procs if p.returncode not in (None, 0)]
+        while True:
+            codes = [p.poll() for p in procs]          # poll every rank, every time
+            if all(c is not None for c in codes):
+                break
+            failed = [c for c in codes if c not in (None, 0)]
             if failed or (timeout is not None and time.monotonic() - t0 > timeout):
                 worst = max([abs(c) for c in failed] + [124 if not failed else 0])
                 break
             time.sleep(0.01)
     finally:
-        for p in procs:        # exactly the processes started above
-            if p.poll() is None:
-                p.terminate()
+        stopped_early = any(p.poll() is None for p in procs)
+        for p in procs:
+            if p.poll() is None or stopped_early:
+                stop(p, signal.SIGTERM)
         for p in procs:
             try:
                 p.wait(timeout=10)
             except subprocess.TimeoutExpired:
-                p.kill()
+                stop(p, signal.SIGKILL)
+                p.wait()
     try:
         os.unlink("/dev/shm/ftpw-" + base["FT_SESSION"])   # a job that was stopped half-way leaves its control segment
     except OSError:
