@@ -86,6 +86,7 @@ def _declare(lib):
         "ft_proc_barrier": (i, [vp]),
         "ft_proc_last_error": (C.c_char_p, [vp]),
         "ft_proc_allreduce": (i, [vp, *shape, i, i, vp, vp, u64, ip]),
+        "ft_proc_phase": (i, [vp, *shape, i, i, vp, u64, i, ip]),
         "ft_proc_heap_create": (i, [vp, sz]),
         "ft_proc_alloc": (vp, [vp, sz]),
         "ft_proc_free": (i, [vp, vp]),

@@ -122,6 +122,9 @@ int ft_proc_world_rank(ft_proc_world* w);
 int ft_proc_world_size(ft_proc_world* w);
 int ft_proc_barrier(ft_proc_world* w);
 const char* ft_proc_last_error(ft_proc_world* w);
+/* one half alone, in place: phase 1 = reduce-scatter stages, 2 = all-gather stages (see ft_cpu_phase) */
+int ft_proc_phase(ft_proc_world* w, const int* widths, int nw, int lonely, int ring, int op, int dtype, void* buf,
+                  uint64_t count, int phase, int* status_out);
 /* Symmetric heap of the process world (the host twin of the GPU communicator's): ft_proc_heap_create is
  * collective and gives every rank one shared segment of `bytes` that all the others map; a buffer from
  * ft_proc_alloc is reduced in place with plain loads from the peers' mappings - no system call, no copy -

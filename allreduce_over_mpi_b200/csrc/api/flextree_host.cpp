@@ -228,6 +228,14 @@ int ft_proc_world_rank(ft_proc_world* h) { return h ? h->w.rank : -1; }
 int ft_proc_world_size(ft_proc_world* h) { return h ? h->w.n : 0; }
 int ft_proc_barrier(ft_proc_world* h) { return h ? h->w.barrier().code : FT_ERR_INVALID_ARG; }
 const char* ft_proc_last_error(ft_proc_world* h) { return h ? h->w.error.c_str() : "null world"; }
+int ft_proc_phase(ft_proc_world* h, const int* widths, int nw, int lonely, int ring, int op, int dtype, void* buf,
+                  uint64_t count, int phase, int* status_out) {
+  if (!h || (phase != 1 && phase != 2)) return FT_ERR_INVALID_ARG;
+  const auto& p = cached_plan(h->w.n, make_shape(widths, nw, lonely, ring));
+  ft::RankStatus st = h->w.allreduce(p, (ft_op)op, (ft_dtype)dtype, nullptr, buf, count, phase);
+  if (status_out) { status_out[0] = st.code; status_out[1] = st.stage; status_out[2] = st.peer; }
+  return st.code;
+}
 int ft_proc_heap_create(ft_proc_world* h, size_t bytes) { return h && h->w.heap_create(bytes) ? FT_OK : FT_ERR_NOT_AVAILABLE; }
 void* ft_proc_alloc(ft_proc_world* h, size_t bytes) { return h ? h->w.heap_alloc(bytes) : nullptr; }
 int ft_proc_free(ft_proc_world* h, void* p) { return h && h->w.heap_free(p) ? FT_OK : FT_ERR_INVALID_ARG; }

@@ -148,6 +148,22 @@ class ProcWorld {
     return n > 1 ? rendezvous(everyone, ++epoch_, 0) : RankStatus{};
   }
 
+  // Rendezvous that opens step `s` of a call running stages [first, last): the stage's own set, or after the last
+  // stage the plan's closing set (every rank when a half runs alone).  Returns true when the call is over.
+  bool open_step(const Plan& p, int s, int last, int phase, uint32_t base, RankStatus* st) {
+    const bool closing = s == last;
+    const int index = closing ? p.num_stages : s;
+    if (closing && phase) {
+      std::vector<int> everyone;
+      for (int q = 0; q < n; ++q)
+        if (q != rank) everyone.push_back(q);
+      *st = rendezvous(everyone, base + (uint32_t)index + 1, index);
+    } else {
+      *st = rendezvous(p.sync[index][rank], base + (uint32_t)index + 1, index);
+    }
+    return st->code != FT_OK || closing;
+  }
+
   // `len` bytes at byte offset `off` of the buffer that `peer` exposes for the running call.
   bool read_peer(int peer, uint64_t off, void* dst, size_t len) {
     const uint64_t base = sh_->buf[peer].load(std::memory_order_acquire);
@@ -188,7 +204,9 @@ class ProcWorld {
   }
 
   // One rank's part of an all-reduce, in place on recvbuf (sendbuf null or == recvbuf) or out of place.
-  RankStatus allreduce(const Plan& p, ft_op op, ft_dtype dt, const void* sendbuf, void* recvbuf, uint64_t count) {
+  // phase 0: the whole all-reduce; 1: the reduce-scatter half alone; 2: the all-gather half alone (each half keeps its
+  // stages' rendezvous numbers and closes with a rendezvous of ALL ranks, like ft_reduce_scatter / ft_all_gather).
+  RankStatus allreduce(const Plan& p, ft_op op, ft_dtype dt, const void* sendbuf, void* recvbuf, uint64_t count, int phase = 0) {
     RankStatus st;
     if (!sh_) { st.code = FT_ERR_INVALID_ARG; return st; }
     if (!p.ok() || p.world != n) { st.code = FT_ERR_INVALID_TOPO; return st; }
@@ -202,15 +220,17 @@ class ProcWorld {
     Blocks g(count, n);
     const uint32_t base = epoch_;
     epoch_ = base + (uint32_t)p.num_stages + 1;
+    const int first = phase == 2 ? p.num_stages / 2 : 0;
+    const int last = phase == 1 ? p.num_stages / 2 : p.num_stages;   // one past the last stage that runs
     // a tensor in the symmetric heap: every peer has it mapped at the same offset of that peer's heap
     if (heap_size_ && in_heap(recvbuf, count * es)) {
       const uint64_t off_in_heap = (uint64_t)(static_cast<unsigned char*>(recvbuf) - heap_base_[rank]);
-      return run_direct(p, op, dt, g, base, es, [&](int q) { return heap_base_[q] + off_in_heap; });
+      return run_direct(p, op, dt, g, base, es, [&](int q) { return heap_base_[q] + off_in_heap; }, first, last, phase);
     }
-    if (count * es <= ProcShared::kEagerBytes) {
+    if (count * es <= ProcShared::kEagerBytes && phase == 0) {   // a half alone leaves partial sums behind: not on a scratch copy
       // the whole call runs on working copies inside the control segment, exactly like the thread world
       std::memcpy(sh_->eager[rank], recvbuf, count * es);
-      st = run_direct(p, op, dt, g, base, es, [&](int q) { return sh_->eager[q]; });
+      st = run_direct(p, op, dt, g, base, es, [&](int q) { return sh_->eager[q]; }, first, last, phase);
       if (st.code == FT_OK) std::memcpy(recvbuf, sh_->eager[rank], count * es);
       return st;
     }
@@ -220,9 +240,8 @@ class ProcWorld {
     for (int s = 0; s < p.num_stages; ++s)
       for (const Pull& pl : p.stages[rank][s].pulls) max_src = std::max<int>(max_src, (int)pl.srcs.size());
     if (tmp_.size() < (size_t)max_src * tile_bytes_) tmp_.resize((size_t)max_src * tile_bytes_);
-    for (int s = 0; s <= p.num_stages; ++s) {
-      st = rendezvous(p.sync[s][rank], base + (uint32_t)s + 1, s);
-      if (st.code != FT_OK || s == p.num_stages) return st;
+    for (int s = first; s <= last; ++s) {
+      if (open_step(p, s, last, phase, base, &st)) return st;
       const std::vector<Pull>& pulls = p.stages[rank][s].pulls;
       size_t i = 0;
       while (i < pulls.size()) {
@@ -362,12 +381,12 @@ class ProcWorld {
  private:
   // The plan on working copies that every rank can address: base_of(q) is rank q's copy as mapped here.
   template <class BaseOf>
-  RankStatus run_direct(const Plan& p, ft_op op, ft_dtype dt, const Blocks& g, uint32_t base, size_t es, BaseOf base_of) {
+  RankStatus run_direct(const Plan& p, ft_op op, ft_dtype dt, const Blocks& g, uint32_t base, size_t es, BaseOf base_of, int first,
+                        int last, int phase) {
     RankStatus st;
     unsigned char* work = base_of(rank);
-    for (int s = 0; s <= p.num_stages; ++s) {
-      st = rendezvous(p.sync[s][rank], base + (uint32_t)s + 1, s);
-      if (st.code != FT_OK || s == p.num_stages) return st;
+    for (int s = first; s <= last; ++s) {
+      if (open_step(p, s, last, phase, base, &st)) return st;
       for (const Pull& pl : p.stages[rank][s].pulls) {
         const uint64_t off = g.offset(pl.block), len = g.length(pl.block);
         if (!len) continue;

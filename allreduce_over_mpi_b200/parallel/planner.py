@@ -380,6 +380,29 @@ class ProcWorld:
             raise FlexTreeError(code, f"rendezvous {st[1]}, peer {st[2]}: {lib().ft_proc_last_error(self._h).decode()}")
         return dst
 
+    def _phase(self, tensor: torch.Tensor, shape, op: str, phase: int) -> Shape:
+        if tensor.is_cuda or not tensor.is_contiguous():
+            raise ValueError("needs a contiguous CPU tensor")
+        shp = shape or shape_from_env(self.world)[0]
+        st = (C.c_int * 3)()
+        code = lib().ft_proc_phase(self._h, *shp.c_args(), OPS[op], ft_dtype(tensor.dtype), tensor.data_ptr(), tensor.numel(), phase, st)
+        if code:
+            raise FlexTreeError(code, f"rendezvous {st[1]}, peer {st[2]}: {lib().ft_proc_last_error(self._h).decode()}")
+        return shp
+
+    def reduce_scatter(self, tensor: torch.Tensor, shape: Shape | None = None, op: str = "sum") -> list[torch.Tensor]:
+        """Reduce-scatter half alone, in place; returns views of the block(s) this rank then holds complete
+        (block b covers elements [b * B, (b + 1) * B), B = ceil(numel / world))."""
+        shp = self._phase(tensor, shape, op, 1)
+        B = -(-tensor.numel() // self.world)
+        flat = tensor.view(-1)
+        return [flat[min(flat.numel(), b * B):min(flat.numel(), (b + 1) * B)] for b in owned_blocks(self.world, shp, self.rank)]
+
+    def all_gather(self, tensor: torch.Tensor, shape: Shape | None = None) -> torch.Tensor:
+        """All-gather half alone: every rank's own blocks are taken as final and copied to all the others."""
+        self._phase(tensor, shape, "sum", 2)
+        return tensor
+
     def heap_create(self, nbytes: int):
         """Collective, once: every rank gets a shared segment of ``nbytes`` that all the others map.  Tensors from
         :meth:`alloc` are then reduced in place with plain loads from the peers' mappings (no system call, no

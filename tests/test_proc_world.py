@@ -44,6 +44,17 @@ def _rank(rank, world, session, topo, lonely, q):
         b.fill_(float(rank + 1))
         w.all_reduce(b)
         ok = ok and bool((b == world * (world + 1) / 2).all())
+    # the two halves as calls of their own, on private memory and on a heap tensor; what a rank does not own is
+    # overwritten in between
+    for t in (torch.empty(90_001, dtype=torch.float64), w.alloc(90_001, torch.float64)):
+        t.fill_(float(rank + 1))
+        mine = w.reduce_scatter(t)
+        ok = ok and len(mine) == 1 and bool((mine[0] == world * (world + 1) / 2).all())
+        keep = mine[0].clone()
+        t.fill_(float("nan"))
+        mine[0].copy_(keep)
+        w.all_gather(t)
+        ok = ok and bool((t == world * (world + 1) / 2).all())
     w.free(b)
     c = w.alloc(300, torch.float64)
     ok = ok and c.data_ptr() == b.data_ptr() and w.symmetric(c)      # first fit: the freed block is handed out again
