@@ -367,11 +367,20 @@ class ProcWorld:
             raise FlexTreeError(9, err.value.decode())
         self.rank, self.world = rank, world
 
-    def all_reduce(self, tensor: torch.Tensor, shape: Shape | None = None, op: str = "sum", out: torch.Tensor | None = None) -> torch.Tensor:
-        """All-reduce a contiguous CPU tensor across the processes (in place unless ``out`` is given)."""
+    device = torch.device("cpu")   # the surface FlexTreeDDP expects of a communicator: alloc, all_reduce, world, rank, device
+
+    def all_reduce(self, tensor: torch.Tensor, shape: Shape | str | None = None, op: str = "sum", out: torch.Tensor | None = None,
+                   **_ignored) -> torch.Tensor:
+        """All-reduce a contiguous CPU tensor across the processes (in place unless ``out`` is given).
+        ``op``: "sum", "band" or "avg" (floating types; the sum divided by the world size)."""
         dst = tensor if out is None else out
         if tensor.is_cuda or not tensor.is_contiguous() or not dst.is_contiguous() or dst.numel() != tensor.numel():
             raise ValueError("needs contiguous CPU tensors of equal size")
+        if op == "avg":
+            self.all_reduce(tensor, shape, "sum", out)
+            return dst.div_(self.world)
+        if isinstance(shape, str):
+            shape = Shape.parse(shape)
         shp = shape or shape_from_env(self.world)[0]
         st = (C.c_int * 3)()
         code = lib().ft_proc_allreduce(self._h, *shp.c_args(), OPS[op], ft_dtype(tensor.dtype),
