@@ -412,6 +412,23 @@ class ProcWorld:
         self._phase(tensor, shape, "sum", 2)
         return tensor
 
+    def profile_phases(self, tensor: torch.Tensor, shape: Shape | None = None, iters: int = 5) -> dict:
+        """Host time (ms, this rank, barrier to return) of the two halves, each issued as a call of its own: what the
+        reference's SHOW_TIME switch logs around its reduce-scatter and all-gather loops (mpi_mod.hpp:31-35,
+        :1597-1599, :1645-1647).  The tensor's contents are reduced ``iters`` times."""
+        import time
+        acc = [0.0, 0.0]
+        for _ in range(iters):
+            self.barrier()
+            t0 = time.perf_counter()
+            self.reduce_scatter(tensor, shape)
+            t1 = time.perf_counter()
+            self.all_gather(tensor, shape)
+            t2 = time.perf_counter()
+            acc[0] += (t1 - t0) * 1e3 / iters
+            acc[1] += (t2 - t1) * 1e3 / iters
+        return {"reduce_scatter_ms": acc[0], "all_gather_ms": acc[1]}
+
     def heap_create(self, nbytes: int):
         """Collective, once: every rank gets a shared segment of ``nbytes`` that all the others map.  Tensors from
         :meth:`alloc` are then reduced in place with plain loads from the peers' mappings (no system call, no

@@ -55,6 +55,8 @@ def _rank(rank, world, session, topo, lonely, q):
         mine[0].copy_(keep)
         w.all_gather(t)
         ok = ok and bool((t == world * (world + 1) / 2).all())
+    times = w.profile_phases(torch.ones(50_000), iters=2)
+    ok = ok and times["reduce_scatter_ms"] > 0 and times["all_gather_ms"] > 0
     w.free(b)
     c = w.alloc(300, torch.float64)
     ok = ok and c.data_ptr() == b.data_ptr() and w.symmetric(c)      # first fit: the freed block is handed out again
