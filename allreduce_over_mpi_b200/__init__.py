@@ -3,7 +3,8 @@ tree-width cost model and an MPI_Allreduce-style entry point.
 
 Sub-packages
     ops       n-way reduce kernels (single GPU) and their CPU oracle
-    parallel  planner / cost model bindings, the multi-GPU communicator, DDP integration
+    parallel  planner / cost model bindings, the multi-GPU communicator, the CPU worlds (ranks as threads or as
+              processes of one host), DDP integration, calibration, a one-host launcher
     models    GPT-2 used by the data-parallel benchmark
     utils     logging, timing, clock sampling
 """
