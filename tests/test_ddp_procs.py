@@ -3,8 +3,13 @@ and no MPI library at all.  Gradient buckets live in the world's shared heap and
 import multiprocessing as mp
 import uuid
 
+import pytest
 import torch
 import torch.nn as nn
+
+from test_proc_world import _cross_memory_read_works
+
+pytestmark = pytest.mark.skipif(not _cross_memory_read_works(), reason="process_vm_readv is not available in this sandbox")
 
 
 def make_model(seed):
