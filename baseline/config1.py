@@ -104,6 +104,7 @@ def main(argv=None) -> int:
     ap.add_argument("--repeat", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--omp", type=int, nargs="+", default=[0, 1], help="OMP_THREAD_LIMIT values tried for the reference (0 = unset)")
+    ap.add_argument("--no-procs", action="store_true", help="leave the process-world arms out (sandboxes without process_vm_readv)")
     a = ap.parse_args(argv)
     for exe in ("ref_config1", "ft_config1"):
         if not os.path.exists(os.path.join(REF, exe)):
@@ -116,7 +117,7 @@ def main(argv=None) -> int:
         ref = min(good, key=lambda r: r["ms_min"]) if good else refs[0]
         ours = run_flextree(world, topo, lonely, a.count, a.repeat, a.warmup)
         rows = [ref, ours]
-        if os.path.exists(os.path.join(REF, "ft_config1_procs")):
+        if os.path.exists(os.path.join(REF, "ft_config1_procs")) and not a.no_procs:
             rows.append(run_flextree_procs(world, topo, lonely, a.count, a.repeat, a.warmup))
             rows.append(run_flextree_procs(world, topo, lonely, a.count, a.repeat, a.warmup, heap=True))
         for d in rows[1:]:
