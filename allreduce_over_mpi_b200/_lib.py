@@ -38,6 +38,13 @@ class V1Params(C.Structure):
                 ("push_gain", C.c_double), ("peer_eff", C.c_double * (FT_MAX_RANKS + 1))]
 
 
+class Choice(C.Structure):
+    """ft_choice of csrc/api/flextree.h: what the selection policy picked for a message."""
+    _fields_ = [("algo", C.c_int), ("nw", C.c_int), ("widths", C.c_int * 16), ("lonely", C.c_int), ("ring", C.c_int),
+                ("from_table", C.c_int), ("hybrid_bytes", C.c_double), ("hybrid_lanes", C.c_double),
+                ("algo_name", C.c_char * 16)]
+
+
 _lib = None
 
 
@@ -60,7 +67,18 @@ def _declare(lib):
         "ft_cost_v1_oneshot": (dbl, [i, u64, C.POINTER(V1Params)]),
         "ft_cost_v1_nvls": (dbl, [i, u64, C.POINTER(V1Params)]),
         "ft_pick_algorithm": (i, [i, u64, C.POINTER(V1Params), i, i, ip, i, ip, ip, cp, sz, C.POINTER(dbl)]),
+        "ft_pick_algorithm2": (i, [i, u64, C.POINTER(V1Params), i, i, i, ip, i, ip, ip, cp, sz, C.POINTER(dbl)]),
         "ft_executable_shapes": (sz, [i, cp, sz]),
+        "ft_policy_create": (vp, [i]),
+        "ft_policy_destroy": (None, [vp]),
+        "ft_policy_default_path": (sz, [cp, sz]),
+        "ft_policy_load": (i, [vp, cp, cp, sz]),
+        "ft_policy_set_params": (i, [vp, C.POINTER(V1Params)]),
+        "ft_policy_get_params": (i, [vp, C.POINTER(V1Params)]),
+        "ft_policy_clear_rows": (None, [vp]),
+        "ft_policy_num_rows": (i, [vp]),
+        "ft_policy_add_row": (i, [vp, u64, cp, cp]),
+        "ft_policy_choose": (i, [vp, u64, i, i, u64, u64, C.POINTER(Choice)]),
         "ft_parse_topo": (i, [cp, cp, i, ip, i, ip, ip, ip, ip, cp, sz]),
         "ft_validate_shape": (i, [i, *shape, cp, sz]),
         "ft_plan_check": (i, [i, *shape, cp, sz]),

@@ -13,6 +13,12 @@ def declare(lib) -> None:
         "ft_reduce_nway_scaled": (i, [i, i, C.POINTER(vp), vp, i, sz, f32, vp]),
         "ft_last_cuda_error": (cp, []),
         "ft_launch_count": (u64, []),
+        "ft_host_pipe_create": (i, [i, sz, i, i, C.POINTER(vp)]),
+        "ft_host_pipe_destroy": (None, [vp]),
+        "ft_host_pipe_last_error": (cp, [vp]),
+        "ft_host_pipe_reduce": (i, [vp, i, i, C.POINTER(vp), i, ip, C.POINTER(vp), i, sz, vp]),
+        "ft_allreduce_host": (i, [vp, vp, vp, sz, i, i, *shape, i, f32, vp]),
+        "ft_comm_set_host_chunk": (None, [vp, sz]),
         "ft_comm_create": (i, [i, i, i, sz, sz, i, C.POINTER(vp)]),
         "ft_comm_destroy": (i, [vp]),
         "ft_comm_last_error": (cp, [vp]),
@@ -42,7 +48,8 @@ def declare(lib) -> None:
         "ft_comm_set_hybrid": (None, [vp, dbl, dbl]),
         "ft_comm_set_ll_max": (None, [vp, sz]),
         "ft_comm_set_nvls_ctas_per_sm": (None, [vp, i]),
-        "ft_comm_set_staged_ctas_per_sm": (None, [vp, i]),
+        "ft_comm_policy": (vp, [vp]),
+        "ft_comm_choose": (i, [vp, sz, i, i, vp, vp]),
         "ft_allreduce_emulate_push": (i, [vp, vp, sz, i, i, f32, vp]),
         "ft_allreduce_emulate_ll": (i, [vp, vp, vp, sz, i, i, f32, i, u64, vp]),
         "ft_allreduce": (i, [vp, vp, vp, sz, i, i, *shape, i, f32, vp]),

@@ -64,8 +64,8 @@ def time_collective(fn, iters: int, warmup: int, flush: bool = True) -> float:
 
 
 # Roofline of an all-reduce on NVSwitch: each GPU must take in 2(N-1)/N * S bytes over its links, so the
-# bus bandwidth cannot exceed the per-direction link bandwidth; 770 GB/s is the measured peer-copy rate of this
-# pool's B200s (900 GB/s nominal).  The HBM side (at most ~3 S bytes per GPU) is an order of magnitude below its roof.
+# bus bandwidth cannot exceed the per-direction link bandwidth; 770 GB/s is the measured peer-copy rate
+# (calibration; 900 GB/s nominal).  The HBM side (at most ~3 S bytes per GPU) is an order of magnitude below its roof.
 LINK_GBPS = 770.0
 
 
@@ -185,8 +185,8 @@ def sweep(a, comm: FlexTreeComm, rank: int, world: int) -> list[dict]:
     return rows
 
 
-def make_comm(max_bytes: int, staging: int = 64 << 20) -> FlexTreeComm:
-    return FlexTreeComm(heap_bytes=max_bytes + (4 << 20), staging_bytes=staging)
+def make_comm(max_bytes: int, staging: int = 64 << 20, extra: int = 0) -> FlexTreeComm:
+    return FlexTreeComm(heap_bytes=max_bytes + (4 << 20) + extra, staging_bytes=staging)
 
 
 def phase_times(a, comm: FlexTreeComm, rank: int, world: int) -> list[dict]:
@@ -262,7 +262,8 @@ def bench_allreduce_main(a) -> dict:
     dtype = getattr(torch, a.dtype)
     es = torch.empty((), dtype=dtype).element_size()
     count = a.bytes // es
-    comm = make_comm(a.bytes)
+    chunk = getattr(a, "e2e_chunk", 16 << 20)
+    comm = make_comm(a.bytes, extra=0 if a.no_e2e else 3 * chunk + (1 << 20))
     buf = comm.alloc(count, dtype)
     fill(buf, rank)
     comm.all_reduce(buf)
@@ -272,9 +273,12 @@ def bench_allreduce_main(a) -> dict:
     name, shp = comm.choose(a.bytes, True, dtype)
     warm = max(a.warmup, 3)
     sampler = ClockSampler(gpu_index=local).start() if rank == 0 else None
+    fill(buf, rank)
 
+    # "avg" = sum with the 1/N factor fused into the reduction's store: the buffer is reduced in place step after
+    # step and stays in [-1, 1) instead of growing by N per step
     def step():
-        comm.all_reduce(buf)
+        comm.all_reduce(buf, op="avg")
 
     for _ in range(warm):
         step()
@@ -294,30 +298,33 @@ def bench_allreduce_main(a) -> dict:
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = t.item() / a.steps
     comm.check()
+    finite = bool(torch.isfinite(buf).all().item())
     # keep the same load running (untimed) until the clock sampler has seen ~0.8 s of it
     for _ in range(min(4000, int(800.0 / max(ms, 1e-3)) + 1)):
         step()
     torch.cuda.synchronize()
     clocks = sampler.stop() if sampler is not None else None
-    nccl_ms = time_collective(lambda: dist.all_reduce(buf), min(a.steps, 10), warm, flush=False)
+    nccl_ms = time_collective(lambda: dist.all_reduce(buf, op=dist.ReduceOp.AVG), min(a.steps, 10), warm, flush=False)
     per_gpu = busbw(a.bytes, ms, world)
     nccl_per_gpu = busbw(a.bytes, nccl_ms, world)
     res = {
-        # whole-job figure: every GPU sustains the bus bandwidth at once, so the job moves N times that
-        "metric": "all-reduce bus bandwidth GB/s, whole job = N x per-GPU busbw; busbw = bytes/t * 2(N-1)/N, t = max over ranks",
-        "value": round(per_gpu * world, 1), "per_gpu_busbw_GBps": round(per_gpu, 1),
+        "metric": "all-reduce bus bandwidth GB/s per GPU; busbw = bytes/t * 2(N-1)/N, t = max over ranks",
+        "value": round(per_gpu, 1), "per_gpu_busbw_GBps": round(per_gpu, 1), "whole_job_GBps": round(per_gpu * world, 1),
+        "value_is": "bus bandwidth each GPU sustains (the conventional figure); all N GPUs sustain it at once, whole_job_GBps = N x value",
         "unit": "GB/s", "n_gpus": world, "steps": a.steps, "warmup": warm,
         "ms_per_step": round(ms, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": a.dtype, "data": "synthetic uniform[-1,1) seeded per rank",
         "config": {"model": "all-reduce", "message_bytes": a.bytes, "global_batch": None, "seq_len": None,
                    "parallelism": f"dp{world}", "algorithm": name, "shape": str(shp), "in_place": "symmetric heap (zero copy)",
+                   "op": "avg (sum, 1/N fused into the store)",
                    "l2": "input larger than L2" if a.bytes > (126 << 20) else "input smaller than L2, not flushed inside the back-to-back loop"},
-        "impl": "flextree", "nvls": comm.has_nvls, "max_abs_err_first_call": err,
+        "impl": "flextree", "nvls": comm.has_nvls, "max_abs_err_first_call": err, "finite_after_timed_steps": finite,
         "nccl_same_buffer": {"ms": round(nccl_ms, 5), "busbw_GBps": round(nccl_per_gpu, 1), "whole_job_GBps": round(nccl_per_gpu * world, 1)},
         "frac_of_nvlink_770GBps": round(per_gpu / 770.0, 3),
+        "frac_of_nvls_roofline": round(per_gpu / (770.0 * 2 * (world - 1) / (world + 1)), 3),
         "scaling_note": "per-GPU message size is fixed (weak scaling); the 1-GPU run of this benchmark measures the n-way reduce kernel "
                         "(HBM-bound, no link involved), so its value is not comparable with the values at N > 1",
-        "gpu_launches": int(launches), "clocks": clocks,
+        "gpu_launches": int(launches), "clocks": clocks, "algorithms_used": comm.stats(),
     }
     if not a.no_e2e:
         res["e2e"] = e2e_allreduce(a, comm, buf, count, dtype, world)
@@ -337,20 +344,28 @@ def bench_allreduce_main(a) -> dict:
 
 
 def e2e_allreduce(a, comm, buf, count, dtype, world) -> dict:
-    """Same step through the public API with the input copied from pinned host memory into the
-    symmetric tensor and a scalar of the result read back every step."""
+    """The same message end to end through the public API for operands in host memory
+    (``comm.all_reduce_host``, what ``MPI_Allreduce_FT`` runs for host buffers): every step takes the whole input
+    from pinned host memory and leaves the WHOLE result in pinned host memory; both copies are inside the timed
+    region and are pipelined chunk by chunk with the NVLink all-reduce."""
+    g = torch.Generator().manual_seed(77 + comm.rank)
     host = torch.empty(count, dtype=dtype).pin_memory()
-    host.copy_(torch.rand(count).to(dtype))
-    probe = torch.empty(16, dtype=dtype).pin_memory()
+    host.copy_((torch.rand(count, generator=g) * 2 - 1).to(dtype))
+    out = torch.empty(count, dtype=dtype).pin_memory()
+    lib_chunk = getattr(a, "e2e_chunk", 16 << 20)
+    from .._lib import lib
+    lib().ft_comm_set_host_chunk(comm._h, lib_chunk)
     steps = max(2, min(a.steps, 5))
 
     def step():
-        buf.copy_(host, non_blocking=True)
-        comm.all_reduce(buf)
-        probe.copy_(buf[:16], non_blocking=True)
+        comm.all_reduce_host(host, out=out, op="avg")
 
     step()
     torch.cuda.synchronize()
+    # check against the same sum made by NCCL from the same host data
+    ref = host.to(comm.device).float()
+    dist.all_reduce(ref)
+    err = (out.to(comm.device).float() - ref / world).abs().max().item()
     dist.barrier()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s.record()
@@ -361,10 +376,13 @@ def e2e_allreduce(a, comm, buf, count, dtype, world) -> dict:
     t = torch.tensor([s.elapsed_time(e)], dtype=torch.float64, device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = t.item() / steps
+    comm.check()
     nbytes = count * host.element_size()
     per_gpu = busbw(nbytes, ms, world)
-    return {"value": round(per_gpu * world, 1), "per_gpu_busbw_GBps": round(per_gpu, 1), "unit": "GB/s", "ms_per_step": round(ms, 4),
-            "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": probe.numel() * probe.element_size(), "steps": steps}
+    return {"value": round(per_gpu, 1), "per_gpu_busbw_GBps": round(per_gpu, 1), "whole_job_GBps": round(per_gpu * world, 1),
+            "unit": "GB/s", "ms_per_step": round(ms, 4), "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes, "steps": steps,
+            "max_abs_err": err, "chunk_bytes": lib_chunk,
+            "api": "FlexTreeComm.all_reduce_host (pinned host in, whole result to pinned host, chunked and overlapped)"}
 
 
 if __name__ == "__main__":

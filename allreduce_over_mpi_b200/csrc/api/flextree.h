@@ -50,8 +50,44 @@ double ft_cost_v1_nvls(int world, uint64_t bytes, const ft_v1_params* p);
 /* writes the winning shape; algo_out receives "staged", "oneshot", "nvls", "ll" or "push" */
 int ft_pick_algorithm(int world, uint64_t bytes, const ft_v1_params* p, int allow_oneshot, int allow_nvls,
                       int* widths, int cap, int* lonely, int* ring, char* algo_out, size_t algo_cap, double* us);
+/* same with the heap condition separate: allow_push != 0 admits the in-place reduce+push kernel */
+int ft_pick_algorithm2(int world, uint64_t bytes, const ft_v1_params* p, int allow_oneshot, int allow_nvls, int allow_push,
+                       int* widths, int cap, int* lonely, int* ring, char* algo_out, size_t algo_cap, double* us);
 /* every executable shape for `world`, one per line ("2*4", "2*2+1", "ring8") */
 size_t ft_executable_shapes(int world, char* buf, size_t cap);
+
+/* ---- selection policy: calibration table + cost model -> algorithm and shape per message size.
+ * The one place where that choice is made: ft_allreduce(FT_ALGO_AUTO), MPI_Allreduce_FT, ft_bench and the
+ * Python front end all go through it.  A policy is built for one world size. ---- */
+typedef struct ft_policy ft_policy;
+typedef struct ft_choice {
+  int algo;            /* FT_ALGO_STAGED .. FT_ALGO_PUSH */
+  int nw;              /* shape of the plan (FT_ALGO_STAGED); flat for the others */
+  int widths[16];
+  int lonely, ring;
+  int from_table;      /* 1: a measured winner, 0: the cost model (or the small-message default) */
+  double hybrid_bytes, hybrid_lanes;   /* FT_ALGO_HYBRID: share of each block / of the CTAs that goes through the switch */
+  char algo_name[16];
+} ft_choice;
+ft_policy* ft_policy_create(int world);
+void ft_policy_destroy(ft_policy* p);
+/* where ft_policy_load(path = NULL) looks: $FT_CALIBRATION, else parallel/calibration_b200.json beside the library */
+size_t ft_policy_default_path(char* buf, size_t cap);
+/* reads {"params": {...}, "table": {"<world>": [[bytes, algo, shape, ...], ...]}}; returns FT_OK, or
+ * FT_ERR_NOT_AVAILABLE with the reason in err (the policy then keeps what it had: the built-in model) */
+int ft_policy_load(ft_policy* p, const char* path, char* err, size_t err_cap);
+int ft_policy_set_params(ft_policy* p, const ft_v1_params* k);
+int ft_policy_get_params(ft_policy* p, ft_v1_params* k);
+void ft_policy_clear_rows(ft_policy* p);
+int ft_policy_num_rows(ft_policy* p);
+/* one measured winner; algo as in the calibration file ("ll", "oneshot", "staged", "push", "nvls",
+ * "hybrid-<bytes>-<lanes>"), shape as text ("8", "2*4", "2*3+1", "ring8") */
+int ft_policy_add_row(ft_policy* p, uint64_t bytes, const char* algo, const char* shape);
+/* in_heap: 16-byte aligned tensor inside the symmetric heap; nvls_ok: multicast bound and the message
+ * qualifies (float type, multiple of 16 bytes); staging_bytes: one staging slot; ll_auto_max: below it the
+ * low-latency protocol is the default where neither table nor model speaks */
+int ft_policy_choose(ft_policy* p, uint64_t bytes, int in_heap, int nvls_ok, uint64_t staging_bytes, uint64_t ll_auto_max,
+                     ft_choice* out);
 
 /* ---- configuration (reference: get_stages, mpi_mod.hpp:1419-1486) ---- */
 /* returns FT_OK or FT_ERR_INVALID_TOPO (message in err) */
@@ -150,6 +186,21 @@ int ft_reduce_nway(int op, int dtype, const void* const* src, void* dst, int n, 
 int ft_reduce_nway_scaled(int in_dtype, int out_dtype, const void* const* src, void* dst, int n, size_t len,
                           float scale, void* stream);
 const char* ft_last_cuda_error(void);
+
+/* ---- n-way reductions of vectors in host memory, pipelined through one GPU (reference: the copy in / kernel /
+ *      copy out sequence of vector_add/vector_add.cu:81-136, done there one after the other) ----
+ * A pipeline owns three streams and a ring of 3 x (max_in + max_out) device chunks of chunk_bytes.
+ * ft_host_pipe_reduce computes, for every j < n_out, host_dst[j][i] = host_src[0][i] (op) ... (op)
+ * host_src[fanin[j]-1][i] over i < len: the inputs are copied in once per chunk and shared by all outputs; the
+ * copy in of chunk k+1, the reductions of chunk k and the copy out of chunk k-1 run at the same time.
+ * Host buffers should be pinned (cudaHostAlloc / cudaHostRegister), else the copies serialise.  Ordered
+ * after the work in `stream`; `stream` waits for the last chunk, so synchronising it completes the call. */
+typedef struct ft_host_pipe ft_host_pipe;
+int ft_host_pipe_create(int device, size_t chunk_bytes, int max_in, int max_out, ft_host_pipe** out);
+void ft_host_pipe_destroy(ft_host_pipe* p);
+const char* ft_host_pipe_last_error(ft_host_pipe* p);
+int ft_host_pipe_reduce(ft_host_pipe* p, int op, int dtype, const void* const* host_src, int n_in, const int* fanin,
+                        void* const* host_dst, int n_out, size_t len, void* stream);
 /* number of kernels launched by this library in this process (all entry points) */
 uint64_t ft_launch_count(void);
 

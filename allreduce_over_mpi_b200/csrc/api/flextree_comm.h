@@ -22,7 +22,7 @@
 #ifndef FLEXTREE_COMM_H_
 #define FLEXTREE_COMM_H_
 
-#include "ft_types.h"
+#include "flextree.h"
 
 #ifdef __cplusplus
 extern "C" {
@@ -31,7 +31,7 @@ extern "C" {
 typedef struct ft_comm ft_comm;
 
 enum { FT_MEM_IPC = 0, FT_MEM_VMM = 1 };
-enum { FT_ALGO_AUTO = 0, FT_ALGO_STAGED = 1, FT_ALGO_ONESHOT = 2, FT_ALGO_NVLS = 3, FT_ALGO_HYBRID = 4, FT_ALGO_LL = 5, FT_ALGO_PUSH = 6 };
+/* FT_ALGO_* are defined in ft_types.h */
 
 /* heap_bytes: symmetric memory for user tensors (ft_comm_alloc) and internal staging.
  * staging_bytes: size of ONE staging slot (two are carved out of the heap); bounds the
@@ -50,6 +50,12 @@ int ft_comm_import_ipc(ft_comm* c, int peer, const void* blob64);
  * single-GPU emulation): map each other directly, then finalize all of them */
 int ft_comm_connect_local(ft_comm** comms, int n);
 int ft_comm_finalize(ft_comm* c);
+/* The communicator's selection policy (created by ft_comm_finalize from $FT_CALIBRATION or the packaged
+ * calibration file; owned by the communicator).  ft_policy_load / ft_policy_add_row on it change what
+ * FT_ALGO_AUTO picks. */
+ft_policy* ft_comm_policy(ft_comm* c);
+/* what FT_ALGO_AUTO would run for `count` elements of `dtype` at `buf` (NULL: a tensor outside the heap) */
+int ft_comm_choose(ft_comm* c, size_t count, int dtype, int op, const void* buf, ft_choice* out);
 
 /* NVLS multicast (optional; VMM heaps only) */
 int ft_comm_mc_supported(ft_comm* c);
@@ -81,13 +87,24 @@ void ft_comm_set_max_lanes(ft_comm* c, int lanes);              /* CTAs per coll
  * (sendbuf must be NULL or == recvbuf).  Otherwise the input is staged through the
  * internal slots and the result lands in recvbuf (count * size <= staging_bytes).
  * shape: (widths, nw, lonely, ring) as in flextree.h; nw == 0 means flat.
- * algo: FT_ALGO_*; AUTO picks the low-latency push protocol up to 8 KiB, one-shot up to
- * `oneshot_max_bytes` (64 KiB unless changed with ft_comm_set_oneshot_max), else the staged plan.
+ * algo: FT_ALGO_*; AUTO asks the communicator's selection policy (ft_comm_policy: the measured winner for
+ * this world and message size from the calibration file, else the NVSwitch cost model), unless a shape is
+ * given, which selects the staged plan.  A device tensor outside the heap that exceeds one staging slot is
+ * reduced piecewise.
  * scale: multiplied into floating-point results (1/world for averaging).
  * Asynchronous on `stream`; errors of device-side waits surface in ft_comm_status. */
 int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op, const int* widths,
                  int nw, int lonely, int ring, int algo, float scale, void* stream);
 void ft_comm_set_oneshot_max(ft_comm* c, size_t bytes);
+/* All-reduce of host memory (pinned for full speed): host_send (NULL: in place) -> host_recv.  The message is
+ * pipelined through three chunk buffers of the symmetric heap on internal streams, so the host-to-device copy of
+ * chunk k+1, the NVLink all-reduce of chunk k and the device-to-host copy of chunk k-1 overlap.  Collective:
+ * every rank calls it (the chunk buffers are allocated from the heap on the first call).  Ordered after the work
+ * already in `stream`; `stream` waits for the last chunk, so synchronising it completes the call.
+ * ft_comm_set_host_chunk sets the chunk size (default 32 MiB) before the first such call. */
+int ft_allreduce_host(ft_comm* c, const void* host_send, void* host_recv, size_t count, int dtype, int op,
+                      const int* widths, int nw, int lonely, int ring, int algo, float scale, void* stream);
+void ft_comm_set_host_chunk(ft_comm* c, size_t bytes);
 /* The two halves of the staged all-reduce as collectives of their own (the reference runs them
  * only back to back inside tree_allreduce, mpi_mod.hpp:1550-1599 and :1620-1647).  Both work in
  * place on a buffer inside the symmetric heap, cut into `world` blocks of
@@ -123,8 +140,6 @@ int ft_allreduce_emulate_ll(ft_comm* c, const void* sendbuf, void* recvbuf, size
 void ft_comm_set_ll_max(ft_comm* c, size_t bytes);
 /* CTAs per SM of the NVLS kernels (1..3, default 1) */
 void ft_comm_set_nvls_ctas_per_sm(ft_comm* c, int n);
-/* CTAs per SM of the staged (plan-driven) kernel: pinned to 1 (a second CTA per SM measured slower) */
-void ft_comm_set_staged_ctas_per_sm(ft_comm* c, int n);
 /* one-shot emulation: phase 1 = publish input (all ranks first), phase 4 = reduce */
 int ft_allreduce_emulate_oneshot(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op,
                                  float scale, int phase, uint64_t call, void* stream);

@@ -1,6 +1,9 @@
 // Host half of the C API: planner, cost models, configuration, CPU executors.
 // Pure C++17; nothing here touches CUDA, so it runs (and is tested) without a GPU.
+#include <dlfcn.h>
+
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -12,6 +15,7 @@
 #include "../planner/cpu_executor.hpp"
 #include "../planner/factorize.hpp"
 #include "../planner/plan.hpp"
+#include "policy_handle.hpp"
 #include "../planner/proc_world.hpp"
 #include "flextree.h"
 #include "../runtime/dev_plan.hpp"
@@ -59,6 +63,23 @@ ft::V1Params to_params(const ft_v1_params* p) {
 }  // namespace
 
 struct ft_cpu_world { ft::CpuWorld w; };
+
+// C form of a policy answer (also used by the communicator runtime)
+void ft_policy_fill_choice(const ft::PolicyChoice& c, ft_choice* out) {
+  std::memset(out, 0, sizeof *out);
+  static const char* names[] = {"auto", "staged", "oneshot", "nvls", "hybrid", "ll", "push"};
+  out->algo = FT_ALGO_STAGED;
+  for (int i = 1; i < 7; ++i)
+    if (c.algo == names[i]) out->algo = i;
+  std::snprintf(out->algo_name, sizeof out->algo_name, "%s", names[out->algo]);
+  out->nw = (int)(c.shape.widths.size() < 16 ? c.shape.widths.size() : 16);
+  for (int i = 0; i < out->nw; ++i) out->widths[i] = c.shape.widths[i];
+  out->lonely = c.shape.lonely;
+  out->ring = c.shape.ring ? 1 : 0;
+  out->from_table = c.from_table ? 1 : 0;
+  out->hybrid_bytes = c.hybrid_bytes;
+  out->hybrid_lanes = c.hybrid_lanes;
+}
 
 extern "C" {
 
@@ -117,6 +138,75 @@ int ft_pick_algorithm(int world, uint64_t bytes, const ft_v1_params* p, int allo
   put(c.algo, algo_out, algo_cap);
   return (int)c.shape.widths.size();
 }
+int ft_pick_algorithm2(int world, uint64_t bytes, const ft_v1_params* p, int allow_oneshot, int allow_nvls, int allow_push,
+                       int* widths, int cap, int* lonely, int* ring, char* algo_out, size_t algo_cap, double* us) {
+  auto c = ft::pick_algorithm(world, bytes, to_params(p), allow_oneshot != 0, allow_nvls != 0, allow_push != 0);
+  for (int i = 0; i < (int)c.shape.widths.size() && i < cap; ++i) widths[i] = c.shape.widths[i];
+  if (lonely) *lonely = c.shape.lonely;
+  if (ring) *ring = c.shape.ring;
+  if (us) *us = c.us;
+  put(c.algo, algo_out, algo_cap);
+  return (int)c.shape.widths.size();
+}
+
+// ---- selection policy
+ft_policy* ft_policy_create(int world) {
+  if (world < 1 || world > FT_MAX_RANKS) return nullptr;
+  return new ft_policy(world);
+}
+void ft_policy_destroy(ft_policy* p) { delete p; }
+size_t ft_policy_default_path(char* buf, size_t cap) {
+  std::string path;
+  if (const char* e = std::getenv("FT_CALIBRATION"); e && *e) {
+    path = e;
+  } else {
+    Dl_info info;
+    if (dladdr((const void*)&ft_policy_default_path, &info) && info.dli_fname) {
+      std::string lib = info.dli_fname;   // .../allreduce_over_mpi_b200/lib/libflextree.so
+      const size_t slash = lib.rfind('/');
+      const std::string dir = slash == std::string::npos ? std::string(".") : lib.substr(0, slash);
+      path = dir + "/../parallel/calibration_b200.json";
+    }
+  }
+  return put(path, buf, cap);
+}
+int ft_policy_load(ft_policy* p, const char* path, char* err, size_t err_cap) {
+  if (!p) return FT_ERR_INVALID_ARG;
+  char dflt[1024];
+  if (!path || !*path) { ft_policy_default_path(dflt, sizeof dflt); path = dflt; }
+  std::string why;
+  int skipped = 0;
+  if (!p->p.load(path, &why, &skipped)) { put(why, err, err_cap); return FT_ERR_NOT_AVAILABLE; }
+  put(skipped ? std::to_string(skipped) + " table rows skipped (unknown algorithm or invalid shape)" : "", err, err_cap);
+  return FT_OK;
+}
+int ft_policy_set_params(ft_policy* p, const ft_v1_params* k) {
+  if (!p || !k) return FT_ERR_INVALID_ARG;
+  p->p.set_params(to_params(k));
+  return FT_OK;
+}
+int ft_policy_get_params(ft_policy* p, ft_v1_params* out) {
+  if (!p || !out) return FT_ERR_INVALID_ARG;
+  const ft::V1Params k = p->p.params();
+  out->launch_us = k.launch_us; out->sync_us = k.sync_us; out->link_gbs = k.link_gbs; out->hbm_gbs = k.hbm_gbs;
+  out->stage_floor_us = k.stage_floor_us; out->nvls_gbs = k.nvls_gbs; out->oneshot_max_bytes = k.oneshot_max_bytes;
+  out->ll_us = k.ll_us; out->ll_max_bytes = k.ll_max_bytes; out->push_gain = k.push_gain;
+  for (int i = 0; i <= FT_MAX_RANKS; ++i) out->peer_eff[i] = i < (int)k.peer_eff.size() ? k.peer_eff[i] : 1.0;
+  return FT_OK;
+}
+void ft_policy_clear_rows(ft_policy* p) { if (p) p->p.clear_rows(); }
+int ft_policy_num_rows(ft_policy* p) { return p ? (int)p->p.num_rows() : 0; }
+int ft_policy_add_row(ft_policy* p, uint64_t bytes, const char* algo, const char* shape) {
+  if (!p || !algo || !shape) return FT_ERR_INVALID_ARG;
+  return p->p.add_row(bytes, algo, shape) ? FT_OK : FT_ERR_INVALID_ARG;
+}
+int ft_policy_choose(ft_policy* p, uint64_t bytes, int in_heap, int nvls_ok, uint64_t staging_bytes, uint64_t ll_auto_max,
+                     ft_choice* out) {
+  if (!p || !out) return FT_ERR_INVALID_ARG;
+  ft_policy_fill_choice(p->p.choose(bytes, in_heap != 0, nvls_ok != 0, staging_bytes, ll_auto_max), out);
+  return FT_OK;
+}
+
 size_t ft_executable_shapes(int world, char* buf, size_t cap) {
   std::string s;
   for (auto& sh : ft::executable_shapes(world)) s += sh.str() + "\n";

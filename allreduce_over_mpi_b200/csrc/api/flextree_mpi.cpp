@@ -22,8 +22,12 @@ struct ft_mpi_comm {
   ft_proc_world* procs = nullptr;   // ... or process world ...
   ft_comm* gpu = nullptr;           // ... or GPU communicator
   void* stream = nullptr;
-  void* bounce = nullptr;           // symmetric-heap region for host buffers (GPU communicator)
-  size_t bounce_bytes = 0;
+  // FT_TOPO / FT_LONELY are looked up on every call like the reference does, but parsed (and the plan fetched)
+  // only when their text changed since the communicator's previous call
+  bool have_cfg = false;
+  std::string topo_text, lonely_text;
+  ft::ShapeConfig cfg;
+  const ft::Plan* plan = nullptr;   // thread world: the plan of cfg.shape
 };
 
 namespace {
@@ -142,7 +146,18 @@ int MPI_Allreduce_FT_c(const void* sendbuf, void* recvbuf, size_t count, FT_Data
     return fail(FT_ERR_UNSUPPORTED_TYPE, std::string("Type ") + ft_dtype_name((ft_dtype)datatype) + " is not supported in MPI mode.");
 
   // tree shape from the environment, on every call like the reference
-  ft::ShapeConfig cfg = ft::shape_from_env(world);
+  {
+    const char* t = std::getenv("FT_TOPO");
+    const char* l = std::getenv("FT_LONELY");
+    if (!comm->have_cfg || comm->topo_text != (t ? t : "") || comm->lonely_text != (l ? l : "")) {
+      comm->topo_text = t ? t : "";
+      comm->lonely_text = l ? l : "";
+      comm->cfg = ft::parse_topo(comm->topo_text, comm->lonely_text, world);
+      comm->plan = nullptr;
+      comm->have_cfg = true;
+    }
+  }
+  const ft::ShapeConfig& cfg = comm->cfg;
   if (!cfg.ok()) return fail(FT_ERR_INVALID_TOPO, cfg.error);
   ft::Shape shape = cfg.shape;
   if (const char* dbg = std::getenv("FT_DEBUG"); dbg && dbg[0] == '1') {
@@ -159,7 +174,8 @@ int MPI_Allreduce_FT_c(const void* sendbuf, void* recvbuf, size_t count, FT_Data
       return 0;
     }
     if (cfg.is_auto) shape = ft::Shape::flat(world);  // on shared host memory every shape moves the same bytes
-    const ft::Plan& plan = plan_for(world, shape);
+    if (!comm->plan) comm->plan = &plan_for(world, shape);
+    const ft::Plan& plan = *comm->plan;
     ft::RankStatus st = ft::cpu_allreduce(comm->threads->w, comm->rank, plan, (ft_op)op, (ft_dtype)datatype,
                                           in_place ? nullptr : sendbuf, recvbuf, count, 0, nullptr, 1);
     if (st.code != FT_OK)
@@ -195,31 +211,30 @@ int MPI_Allreduce_FT_c(const void* sendbuf, void* recvbuf, size_t count, FT_Data
     if (rc != FT_OK) return fail(rc, ft_comm_last_error(g));
     return 0;
   }
-  // host buffers: bounce through a region of the symmetric heap, piecewise if need be
-  const size_t bytes = count * es;
-  if (!comm->bounce) {
-    size_t want = ft_comm_heap_bytes(g) / 4;
-    if (want > (256u << 20)) want = 256u << 20;
-    want = want / 256 * 256;
-    comm->bounce = want ? ft_comm_alloc(g, want) : nullptr;
-    comm->bounce_bytes = comm->bounce ? want : 0;
-    if (!comm->bounce) return fail(FT_ERR_TOO_LARGE, "MPI_Allreduce_FT: no room in the symmetric heap for host-buffer staging");
-  }
+  // Host buffers (the reference's only kind): pipelined through the GPU, see ft_allreduce_host.  A call that mixes
+  // a host and a device buffer is first brought to one side with a plain copy.
   cudaStream_t st = (cudaStream_t)comm->stream;
-  const size_t per = comm->bounce_bytes / es;
-  const char* src = (const char*)(in_place ? recvbuf : sendbuf);
-  for (size_t lo = 0; lo < count; lo += per) {
-    const size_t n = count - lo < per ? count - lo : per;
-    if (cudaMemcpyAsync(comm->bounce, src + lo * es, n * es, cudaMemcpyDefault, st) != cudaSuccess)
+  const size_t bytes = count * es;
+  if (dev_recv) {   // host source, device result
+    if (cudaMemcpyAsync(recvbuf, sendbuf, bytes, cudaMemcpyHostToDevice, st) != cudaSuccess)
       return fail(FT_ERR_CUDA, "MPI_Allreduce_FT: host-to-device copy failed");
-    int rc = ft_allreduce(g, nullptr, comm->bounce, n, datatype, op, explicit_shape ? widths : nullptr, explicit_shape ? nw : 0,
+    int rc = ft_allreduce(g, nullptr, recvbuf, count, datatype, op, explicit_shape ? widths : nullptr, explicit_shape ? nw : 0,
                           explicit_shape ? shape.lonely : 0, explicit_shape ? shape.ring : 0, algo, 1.0f, comm->stream);
     if (rc != FT_OK) return fail(rc, ft_comm_last_error(g));
-    if (cudaMemcpyAsync((char*)recvbuf + lo * es, comm->bounce, n * es, cudaMemcpyDefault, st) != cudaSuccess ||
-        cudaStreamSynchronize(st) != cudaSuccess)
-      return fail(FT_ERR_CUDA, "MPI_Allreduce_FT: device-to-host copy failed");
+    return 0;
   }
-  (void)bytes;
+  if (dev_send && !in_place) {   // device source, host result
+    if (cudaMemcpyAsync(recvbuf, sendbuf, bytes, cudaMemcpyDeviceToHost, st) != cudaSuccess || cudaStreamSynchronize(st) != cudaSuccess)
+      return fail(FT_ERR_CUDA, "MPI_Allreduce_FT: device-to-host copy failed");
+    sendbuf = nullptr;
+  }
+  {
+    int rc = ft_allreduce_host(g, in_place || !sendbuf ? nullptr : sendbuf, recvbuf, count, datatype, op,
+                               explicit_shape ? widths : nullptr, explicit_shape ? nw : 0, explicit_shape ? shape.lonely : 0,
+                               explicit_shape ? shape.ring : 0, algo, 1.0f, comm->stream);
+    if (rc != FT_OK) return fail(rc, ft_comm_last_error(g));
+    if (cudaStreamSynchronize(st) != cudaSuccess) return fail(FT_ERR_CUDA, "MPI_Allreduce_FT: the pipelined host all-reduce failed");
+  }
   int status[5];
   if (ft_comm_status(g, status) != FT_OK)
     return fail(status[0], std::string("MPI_Allreduce_FT: ") + ft_status_name((ft_status)status[0]) + " waiting for rank " + std::to_string(status[2]));

@@ -47,6 +47,9 @@ typedef enum ft_status {
   FT_ERR_NOT_AVAILABLE = 9
 } ft_status;
 
+/* All-reduce algorithms of the GPU communicator (flextree_comm.h); AUTO asks the selection policy. */
+enum { FT_ALGO_AUTO = 0, FT_ALGO_STAGED = 1, FT_ALGO_ONESHOT = 2, FT_ALGO_NVLS = 3, FT_ALGO_HYBRID = 4, FT_ALGO_LL = 5, FT_ALGO_PUSH = 6 };
+
 /* Maximum number of sources of one n-way reduction (own copy included).  The
  * reference stops at 20 (MAX_NUM_BLOCKS, mpi_mod.hpp:811). */
 #define FT_MAX_FANIN 32

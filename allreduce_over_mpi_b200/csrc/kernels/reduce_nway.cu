@@ -19,19 +19,13 @@
 #include <mutex>
 
 #include "../api/flextree.h"
+#include "reduce_nway.cuh"
 #include "vec.cuh"
 
 namespace ftk {
 
 static std::atomic<uint64_t> g_launches{0};
 
-struct NwayArgs {
-  const void* src[FT_MAX_FANIN];
-  void* dst;
-  unsigned long long nvec;   // 16-byte vectors
-  unsigned long long nunit;  // scalar units (see ScalarOp) for the scalar kernel
-  int n;
-};
 
 // ---------------------------------------------------------------------------- vector path
 template <int POL, int UNROLL, int GROUP>
@@ -330,6 +324,24 @@ static int run_policy(NwayArgs& a, size_t bytes, int variant, cudaStream_t st) {
   a.nunit = bytes / unit;
   a.nvec = aligned ? bytes / 16 : 0;
   cudaError_t e = cudaSuccess;
+  // 32-byte accesses (reduce_nway_wide.cu) when every pointer sits on a 32-byte boundary
+  if (a.nvec >= 2 && variant >= 1000) {
+    bool a32 = ((uintptr_t)a.dst & 31) == 0;
+    for (int k = 0; k < a.n; ++k) a32 = a32 && (((uintptr_t)a.src[k] & 31) == 0);
+    if (a32) {
+      const unsigned long long n32 = bytes / 32;
+      e = launch_wide(POL, a, n32, variant, dev_info().sms, st);
+      if (e == cudaSuccess) {
+        g_launches++;
+        e = launch_scalar<POL>(a, n32 * 32 / unit, st);
+        if (e != cudaSuccess) return cuda_fail(e, "reduce_nway scalar launch");
+        return FT_OK;
+      }
+      if (e != cudaErrorInvalidValue) return cuda_fail(e, "reduce_nway wide launch");
+      cudaGetLastError();
+      e = cudaSuccess;   // no such instantiation: the 16-byte kernels take it
+    }
+  }
   if (a.nvec) {
     bool done = false;
     if (variant == 2) { e = launch_tma<POL>(a, st); done = true; }

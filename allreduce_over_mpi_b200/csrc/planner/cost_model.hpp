@@ -165,9 +165,10 @@ struct V1Choice {
   double us = std::numeric_limits<double>::infinity();
 };
 
-// allow_nvls also stands for "the tensor lives in the symmetric heap": NVLS and reduce+push work in place only.
+// NVLS and reduce+push work in place on a tensor in the symmetric heap only: allow_nvls says that the
+// message qualifies for the switch reduction, allow_push (< 0: same as allow_nvls) that it lives in the heap.
 inline V1Choice pick_algorithm(int world, uint64_t bytes, const V1Params& k, bool allow_oneshot = true,
-                               bool allow_nvls = true) {
+                               bool allow_nvls = true, int allow_push = -1) {
   V1Choice best;
   for (auto& s : executable_shapes(world)) {
     Plan p = build_plan(world, s);
@@ -181,7 +182,9 @@ inline V1Choice pick_algorithm(int world, uint64_t bytes, const V1Params& k, boo
   if (allow_nvls) {
     double c = cost_v1_nvls(world, bytes, k);
     if (c < best.us) { best.us = c; best.shape = Shape::flat(world); best.algo = "nvls"; }
-    c = cost_v1_push(world, bytes, k);
+  }
+  if (allow_push < 0 ? allow_nvls : allow_push != 0) {
+    double c = cost_v1_push(world, bytes, k);
     if (c < best.us) { best.us = c; best.shape = Shape::flat(world); best.algo = "push"; }
   }
   if (allow_oneshot) {

@@ -13,6 +13,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <algorithm>
 #include <cstring>
 #include <map>
@@ -22,6 +23,7 @@
 
 #include "../api/flextree.h"
 #include "../api/flextree_comm.h"
+#include "../api/policy_handle.hpp"
 #include "../kernels/comm_dev.h"
 #include "../kernels/pol_ids.h"
 #include "../planner/plan.hpp"
@@ -132,9 +134,20 @@ struct ft_comm {
   size_t oneshot_max = 64 << 10;
   double hybrid_fraction = 0.7, hybrid_lane_fraction = 0.5;
   size_t ll_max = 8 << 10;   // AUTO uses the low-latency protocol up to this size
-  int staged_ctas_per_sm = 1;
   int nvls_ctas_per_sm = 1;   // measured on 8 GPUs: 2 or 3 CTAs per SM lose 5-15 % at 256 MiB and above
   std::map<std::string, DevPlanEntry> plans;
+  // ft_allreduce_host: chunk buffers in the heap + three streams, made on first use
+  struct HostPipe {
+    static constexpr int kDepth = 3;
+    cudaStream_t in = nullptr, run = nullptr, out = nullptr;
+    cudaEvent_t start = nullptr, in_done[kDepth] = {}, run_done[kDepth] = {}, out_done[kDepth] = {};
+    unsigned char* slot[kDepth] = {};
+    size_t chunk = 0;
+    bool used[kDepth] = {};
+  } hp;
+  size_t host_chunk_bytes = 32u << 20;
+  int forced_algo = FT_ALGO_AUTO;   // FT_ALGO=<name> in the environment: what AUTO resolves to, whatever the size
+  ft_policy* policy = nullptr;   // algorithm / shape per message size (calibration table + cost model)
   ftk::CommDev dev{};
   bool finalized = false;
   std::string err;
@@ -261,6 +274,17 @@ int prepare(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dt
   return FT_OK;
 }
 
+bool nvls_eligible(ft_comm* c, const Prepared& pr) {
+  return c->mc_bound && c->mc_va && pr.heap_resident && pr.bytes % 16 == 0 &&
+         (pr.pol == ftk::POL_F32 || pr.pol == ftk::POL_BF16 || pr.pol == ftk::POL_F16);
+}
+ft::PolicyChoice choose_for(ft_comm* c, const Prepared& pr) {
+  if (!c->policy) {   // a communicator that was never finalized still answers from the model
+    c->policy = new ft_policy(c->world);
+  }
+  return c->policy->p.choose(pr.bytes, pr.heap_resident, nvls_eligible(c, pr), c->staging_bytes, c->ll_max);
+}
+
 int launch_staged_call(ft_comm* c, const Prepared& pr, const void* sendbuf, void* recvbuf, size_t count,
                        const ft::Shape& shape, float scale, int stage_begin, int stage_end, bool do_sync, cudaStream_t st,
                        bool phase_alone = false) {
@@ -297,7 +321,7 @@ int launch_staged_call(ft_comm* c, const Prepared& pr, const void* sendbuf, void
     a.end_sync = 0;
     a.user_vec_ok = (((uintptr_t)a.user_in | (uintptr_t)a.user_out) & 15) == 0;
   }
-  const int lanes = pick_lanes(c, a.block_elems * pr.es, 8192, c->staged_ctas_per_sm);
+  const int lanes = pick_lanes(c, a.block_elems * pr.es, 8192);
   cudaError_t e = ftk::launch_staged(pr.pol, c->dev, a, lanes, st);
   if (e != cudaSuccess) return fail(c, FT_ERR_CUDA, std::string("staged launch: ") + cudaGetErrorString(e));
   return FT_OK;
@@ -424,7 +448,7 @@ int ft_comm_destroy(ft_comm* c) {
   if (d.ok && (c->mc_bound || c->mc_joined || c->mc_have)) {
     if (c->mc_va) { d.p_cuMemUnmap(c->mc_va, c->total_bytes); d.p_cuMemAddressFree(c->mc_va, c->total_bytes); }
     if (c->mc_bound && d.p_cuMulticastUnbind) d.p_cuMulticastUnbind(c->mc_handle, c->device, 0, c->total_bytes);
-    if (c->mc_handle) d.p_cuMemRelease(c->mc_handle);
+    if (c->mc_handle && c->mc_have) d.p_cuMemRelease(c->mc_handle);
   }
   for (int r = 0; r < c->world; ++r) {
     if (r == c->rank || !c->peer_base[r]) continue;
@@ -444,6 +468,14 @@ int ft_comm_destroy(ft_comm* c) {
     cudaFree(c->ipc_ptr);
   }
   for (auto& kv : c->plans) { cudaFree(kv.second.plan); cudaFree(kv.second.pulls); }
+  if (c->hp.in) {
+    cudaStreamDestroy(c->hp.in); cudaStreamDestroy(c->hp.run); cudaStreamDestroy(c->hp.out);
+    cudaEventDestroy(c->hp.start);
+    for (int k = 0; k < ft_comm::HostPipe::kDepth; ++k) {
+      cudaEventDestroy(c->hp.in_done[k]); cudaEventDestroy(c->hp.run_done[k]); cudaEventDestroy(c->hp.out_done[k]);
+    }
+  }
+  delete c->policy;
   cudaFree(c->call_count);
   cudaFree(c->arrived);
   if (c->status_host) cudaFreeHost(c->status_host);
@@ -521,6 +553,46 @@ int ft_comm_connect_local(ft_comm** comms, int n) {
       c->peer_base[j] = local_base(o);
     }
   }
+  // NVLS for a world that lives in one process: one multicast object, every rank's device added, every
+  // rank's heap bound at offset 0, one mapping per rank.  Needs VMM heaps on distinct devices that all
+  // support multicast; anything else (or FT_NVLS=0) leaves the world on plain peer access.
+  bool want_mc = n > 1;
+  if (const char* e = std::getenv("FT_NVLS"); e && e[0] == '0') want_mc = false;
+  for (int i = 0; i < n && want_mc; ++i) {
+    want_mc = comms[i]->mem_kind == FT_MEM_VMM && ft_comm_mc_supported(comms[i]);
+    for (int j = 0; j < i && want_mc; ++j) want_mc = comms[j]->device != comms[i]->device;
+  }
+  if (want_mc) {
+    Driver& d = driver();
+    CUmulticastObjectProp mp{};
+    mp.numDevices = (unsigned)n;
+    mp.size = comms[0]->total_bytes;
+    mp.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+    CUmemGenericAllocationHandle h = 0;
+    bool ok = d.p_cuMulticastCreate(&h, &mp) == CUDA_SUCCESS;
+    for (int i = 0; i < n && ok; ++i) ok = d.p_cuMulticastAddDevice(h, comms[i]->device) == CUDA_SUCCESS;
+    for (int i = 0; i < n && ok; ++i) {
+      ft_comm* c = comms[i];
+      cudaSetDevice(c->device);
+      ok = d.p_cuMulticastBindMem(h, 0, c->handle, 0, c->total_bytes, 0) == CUDA_SUCCESS;
+      if (!ok) break;
+      c->mc_handle = h;
+      c->mc_bound = true;
+      c->mc_have = i == 0;   // rank 0 releases the object; the others only unbind and unmap
+      ok = map_handle(c, h, c->total_bytes, &c->mc_va) == FT_OK;
+    }
+    if (!ok) {   // undo: a half-bound world must not claim NVLS
+      for (int i = 0; i < n; ++i) {
+        ft_comm* c = comms[i];
+        if (c->mc_va) { d.p_cuMemUnmap(c->mc_va, c->total_bytes); d.p_cuMemAddressFree(c->mc_va, c->total_bytes); c->mc_va = 0; }
+        if (c->mc_bound && d.p_cuMulticastUnbind) d.p_cuMulticastUnbind(h, c->device, 0, c->total_bytes);
+        c->mc_bound = c->mc_have = false;
+        c->mc_handle = 0;
+        c->err.clear();
+      }
+      if (h) d.p_cuMemRelease(h);
+    }
+  }
   for (int i = 0; i < n; ++i) {
     int rc = ft_comm_finalize(comms[i]);
     if (rc != FT_OK) return rc;
@@ -546,6 +618,41 @@ int ft_comm_finalize(ft_comm* c) {
   d.world = c->world;
   d.timeout_ns = (unsigned long long)(c->timeout_ms * 1e6);
   c->finalized = true;
+  // The selection policy: the calibration file named by FT_CALIBRATION, else the packaged one; without
+  // either the cost model's built-in parameters decide.
+  if (!c->policy) {
+    c->policy = new ft_policy(c->world);
+    char why[256];
+    ft_policy_load(c->policy, nullptr, why, sizeof why);
+  }
+  if (const char* e = std::getenv("FT_ALGO"); e && *e) {
+    static const char* names[] = {"auto", "staged", "oneshot", "nvls", "hybrid", "ll", "push"};
+    for (int i = 0; i < 7; ++i)
+      if (!std::strcmp(e, names[i])) c->forced_algo = i;
+  }
+  // Device tables of the shapes a call is likely to ask for are built now, so that the first step of a
+  // training loop (or a CUDA graph capture) never stops for an allocation and a synchronous upload.
+  if (c->world > 1) {
+    FT_CUDA(c, cudaSetDevice(c->device));
+    DevPlanEntry* pe = nullptr;
+    int rc = get_plan(c, ft::Shape::flat(c->world), &pe);
+    if (rc == FT_OK) rc = get_plan(c, ft::Shape::make_ring(c->world), &pe);
+    if (rc != FT_OK) return rc;
+    for (const ft::Shape& s : c->policy->p.table_shapes())
+      if (get_plan(c, s, &pe) != FT_OK) c->err.clear();   // a bad row costs nothing: the call that wants it reports
+  }
+  return FT_OK;
+}
+
+ft_policy* ft_comm_policy(ft_comm* c) { return c ? c->policy : nullptr; }
+
+int ft_comm_choose(ft_comm* c, size_t count, int dtype, int op, const void* buf, ft_choice* out) {
+  if (!c || !out) return FT_ERR_INVALID_ARG;
+  Prepared pr;
+  int dummy = 0;
+  int rc = prepare(c, nullptr, buf ? (void*)buf : (void*)&dummy, count, dtype, op, &pr);
+  if (rc != FT_OK) return rc;
+  ft_policy_fill_choice(choose_for(c, pr), out);
   return FT_OK;
 }
 
@@ -613,7 +720,13 @@ int ft_comm_free(ft_comm* c, void* p) {
     return fail(c, FT_ERR_INVALID_ARG, "ft_comm_free: not the start of a block from ft_comm_alloc");
   return FT_OK;
 }
-void ft_comm_alloc_reset(ft_comm* c) { if (c) c->heap_alloc.reset(); }
+void ft_comm_alloc_reset(ft_comm* c) {
+  if (!c) return;
+  c->heap_alloc.reset();
+  // the host pipeline's chunk buffers came from the heap too: it takes new ones on its next call
+  c->hp.chunk = 0;
+  for (bool& u : c->hp.used) u = false;
+}
 size_t ft_comm_heap_free_bytes(ft_comm* c) { return c ? c->heap_alloc.largest_free() : 0; }
 int ft_comm_rank(ft_comm* c) { return c ? c->rank : -1; }
 int ft_comm_world(ft_comm* c) { return c ? c->world : 0; }
@@ -647,11 +760,41 @@ int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, i
     }
     return FT_OK;
   }
+  ft::Shape auto_shape;
   if (algo == FT_ALGO_AUTO) {
-    if (nw > 0 || ring) algo = FT_ALGO_STAGED;
-    else if (pr.bytes <= c->ll_max) algo = FT_ALGO_LL;
-    else if (pr.bytes <= c->oneshot_max && pr.bytes <= c->staging_bytes) algo = FT_ALGO_ONESHOT;
-    else algo = FT_ALGO_STAGED;
+    if (nw > 0 || ring) {
+      algo = FT_ALGO_STAGED;
+    } else if (c->forced_algo != FT_ALGO_AUTO) {
+      algo = c->forced_algo;
+    } else {   // one policy for every caller: measured winner for this size, else the cost model
+      const ft::PolicyChoice ch = choose_for(c, pr);
+      ft_choice cc;
+      ft_policy_fill_choice(ch, &cc);
+      algo = cc.algo;
+      if (algo == FT_ALGO_STAGED) {
+        auto_shape = ch.shape;
+        widths = auto_shape.widths.data();
+        nw = (int)auto_shape.widths.size();
+        lonely = auto_shape.lonely;
+        ring = auto_shape.ring ? 1 : 0;
+      } else if (algo == FT_ALGO_HYBRID) {
+        ft_comm_set_hybrid(c, ch.hybrid_bytes, ch.hybrid_lanes);
+      }
+    }
+  }
+  // A device tensor outside the heap that is larger than one staging slot goes through the slots piecewise.
+  if (!pr.heap_resident && pr.bytes > c->staging_bytes && (algo == FT_ALGO_STAGED || algo == FT_ALGO_ONESHOT)) {
+    const size_t per = (c->staging_bytes / pr.es) / 64 * 64;
+    if (!per) return fail(c, FT_ERR_TOO_LARGE, "staging slot smaller than 64 elements");
+    const unsigned char* src = (const unsigned char*)sendbuf;
+    unsigned char* dst = (unsigned char*)recvbuf;
+    for (size_t lo = 0; lo < count; lo += per) {
+      const size_t n = count - lo < per ? count - lo : per;
+      rc = ft_allreduce(c, src ? src + lo * pr.es : nullptr, dst + lo * pr.es, n, dtype, op, widths, nw, lonely, ring,
+                        FT_ALGO_STAGED, scale, stream);
+      if (rc != FT_OK) return rc;
+    }
+    return FT_OK;
   }
   if (algo >= 0 && algo < 7) { c->stat_calls[algo]++; c->stat_bytes[algo] += pr.bytes; }
   if (algo == FT_ALGO_LL) return launch_ll_call(c, pr, sendbuf, recvbuf, count, scale, 3, true, 0, st);
@@ -685,6 +828,78 @@ int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, i
     return FT_OK;
   }
   return launch_staged_call(c, pr, sendbuf, recvbuf, count, make_shape(c->world, widths, nw, lonely, ring), scale, -1, -1, true, st);
+}
+
+// All-reduce of data that lives in host memory, the form the reference's entry point takes
+// (mpi_mod.hpp:1723-1778 works on host buffers only).  The message is cut into chunks that travel
+// through three buffers of the symmetric heap on three streams: while chunk k is being reduced over
+// NVLink, chunk k+1 is on its way in over PCIe and chunk k-1 on its way out, so a large message costs
+// about max(host-to-device, device-to-host) time instead of their sum plus the collective.
+// Every rank has to make the call (the chunk buffers are taken from the heap on first use, which keeps
+// the heaps symmetric only if every rank does it at the same point of its allocation sequence).
+// Asynchronous with respect to the host for pinned buffers; ordered after what `stream` holds at the
+// call, and `stream` waits for the last chunk.
+void ft_comm_set_host_chunk(ft_comm* c, size_t bytes) { if (c && !c->hp.chunk) c->host_chunk_bytes = bytes < 65536 ? 65536 : bytes; }
+
+int ft_allreduce_host(ft_comm* c, const void* host_send, void* host_recv, size_t count, int dtype, int op, const int* widths,
+                      int nw, int lonely, int ring, int algo, float scale, void* stream) {
+  if (!c || !c->finalized) return fail(c, FT_ERR_INVALID_ARG, "communicator not finalized");
+  const size_t es = ft_dtype_size((ft_dtype)dtype);
+  if (!es || ftk::policy_id(op, dtype) < 0)
+    return fail(c, FT_ERR_UNSUPPORTED_TYPE, std::string("Type ") + ft_dtype_name((ft_dtype)dtype) + " is not supported");
+  if (!host_recv && count) return fail(c, FT_ERR_INVALID_ARG, "recvbuf is null");
+  if (count == 0) return FT_OK;
+  FT_CUDA(c, cudaSetDevice(c->device));
+  constexpr int D = ft_comm::HostPipe::kDepth;
+  ft_comm::HostPipe& hp = c->hp;
+  if (!hp.in) {
+    FT_CUDA(c, cudaStreamCreateWithFlags(&hp.in, cudaStreamNonBlocking));
+    FT_CUDA(c, cudaStreamCreateWithFlags(&hp.run, cudaStreamNonBlocking));
+    FT_CUDA(c, cudaStreamCreateWithFlags(&hp.out, cudaStreamNonBlocking));
+    FT_CUDA(c, cudaEventCreateWithFlags(&hp.start, cudaEventDisableTiming));
+    for (int k = 0; k < D; ++k) {
+      FT_CUDA(c, cudaEventCreateWithFlags(&hp.in_done[k], cudaEventDisableTiming));
+      FT_CUDA(c, cudaEventCreateWithFlags(&hp.run_done[k], cudaEventDisableTiming));
+      FT_CUDA(c, cudaEventCreateWithFlags(&hp.out_done[k], cudaEventDisableTiming));
+    }
+  }
+  if (!hp.chunk) {   // the same arithmetic on every rank: equal heaps give equal chunk sizes and offsets
+    size_t chunk = c->host_chunk_bytes;
+    const size_t room = c->heap_alloc.largest_free() / D;
+    if (chunk > room) chunk = room;
+    chunk = chunk / 4096 * 4096;
+    if (!chunk) return fail(c, FT_ERR_TOO_LARGE, "no room in the symmetric heap for the host staging chunks");
+    for (int k = 0; k < D; ++k) {
+      hp.slot[k] = (unsigned char*)ft_comm_alloc(c, chunk);
+      if (!hp.slot[k]) return fail(c, FT_ERR_TOO_LARGE, "no room in the symmetric heap for the host staging chunks");
+    }
+    hp.chunk = chunk;
+  }
+  const size_t per = hp.chunk / es / 64 * 64;   // elements per chunk: whole 16-byte vectors for every type
+  cudaStream_t user = (cudaStream_t)stream;
+  FT_CUDA(c, cudaEventRecord(hp.start, user));
+  FT_CUDA(c, cudaStreamWaitEvent(hp.in, hp.start, 0));
+  // results of an earlier call may still be leaving a buffer on the output stream
+  const unsigned char* src = (const unsigned char*)(host_send ? host_send : host_recv);
+  unsigned char* dst = (unsigned char*)host_recv;
+  int k = 0;
+  for (size_t lo = 0; lo < count; lo += per, k = (k + 1) % D) {
+    const size_t n = count - lo < per ? count - lo : per;
+    if (hp.used[k]) FT_CUDA(c, cudaStreamWaitEvent(hp.in, hp.out_done[k], 0));   // the buffer's previous chunk has left
+    FT_CUDA(c, cudaMemcpyAsync(hp.slot[k], src + lo * es, n * es, cudaMemcpyHostToDevice, hp.in));
+    FT_CUDA(c, cudaEventRecord(hp.in_done[k], hp.in));
+    FT_CUDA(c, cudaStreamWaitEvent(hp.run, hp.in_done[k], 0));
+    int rc = ft_allreduce(c, nullptr, hp.slot[k], n, dtype, op, widths, nw, lonely, ring, algo, scale, hp.run);
+    if (rc != FT_OK) return rc;
+    FT_CUDA(c, cudaEventRecord(hp.run_done[k], hp.run));
+    FT_CUDA(c, cudaStreamWaitEvent(hp.out, hp.run_done[k], 0));
+    FT_CUDA(c, cudaMemcpyAsync(dst + lo * es, hp.slot[k], n * es, cudaMemcpyDeviceToHost, hp.out));
+    FT_CUDA(c, cudaEventRecord(hp.out_done[k], hp.out));
+    hp.used[k] = true;
+  }
+  for (int j = 0; j < D; ++j)
+    if (hp.used[j]) FT_CUDA(c, cudaStreamWaitEvent(user, hp.out_done[j], 0));
+  return FT_OK;
 }
 
 // The two halves of the staged plan as collectives of their own (in place, symmetric heap only).
@@ -762,9 +977,6 @@ int ft_allreduce_emulate_ll(ft_comm* c, const void* sendbuf, void* recvbuf, size
   if (count == 0) return FT_OK;
   return launch_ll_call(c, pr, sendbuf, recvbuf, count, scale, (uint32_t)phase & 3u, false, call, (cudaStream_t)stream);
 }
-// Measured on 8 GPUs: a second CTA per SM does not help the staged kernel (and it needs more than 64
-// registers since its loops are software pipelined), so the setting is pinned to 1.
-void ft_comm_set_staged_ctas_per_sm(ft_comm* c, int n) { (void)n; if (c) c->staged_ctas_per_sm = 1; }
 void ft_comm_set_nvls_ctas_per_sm(ft_comm* c, int n) { if (c && n >= 1 && n <= 3) c->nvls_ctas_per_sm = n; }
 void ft_comm_set_ll_max(ft_comm* c, size_t bytes) { if (c) c->ll_max = bytes < ftk::kLLMaxBytes ? bytes : ftk::kLLMaxBytes; }
 

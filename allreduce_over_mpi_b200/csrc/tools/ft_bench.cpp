@@ -214,15 +214,24 @@ int main(int argc, char** argv) {
     for (int r = 0; r < world; ++r) devs[r] = r;
     if (nccl.CommInitAll(ncomms.data(), world, devs.data()) != 0) { fprintf(stderr, "ncclCommInitAll failed\n"); return 1; }
   } else if (gpu) {
+    // heaps from the virtual-memory API where the driver offers it (that is what NVLS multicast binds to),
+    // else plain cudaMalloc + peer access
     const size_t heap = ((o.size * es + (1 << 20)) + 255) / 256 * 256;
-    for (int r = 0; r < world; ++r) {
-      cudaSetDevice(r);
-      if (ft_comm_create(r, world, r, heap, 1 << 20, FT_MEM_IPC, &comms[r]) != FT_OK) {
-        fprintf(stderr, "rank %d: %s\n", r, ft_comm_last_error(comms[r]));
-        return 1;
+    bool up = false;
+    for (int kind : {FT_MEM_VMM, FT_MEM_IPC}) {
+      bool ok = true;
+      for (int r = 0; r < world && ok; ++r) {
+        cudaSetDevice(r);
+        ok = ft_comm_create(r, world, r, heap, 1 << 20, kind, &comms[r]) == FT_OK;
+        if (!ok && kind == FT_MEM_IPC) fprintf(stderr, "rank %d: %s\n", r, ft_comm_last_error(comms[r]));
       }
+      if (ok && ft_comm_connect_local(comms.data(), world) == FT_OK) { up = true; break; }
+      if (kind == FT_MEM_IPC && ok) fprintf(stderr, "connect: %s\n", ft_comm_last_error(comms[0]));
+      for (auto*& c : comms) { if (c) ft_comm_destroy(c); c = nullptr; }
     }
-    if (ft_comm_connect_local(comms.data(), world) != FT_OK) { fprintf(stderr, "connect: %s\n", ft_comm_last_error(comms[0])); return 1; }
+    if (!up) return 1;
+    printf("  - symmetric memory: %s, nvls %s\n", ft_comm_mem_kind(comms[0]) == FT_MEM_VMM ? "vmm" : "ipc",
+           ft_comm_has_nvls(comms[0]) ? "on" : "off");
   } else {
     cpu_world = ft_cpu_world_create(world, 60.0);
   }

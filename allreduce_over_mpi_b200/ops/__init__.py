@@ -1,1 +1,1 @@
-from .reduce import reduce_nway, reduce_nway_scaled, cpu_reduce, launch_count  # noqa: F401
+from .reduce import HostReducePipeline, reduce_nway, reduce_nway_scaled, cpu_reduce, launch_count  # noqa: F401

@@ -106,3 +106,54 @@ def reduce_nway_scaled(tensors: Sequence[torch.Tensor], scale: float = 1.0,
 def launch_count() -> int:
     """Kernels launched by libflextree in this process so far."""
     return int(lib().ft_launch_count())
+
+
+class HostReducePipeline:
+    """n-way reductions of vectors that live in pinned HOST memory, streamed through one GPU.
+
+    ``run(inputs, fanins, outs)`` computes ``outs[j] = inputs[0] (op) ... (op) inputs[fanins[j]-1]`` for every j.
+    The vectors are cut into chunks; the host-to-device copy of chunk k+1, the reductions of chunk k and the
+    device-to-host copy of chunk k-1 run at the same time on three streams (native: csrc/runtime/host_pipeline.cpp),
+    so a call costs about max(bytes in, bytes out) over the PCIe rate, where copy in / kernel / copy out one after
+    the other (what the reference's benchmark does, vector_add/vector_add.cu:81-136) costs their sum.
+    """
+
+    def __init__(self, device=None, chunk_bytes: int = 16 << 20, max_inputs: int = 8, max_outputs: int = 4):
+        dev = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+        self.device = dev
+        self._h = C.c_void_p()
+        with torch.cuda.device(dev):
+            code = lib().ft_host_pipe_create(dev.index or 0, chunk_bytes, max_inputs, max_outputs, C.byref(self._h))
+        if code:
+            what = lib().ft_host_pipe_last_error(self._h).decode() if self._h else ""
+            self.close()
+            check(code, what)
+
+    def run(self, inputs: Sequence[torch.Tensor], fanins: Sequence[int], outs: Sequence[torch.Tensor], op: str = "sum",
+            stream: torch.cuda.Stream | None = None) -> Sequence[torch.Tensor]:
+        """Asynchronous for pinned tensors: the results are complete once ``stream`` (default: the current
+        stream of the pipeline's device) has been synchronised."""
+        t0 = inputs[0]
+        for t in list(inputs) + list(outs):
+            if t.is_cuda or not t.is_contiguous() or t.dtype != t0.dtype or t.numel() != t0.numel():
+                raise ValueError("inputs and outputs must be contiguous CPU tensors of one dtype and size")
+        if len(fanins) != len(outs):
+            raise ValueError("one fan-in per output")
+        fan = (C.c_int * len(fanins))(*[int(f) for f in fanins])
+        with torch.cuda.device(self.device):
+            st = (stream or torch.cuda.current_stream()).cuda_stream
+            code = lib().ft_host_pipe_reduce(self._h, OPS[op], ft_dtype(t0.dtype), _ptr_array(inputs), len(inputs), fan,
+                                             _ptr_array(outs), len(outs), t0.numel(), C.c_void_p(st))
+        check(code, lib().ft_host_pipe_last_error(self._h).decode() if code else "")
+        return outs
+
+    def close(self):
+        if self._h:
+            lib().ft_host_pipe_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001 - interpreter teardown
+            pass

@@ -24,11 +24,11 @@ from typing import Sequence
 
 import torch
 
-from .._lib import FlexTreeError, OPS, lib
+from .._lib import Choice, FlexTreeError, OPS, lib
 from ..ops.reduce import ft_dtype
 from ..utils import log
 from . import planner
-from .planner import CostParams, Shape
+from .planner import Shape
 
 ALGOS = {"auto": 0, "staged": 1, "oneshot": 2, "nvls": 3, "hybrid": 4, "ll": 5, "push": 6}
 LL_MAX_BYTES = 256 << 10
@@ -70,12 +70,10 @@ class _CommBase:
         self.rank = 0
         self.world = 1
         self.device = torch.device("cuda", 0)
-        self.cost = CostParams.load()
-        self.table = planner.load_choice_table()
         self.default_shape: Shape | None = None
         self.auto = True
         self.has_nvls = False
-        self._choices: dict = {}
+        self._policy = None   # (world, handle) of a free-standing native policy, see _policy_handle()
         self.ll_auto_max = int(os.environ.get("FT_LL_MAX_BYTES", 8 << 10))
         self._heap_range = None
         self._poisoned = False
@@ -103,8 +101,7 @@ class _CommBase:
             self.set_timeout_ms(float(os.environ["FT_TIMEOUT_MS"]))
         if os.environ.get("FT_MAX_LANES"):
             self.set_max_lanes(int(os.environ["FT_MAX_LANES"]))
-        if os.environ.get("FT_STAGED_CTAS_PER_SM"):
-            lib().ft_comm_set_staged_ctas_per_sm(self._h, int(os.environ["FT_STAGED_CTAS_PER_SM"]))
+        lib().ft_comm_set_ll_max(self._h, self.ll_auto_max)
         if os.environ.get("FT_NVLS_CTAS_PER_SM"):
             lib().ft_comm_set_nvls_ctas_per_sm(self._h, int(os.environ["FT_NVLS_CTAS_PER_SM"]))
 
@@ -195,26 +192,34 @@ class _CommBase:
         return self._heap_range[0] <= p and p + t.numel() * t.element_size() <= self._heap_range[1] and p % 16 == 0
 
     # -- selection
+    def _policy_handle(self):
+        """The native selection policy: the communicator's own once it exists, else a free-standing one
+        for this world size loaded from the same calibration file (host-only use and tests)."""
+        if self._h:
+            h = lib().ft_comm_policy(self._h)
+            if h:
+                return h
+        if self._policy is None or self._policy[0] != self.world:
+            h = lib().ft_policy_create(self.world)
+            err = C.create_string_buffer(256)
+            lib().ft_policy_load(h, None, err, 256)
+            self._policy = (self.world, h)
+        return self._policy[1]
+
     def choose(self, nbytes: int, in_heap: bool, dtype: torch.dtype) -> tuple[str, Shape]:
-        """Algorithm and shape for a message, from the calibrated cost model."""
+        """Algorithm and shape for a message: the measured winner for this world and size from the calibration
+        table, else the calibrated cost model.  This asks the same native policy object that
+        ``ft_allreduce(FT_ALGO_AUTO)``, ``MPI_Allreduce_FT`` and ``ft_bench`` use (csrc/planner/policy.hpp)."""
         nvls_ok = self.has_nvls and in_heap and dtype in (torch.float32, torch.bfloat16, torch.float16) and nbytes % 16 == 0
-        key = (nbytes, nvls_ok)
-        hit = self._choices.get(key)
-        if hit is None and self.table:   # measured winners for this world size, nearest size on a log scale
-            import math
-            rows = [r for r in self.table.get(str(self.world), []) if (nvls_ok or not (r[1] == "nvls" or r[1].startswith("hybrid"))) and (in_heap or r[1] != "push") and
-                    (r[1] != "oneshot" or nbytes <= self.staging_bytes) and (r[1] != "ll" or nbytes <= LL_MAX_BYTES)]
-            # the table speaks only for the range of sizes that was measured (one octave of slack)
-            if rows and min(r[0] for r in rows) / 2 <= nbytes <= max(r[0] for r in rows) * 2:
-                b = min(rows, key=lambda r: abs(math.log(max(r[0], 1)) - math.log(max(nbytes, 1))))
-                hit = self._choices[key] = (b[1], Shape.parse(b[2]))
-        if hit is None and nbytes <= self.ll_auto_max and self.world > 1:
-            hit = self._choices[key] = ("ll", Shape.flat(self.world))
-        if hit is None:   # scoring every shape costs ~0.1 ms of host time: do it once per message size
-            algo, shape, _ = planner.pick_algorithm(self.world, nbytes, self.cost, allow_oneshot=nbytes <= self.staging_bytes,
-                                                    allow_nvls=nvls_ok)
-            hit = self._choices[key] = (algo, shape)
-        return hit
+        out = Choice()
+        code = lib().ft_policy_choose(self._policy_handle(), nbytes, int(bool(in_heap)), int(bool(nvls_ok)),
+                                      int(self.staging_bytes), int(self.ll_auto_max), C.byref(out))
+        if code:
+            raise FlexTreeError(code, "selection policy")
+        name = out.algo_name.decode()
+        if name == "hybrid":
+            name = f"hybrid-{out.hybrid_bytes:g}-{out.hybrid_lanes:g}"
+        return name, Shape(tuple(out.widths[i] for i in range(out.nw)), out.lonely, bool(out.ring))
 
     # -- the collective
     def all_reduce(self, tensor: torch.Tensor, op: str = "sum", shape=None, algo: str = "auto", scale: float = 1.0,
@@ -243,19 +248,9 @@ class _CommBase:
             shp = self.default_shape
         a = ALGOS[algo]
         nbytes = tensor.numel() * tensor.element_size()
-        resident = self.in_heap(dst)
-        if shp is None and a == 0 and self.world > 1:
-            name, shp = self.choose(nbytes, resident, tensor.dtype)
-            if name.startswith("hybrid-"):   # "hybrid-<byte fraction>-<lane fraction>" from the calibration table
-                _, bf, lf = name.split("-")
-                self.set_hybrid(float(bf), float(lf))
-                name = "hybrid"
-            a = ALGOS[name]
-            if name != "staged":
-                shp = None
+        # algo "auto" without a shape: the native policy decides inside ft_allreduce (see choose())
         st = (stream or torch.cuda.current_stream(self.device)).cuda_stream
         dt = ft_dtype(tensor.dtype)
-        es = tensor.element_size()
 
         def call(src_ptr, dst_ptr, count):
             if shp is None:
@@ -270,15 +265,37 @@ class _CommBase:
             torch.cuda.nvtx.range_push(f"flextree.all_reduce {nbytes}B {algo if a else 'auto'}")
         with torch.cuda.device(self.device):
             src_ptr = None if dst.data_ptr() == tensor.data_ptr() else tensor.data_ptr()
-            if resident or nbytes <= self.staging_bytes or self.world == 1:
-                call(src_ptr, dst.data_ptr(), tensor.numel())
-            else:  # larger than a staging slot: go through it piecewise
-                per = (self.staging_bytes // es) // 64 * 64
-                for lo in range(0, tensor.numel(), per):
-                    n = min(per, tensor.numel() - lo)
-                    call((src_ptr + lo * es) if src_ptr else None, dst.data_ptr() + lo * es, n)
+            call(src_ptr, dst.data_ptr(), tensor.numel())   # tensors larger than a staging slot are split natively
         if nvtx:
             torch.cuda.nvtx.range_pop()
+        return dst
+
+    def all_reduce_host(self, src: torch.Tensor, out: torch.Tensor | None = None, op: str = "sum", shape=None,
+                        algo: str = "auto", scale: float = 1.0, stream: torch.cuda.Stream | None = None) -> torch.Tensor:
+        """All-reduce of a tensor in (pinned) HOST memory, the form the reference's ``MPI_Allreduce_FT`` takes
+        (allreduce_over_mpi/mpi_mod.hpp:1723-1778 knows host buffers only).  The message is pipelined through
+        three chunk buffers of the symmetric heap: the copy in of chunk k+1, the NVLink all-reduce of chunk k and
+        the copy out of chunk k-1 overlap.  Collective: every rank calls it.  The result (``out``, default in
+        place) is complete once ``stream`` (default: the current stream) has been synchronised."""
+        dst = src if out is None else out
+        for t in (src, dst):
+            if t.is_cuda or not t.is_contiguous():
+                raise ValueError("all_reduce_host needs contiguous CPU tensors (pinned for full speed)")
+        if dst.numel() != src.numel() or dst.dtype != src.dtype:
+            raise ValueError("out must match the input")
+        if self._poisoned:
+            raise FlexTreeError(5, "a device-side wait timed out earlier: rebuild the communicator")
+        if op == "avg":
+            op, scale = "sum", scale / self.world
+        shp = _as_shape(shape, self.world)
+        if shp is None and not self.auto:
+            shp = self.default_shape
+        arr, nw, lonely, ring = (None, 0, 0, 0) if shp is None else shp.c_args()
+        with torch.cuda.device(self.device):
+            st = (stream or torch.cuda.current_stream(self.device)).cuda_stream
+            self._check(lib().ft_allreduce_host(self._h, None if dst.data_ptr() == src.data_ptr() else src.data_ptr(), dst.data_ptr(),
+                                                src.numel(), ft_dtype(src.dtype), OPS[op], arr, nw, lonely, ring, ALGOS[algo],
+                                                float(scale), C.c_void_p(st)))
         return dst
 
     # -- the two halves of the staged plan as collectives of their own
@@ -399,6 +416,9 @@ class _CommBase:
             self._canaries = None if self._canaries is None else []
             lib().ft_comm_destroy(self._h)
             self._h = C.c_void_p()
+        if self._policy is not None:
+            lib().ft_policy_destroy(self._policy[1])
+            self._policy = None
 
     def __del__(self):
         try:

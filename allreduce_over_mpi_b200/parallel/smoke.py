@@ -17,7 +17,38 @@ def smoke_comm_and_model(dev: torch.device) -> None:
     w.all_reduce(ys, algo="oneshot")
     torch.cuda.synchronize(dev)
     assert all(bool((x == 10).all()) for x in xs) and all(bool((y == 10).all()) for y in ys)
+    # the low-latency push protocol, the flat reduce + push kernel (heap tensors) and a lonely layout, same world
+    zs = [torch.full((777,), float(r + 1), device=dev) for r in range(4)]
+    w.all_reduce(zs, algo="ll")
+    ps = [w.ranks[r].alloc(4096, torch.bfloat16) for r in range(4)]
+    for r, p in enumerate(ps):
+        p.fill_(float(r + 1))
+    w.all_reduce(ps, algo="push", op="avg")
+    torch.cuda.synchronize(dev)
+    assert all(bool((z == 10).all()) for z in zs) and all(bool((p == 2.5).all()) for p in ps)
     w.close()
+    w5 = LocalWorld(5, devices=[dev.index] * 5, heap_bytes=1 << 20, staging_bytes=1 << 20)
+    ls = [torch.full((1000,), float(r + 1), device=dev) for r in range(5)]
+    w5.all_reduce(ls, shape="2*2+1")
+    torch.cuda.synchronize(dev)
+    assert all(bool((x == 15).all()) for x in ls)
+    w5.close()
+    # single-GPU n-way reduce: 8 bytes per thread (fp32, fan-in 4), 32-byte accesses, the scaled / casting kernel,
+    # and the pipeline for operands in host memory
+    from ..ops import HostReducePipeline, reduce_nway, reduce_nway_scaled
+    fs = [torch.randn(1 << 16, device=dev) for _ in range(4)]
+    want = torch.stack(fs).sum(0)
+    assert torch.allclose(reduce_nway(fs), want, atol=1e-5)
+    assert torch.allclose(reduce_nway(fs[:2], variant=2011), fs[0] + fs[1], atol=1e-6)
+    got = reduce_nway_scaled(fs, scale=0.25, out_dtype=torch.bfloat16)
+    assert torch.allclose(got.float(), want * 0.25, atol=3e-2)
+    hin = [f.cpu().pin_memory() for f in fs]
+    hout = [torch.empty_like(hin[0]).pin_memory() for _ in range(2)]
+    pipe = HostReducePipeline(device=dev, chunk_bytes=64 << 10, max_inputs=4, max_outputs=2)
+    pipe.run(hin, [2, 4], hout)
+    torch.cuda.synchronize(dev)
+    assert torch.allclose(hout[1], want.cpu(), atol=1e-5) and torch.allclose(hout[0], (fs[0] + fs[1]).cpu(), atol=1e-6)
+    pipe.close()
     # one forward + backward + optimiser step of a 2-layer GPT-2 whose gradients live in the
     # communicator's symmetric heap and go through FlexTreeDDP (world of one rank)
     w1 = LocalWorld(1, devices=[dev.index], heap_bytes=16 << 20, staging_bytes=1 << 20)

@@ -40,6 +40,7 @@ def parse():
     ap.add_argument("--elems", type=int, default=64 << 20, help="vector length of the 1-GPU n-way reduce")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--e2e-chunk", type=int, default=16 << 20, help="chunk size of the host pipelines in the end-to-end step")
     return ap.parse_args()
 
 
@@ -110,6 +111,25 @@ def bench_nway(a) -> dict:
     # correctness of what was timed
     want = torch.stack([v.float() for v in vecs[:4]]).sum(0)
     err = (outs[4].float() - want).abs().max().item()
+    del want
+    # the same four fan-ins on bf16 vectors of the same length (fp32 accumulation, one rounding), untimed above
+    per_n16 = {}
+    if a.dtype == "float32":
+        v16 = [v.to(torch.bfloat16) for v in vecs]
+        o16 = torch.empty_like(v16[0])
+        for n in FANINS:
+            for _ in range(3):
+                reduce_nway(v16[:n], out=o16)
+            ms = []
+            for _ in range(5):
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record(); reduce_nway(v16[:n], out=o16); e.record(); e.synchronize()
+                ms.append(s.elapsed_time(e))
+            t = statistics.median(ms)
+            per_n16[str(n)] = {"ms": round(t, 4), "GBps": round((n + 1) * nbytes / 2 / (t * 1e-3) / 1e9, 1)}
+        want16 = torch.stack([v.float() for v in v16[:8]]).sum(0)
+        per_n16["max_abs_err_n8"] = (o16.float() - want16).abs().max().item()
+        del v16, o16, want16
 
     pk, how = peaks()
     res = {
@@ -120,37 +140,39 @@ def bench_nway(a) -> dict:
         "config": {"model": "n-way reduce-sum, n in {2,3,4,8}", "elems_per_vector": elems, "global_batch": None,
                    "seq_len": None, "parallelism": "single GPU", "l2": "inputs larger than L2 (256 MiB per vector)",
                    "accumulate": "fp32"},
-        "impl": "flextree", "per_fanin": per_n, "frac_of_hbm_copy_peak": round(value / pk["hbm_gbs"], 3),
+        "impl": "flextree", "per_fanin": per_n, "per_fanin_bf16": per_n16, "frac_of_hbm_copy_peak": round(value / pk["hbm_gbs"], 3),
         "peak_source": f"of {how} ({pk['hbm_gbs']} GB/s copy)", "max_abs_err": err,
         "gpu_launches": int(launches), "clocks": clocks,
         "scaling_note": "one GPU has no link to measure: this run times the n-way reduce kernel (HBM-bound), the runs at "
                         "N > 1 time the all-reduce (NVLink-bound); the two values are different quantities",
     }
     if not a.no_e2e:
-        res["e2e"] = e2e_nway(a, vecs, outs, step_bytes)
+        del outs
+        res["e2e"] = e2e_nway(a, vecs, step_bytes)
     return res
 
 
-def e2e_nway(a, vecs, outs, step_bytes) -> dict:
-    """Same step through the public API with the inputs copied from pinned host memory and the
-    results read back every step."""
+def e2e_nway(a, vecs, step_bytes) -> dict:
+    """The same step end to end through the public API for operands in host memory
+    (``ops.HostReducePipeline``): every step copies the 8 input vectors from pinned host memory to the
+    device, reduces the four fan-ins and copies the four results back to pinned host memory.  The copies are
+    part of the timed region; the pipeline overlaps them chunk by chunk with each other and with the kernels."""
     import torch
-    from allreduce_over_mpi_b200.ops import reduce_nway
+    from allreduce_over_mpi_b200.ops import HostReducePipeline
     host_in = [torch.empty(v.shape, dtype=v.dtype).pin_memory() for v in vecs]
     for h, v in zip(host_in, vecs):
         h.copy_(v)
-    host_out = {n: torch.empty(vecs[0].shape, dtype=vecs[0].dtype).pin_memory() for n in FANINS}
+    host_out = [torch.empty(vecs[0].shape, dtype=vecs[0].dtype).pin_memory() for _ in FANINS]
     steps = max(2, min(a.steps, 4))
+    pipe = HostReducePipeline(chunk_bytes=a.e2e_chunk, max_inputs=len(host_in), max_outputs=len(FANINS))
 
     def step():
-        for h, v in zip(host_in, vecs):
-            v.copy_(h, non_blocking=True)
-        for n in FANINS:
-            reduce_nway(vecs[:n], out=outs[n])
-            host_out[n].copy_(outs[n], non_blocking=True)
+        pipe.run(host_in, FANINS, host_out)
 
     step()
     torch.cuda.synchronize()
+    want = torch.stack([h[:4096].float() for h in host_in[:FANINS[-1]]]).sum(0)
+    err = (host_out[-1][:4096].float() - want).abs().max().item()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s.record()
     for _ in range(steps):
@@ -158,10 +180,13 @@ def e2e_nway(a, vecs, outs, step_bytes) -> dict:
     e.record()
     torch.cuda.synchronize()
     ms = s.elapsed_time(e) / steps
+    pipe.close()
     h2d = sum(h.numel() * h.element_size() for h in host_in)
-    d2h = sum(h.numel() * h.element_size() for h in host_out.values())
+    d2h = sum(h.numel() * h.element_size() for h in host_out)
     return {"value": round(step_bytes / (ms * 1e-3) / 1e9, 1), "unit": "GB/s", "ms_per_step": round(ms, 3),
-            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": steps}
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": steps, "max_abs_err": err,
+            "api": "ops.HostReducePipeline.run (pinned host in, pinned host out, chunked and overlapped)",
+            "chunk_bytes": a.e2e_chunk}
 
 
 # ------------------------------------------------------------------------------ main

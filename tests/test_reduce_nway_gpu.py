@@ -129,3 +129,47 @@ def test_bad_arguments():
         reduce_nway([torch.rand(4, device=DEV)] * 33)
     with pytest.raises(ValueError):
         reduce_nway([torch.rand(4, device=DEV), torch.rand(5, device=DEV)])
+
+
+# U * 1000 + LD * 100 + ST * 10 + T of the 32-byte-access kernels (csrc/kernels/reduce_nway_wide.cu)
+WIDE = [1000, 1011, 1113, 2002, 2011, 2110, 2112, 2213, 4000, 4011]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n", [2, 3, 4, 8])
+def test_wide_access_variants_match_the_default_kernels(dtype, n):
+    """Every 256-bit configuration gives the bits of the 16-byte kernels (same summation order), for a length with
+    a ragged tail; configurations that have no instantiation for a fan-in fall back silently."""
+    ts = [rand(1_000_003, dtype, 40 + k) for k in range(n)]
+    want = reduce_nway(ts)
+    exact = torch.stack(ts).double().sum(0)
+    assert torch.allclose(want.double(), exact, atol=1e-5 if dtype == torch.float32 else 4e-2)
+    for v in WIDE:
+        out = reduce_nway(ts, variant=v)
+        assert torch.equal(out, want), (v, (out.float() - want.float()).abs().max().item())
+    # a base that is 16- but not 32-byte aligned takes the 16-byte kernels
+    off = [t[4:] if dtype == torch.float32 else t[8:] for t in ts]
+    assert torch.equal(reduce_nway(off, variant=2011), reduce_nway(off))
+
+
+def test_host_pipeline_reduces_prefixes_of_pinned_vectors():
+    """Operands in pinned host memory, chunked through the device: several fan-ins over shared inputs, a length
+    that is not a multiple of the chunk, two calls back to back on one pipeline."""
+    from allreduce_over_mpi_b200.ops import HostReducePipeline
+    n, length = 5, 300_007
+    g = torch.Generator().manual_seed(5)
+    hin = [(torch.rand(length, generator=g) * 2 - 1).pin_memory() for _ in range(n)]
+    hout = [torch.empty(length).pin_memory() for _ in range(3)]
+    pipe = HostReducePipeline(device=DEV, chunk_bytes=256 << 10, max_inputs=n, max_outputs=3)
+    for _ in range(2):
+        for h in hout:
+            h.fill_(float("nan"))
+        pipe.run(hin, [1, 3, 5], hout)
+        torch.cuda.synchronize()
+        for fan, h in zip([1, 3, 5], hout):
+            want = torch.stack(hin[:fan]).double().sum(0)
+            assert torch.allclose(h.double(), want, atol=1e-5), fan
+        hin[0].add_(1.0)
+    with pytest.raises(Exception):
+        pipe.run(hin, [6], hout[:1])
+    pipe.close()

@@ -83,6 +83,68 @@ def test_selection_from_the_committed_calibration():
                 assert c.choose(nbytes, in_heap, torch.float32) == (name, shape)
 
 
+def test_heap_and_non_heap_tensors_of_one_size_do_not_share_a_cached_pick():
+    """reduce+push works in place on heap tensors only: a pick cached for a heap tensor must never be handed to a
+    tensor of the same size outside the heap (which would be refused at launch), nor the other way round."""
+    from allreduce_over_mpi_b200.parallel.comm import _CommBase
+    for world in (2, 3, 4):
+        for first in (True, False):
+            c = _CommBase()
+            c.world, c.has_nvls, c.staging_bytes = world, False, 64 << 20
+            for nbytes in (1 << 20, 16 << 20, 48 << 20):
+                a = c.choose(nbytes, first, torch.float32)
+                b = c.choose(nbytes, not first, torch.float32)
+                fresh = _CommBase()
+                fresh.world, fresh.has_nvls, fresh.staging_bytes = world, False, 64 << 20
+                assert b == fresh.choose(nbytes, not first, torch.float32), (world, nbytes, first, a, b)
+                outside = b if first else a
+                assert outside[0] not in ("push", "nvls") and not outside[0].startswith("hybrid")
+
+
+def test_native_policy_returns_every_row_of_the_committed_table(tmp_path):
+    """The native policy (what ft_allreduce(FT_ALGO_AUTO), MPI_Allreduce_FT and ft_bench consult) answers each
+    measured size of the committed calibration file with that row's winner; files that are not JSON are
+    refused with a reason and leave the policy on the built-in model."""
+    import ctypes as C
+    import json
+    from allreduce_over_mpi_b200._lib import Choice, lib
+    L = lib()
+    path = planner.calibration_path()
+    table = json.load(open(path))["table"]
+    assert table, "committed calibration has no table"
+    for world_s, rows in table.items():
+        world = int(world_s)
+        h = L.ft_policy_create(world)
+        err = C.create_string_buffer(256)
+        assert L.ft_policy_load(h, path.encode(), err, 256) == 0 and err.value == b"", err.value
+        assert L.ft_policy_num_rows(h) == len(rows)
+        for r in rows:
+            nbytes, algo, shape = r[0], r[1], r[2]
+            out = Choice()
+            assert L.ft_policy_choose(h, nbytes, 1, 1, 64 << 20, 8 << 10, C.byref(out)) == 0
+            assert out.from_table == 1
+            assert out.algo_name.decode() == algo.split("-")[0], (world, r, out.algo_name)
+            if algo == "staged":
+                got = planner.Shape(tuple(out.widths[i] for i in range(out.nw)), out.lonely, bool(out.ring))
+                assert str(got) == str(planner.Shape.parse(shape))
+        L.ft_policy_destroy(h)
+    bad = tmp_path / "broken.json"
+    bad.write_text('{"params": {"launch_us": 3.0}, "table": {"8": [[1024, "ll", "8"],]}}')
+    h = L.ft_policy_create(8)
+    err = C.create_string_buffer(256)
+    assert L.ft_policy_load(h, str(bad).encode(), err, 256) != 0 and b"offset" in err.value
+    assert L.ft_policy_num_rows(h) == 0
+    odd = tmp_path / "odd_rows.json"
+    odd.write_text(json.dumps({"params": {"launch_us": 3.0, "peer_eff": {"2": 0.5}},
+                               "table": {"8": [[1024, "ll", "8", 1.0], [4096, "warp-drive", "8"], [8192, "staged", "3*3"]]}}))
+    assert L.ft_policy_load(h, str(odd).encode(), err, 256) == 0 and b"2 table rows skipped" in err.value
+    assert L.ft_policy_num_rows(h) == 1
+    from allreduce_over_mpi_b200._lib import V1Params
+    k = V1Params()
+    assert L.ft_policy_get_params(h, C.byref(k)) == 0 and k.launch_us == 3.0 and k.peer_eff[2] == 0.5
+    L.ft_policy_destroy(h)
+
+
 def _liveness_worker(rank, world, port, leave_after, q):
     import time
     import torch.distributed as dist
