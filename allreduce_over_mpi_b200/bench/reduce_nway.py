@@ -33,17 +33,30 @@ def measured_hbm_gbs() -> tuple[float, str]:
     return 6650.0, "fallback"
 
 
-def run(n: int, elems: int, dtype: torch.dtype, variant: int, iters: int, warmup: int, check: bool, cpu: bool) -> dict:
+def run(n: int, elems: int, dtype: torch.dtype, variant: int, iters: int, warmup: int, check: bool, cpu: bool, b2b: int = 0) -> dict:
     dev = "cuda:0"
     g = torch.Generator(device=dev).manual_seed(1234 + n)
     ts = [(torch.rand(elems, generator=g, device=dev) * 2 - 1).to(dtype) for _ in range(n)]
     out = torch.empty_like(ts[0])
-    ms = cuda_time(lambda: reduce_nway(ts, out=out, variant=variant), iters=iters, warmup=warmup, flush=True)
+    if b2b > 0:   # `b2b` launches back to back between one pair of events (inputs larger than L2, no flush):
+        ms = []   # what a training step or the headline benchmark sees, without the ramp of a lone launch
+        for _ in range(warmup):
+            reduce_nway(ts, out=out, variant=variant)
+        for _ in range(iters):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(b2b):
+                reduce_nway(ts, out=out, variant=variant)
+            e.record()
+            e.synchronize()
+            ms.append(s.elapsed_time(e) / b2b)
+    else:
+        ms = cuda_time(lambda: reduce_nway(ts, out=out, variant=variant), iters=iters, warmup=warmup, flush=True)
     t = statistics.median(ms)
     nbytes = elems * ts[0].element_size()
     gbs = (n + 1) * nbytes / (t * 1e-3) / 1e9
     peak, how = measured_hbm_gbs()
-    row = {"bench": "reduce_nway", "n": n, "elems": elems, "dtype": str(dtype).split(".")[-1], "variant": variant,
+    row = {"bench": "reduce_nway", "n": n, "elems": elems, "dtype": str(dtype).split(".")[-1], "variant": variant, "back_to_back": b2b,
            "ms_median": round(t, 4), "ms_min": round(min(ms), 4), "GBps": round(gbs, 1),
            "frac_of_hbm": round(gbs / peak, 3), "hbm_peak_GBps": peak, "peak_source": f"of {how}"}
     if check or cpu:
@@ -71,6 +84,7 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--check", action="store_true", help="verify against the CPU kernel")
     ap.add_argument("--cpu", action="store_true", help="also time the CPU kernel")
+    ap.add_argument("--b2b", type=int, default=0, help="time this many launches back to back per sample instead of lone launches after an L2 flush")
     ap.add_argument("--out", default=None, help="append JSON lines to this file")
     a = ap.parse_args(argv)
     if not torch.cuda.is_available():
@@ -81,7 +95,7 @@ def main(argv=None):
     for dt in a.dtypes:
         for n in a.fanin:
             for v in a.variants:
-                row = run(n, a.elems, getattr(torch, dt), v, a.iters, a.warmup, a.check, a.cpu)
+                row = run(n, a.elems, getattr(torch, dt), v, a.iters, a.warmup, a.check, a.cpu, a.b2b)
                 rows.append(row)
                 line = json.dumps(row)
                 print(line, flush=True)
