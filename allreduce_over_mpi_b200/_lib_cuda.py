@@ -48,6 +48,8 @@ def declare(lib) -> None:
         "ft_comm_set_hybrid": (None, [vp, dbl, dbl]),
         "ft_comm_set_ll_max": (None, [vp, sz]),
         "ft_comm_set_nvls_ctas_per_sm": (None, [vp, i]),
+        "ft_comm_set_nvls_config": (i, [vp, i, i, i, i, sz]),
+        "ft_comm_set_phase_nvls": (None, [vp, i]),
         "ft_comm_policy": (vp, [vp]),
         "ft_comm_choose": (i, [vp, sz, i, i, vp, vp]),
         "ft_allreduce_emulate_push": (i, [vp, vp, sz, i, i, f32, vp]),

@@ -116,7 +116,10 @@ void ft_comm_set_host_chunk(ft_comm* c, size_t bytes);
  *                      leaves every rank with every block.
  * ft_reduce_scatter followed by ft_all_gather on the same buffer and shape equals ft_allreduce
  * with FT_ALGO_STAGED.  Each call closes with a rendezvous of all ranks, so the buffer may be
- * rewritten as soon as the call has completed on the caller's stream. */
+ * rewritten as soon as the call has completed on the caller's stream.
+ * With the flat shape, on a float tensor of a multiple of 16 bytes and NVLS multicast bound, each half is one
+ * multimem pass through the switch: multimem.ld_reduce of block `rank` into the own buffer (reduce-scatter),
+ * multimem.st of block `rank` to every rank (all-gather). */
 int ft_reduce_scatter(ft_comm* c, void* buf, size_t count, int dtype, int op, const int* widths, int nw, int lonely,
                       int ring, float scale, void* stream);
 int ft_all_gather(ft_comm* c, void* buf, size_t count, int dtype, const int* widths, int nw, int lonely, int ring,
@@ -140,6 +143,13 @@ int ft_allreduce_emulate_ll(ft_comm* c, const void* sendbuf, void* recvbuf, size
 void ft_comm_set_ll_max(ft_comm* c, size_t bytes);
 /* CTAs per SM of the NVLS kernels (1..3, default 1) */
 void ft_comm_set_nvls_ctas_per_sm(ft_comm* c, int n);
+/* Launch shape of the NVLS kernels.  threads per CTA (multiple of 32 in 128..1024; 0 keeps), 16-byte vectors in
+ * flight per thread (2, 4, 8; 0 keeps), weak: 1 = multimem.*.weak, 0 = .relaxed.sys (< 0 keeps), max_lanes: cap on
+ * the CTAs of one launch (0 = one per SM; < 0 keeps), stripe_bytes: all-reduce ownership, 0 = rank r reduces block r,
+ * else stripes of this size dealt round-robin ((size_t)-1 keeps). */
+int ft_comm_set_nvls_config(ft_comm* c, int threads, int unroll, int weak, int max_lanes, size_t stripe_bytes);
+/* ft_reduce_scatter / ft_all_gather use the multimem kernels for the flat shape on eligible tensors (default on) */
+void ft_comm_set_phase_nvls(ft_comm* c, int on);
 /* one-shot emulation: phase 1 = publish input (all ranks first), phase 4 = reduce */
 int ft_allreduce_emulate_oneshot(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op,
                                  float scale, int phase, uint64_t call, void* stream);

@@ -104,8 +104,16 @@ struct NvlsArgs {
   uint64_t work_off;
   uint64_t count;
   uint64_t block_elems;
+  uint64_t stripe_bytes;      // NVLS all-reduce only: 0 = rank r owns block r; else stripes of this size dealt round-robin
   uint32_t elem_size;
   float scale;
+};
+
+// Launch shape of the NVLS kernels (tuning knobs of the communicator).
+struct NvlsConfig {
+  int threads = 512;          // per CTA
+  int unroll = 4;             // 16-byte vectors in flight per thread
+  int weak = 0;               // 1: multimem.*.weak instead of .relaxed.sys
 };
 
 }  // namespace ftk

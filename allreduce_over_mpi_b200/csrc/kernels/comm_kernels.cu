@@ -9,8 +9,9 @@
 //    Barrier loop (allreduce_over_mpi/mpi_mod.hpp:1550-1596, :1620-1644).
 //  * oneshot_allreduce_kernel  every rank publishes its input in a staging slot, one
 //    rendezvous, every rank sums all N copies itself (latency-optimal for small sizes).
-//  * nvls_allreduce_kernel     multimem.ld_reduce / multimem.st through the NVSwitch
-//    multicast mapping (in-switch reduction), where the box exposes it.
+//  * nvls_kernel               multimem.ld_reduce / multimem.st through the NVSwitch
+//    multicast mapping (in-switch reduction), where the box exposes it: all-reduce, and
+//    its two halves (reduce-scatter, all-gather) as passes of their own.
 //  * hybrid_allreduce_kernel   both at once on disjoint parts of the message.
 //  * push_allreduce_kernel     flat two-shot in one pass: pull + sum + posted writes to every rank.
 //  * ll_allreduce_kernel       push protocol with the flag inside every 8-byte word, no
@@ -462,69 +463,79 @@ __global__ void __launch_bounds__(kThreads) ll_allreduce_kernel(const __grid_con
 
 // ------------------------------------------------------------------------------- NVLS
 // multimem.ld_reduce sums one 16-byte vector across every GPU bound to the multicast
-// object inside the switch; multimem.st writes one to all of them.
-template <int POL> struct Nvls;
-template <> struct Nvls<POL_F32> {
-  __device__ static __forceinline__ uint4 ld(const void* p) {
-    uint4 v;
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-    return v;
-  }
-};
-template <> struct Nvls<POL_BF16> {
-  __device__ static __forceinline__ uint4 ld(const void* p) {
-    uint4 v;
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-    return v;
-  }
-};
-template <> struct Nvls<POL_F16> {
-  __device__ static __forceinline__ uint4 ld(const void* p) {
-    uint4 v;
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-    return v;
-  }
-};
+// object inside the switch; multimem.st writes one to all of them.  WEAK selects the
+// .weak form of both (no ordering of its own; the rendezvous around the pass orders them).
+template <int POL, int WEAK> struct Nvls;
+#define FT_NVLS_LD(POL_ID, SUFFIX)                                                                                  \
+  template <> struct Nvls<POL_ID, 0> {                                                                              \
+    __device__ static __forceinline__ uint4 ld(const void* p) {                                                     \
+      uint4 v;                                                                                                      \
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add" SUFFIX " {%0,%1,%2,%3}, [%4];"                       \
+                   : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");                               \
+      return v;                                                                                                     \
+    }                                                                                                               \
+  };                                                                                                                \
+  template <> struct Nvls<POL_ID, 1> {                                                                              \
+    __device__ static __forceinline__ uint4 ld(const void* p) {                                                     \
+      uint4 v;                                                                                                      \
+      asm volatile("multimem.ld_reduce.weak.global.add" SUFFIX " {%0,%1,%2,%3}, [%4];"                              \
+                   : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");                               \
+      return v;                                                                                                     \
+    }                                                                                                               \
+  };
+FT_NVLS_LD(POL_F32, ".v4.f32")
+FT_NVLS_LD(POL_BF16, ".acc::f32.v4.bf16x2")
+FT_NVLS_LD(POL_F16, ".acc::f32.v4.f16x2")
+#undef FT_NVLS_LD
+template <int WEAK>
 __device__ __forceinline__ void multimem_st(void* p, uint4 v) {
-  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  if (WEAK) asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  else asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-// Reduce `nvec` 16-byte vectors at multicast address `mc` inside the switch and broadcast the
-// result to every rank: kU in-switch reductions per thread, then their kU broadcasts.  Issuing
-// the next step's reductions before the current stores (as the peer-load loops do) was measured
-// 4 % SLOWER at 64 MiB and above on 4 and 8 GPUs, as was a second CTA per SM: the switch, not
-// the number of requests in flight, is the limit.
-template <int POL>
-__device__ __forceinline__ void nvls_reduce_broadcast(unsigned char* mc, uint64_t nvec, float scale) {
+// What one lane does with its `nvec` 16-byte vectors at multicast address `mc` (and the same
+// range of this rank's own heap at `own`):
+//   MODE 0  all-reduce: reduce inside the switch, broadcast the result to every rank;
+//   MODE 1  reduce-scatter: reduce inside the switch, keep the result in the own buffer only;
+//   MODE 2  all-gather: broadcast the own buffer's contents to every rank.
+// KU vectors are in flight per thread: KU reductions (or loads), then their KU stores.
+template <int POL, int MODE, int KU, int WEAK>
+__device__ __forceinline__ void nvls_pass(unsigned char* mc, unsigned char* own, uint64_t nvec, float scale) {
   using P = typename PolById<POL>::type;
-  constexpr int kU = 4;
-  for (uint64_t base = 0; base < nvec; base += (uint64_t)blockDim.x * kU) {
-    uint4 v[kU];
-    uint64_t idx[kU];
+  for (uint64_t base = 0; base < nvec; base += (uint64_t)blockDim.x * KU) {
+    uint4 v[KU];
+    uint64_t idx[KU];
 #pragma unroll
-    for (int u = 0; u < kU; ++u) {
+    for (int u = 0; u < KU; ++u) {
       idx[u] = base + (uint64_t)u * blockDim.x + threadIdx.x;
-      v[u] = idx[u] < nvec ? Nvls<POL>::ld(mc + idx[u] * 16) : make_uint4(0, 0, 0, 0);
+      if (idx[u] < nvec) v[u] = MODE == 2 ? ld_stream(own + idx[u] * 16) : Nvls<POL, WEAK>::ld(mc + idx[u] * 16);
+      else v[u] = make_uint4(0, 0, 0, 0);
     }
-    if (scale != 1.0f) {
+    if (MODE != 2 && scale != 1.0f) {
 #pragma unroll
-      for (int u = 0; u < kU; ++u) {
+      for (int u = 0; u < KU; ++u) {
         typename P::Acc t;
         P::init(t, v[u]);
         v[u] = P::fins(t, scale);
       }
     }
 #pragma unroll
-    for (int u = 0; u < kU; ++u)
-      if (idx[u] < nvec) multimem_st(mc + idx[u] * 16, v[u]);
+    for (int u = 0; u < KU; ++u)
+      if (idx[u] < nvec) {
+        if (MODE == 1) st_vec(own + idx[u] * 16, v[u]);
+        else multimem_st<WEAK>(mc + idx[u] * 16, v[u]);
+      }
   }
 }
 
-// In place on the symmetric work buffer: rank r reduces block r (lane-sliced) through the
-// switch and broadcasts the result to every rank.  Requires count*es to be a multiple of 16.
-template <int POL>
-__global__ void __launch_bounds__(kThreads) nvls_allreduce_kernel(const __grid_constant__ CommDev c, const __grid_constant__ NvlsArgs a) {
-  using P = typename PolById<POL>::type;
+// In place on the symmetric work buffer.  Rank r handles the parts of the message it owns, lane-sliced:
+// with stripe_bytes == 0 that is block r (one contiguous 1/N of the message, the blocks of the plans);
+// otherwise the message is cut into stripes of stripe_bytes dealt round-robin to the ranks, so that at
+// any moment the N ranks work on neighbouring addresses.  Requires count*es to be a multiple of 16.
+// Rendezvous before the pass (every rank's input is in place / nobody still reads what gets overwritten)
+// and after it (every rank's stores have landed everywhere).
+template <int POL, int MODE, int KU, int WEAK>
+__global__ void __launch_bounds__(1024) nvls_kernel(const __grid_constant__ CommDev c, const __grid_constant__ NvlsArgs a) {
   __shared__ int abort_flag;
   __shared__ unsigned long long call_slot;
   const int lane = blockIdx.x, nlanes = gridDim.x;
@@ -533,19 +544,29 @@ __global__ void __launch_bounds__(kThreads) nvls_allreduce_kernel(const __grid_c
   LaneSync sync{c.flags, c.flags[c.rank], c.rank, c.world, lane, FT_MAX_RANKS, c.timeout_ns, c.status, &abort_flag};
   const unsigned long long all = c.world >= 64 ? ~0ull : ((1ull << c.world) - 1);
   const uint32_t es = a.elem_size;
-  const uint64_t block_bytes = a.block_elems * es, total_bytes = a.count * es;
-  uint64_t chunk = (block_bytes + nlanes - 1) / nlanes;
-  chunk = (chunk + 15) & ~15ull;
-  const uint64_t lo = (uint64_t)c.rank * block_bytes;
-  const uint64_t len = lo >= total_bytes ? 0 : (total_bytes - lo < block_bytes ? total_bytes - lo : block_bytes);
-  const LaneSlice sl = lane_slice(len, chunk, lane);
+  const uint64_t total_bytes = a.count * es;
 
-  lane_rendezvous(sync, all, call * kCallStride + 1, 0);   // every rank's input is in place
+  lane_rendezvous(sync, all, call * kCallStride + 1, 0);
   if (abort_flag) return;
-  unsigned char* mc = c.mc_heap + a.work_off + lo + sl.off;
-  nvls_reduce_broadcast<POL>(mc, sl.bytes / 16, a.scale);
-  // all my broadcasts are ordered before my signal; after the rendezvous every rank's
-  // slice has landed here too
+  if (a.stripe_bytes == 0) {
+    const uint64_t block_bytes = a.block_elems * es;
+    uint64_t chunk = (block_bytes + nlanes - 1) / nlanes;
+    chunk = (chunk + 15) & ~15ull;
+    const uint64_t lo = (uint64_t)c.rank * block_bytes;
+    const uint64_t len = lo >= total_bytes ? 0 : (total_bytes - lo < block_bytes ? total_bytes - lo : block_bytes);
+    const LaneSlice sl = lane_slice(len, chunk, lane);
+    const uint64_t off = a.work_off + lo + sl.off;
+    nvls_pass<POL, MODE, KU, WEAK>(c.mc_heap + off, c.heap[c.rank] + off, sl.bytes / 16, a.scale);
+  } else {
+    // stripe s belongs to rank s % world; lanes deal this rank's stripes round-robin among themselves
+    const uint64_t nstripes = (total_bytes + a.stripe_bytes - 1) / a.stripe_bytes;
+    for (uint64_t s = (uint64_t)c.rank + (uint64_t)lane * c.world; s < nstripes; s += (uint64_t)nlanes * c.world) {
+      const uint64_t lo = s * a.stripe_bytes;
+      const uint64_t len = total_bytes - lo < a.stripe_bytes ? total_bytes - lo : a.stripe_bytes;
+      nvls_pass<POL, MODE, KU, WEAK>(c.mc_heap + a.work_off + lo, c.heap[c.rank] + a.work_off + lo, len / 16, a.scale);
+    }
+  }
+  // all my stores are ordered before my signal; after the rendezvous every rank's part has landed here too
   __threadfence_system();
   lane_rendezvous(sync, all, call * kCallStride + 2, 1);
 }
@@ -598,7 +619,7 @@ __global__ void __launch_bounds__(kThreads, 1) hybrid_allreduce_kernel(const __g
   if (is_nvls) {
     const LaneSlice sl = my_slice(c.rank);
     unsigned char* mc = c.mc_heap + a.work_off + (uint64_t)c.rank * block_bytes + sl.off;
-    nvls_reduce_broadcast<POL>(mc, sl.bytes / 16, a.scale);
+    nvls_pass<POL, 0, 4, 0>(mc, nullptr, sl.bytes / 16, a.scale);
     __threadfence_system();
     lane_rendezvous(sync, all, call * kCallStride + 2, 1);
     return;
@@ -736,15 +757,41 @@ cudaError_t launch_oneshot(int pol, const CommDev& c, const OneShotArgs& a, uint
   FT_POL_SWITCH(pol, CALL)
 #undef CALL
 }
-cudaError_t launch_nvls(int pol, const CommDev& c, const NvlsArgs& a, int lanes, cudaStream_t st) {
-  ft_count_launch(1);
-  switch (pol) {
-    case POL_F32: nvls_allreduce_kernel<POL_F32><<<lanes, kThreads, 0, st>>>(c, a); break;
-    case POL_BF16: nvls_allreduce_kernel<POL_BF16><<<lanes, kThreads, 0, st>>>(c, a); break;
-    case POL_F16: nvls_allreduce_kernel<POL_F16><<<lanes, kThreads, 0, st>>>(c, a); break;
+// mode: 0 all-reduce, 1 reduce-scatter, 2 all-gather.  cfg: threads per CTA (128..1024, a multiple of 32), vectors in
+// flight per thread (2, 4 or 8) and the .weak form of the multimem instructions.
+template <int POL, int MODE, int KU>
+static cudaError_t launch_nvls_w(const CommDev& c, const NvlsArgs& a, int lanes, const NvlsConfig& cfg, cudaStream_t st) {
+  if (cfg.weak) nvls_kernel<POL, MODE, KU, 1><<<lanes, cfg.threads, 0, st>>>(c, a);
+  else nvls_kernel<POL, MODE, KU, 0><<<lanes, cfg.threads, 0, st>>>(c, a);
+  return cudaGetLastError();
+}
+template <int POL, int MODE>
+static cudaError_t launch_nvls_u(const CommDev& c, const NvlsArgs& a, int lanes, const NvlsConfig& cfg, cudaStream_t st) {
+  switch (cfg.unroll) {
+    case 2: return launch_nvls_w<POL, MODE, 2>(c, a, lanes, cfg, st);
+    case 4: return launch_nvls_w<POL, MODE, 4>(c, a, lanes, cfg, st);
+    case 8: return launch_nvls_w<POL, MODE, 8>(c, a, lanes, cfg, st);
     default: return cudaErrorInvalidValue;
   }
-  return cudaGetLastError();
+}
+template <int POL>
+static cudaError_t launch_nvls_m(const CommDev& c, const NvlsArgs& a, int lanes, int mode, const NvlsConfig& cfg, cudaStream_t st) {
+  switch (mode) {
+    case 0: return launch_nvls_u<POL, 0>(c, a, lanes, cfg, st);
+    case 1: return launch_nvls_u<POL, 1>(c, a, lanes, cfg, st);
+    case 2: return launch_nvls_u<POL, 2>(c, a, lanes, cfg, st);
+    default: return cudaErrorInvalidValue;
+  }
+}
+cudaError_t launch_nvls(int pol, const CommDev& c, const NvlsArgs& a, int lanes, int mode, const NvlsConfig& cfg, cudaStream_t st) {
+  if (cfg.threads < 128 || cfg.threads > 1024 || cfg.threads % 32) return cudaErrorInvalidValue;
+  ft_count_launch(1);
+  switch (pol) {
+    case POL_F32: return launch_nvls_m<POL_F32>(c, a, lanes, mode, cfg, st);
+    case POL_BF16: return launch_nvls_m<POL_BF16>(c, a, lanes, mode, cfg, st);
+    case POL_F16: return launch_nvls_m<POL_F16>(c, a, lanes, mode, cfg, st);
+    default: return cudaErrorInvalidValue;
+  }
 }
 template <int POL> static cudaError_t launch_ll_t(const CommDev& c, const LLArgs& a, cudaStream_t st) {
   const uint64_t nitems = (a.count * a.elem_size + 15) / 16;

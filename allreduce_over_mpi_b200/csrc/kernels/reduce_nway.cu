@@ -7,7 +7,8 @@
 // travel in a __grid_constant__ parameter block and the fan-in loop is unrolled in
 // groups so that GROUP x UNROLL independent 16-byte loads are in flight per thread.
 //
-// Two data paths:
+// Data paths:
+//   * 32-byte path (reduce_nway_wide.cu): the default whenever every pointer sits on a 32-byte boundary;
 //   * vector path: persistent grid-stride loop of 16-byte non-allocating loads;
 //   * TMA path: per-CTA ring of shared-memory stages filled by 1-D bulk async copies
 //     (cp.async.bulk, completion on an mbarrier) and drained by all threads.
@@ -325,12 +326,12 @@ static int run_policy(NwayArgs& a, size_t bytes, int variant, cudaStream_t st) {
   a.nvec = aligned ? bytes / 16 : 0;
   cudaError_t e = cudaSuccess;
   // 32-byte accesses (reduce_nway_wide.cu) when every pointer sits on a 32-byte boundary
-  if (a.nvec >= 2 && variant >= 1000) {
+  if (a.nvec >= 2 && (variant >= 1000 || variant == 0)) {
     bool a32 = ((uintptr_t)a.dst & 31) == 0;
     for (int k = 0; k < a.n; ++k) a32 = a32 && (((uintptr_t)a.src[k] & 31) == 0);
     if (a32) {
       const unsigned long long n32 = bytes / 32;
-      e = launch_wide(POL, a, n32, variant, dev_info().sms, st);
+      e = launch_wide(POL, a, n32, variant >= 1000 ? variant : 0, dev_info().sms, st);
       if (e == cudaSuccess) {
         g_launches++;
         e = launch_scalar<POL>(a, n32 * 32 / unit, st);

@@ -14,8 +14,8 @@ struct NwayArgs {
   int n;
 };
 
-// 32-byte-per-access kernels (reduce_nway_wide.cu).  `code` selects a tuning configuration
-// (see wide_config_of); returns cudaErrorInvalidValue when (pol, fan-in, code) has no
+// 32-byte-per-access kernels (reduce_nway_wide.cu).  `code` selects a configuration (0: the default;
+// see launch_cfg there); returns cudaErrorInvalidValue when (policy, fan-in, code) has no
 // instantiation, in which case the caller falls back to the 16-byte kernels.
 cudaError_t launch_wide(int pol, const NwayArgs& a, unsigned long long n32, int code, int sms, cudaStream_t st);
 

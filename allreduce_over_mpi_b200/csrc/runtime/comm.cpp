@@ -34,7 +34,7 @@
 namespace ftk {
 cudaError_t launch_staged(int pol, const CommDev& c, const StagedArgs& a, int lanes, cudaStream_t st);
 cudaError_t launch_oneshot(int pol, const CommDev& c, const OneShotArgs& a, uint64_t slot_bytes, int lanes, cudaStream_t st);
-cudaError_t launch_nvls(int pol, const CommDev& c, const NvlsArgs& a, int lanes, cudaStream_t st);
+cudaError_t launch_nvls(int pol, const CommDev& c, const NvlsArgs& a, int lanes, int mode, const NvlsConfig& cfg, cudaStream_t st);
 cudaError_t launch_push(int pol, const CommDev& c, const NvlsArgs& a, int lanes, bool do_sync, cudaStream_t st);
 cudaError_t launch_ll(int pol, const CommDev& c, const LLArgs& a, cudaStream_t st);
 cudaError_t launch_hybrid(int pol, const CommDev& c, const NvlsArgs& a, int lanes, int nvls_lanes, uint64_t nvls_bytes, cudaStream_t st);
@@ -135,6 +135,10 @@ struct ft_comm {
   double hybrid_fraction = 0.7, hybrid_lane_fraction = 0.5;
   size_t ll_max = 8 << 10;   // AUTO uses the low-latency protocol up to this size
   int nvls_ctas_per_sm = 1;   // measured on 8 GPUs: 2 or 3 CTAs per SM lose 5-15 % at 256 MiB and above
+  ftk::NvlsConfig nvls_cfg;   // threads per CTA, vectors in flight per thread, instruction form
+  int nvls_max_lanes = 0;     // 0: as many lanes as SMs (times nvls_ctas_per_sm)
+  size_t nvls_stripe = 0;
+  bool phase_nvls = true;     // ft_reduce_scatter / ft_all_gather may use the multimem kernels (flat shape, eligible tensor)     // all-reduce: 0 = rank r owns block r, else round-robin stripes of this many bytes
   std::map<std::string, DevPlanEntry> plans;
   // ft_allreduce_host: chunk buffers in the heap + three streams, made on first use
   struct HostPipe {
@@ -812,6 +816,7 @@ int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, i
     a.block_elems = pick_block_elems(count, c->world, pr.es);
     a.scale = scale;
     int lanes = pick_lanes(c, a.block_elems * pr.es, 8192, c->nvls_ctas_per_sm);
+    if (c->nvls_max_lanes > 0 && lanes > c->nvls_max_lanes) lanes = c->nvls_max_lanes;
     cudaError_t e;
     if (algo == FT_ALGO_HYBRID && lanes >= 8) {
       // share of each block that goes through the switch, and the same share of the lanes
@@ -822,7 +827,8 @@ int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, i
       if (nvls_lanes > lanes - 1) nvls_lanes = lanes - 1;
       e = ftk::launch_hybrid(pr.pol, c->dev, a, lanes, nvls_lanes, nvls_bytes, st);
     } else {
-      e = ftk::launch_nvls(pr.pol, c->dev, a, lanes, st);
+      a.stripe_bytes = c->nvls_stripe;
+      e = ftk::launch_nvls(pr.pol, c->dev, a, lanes, 0, c->nvls_cfg, st);
     }
     if (e != cudaSuccess) return fail(c, e == cudaErrorInvalidValue ? FT_ERR_UNSUPPORTED_TYPE : FT_ERR_CUDA, std::string("NVLS launch: ") + cudaGetErrorString(e));
     return FT_OK;
@@ -918,11 +924,28 @@ static int phase_call(ft_comm* c, void* buf, size_t count, int dtype, int op, co
   }
   DevPlanEntry* pe = nullptr;
   const ft::Shape shape = make_shape(c->world, widths, nw, lonely, ring);
+  c->stat_calls[gather ? 8 : 7]++;
+  c->stat_bytes[gather ? 8 : 7] += pr.bytes;
+  // Flat shape on a tensor the switch can reduce: one multimem pass (ld_reduce of the own block into the own
+  // buffer, or multimem.st of the own block to everyone) instead of N-1 peer loads per vector.  Block r ends up
+  // on / comes from rank r, exactly as in the flat plan.
+  const bool flat = !shape.ring && shape.lonely == 0 && shape.widths.size() == 1;
+  if (flat && c->phase_nvls && nvls_eligible(c, pr)) {
+    ftk::NvlsArgs a{};
+    a.work_off = (uint64_t)((unsigned char*)buf - local_base(c));
+    a.count = count;
+    a.elem_size = pr.es;
+    a.block_elems = pick_block_elems(count, c->world, pr.es);
+    a.scale = gather ? 1.0f : scale;
+    int lanes = pick_lanes(c, a.block_elems * pr.es, 8192, c->nvls_ctas_per_sm);
+    if (c->nvls_max_lanes > 0 && lanes > c->nvls_max_lanes) lanes = c->nvls_max_lanes;
+    cudaError_t e = ftk::launch_nvls(pr.pol, c->dev, a, lanes, gather ? 2 : 1, c->nvls_cfg, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(c, FT_ERR_CUDA, std::string("NVLS phase launch: ") + cudaGetErrorString(e));
+    return FT_OK;
+  }
   rc = get_plan(c, shape, &pe);
   if (rc != FT_OK) return rc;
   const int half = pe->nstages / 2;
-  c->stat_calls[gather ? 8 : 7]++;
-  c->stat_bytes[gather ? 8 : 7] += pr.bytes;
   return launch_staged_call(c, pr, nullptr, buf, count, shape, scale, gather ? half : 0, gather ? pe->nstages : half, true,
                             (cudaStream_t)stream, true);
 }
@@ -978,6 +1001,25 @@ int ft_allreduce_emulate_ll(ft_comm* c, const void* sendbuf, void* recvbuf, size
   return launch_ll_call(c, pr, sendbuf, recvbuf, count, scale, (uint32_t)phase & 3u, false, call, (cudaStream_t)stream);
 }
 void ft_comm_set_nvls_ctas_per_sm(ft_comm* c, int n) { if (c && n >= 1 && n <= 3) c->nvls_ctas_per_sm = n; }
+int ft_comm_set_nvls_config(ft_comm* c, int threads, int unroll, int weak, int max_lanes, size_t stripe_bytes) {
+  if (!c) return FT_ERR_INVALID_ARG;
+  if (threads) {
+    if (threads < 128 || threads > 1024 || threads % 32) return fail(c, FT_ERR_INVALID_ARG, "NVLS threads per CTA: a multiple of 32 in 128..1024");
+    c->nvls_cfg.threads = threads;
+  }
+  if (unroll) {
+    if (unroll != 2 && unroll != 4 && unroll != 8) return fail(c, FT_ERR_INVALID_ARG, "NVLS vectors in flight per thread: 2, 4 or 8");
+    c->nvls_cfg.unroll = unroll;
+  }
+  if (weak >= 0) c->nvls_cfg.weak = weak ? 1 : 0;
+  if (max_lanes >= 0) c->nvls_max_lanes = max_lanes;
+  if (stripe_bytes != (size_t)-1) {
+    if (stripe_bytes % 16) return fail(c, FT_ERR_INVALID_ARG, "NVLS stripe: a multiple of 16 bytes");
+    c->nvls_stripe = stripe_bytes;
+  }
+  return FT_OK;
+}
+void ft_comm_set_phase_nvls(ft_comm* c, int on) { if (c) c->phase_nvls = on != 0; }
 void ft_comm_set_ll_max(ft_comm* c, size_t bytes) { if (c) c->ll_max = bytes < ftk::kLLMaxBytes ? bytes : ftk::kLLMaxBytes; }
 
 int ft_plan_num_stages_for(ft_comm* c, const int* widths, int nw, int lonely, int ring) {

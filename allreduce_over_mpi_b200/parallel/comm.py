@@ -102,6 +102,12 @@ class _CommBase:
         if os.environ.get("FT_MAX_LANES"):
             self.set_max_lanes(int(os.environ["FT_MAX_LANES"]))
         lib().ft_comm_set_ll_max(self._h, self.ll_auto_max)
+        env = os.environ
+        if any(env.get(k) for k in ("FT_NVLS_THREADS", "FT_NVLS_UNROLL", "FT_NVLS_WEAK", "FT_NVLS_MAX_LANES", "FT_NVLS_STRIPE")):
+            self.set_nvls_config(threads=int(env.get("FT_NVLS_THREADS", 0)), unroll=int(env.get("FT_NVLS_UNROLL", 0)),
+                                 weak=int(env["FT_NVLS_WEAK"]) if env.get("FT_NVLS_WEAK") else None,
+                                 max_lanes=int(env["FT_NVLS_MAX_LANES"]) if env.get("FT_NVLS_MAX_LANES") else None,
+                                 stripe_bytes=int(env["FT_NVLS_STRIPE"]) if env.get("FT_NVLS_STRIPE") else None)
         if os.environ.get("FT_NVLS_CTAS_PER_SM"):
             lib().ft_comm_set_nvls_ctas_per_sm(self._h, int(os.environ["FT_NVLS_CTAS_PER_SM"]))
 
@@ -114,6 +120,16 @@ class _CommBase:
 
     def set_oneshot_max(self, nbytes: int):
         lib().ft_comm_set_oneshot_max(self._h, nbytes)
+
+    def set_nvls_config(self, threads: int = 0, unroll: int = 0, weak: int | None = None, max_lanes: int | None = None,
+                        stripe_bytes: int | None = None):
+        """Launch shape of the NVLS kernels: threads per CTA, 16-byte vectors in flight per thread (2/4/8), the
+        ``.weak`` instruction form, a cap on the CTAs per launch (0: one per SM) and, for the all-reduce, ownership by
+        round-robin stripes of ``stripe_bytes`` instead of one block per rank (0).  Arguments left at their
+        defaults keep the current setting.  Environment: FT_NVLS_THREADS / _UNROLL / _WEAK / _MAX_LANES / _STRIPE."""
+        self._check(lib().ft_comm_set_nvls_config(self._h, threads, unroll, -1 if weak is None else int(weak),
+                                                  -1 if max_lanes is None else int(max_lanes),
+                                                  C.c_size_t(-1).value if stripe_bytes is None else int(stripe_bytes)))
 
     def set_hybrid(self, byte_fraction: float, lane_fraction: float):
         """Split used by algo="hybrid": share of each block reduced in the switch, share of the CTAs doing it."""

@@ -38,8 +38,9 @@ def smoke_comm_and_model(dev: torch.device) -> None:
     from ..ops import HostReducePipeline, reduce_nway, reduce_nway_scaled
     fs = [torch.randn(1 << 16, device=dev) for _ in range(4)]
     want = torch.stack(fs).sum(0)
-    assert torch.allclose(reduce_nway(fs), want, atol=1e-5)
-    assert torch.allclose(reduce_nway(fs[:2], variant=2011), fs[0] + fs[1], atol=1e-6)
+    assert torch.allclose(reduce_nway(fs), want, atol=1e-5)                  # 32-byte accesses (the default)
+    assert torch.allclose(reduce_nway(fs, variant=24), want, atol=1e-5)      # 8 bytes per thread
+    assert torch.allclose(reduce_nway(fs[:2], variant=13), fs[0] + fs[1], atol=1e-6)   # 16-byte vectors, persistent grid
     got = reduce_nway_scaled(fs, scale=0.25, out_dtype=torch.bfloat16)
     assert torch.allclose(got.float(), want * 0.25, atol=3e-2)
     hin = [f.cpu().pin_memory() for f in fs]

@@ -89,6 +89,92 @@ def main():
         dist.destroy_process_group()
         return 0 if all(flags) else 1
 
+    if mode == "mpi":
+        # the MPI-style C entry on a GPU communicator: device buffers (in and out of place, AUTO selection and an
+        # explicit FT_TOPO), host buffers through the pipelined path, and the Python all_reduce_host
+        import ctypes as C
+        from allreduce_over_mpi_b200._lib import DTYPES, OPS, lib
+        from allreduce_over_mpi_b200.parallel.mpi_compat import IN_PLACE
+        L = lib()
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        mc = L.ft_mpi_from_comm(comm._h, C.c_void_p(stream))
+        good = True
+        it = 0
+
+        def close_enough(t, count, dtype, it_, what):
+            nonlocal good
+            want = expected(count, dtype, world, dev, it_)
+            tol = 1e-4 if dtype == torch.float32 else 0.3
+            err = (t.to(dev).double() - want).abs().max().item()
+            if not err <= tol:
+                good = False
+                print(f"[rank {rank}] MPI_Allreduce_FT {what}: err {err}", flush=True)
+            report["cases"] += 1
+
+        explicit = {4: ("2,2", "0"), 5: ("2,2", "1"), 6: ("2,3", "0"), 7: ("2,3", "1"), 8: ("2,4", "0")}.get(world, (str(world), "0"))
+        for topo in (None, explicit[0]):
+            if topo is None:
+                os.environ.pop("FT_TOPO", None)
+                os.environ.pop("FT_LONELY", None)
+            else:
+                os.environ["FT_TOPO"], os.environ["FT_LONELY"] = explicit
+            for dtype, name in ((torch.float32, "float32"), (torch.bfloat16, "bfloat16")):
+                for count in (35, 70_001, (3 << 20) + 16):
+                    it += 1
+                    comm.free_all()
+                    sym = comm.alloc(count, dtype)                 # device, heap resident, in place
+                    fill(sym, rank, it)
+                    rc = L.MPI_Allreduce_FT_c(IN_PLACE, sym.data_ptr(), count, DTYPES[name], OPS["sum"], mc)
+                    torch.cuda.synchronize()
+                    good = good and rc == 0
+                    close_enough(sym, count, dtype, it, f"heap {topo} {name} {count}")
+                    it += 1
+                    src = torch.empty(count, dtype=dtype, device=dev)   # device, outside the heap, out of place
+                    dst = torch.empty_like(src)
+                    fill(src, rank, it)
+                    rc = L.MPI_Allreduce_FT_c(src.data_ptr(), dst.data_ptr(), count, DTYPES[name], OPS["sum"], mc)
+                    torch.cuda.synchronize()
+                    good = good and rc == 0
+                    close_enough(dst, count, dtype, it, f"device {topo} {name} {count}")
+                    it += 1
+                    fill(src, rank, it)
+                    hsrc = src.cpu().pin_memory()                   # host buffers: pipelined through the GPU
+                    hdst = torch.empty_like(hsrc).pin_memory()
+                    rc = L.MPI_Allreduce_FT_c(hsrc.data_ptr(), hdst.data_ptr(), count, DTYPES[name], OPS["sum"], mc)
+                    good = good and rc == 0
+                    close_enough(hdst, count, dtype, it, f"host {topo} {name} {count}")
+                    rc = L.MPI_Allreduce_FT_c(IN_PLACE, hsrc.data_ptr(), count, DTYPES[name], OPS["sum"], mc)
+                    good = good and rc == 0
+                    close_enough(hsrc, count, dtype, it, f"host in place {topo} {name} {count}")
+        os.environ.pop("FT_TOPO", None)
+        os.environ.pop("FT_LONELY", None)
+        # a device tensor outside the heap that is larger than one staging slot is split natively
+        it += 1
+        big = torch.empty((comm.staging_bytes // 4) * 2 + 1000, dtype=torch.float32, device=dev)
+        fill(big, rank, it)
+        rc = L.MPI_Allreduce_FT_c(IN_PLACE, big.data_ptr(), big.numel(), DTYPES["float32"], OPS["sum"], mc)
+        torch.cuda.synchronize()
+        good = good and rc == 0
+        close_enough(big, big.numel(), torch.float32, it, "larger than a slot")
+        # Python front end of the pipelined host path, pageable memory too, averaged
+        it += 1
+        fill(big, rank, it)
+        hp = big.cpu()
+        out = comm.all_reduce_host(hp, out=torch.empty_like(hp), op="avg")
+        torch.cuda.synchronize()
+        close_enough(out * world, big.numel(), torch.float32, it, "all_reduce_host pageable avg")
+        comm.check()
+        L.ft_mpi_comm_free(mc)
+        report["stats"] = comm.stats()
+        flags = [None] * world
+        dist.all_gather_object(flags, good)
+        if rank == 0:
+            print("RESULT " + json.dumps({"ok": all(flags), **report}), flush=True)
+        comm.close()
+        dist.barrier()
+        dist.destroy_process_group()
+        return 0 if all(flags) else 1
+
     if mode == "phases":
         # reduce-scatter and all-gather as calls of their own: the owned block is complete after the
         # first, everything else is then overwritten with NaN, and the second alone rebuilds the result

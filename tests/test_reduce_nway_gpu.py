@@ -132,14 +132,14 @@ def test_bad_arguments():
 
 
 # U * 1000 + LD * 100 + ST * 10 + T of the 32-byte-access kernels (csrc/kernels/reduce_nway_wide.cu)
-WIDE = [1000, 1011, 1113, 2002, 2011, 2110, 2112, 2213, 4000, 4011]
+WIDE = [1000, 1001, 1003, 1010, 1011, 1013, 1110, 1111, 2000, 2010, 2011, 2013, 2110, 2113, 24, 13]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("n", [2, 3, 4, 8])
 def test_wide_access_variants_match_the_default_kernels(dtype, n):
-    """Every 256-bit configuration gives the bits of the 16-byte kernels (same summation order), for a length with
-    a ragged tail; configurations that have no instantiation for a fan-in fall back silently."""
+    """Every 256-bit configuration and the 16-byte kernels (variants 13 and 24) give the same bits (same summation
+    order), for a length with a ragged tail; configurations that have no instantiation for a fan-in fall back silently."""
     ts = [rand(1_000_003, dtype, 40 + k) for k in range(n)]
     want = reduce_nway(ts)
     exact = torch.stack(ts).double().sum(0)

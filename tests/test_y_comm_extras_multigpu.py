@@ -28,3 +28,28 @@ def test_ddp_gradients_equal_nccl_ddp():
     res = run_worker(n, "ddp", port=29591)
     assert res["ok"], res
     assert res["flextree_max_abs_err"] < 1e-4 and res["hook_max_abs_err"] < 1e-4
+
+
+def test_mpi_style_entry_on_gpu_communicators():
+    """MPI_Allreduce_FT (the reference's entry point, mpi_mod.hpp:1723-1778) on GPU communicators: device buffers in and
+    out of the heap, host buffers through the pipelined path, with the automatic choice and with FT_TOPO set."""
+    n = min(ngpu(), 8)
+    if n < 2:
+        pytest.skip("needs 2 GPUs")
+    res = run_worker(n, "mpi", port=29601)
+    assert res["ok"] and res["cases"] >= 40, res
+
+
+def test_native_benchmark_checks_itself_on_gpus():
+    """lib/ft_bench --comm-type flextree --check: ranks as threads of one process, heaps from the virtual-memory API,
+    the algorithm chosen by the native policy."""
+    import os
+    import subprocess
+    n = min(ngpu(), 8)
+    if n < 2:
+        pytest.skip("needs 2 GPUs")
+    exe = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "allreduce_over_mpi_b200", "lib", "ft_bench")
+    for size, extra in ((35, []), (1 << 22, []), (1 << 22, ["--dtype", "bf16"]), (1 << 20, ["--phases"])):
+        r = subprocess.run([exe, "--gpus", str(n), "--size", str(size), "--repeat", "2", "--check", *extra], capture_output=True,
+                           text=True, timeout=300)
+        assert r.returncode == 0 and "CHECK (test passed)" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
