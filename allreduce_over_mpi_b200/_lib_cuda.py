@@ -11,6 +11,7 @@ def declare(lib) -> None:
     sig = {
         "ft_reduce_nway": (i, [i, i, C.POINTER(vp), vp, i, sz, i, vp]),
         "ft_reduce_nway_scaled": (i, [i, i, C.POINTER(vp), vp, i, sz, f32, vp]),
+        "ft_scale_inplace": (i, [i, vp, sz, f32, vp]),
         "ft_last_cuda_error": (cp, []),
         "ft_launch_count": (u64, []),
         "ft_host_pipe_create": (i, [i, sz, i, i, C.POINTER(vp)]),

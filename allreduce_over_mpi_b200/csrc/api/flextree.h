@@ -185,6 +185,8 @@ int ft_reduce_nway(int op, int dtype, const void* const* src, void* dst, int n, 
  * FT_BF16; out_dtype FT_F32 or FT_BF16. */
 int ft_reduce_nway_scaled(int in_dtype, int out_dtype, const void* const* src, void* dst, int n, size_t len,
                           float scale, void* stream);
+/* buf[i] *= scale in place for FT_F32 / FT_F64 / FT_BF16 / FT_F16 (16-bit floats through fp32, one rounding) */
+int ft_scale_inplace(int dtype, void* buf, size_t len, float scale, void* stream);
 const char* ft_last_cuda_error(void);
 
 /* ---- n-way reductions of vectors in host memory, pipelined through one GPU (reference: the copy in / kernel /

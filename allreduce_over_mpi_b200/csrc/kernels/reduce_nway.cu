@@ -423,9 +423,50 @@ __global__ void __launch_bounds__(512) reduce_nway_scaled_kernel(const __grid_co
   }
 }
 
+// ---------------------------------------------------------------------------- scale in place
+// buf[i] *= scale for every floating type, with the policies' arithmetic (16-bit floats through fp32,
+// one rounding): what a one-rank "average" all-reduce has to do.
+template <int POL>
+__global__ void __launch_bounds__(256) scale_inplace_kernel(void* buf, unsigned long long nvec, unsigned long long nunit, float scale) {
+  using P = typename PolById<POL>::type;
+  using S = ScalarOp<POL>;
+  using T = typename S::elem;
+  const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+  const unsigned long long tid = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (unsigned long long i = tid; i < nvec; i += stride) {
+    typename P::Acc acc;
+    P::init(acc, ld_stream((const uint4*)buf + i));
+    st_vec((uint4*)buf + i, P::fins(acc, scale));
+  }
+  for (unsigned long long i = nvec * (16 / sizeof(T)) + tid; i < nunit; i += stride)
+    ((T*)buf)[i] = S::store(S::load(((const T*)buf)[i]) * (typename S::acc)scale);
+}
+
 }  // namespace ftk
 
 extern "C" {
+
+int ft_scale_inplace(int dtype, void* buf, size_t len, float scale, void* stream) {
+  using namespace ftk;
+  const int pol = policy_id(FT_SUM, dtype);
+  if (pol != POL_F32 && pol != POL_F64 && pol != POL_BF16 && pol != POL_F16) return FT_ERR_UNSUPPORTED_TYPE;
+  if (len == 0 || scale == 1.0f) return FT_OK;
+  if (!buf) return FT_ERR_INVALID_ARG;
+  const size_t es = ft_dtype_size((ft_dtype)dtype);
+  const unsigned long long nvec = ((uintptr_t)buf & 15) == 0 ? (unsigned long long)len * es / 16 : 0;
+  unsigned long long want = ((nvec ? nvec : len) + 255) / 256, cap = (unsigned long long)dev_info().sms * 8;
+  const int grid = (int)(want < cap ? (want ? want : 1) : cap);
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (pol) {
+    case POL_F32: scale_inplace_kernel<POL_F32><<<grid, 256, 0, st>>>(buf, nvec, len, scale); break;
+    case POL_F64: scale_inplace_kernel<POL_F64><<<grid, 256, 0, st>>>(buf, nvec, len, scale); break;
+    case POL_BF16: scale_inplace_kernel<POL_BF16><<<grid, 256, 0, st>>>(buf, nvec, len, scale); break;
+    default: scale_inplace_kernel<POL_F16><<<grid, 256, 0, st>>>(buf, nvec, len, scale); break;
+  }
+  g_launches++;
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? FT_OK : cuda_fail(e, "scale launch");
+}
 
 int ft_reduce_nway(int op, int dtype, const void* const* src, void* dst, int n, size_t len, int variant, void* stream) {
   using namespace ftk;

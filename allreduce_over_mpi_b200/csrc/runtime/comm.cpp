@@ -17,6 +17,7 @@
 #include <algorithm>
 #include <cstring>
 #include <map>
+#include <memory>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -97,6 +98,14 @@ std::string cu_err(CUresult r) {
 constexpr size_t kFlagBytes = (size_t)ftk::kMaxLanes * FT_MAX_RANKS * sizeof(ftk::flag_t);
 size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+// The multicast object of a world.  Ranks that live in one process share ONE driver handle, which must
+// outlive every rank's binding and mapping: the last rank to let go releases it.
+struct McOwner {
+  CUmemGenericAllocationHandle h = 0;
+  explicit McOwner(CUmemGenericAllocationHandle handle) : h(handle) {}
+  ~McOwner() { if (h && driver().p_cuMemRelease) driver().p_cuMemRelease(h); }
+};
+
 struct DevPlanEntry {
   ftk::DevPlan* plan = nullptr;   // device
   ftk::DevPull* pulls = nullptr;  // device
@@ -122,6 +131,7 @@ struct ft_comm {
   bool peer_is_vmm[FT_MAX_RANKS] = {};
   // multicast
   CUmemGenericAllocationHandle mc_handle = 0;
+  std::shared_ptr<McOwner> mc_owner;   // releases mc_handle when the last holder is gone
   CUdeviceptr mc_va = 0;
   bool mc_have = false, mc_joined = false, mc_bound = false;
   // local device state
@@ -452,7 +462,7 @@ int ft_comm_destroy(ft_comm* c) {
   if (d.ok && (c->mc_bound || c->mc_joined || c->mc_have)) {
     if (c->mc_va) { d.p_cuMemUnmap(c->mc_va, c->total_bytes); d.p_cuMemAddressFree(c->mc_va, c->total_bytes); }
     if (c->mc_bound && d.p_cuMulticastUnbind) d.p_cuMulticastUnbind(c->mc_handle, c->device, 0, c->total_bytes);
-    if (c->mc_handle && c->mc_have) d.p_cuMemRelease(c->mc_handle);
+    c->mc_owner.reset();   // the handle is released with its last holder
   }
   for (int r = 0; r < c->world; ++r) {
     if (r == c->rank || !c->peer_base[r]) continue;
@@ -574,6 +584,8 @@ int ft_comm_connect_local(ft_comm** comms, int n) {
     mp.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
     CUmemGenericAllocationHandle h = 0;
     bool ok = d.p_cuMulticastCreate(&h, &mp) == CUDA_SUCCESS;
+    std::shared_ptr<McOwner> owner;
+    if (ok) owner = std::make_shared<McOwner>(h);
     for (int i = 0; i < n && ok; ++i) ok = d.p_cuMulticastAddDevice(h, comms[i]->device) == CUDA_SUCCESS;
     for (int i = 0; i < n && ok; ++i) {
       ft_comm* c = comms[i];
@@ -581,8 +593,9 @@ int ft_comm_connect_local(ft_comm** comms, int n) {
       ok = d.p_cuMulticastBindMem(h, 0, c->handle, 0, c->total_bytes, 0) == CUDA_SUCCESS;
       if (!ok) break;
       c->mc_handle = h;
+      c->mc_owner = owner;
       c->mc_bound = true;
-      c->mc_have = i == 0;   // rank 0 releases the object; the others only unbind and unmap
+      c->mc_have = true;
       ok = map_handle(c, h, c->total_bytes, &c->mc_va) == FT_OK;
     }
     if (!ok) {   // undo: a half-bound world must not claim NVLS
@@ -592,9 +605,10 @@ int ft_comm_connect_local(ft_comm** comms, int n) {
         if (c->mc_bound && d.p_cuMulticastUnbind) d.p_cuMulticastUnbind(h, c->device, 0, c->total_bytes);
         c->mc_bound = c->mc_have = false;
         c->mc_handle = 0;
+        c->mc_owner.reset();
         c->err.clear();
       }
-      if (h) d.p_cuMemRelease(h);
+      owner.reset();
     }
   }
   for (int i = 0; i < n; ++i) {
@@ -677,6 +691,7 @@ int ft_comm_mc_create(ft_comm* c, int* fd_out) {
   mp.size = c->total_bytes;
   mp.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
   FT_CU(c, driver().p_cuMulticastCreate(&c->mc_handle, &mp));
+  c->mc_owner = std::make_shared<McOwner>(c->mc_handle);
   c->mc_have = true;
   int fd = -1;
   FT_CU(c, driver().p_cuMemExportToShareableHandle(&fd, c->mc_handle, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0));
@@ -688,6 +703,7 @@ int ft_comm_mc_join(ft_comm* c, int fd) {
   if (!ft_comm_mc_supported(c)) return fail(c, FT_ERR_NOT_AVAILABLE, "multicast not supported");
   if (fd >= 0) {
     FT_CU(c, driver().p_cuMemImportFromShareableHandle(&c->mc_handle, (void*)(uintptr_t)fd, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR));
+    c->mc_owner = std::make_shared<McOwner>(c->mc_handle);
     c->mc_have = true;
   }
   if (!c->mc_have) return fail(c, FT_ERR_INVALID_ARG, "no multicast object");
@@ -758,10 +774,9 @@ int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, i
   if (count == 0) return FT_OK;
   if (c->world == 1) {  // single rank: the reference's memcpy shortcut (mpi_mod.hpp:1739-1746)
     if (sendbuf && sendbuf != recvbuf) FT_CUDA(c, cudaMemcpyAsync(recvbuf, sendbuf, pr.bytes, cudaMemcpyDeviceToDevice, st));
-    if (scale != 1.0f && (dtype == FT_F32 || dtype == FT_BF16)) {
-      const void* src[1] = {recvbuf};
-      return ft_reduce_nway_scaled(dtype, dtype, src, recvbuf, 1, count, scale, stream);
-    }
+    // every floating type is scaled, as the kernels of larger worlds do; integer and bitwise results never are
+    if (scale != 1.0f && (dtype == FT_F32 || dtype == FT_BF16 || dtype == FT_F16 || dtype == FT_F64))
+      return ft_scale_inplace(dtype, recvbuf, count, scale, stream);
     return FT_OK;
   }
   ft::Shape auto_shape;
@@ -916,10 +931,8 @@ static int phase_call(ft_comm* c, void* buf, size_t count, int dtype, int op, co
   if (rc != FT_OK) return rc;
   if (count == 0) return FT_OK;
   if (c->world == 1) {
-    if (!gather && scale != 1.0f && (dtype == FT_F32 || dtype == FT_BF16)) {
-      const void* src[1] = {buf};
-      return ft_reduce_nway_scaled(dtype, dtype, src, buf, 1, count, scale, stream);
-    }
+    if (!gather && scale != 1.0f && (dtype == FT_F32 || dtype == FT_BF16 || dtype == FT_F16 || dtype == FT_F64))
+      return ft_scale_inplace(dtype, buf, count, scale, stream);
     return FT_OK;
   }
   DevPlanEntry* pe = nullptr;
@@ -930,7 +943,8 @@ static int phase_call(ft_comm* c, void* buf, size_t count, int dtype, int op, co
   // buffer, or multimem.st of the own block to everyone) instead of N-1 peer loads per vector.  Block r ends up
   // on / comes from rank r, exactly as in the flat plan.
   const bool flat = !shape.ring && shape.lonely == 0 && shape.widths.size() == 1;
-  if (flat && c->phase_nvls && nvls_eligible(c, pr)) {
+  // (with two ranks a multimem pass moves twice the bytes of a plain peer read, and measures slower)
+  if (flat && c->phase_nvls && c->world > 2 && nvls_eligible(c, pr)) {
     ftk::NvlsArgs a{};
     a.work_off = (uint64_t)((unsigned char*)buf - local_base(c));
     a.count = count;

@@ -162,6 +162,7 @@ static int run_as_process_rank(const Opts& o) {
 }
 
 int main(int argc, char** argv) {
+  setvbuf(stdout, nullptr, _IOLBF, 0);   // a reader on a pipe sees every finished line, whatever happens later
   Opts o;
   for (int i = 1; i < argc; ++i) {
     std::string a = argv[i];

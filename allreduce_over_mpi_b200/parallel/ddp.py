@@ -95,6 +95,14 @@ class FlexTreeDDP(nn.Module):
             torch.cuda.synchronize(self.comm.device)
 
     def forward(self, *args, **kwargs):
+        # A backward that raised never reached _finish(): its half-counted buckets and the queued-callback mark
+        # must not leak into the next step, where buckets would launch early or the side stream never be joined.
+        if self._callback_queued or any(b.pending != len(b.params) for b in self.buckets):
+            self._callback_queued = False
+            for b in self.buckets:
+                b.pending = len(b.params)
+            if self.stream is not None:
+                torch.cuda.current_stream(self.comm.device).wait_stream(self.stream)
         return self.module(*args, **kwargs)
 
     @contextlib.contextmanager
@@ -134,7 +142,9 @@ class FlexTreeDDP(nn.Module):
             self.comm.all_reduce(b.flat, op="avg", shape=self.shape, algo=self.algo)
 
     def _finish(self):
-        """End of backward: flush buckets whose parameters got no gradient, join the side stream."""
+        """End of backward: flush buckets only part of whose parameters got a gradient, join the side stream.
+        A bucket none of whose parameters got a gradient is left alone, which is safe only when every rank has
+        the same unused parameters (the rule torch DDP states for find_unused_parameters=False)."""
         for b in self.buckets:
             if 0 < b.pending < len(b.params):
                 self._launch(b)

@@ -119,3 +119,27 @@ def test_release_returns_the_buckets():
     assert comm.live == [] and all(p.grad is None for p in model.parameters()) and ddp.buckets == []
     model(torch.rand(3, 8)).sum().backward()      # the bare module trains on with ordinary gradients
     assert all(p.grad is not None for p in model.parameters())
+
+
+def test_a_backward_that_raised_does_not_poison_the_next_step():
+    """A backward that raises part-way leaves buckets half counted and the end-of-backward callback unrun; the next
+    forward resets both, so the following step launches every bucket exactly once and gives the plain gradients."""
+    torch.manual_seed(0)
+    ref = GPT2(GPT2Config.tiny())
+    model = GPT2(GPT2Config.tiny())
+    model.load_state_dict(ref.state_dict())
+    comm = FakeComm()
+    ddp = FlexTreeDDP(model, comm, bucket_bytes=64 << 10)
+    x = torch.randint(0, 512, (2, 64))
+    # simulate the state a raising backward leaves behind
+    ddp._callback_queued = True
+    ddp.buckets[0].pending -= 1
+    ddp.zero_grad()
+    ref.zero_grad()
+    comm.calls.clear()
+    ref(x, x).backward()
+    ddp(x, x).backward()
+    assert len(comm.calls) == len(ddp.buckets)
+    assert not ddp._callback_queued and all(b.pending == len(b.params) for b in ddp.buckets)
+    for (n1, p1), (_, p2) in zip(ref.named_parameters(), model.named_parameters()):
+        assert torch.allclose(p1.grad, p2.grad, atol=1e-6), n1

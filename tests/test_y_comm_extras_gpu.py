@@ -160,3 +160,40 @@ def test_heap_free_and_reuse():
     want = torch.stack(host).double().sum(0)
     assert all(torch.allclose(t.double().cpu(), want, atol=1e-5) for t in ptrs)
     w.close()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64, torch.bfloat16, torch.float16, torch.int32])
+def test_world_of_one_scales_every_float_type_like_larger_worlds(dtype):
+    """op="avg"-style scaling at world 1: every floating type is scaled (an odd length and an odd offset take the
+    element-wise tail), integers never are - the same numbers a larger world's kernels would give."""
+    w = LocalWorld(1, heap_bytes=1 << 20, staging_bytes=1 << 16)
+    c = w.ranks[0]
+    for count, off in ((1, 0), (4099, 0), (70_003, 1)):
+        base = torch.arange(count + off, device=DEV).remainder(97).to(dtype)
+        x = base[off:].clone() if off == 0 else base[off:]
+        want = x.double() * (0.25 if dtype.is_floating_point else 1.0)
+        c.all_reduce(x, scale=0.25)
+        torch.cuda.synchronize()
+        assert (x.double() - want).abs().max().item() <= tol(dtype) * 10, (dtype, count)
+    h = c.alloc(1000, dtype)
+    h.fill_(8)
+    c.reduce_scatter(h, scale=0.5)
+    c.all_gather(h)
+    torch.cuda.synchronize()
+    assert bool((h == (4 if dtype.is_floating_point else 8)).all())
+    w.close()
+
+
+def test_auto_goes_through_the_native_policy_and_counts_the_algorithm():
+    """algo="auto" leaves the choice to the native policy inside ft_allreduce: what choose() reports for a size is
+    what the usage counters show afterwards; a device tensor larger than one staging slot is split natively."""
+    w = LocalWorld(1, heap_bytes=1 << 20, staging_bytes=1 << 16)
+    c = w.ranks[0]
+    name, shape = c.choose(1 << 20, False, torch.float32)
+    assert name in ("staged", "oneshot", "ll", "push") and P.validate_shape(1, shape) == ""
+    big = torch.ones(100_000, device=DEV)        # 400 kB > the 64 KiB slot; world 1 copies, so the data must survive
+    out = torch.empty_like(big)
+    c.all_reduce(big, out=out)
+    torch.cuda.synchronize()
+    assert bool((out == 1).all())
+    w.close()
