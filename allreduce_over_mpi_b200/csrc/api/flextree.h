@@ -115,7 +115,9 @@ size_t ft_plan_json(int world, const int* widths, int nw, int lonely, int ring, 
 /* one line with the per-call quantities the reference keeps in FlexTree_Context and prints with
  * show_context() (mpi_mod.hpp:776-801): "num_nodes=.., node_label=.., num_lonely=.., data_size=..,
  * num_split=.., split_size=.., data_size_aligned=.., type_size=.., has_lonely=..".
- * MPI_Allreduce_FT prints it to stderr on every call when FT_DEBUG=1 is set. */
+ * MPI_Allreduce_FT prints it to stderr on every call when FT_DEBUG=1 (or higher) is set.  FT_DEBUG=2 also runs the
+ * call as its two halves and prints, per rank, the first 100 values after the reduce-scatter ("Med CHECK") and after
+ * the all-gather ("Tail CHECK"), the reference's data dumps (mpi_mod.hpp:1601-1613, :1657-1670). */
 size_t ft_context_describe(int world, int rank, int lonely, uint64_t count, int dtype, char* buf, size_t cap);
 
 /* ---- CPU reductions and executors ---- */

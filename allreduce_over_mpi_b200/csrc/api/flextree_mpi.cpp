@@ -48,6 +48,41 @@ int fail(int code, const std::string& msg) {
   std::fprintf(stderr, "%s\n", msg.c_str());
   return code;
 }
+// One element of a buffer as text, for the debug dumps.
+std::string value_text(int dtype, const void* base, size_t i) {
+  char b[48];
+  switch (dtype) {
+    case FT_F32: std::snprintf(b, sizeof b, "%g", (double)((const float*)base)[i]); break;
+    case FT_F64: std::snprintf(b, sizeof b, "%g", ((const double*)base)[i]); break;
+    case FT_BF16: {
+      unsigned u = (unsigned)((const unsigned short*)base)[i] << 16;
+      float f;
+      std::memcpy(&f, &u, 4);
+      std::snprintf(b, sizeof b, "%g", (double)f);
+      break;
+    }
+    case FT_F16: std::snprintf(b, sizeof b, "0x%04x", ((const unsigned short*)base)[i]); break;
+    case FT_U8: case FT_BOOL: std::snprintf(b, sizeof b, "%u", ((const unsigned char*)base)[i]); break;
+    case FT_I8: std::snprintf(b, sizeof b, "%d", ((const signed char*)base)[i]); break;
+    case FT_U16: std::snprintf(b, sizeof b, "%u", ((const unsigned short*)base)[i]); break;
+    case FT_I16: std::snprintf(b, sizeof b, "%d", ((const short*)base)[i]); break;
+    case FT_I32: std::snprintf(b, sizeof b, "%d", ((const int*)base)[i]); break;
+    case FT_U32: std::snprintf(b, sizeof b, "%u", ((const unsigned*)base)[i]); break;
+    case FT_I64: std::snprintf(b, sizeof b, "%lld", ((const long long*)base)[i]); break;
+    case FT_U64: std::snprintf(b, sizeof b, "%llu", ((const unsigned long long*)base)[i]); break;
+    default: std::snprintf(b, sizeof b, "?"); break;
+  }
+  return b;
+}
+// "<label> CHECK node <rank>: v0 v1 ..." with the first 100 values of a host buffer, as one write to stderr:
+// the reference's FT_DEBUG dumps after its two phases ("Med CHECK" / "Tail CHECK", mpi_mod.hpp:1601-1613, :1657-1670).
+void dump_values(const char* label, int rank, int dtype, const void* host, size_t count) {
+  std::string line = std::string(label) + " CHECK node " + std::to_string(rank) + ":";
+  for (size_t i = 0; i < count && i < 100; ++i) line += " " + value_text(dtype, host, i);
+  line += "\n";
+  std::fputs(line.c_str(), stderr);
+}
+
 bool is_device_pointer(const void* p) {
   cudaPointerAttributes a;
   if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
@@ -160,12 +195,42 @@ int MPI_Allreduce_FT_c(const void* sendbuf, void* recvbuf, size_t count, FT_Data
   const ft::ShapeConfig& cfg = comm->cfg;
   if (!cfg.ok()) return fail(FT_ERR_INVALID_TOPO, cfg.error);
   ft::Shape shape = cfg.shape;
-  if (const char* dbg = std::getenv("FT_DEBUG"); dbg && dbg[0] == '1') {
+  int debug = 0;
+  if (const char* dbg = std::getenv("FT_DEBUG"); dbg && dbg[0] >= '1' && dbg[0] <= '9') debug = dbg[0] - '0';
+  if (debug >= 1) {
     int rank = 0;
     FT_Comm_rank(comm, &rank);
     char line[256];
     ft_context_describe(world, rank, shape.lonely, count, datatype, line, sizeof line);
     std::fprintf(stderr, "%s", line);
+  }
+
+  // FT_DEBUG=2: the call runs as its two halves, reduce-scatter then all-gather, and every rank prints the first
+  // 100 values of its buffer after each, in rank order where the world has a barrier (threads, processes).
+  if (debug >= 2 && world > 1 && (comm->threads || comm->procs)) {
+    if (cfg.is_auto) shape = ft::Shape::flat(world);
+    if (!in_place) std::memcpy(recvbuf, sendbuf, count * es);
+    const int nw = (int)shape.widths.size();
+    for (int phase = 1; phase <= 2; ++phase) {
+      int st3[3] = {0, 0, 0};
+      const int rc = comm->threads
+                         ? ft_cpu_phase(comm->threads, comm->rank, shape.widths.data(), nw, shape.lonely, shape.ring, op, datatype,
+                                        recvbuf, count, 0, phase, st3)
+                         : ft_proc_phase(comm->procs, shape.widths.data(), nw, shape.lonely, shape.ring, op, datatype, recvbuf, count,
+                                         phase, st3);
+      if (rc != FT_OK)
+        return fail(rc, std::string("MPI_Allreduce_FT: ") + ft_status_name((ft_status)rc) + " at rendezvous " + std::to_string(st3[1]));
+      for (int r = 0; r < world; ++r) {   // one rank at a time, the others wait (both phases end with every rank present)
+        if (r == comm->rank) dump_values(phase == 1 ? "Med" : "Tail", comm->rank, datatype, recvbuf, count);
+        if (comm->procs) ft_proc_barrier(comm->procs);
+        else {   // an all-reduce of one byte over the flat plan is a barrier of the thread world
+          unsigned char b = 0;
+          ft::cpu_allreduce(comm->threads->w, comm->rank, plan_for(world, ft::Shape::flat(world)), FT_SUM, FT_U8, nullptr, &b, 1, 0,
+                            nullptr, 1);
+        }
+      }
+    }
+    return 0;
   }
 
   if (comm->threads) {
@@ -204,6 +269,25 @@ int MPI_Allreduce_FT_c(const void* sendbuf, void* recvbuf, size_t count, FT_Data
   const int algo = explicit_shape ? FT_ALGO_STAGED : FT_ALGO_AUTO;
   const bool dev_recv = is_device_pointer(recvbuf);
   const bool dev_send = in_place ? dev_recv : is_device_pointer(sendbuf);
+  if (debug >= 2 && world > 1 && dev_recv && dev_send) {
+    // GPU ranks: the halves as collectives of their own on a heap tensor, a host copy of the first 100 values after
+    // each; ranks are separate processes without a barrier of their own here, so every dump is one prefixed line
+    const ft::Shape sh = explicit_shape ? shape : ft::Shape::flat(world);
+    cudaStream_t st = (cudaStream_t)comm->stream;
+    if (!in_place && cudaMemcpyAsync(recvbuf, sendbuf, count * es, cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+      return fail(FT_ERR_CUDA, "MPI_Allreduce_FT: device copy failed");
+    unsigned char head[100 * 8];
+    const size_t n = count < 100 ? count : 100;
+    for (int phase = 1; phase <= 2; ++phase) {
+      int rc = phase == 1 ? ft_reduce_scatter(g, recvbuf, count, datatype, op, sh.widths.data(), (int)sh.widths.size(), sh.lonely, sh.ring, 1.0f, comm->stream)
+                          : ft_all_gather(g, recvbuf, count, datatype, sh.widths.data(), (int)sh.widths.size(), sh.lonely, sh.ring, comm->stream);
+      if (rc != FT_OK) return fail(rc, ft_comm_last_error(g));
+      if (cudaMemcpyAsync(head, recvbuf, n * es, cudaMemcpyDeviceToHost, st) != cudaSuccess || cudaStreamSynchronize(st) != cudaSuccess)
+        return fail(FT_ERR_CUDA, "MPI_Allreduce_FT: debug copy failed");
+      dump_values(phase == 1 ? "Med" : "Tail", comm->rank, datatype, head, n);
+    }
+    return 0;
+  }
   if (dev_recv && dev_send) {
     int rc = ft_allreduce(g, in_place ? nullptr : sendbuf, recvbuf, count, datatype, op, explicit_shape ? widths : nullptr,
                           explicit_shape ? nw : 0, explicit_shape ? shape.lonely : 0, explicit_shape ? shape.ring : 0, algo,

@@ -145,3 +145,29 @@ def test_call_context_record_and_debug_print(env, capfd):
         env.pop("FT_DEBUG", None)
     err = capfd.readouterr().err
     assert "num_nodes=5, node_label=4, num_lonely=1, data_size=27, num_split=4, split_size=6, data_size_aligned=30, type_size=4, has_lonely=1" in err
+
+
+def test_debug_level_two_dumps_both_phases_in_rank_order(env, capfd):
+    """FT_DEBUG=2: the call runs as reduce-scatter + all-gather and every rank prints the first values of its buffer
+    after each half, rank after rank (the reference's "Med CHECK" / "Tail CHECK" dumps, mpi_mod.hpp:1601-1613,
+    :1657-1670).  After the first half a rank's own block is complete; after the second everything is."""
+    env["FT_TOPO"], env["FT_DEBUG"] = "2,2", "2"
+    env.pop("FT_LONELY", None)
+    try:
+        bufs = {}
+
+        def rank_fn(r, comm):
+            bufs[r] = torch.full((8,), float(r + 1))
+            return M.MPI_Allreduce_FT(M.IN_PLACE, bufs[r], 8, M.MPI_FLOAT, M.MPI_SUM, comm)
+        assert run_world(4, rank_fn) == [0] * 4
+    finally:
+        env.pop("FT_DEBUG", None)
+    assert all(bool((b == 10).all()) for b in bufs.values())
+    lines = [l for l in capfd.readouterr().err.splitlines() if " CHECK node " in l]
+    assert [l.split(":")[0] for l in lines] == [f"{tag} CHECK node {r}" for tag in ("Med", "Tail") for r in range(4)]
+    for l in lines[:4]:      # blocks of two elements; rank r owns block r after the reduce-scatter
+        r = int(l.split(":")[0].split()[-1])
+        vals = [float(v) for v in l.split(":")[1].split()]
+        assert vals[2 * r:2 * r + 2] == [10.0, 10.0]
+    for l in lines[4:]:
+        assert [float(v) for v in l.split(":")[1].split()] == [10.0] * 8
