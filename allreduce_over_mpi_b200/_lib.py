@@ -22,7 +22,7 @@ DTYPE_SIZE = {0: 1, 1: 1, 2: 2, 3: 2, 4: 4, 5: 8, 6: 4, 7: 8, 8: 1, 9: 4, 10: 8,
 OPS = {"sum": 0, "band": 1}
 STATUS = {0: "ok", 1: "invalid argument", 2: "unsupported type", 3: "unsupported op", 4: "invalid topology",
           5: "timeout waiting for a peer", 6: "CUDA error", 7: "size exceeds limit", 8: "protocol error",
-          9: "not available"}
+          9: "not available", 10: "address outside the symmetric heap (access skipped)"}
 
 
 class FlexTreeError(RuntimeError):
@@ -132,7 +132,12 @@ def lib() -> C.CDLL:
     global _lib
     if _lib is None:
         path = LIB_PATH
-        if not path.exists() or os.environ.get("FT_REBUILD"):
+        if os.environ.get("FT_LIB", "") == "bounds":   # the debugging build whose kernels range-check every heap access
+            path = LIB_PATH.with_name("libflextree_bounds.so")
+            if not path.exists():
+                from .build import build_bounds
+                path = build_bounds()
+        elif not path.exists() or os.environ.get("FT_REBUILD"):
             from .build import ensure_built
             path = ensure_built()
         if not path.exists():

@@ -51,6 +51,8 @@ def declare(lib) -> None:
         "ft_comm_set_nvls_ctas_per_sm": (None, [vp, i]),
         "ft_comm_set_nvls_config": (i, [vp, i, i, i, i, sz]),
         "ft_comm_set_phase_nvls": (None, [vp, i]),
+        "ft_bounds_build": (i, []),
+        "ft_bounds_check_host": (i, [u64, i, i, u64, u64]),
         "ft_comm_policy": (vp, [vp]),
         "ft_comm_choose": (i, [vp, sz, i, i, vp, vp]),
         "ft_allreduce_emulate_push": (i, [vp, vp, sz, i, i, f32, vp]),
@@ -59,6 +61,7 @@ def declare(lib) -> None:
         "ft_reduce_scatter": (i, [vp, vp, sz, i, i, *shape, f32, vp]),
         "ft_all_gather": (i, [vp, vp, sz, i, *shape, vp]),
         "ft_comm_block_elems": (u64, [vp, sz, i]),
+        "ft_block_elems": (u64, [u64, i, i]),
         "ft_allreduce_emulate_stage": (i, [vp, vp, vp, sz, i, i, *shape, f32, i, i, vp]),
         "ft_allreduce_emulate_oneshot": (i, [vp, vp, vp, sz, i, i, f32, i, u64, vp]),
         "ft_comm_status": (i, [vp, ip]),

@@ -35,6 +35,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--others", nargs="*", default=["push", "nccl"], help="also time these on the same buffer: push, staged, hybrid, nccl")
+    ap.add_argument("--peer-lanes", type=int, nargs="+", default=[0], help="CTA caps tried for the peer-load kernels (push, staged); 0 = one per SM")
     ap.add_argument("--phases", action="store_true")
     ap.add_argument("--out", default=None)
     a = ap.parse_args(argv)
@@ -65,18 +66,22 @@ def main(argv=None):
             comm.set_nvls_config(threads=512, unroll=4, weak=0, max_lanes=0, stripe_bytes=0)
             lib().ft_comm_set_nvls_ctas_per_sm(comm._h, 1)
         for other in a.others:
-            if other == "nccl":
-                fn = lambda: dist.all_reduce(buf, op=dist.ReduceOp.AVG)  # noqa: E731
-            elif other == "staged":
-                fn = lambda: comm.all_reduce(buf, algo="staged", op="avg")  # noqa: E731
-            else:
-                if other == "hybrid" and not comm.has_nvls:
-                    continue
-                fn = lambda other=other: comm.all_reduce(buf, algo=other, op="avg")  # noqa: E731
-            ms = time_collective(fn, a.iters, a.warmup)
-            comm.check()
-            emit({"bench": "nvls_sweep", "world": world, "bytes": nbytes, "dtype": a.dtype, "impl": other, "ms": round(ms, 5),
-                  "busbw_GBps": round(busbw(nbytes, ms, world), 1)})
+            lane_caps = a.peer_lanes if other in ("push", "staged") else [0]
+            for cap in lane_caps:
+                if other == "nccl":
+                    fn = lambda: dist.all_reduce(buf, op=dist.ReduceOp.AVG)  # noqa: E731
+                elif other == "staged":
+                    fn = lambda: comm.all_reduce(buf, algo="staged", op="avg")  # noqa: E731
+                else:
+                    if other == "hybrid" and not comm.has_nvls:
+                        continue
+                    fn = lambda other=other: comm.all_reduce(buf, algo=other, op="avg")  # noqa: E731
+                comm.set_max_lanes(cap)     # 0: one CTA per SM
+                ms = time_collective(fn, a.iters, a.warmup)
+                comm.set_max_lanes(0)
+                comm.check()
+                emit({"bench": "nvls_sweep", "world": world, "bytes": nbytes, "dtype": a.dtype, "impl": other, "peer_lanes": cap,
+                      "ms": round(ms, 5), "busbw_GBps": round(busbw(nbytes, ms, world), 1)})
         if a.phases:
             halves = {}
             for label, on in (("multimem", 1), ("peer loads", 0)):

@@ -46,9 +46,9 @@ def headers_mtime() -> float:
     return max(m, Path(__file__).stat().st_mtime)
 
 
-def compile_one(src: Path, verbose: bool) -> tuple[Path, str]:
-    obj = OBJ / (src.stem + ".o")
-    cmd = [NVCC, *ARCH, *COMMON, "-c", str(src), "-o", str(obj)]
+def compile_one(src: Path, verbose: bool, obj_dir: Path = OBJ, defines: tuple = ()) -> tuple[Path, str]:
+    obj = obj_dir / (src.stem + ".o")
+    cmd = [NVCC, *ARCH, *COMMON, *defines, "-c", str(src), "-o", str(obj)]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     r = subprocess.run(cmd, capture_output=True, text=True)
@@ -86,6 +86,32 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB
 
 
+BOUNDS_LIB = PKG / "lib" / "libflextree_bounds.so"
+
+
+def build_bounds(force: bool = False) -> Path:
+    """The debugging build: the same sources with -DFT_BOUNDS, linked as lib/libflextree_bounds.so.  Its collective
+    kernels test every run of heap bytes against the heap size before touching it (csrc/kernels/comm_bounds.h);
+    select it with FT_LIB=bounds in the environment of the process that loads the library."""
+    obj_dir = PKG / "csrc" / "build_bounds"
+    obj_dir.mkdir(parents=True, exist_ok=True)
+    hm = headers_mtime()
+    srcs = sources()
+    todo = [s for s in srcs if force or not (obj_dir / (s.stem + ".o")).exists()
+            or (obj_dir / (s.stem + ".o")).stat().st_mtime < max(s.stat().st_mtime, hm)]
+    if todo:
+        with cf.ThreadPoolExecutor(max_workers=min(len(todo), os.cpu_count() or 4)) as ex:
+            list(ex.map(lambda s: compile_one(s, False, obj_dir, ("-DFT_BOUNDS",)), todo))
+    objs = [obj_dir / (s.stem + ".o") for s in srcs]
+    if todo or not BOUNDS_LIB.exists():
+        cmd = [NVCC, *ARCH, "-shared", "-cudart", "static", "-o", str(BOUNDS_LIB), *map(str, objs),
+               "-Xcompiler", "-fopenmp", "-lpthread", "-ldl", "-lrt"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    return BOUNDS_LIB
+
+
 def build_tools() -> list[Path]:
     """Native command-line tools next to the library: ft_bench, planner_dump, cost_model_sweep."""
     out = []
@@ -119,3 +145,5 @@ def ensure_built() -> Path:
 if __name__ == "__main__":
     p = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print(p)
+    if "--bounds" in sys.argv:
+        print(build_bounds(force="--force" in sys.argv))

@@ -125,6 +125,8 @@ int ft_reduce_scatter(ft_comm* c, void* buf, size_t count, int dtype, int op, co
 int ft_all_gather(ft_comm* c, void* buf, size_t count, int dtype, const int* widths, int nw, int lonely, int ring,
                   void* stream);
 uint64_t ft_comm_block_elems(ft_comm* c, size_t count, int dtype);
+/* the same without a communicator: elements per block for `count` elements of `elem_size` bytes on `world` ranks */
+uint64_t ft_block_elems(uint64_t count, int world, int elem_size);
 /* FT_ALGO_HYBRID: fraction of every block reduced inside the switch (the rest goes over peer
  * loads at the same time) and fraction of the kernel's CTAs given to that part */
 void ft_comm_set_hybrid(ft_comm* c, double byte_fraction, double lane_fraction);
@@ -153,6 +155,13 @@ void ft_comm_set_phase_nvls(ft_comm* c, int on);
 /* one-shot emulation: phase 1 = publish input (all ranks first), phase 4 = reduce */
 int ft_allreduce_emulate_oneshot(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op,
                                  float scale, int phase, uint64_t call, void* stream);
+
+/* Debugging build (python -m allreduce_over_mpi_b200.build --bounds -> lib/libflextree_bounds.so, loaded with
+ * FT_LIB=bounds): the collective kernels test every run of heap bytes against the heap size before touching it; a
+ * run that leaves the heap is skipped and reported as FT_ERR_BOUNDS through ft_comm_status.  ft_bounds_build says
+ * which build this is; ft_bounds_check_host evaluates the same predicate on the host. */
+int ft_bounds_build(void);
+int ft_bounds_check_host(uint64_t heap_bytes, int rank, int world, uint64_t off, uint64_t len);
 
 /* status block written by kernels whose bounded wait ran out: out[0..4] =
  * {ft_status, rendezvous index, peer, lane, calls completed}.  Synchronises nothing: call

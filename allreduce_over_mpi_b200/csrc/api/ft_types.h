@@ -44,7 +44,8 @@ typedef enum ft_status {
   FT_ERR_CUDA = 6,
   FT_ERR_TOO_LARGE = 7,
   FT_ERR_PROTOCOL = 8, /* a peer signalled an unexpected epoch */
-  FT_ERR_NOT_AVAILABLE = 9
+  FT_ERR_NOT_AVAILABLE = 9,
+  FT_ERR_BOUNDS = 10 /* debugging build (-DFT_BOUNDS): a kernel was about to leave the symmetric heap and skipped the access */
 } ft_status;
 
 /* All-reduce algorithms of the GPU communicator (flextree_comm.h); AUTO asks the selection policy. */
@@ -93,6 +94,7 @@ static inline const char* ft_status_name(ft_status s) {
     case FT_ERR_INVALID_TOPO: return "invalid topology"; case FT_ERR_TIMEOUT: return "timeout waiting for a peer";
     case FT_ERR_CUDA: return "CUDA error"; case FT_ERR_TOO_LARGE: return "size exceeds limit";
     case FT_ERR_PROTOCOL: return "protocol error"; case FT_ERR_NOT_AVAILABLE: return "not available";
+    case FT_ERR_BOUNDS: return "address outside the symmetric heap (access skipped)";
     default: return "unknown";
   }
 }

@@ -32,6 +32,7 @@ struct CommDev {
   Status* status;                      // pinned host memory
   int rank, world;
   unsigned long long timeout_ns;
+  uint64_t heap_bytes;                 // bytes of every rank's heap mapping (what the FT_BOUNDS build checks against)
 };
 
 // One pull of the plan, device form.
@@ -110,8 +111,10 @@ struct NvlsArgs {
 };
 
 // Launch shape of the NVLS kernels (tuning knobs of the communicator).
+// Measured on 8 and 4 B200 (64 MiB - 1 GiB): 256 threads x 4 vectors on 32-64 CTAs give 800-840 GB/s bus bandwidth at
+// 8 GPUs where 512 threads on all 148 SMs give 725-740: the switch serves a few hundred KB in flight per GPU best.
 struct NvlsConfig {
-  int threads = 512;          // per CTA
+  int threads = 256;          // per CTA
   int unroll = 4;             // 16-byte vectors in flight per thread
   int weak = 0;               // 1: multimem.*.weak instead of .relaxed.sys
 };

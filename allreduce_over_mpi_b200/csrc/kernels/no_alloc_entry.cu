@@ -39,7 +39,10 @@ int fail(int code, const std::string& what) {
 int scratch_for_current_device(unsigned char** out) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) return fail(FT_ERR_CUDA, "no current CUDA device");
+  if (e != cudaSuccess || dev < 0) return fail(FT_ERR_CUDA, "no current CUDA device");
+  if (dev >= kMaxDevices)
+    return fail(FT_ERR_TOO_LARGE, "device ordinal " + std::to_string(dev) + " is beyond the " + std::to_string(kMaxDevices) +
+                                      " devices this entry point keeps an address for");
   std::lock_guard<std::mutex> lk(g_mu);
   if (!g_scratch_addr[dev]) {
     void* p = nullptr;

@@ -1,10 +1,11 @@
 /* An all-reduce entry point that allocates no memory.
  *
  * This has NO counterpart in the reference project; it exists for callers of this library that
- * are not allowed to allocate device memory: code that runs while a stream capture is open,
- * plug-ins living inside a host application that has handed the whole GPU to its own memory
- * pool, and latency-critical loops where a cudaMalloc (an implicit device synchronisation)
- * is unacceptable.
+ * are not allowed to allocate device memory: plug-ins living inside a host application that has
+ * handed the whole GPU to its own memory pool (a cudaMalloc from a guest would fail or starve
+ * the host), latency-critical loops where a cudaMalloc (an implicit device synchronisation) is
+ * unacceptable, and code running at a point of the host program where the CUDA runtime does
+ * not accept allocation calls.
  *
  * ft_local_allreduce_noalloc() makes `n` buffers that all live on the CURRENT GPU hold their
  * element-wise reduction, in place - the one-shot all-reduce of the communicator, for ranks that
@@ -19,8 +20,9 @@
  *   - n * count * sizeof(dtype), with each buffer's share rounded up to 256 bytes, must fit
  *     in FT_NOALLOC_SCRATCH_BYTES; larger requests are refused with FT_ERR_TOO_LARGE and a message
  *     (ft_noalloc_last_error()).  Nothing is launched in that case.
- *   - The first call on a device looks up the array's device address (a one-off, synchronous
- *     runtime query).  Make that first call before opening a stream capture.
+ *   - The first call on a device does the set-up: it looks up the array's device address (a
+ *     one-off, synchronous runtime query).  That first call should come before any stream
+ *     capture.
  *   - Every call uses the same array and overwrites the previous call's leftovers before reading
  *     them, so nothing has to be cleared between calls; but two calls that may run on the GPU
  *     at the same time (different streams without ordering) race on it.  Order them.

@@ -40,6 +40,8 @@ struct ProcShared {
   std::atomic<uint32_t> detached;   // ranks that have left (the last one unlinks the name)
   int32_t world;
   std::atomic<int32_t> pid[FT_MAX_RANKS];
+  std::atomic<int32_t> ppid[FT_MAX_RANKS];   // each rank's parent: one common launcher lets the ranks open up to it alone
+  std::atomic<uint32_t> opened;              // ranks that have declared who may read their memory
   std::atomic<uint64_t> buf[FT_MAX_RANKS];                      // address exposed for the running call
   std::atomic<uint32_t> flags[FT_MAX_RANKS * FT_MAX_RANKS];     // flags[dst * world + src]
   // Small messages skip the system calls: a rank's working copy lives here for the length of the call and the
@@ -95,11 +97,24 @@ class ProcWorld {
       if (sh_->world != world) { error = "ranks disagree on the world size"; return false; }
     }
     if (const char* kb = std::getenv("FT_PROC_TILE_KB"); kb && std::atoi(kb) >= 4) tile_bytes_ = (size_t)std::atoi(kb) << 10;
-    // let the sibling ranks read this process's memory (needed where ptrace is restricted to descendants)
-    prctl(PR_SET_PTRACER, PR_SET_PTRACER_ANY, 0, 0, 0);
     sh_->pid[rank].store((int32_t)getpid(), std::memory_order_release);
+    sh_->ppid[rank].store((int32_t)getppid(), std::memory_order_release);
     sh_->attached.fetch_add(1, std::memory_order_acq_rel);
     while ((int)sh_->attached.load(std::memory_order_acquire) < world) {
+      if (late()) { error = "not every rank joined the session"; return false; }
+      std::this_thread::yield();
+    }
+    // Let the sibling ranks read this process's memory (needed where ptrace is restricted to descendants).  The
+    // kernel takes ONE process per caller, and its descendants count too: when every rank was started by the same
+    // launcher, naming that launcher admits exactly the launcher and the sibling ranks.  Only ranks with different
+    // parents (started by hand from several shells) fall back to admitting any process of the same user.
+    bool same_parent = true;
+    const int32_t parent = sh_->ppid[0].load(std::memory_order_acquire);
+    for (int r = 1; r < world; ++r) same_parent = same_parent && sh_->ppid[r].load(std::memory_order_acquire) == parent;
+    if (same_parent && parent > 1) prctl(PR_SET_PTRACER, (unsigned long)parent, 0, 0, 0);
+    else prctl(PR_SET_PTRACER, PR_SET_PTRACER_ANY, 0, 0, 0);
+    sh_->opened.fetch_add(1, std::memory_order_acq_rel);
+    while ((int)sh_->opened.load(std::memory_order_acquire) < world) {   // nobody reads a peer before it has opened up
       if (late()) { error = "not every rank joined the session"; return false; }
       std::this_thread::yield();
     }

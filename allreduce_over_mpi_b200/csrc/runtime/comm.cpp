@@ -25,6 +25,7 @@
 #include "../api/flextree.h"
 #include "../api/flextree_comm.h"
 #include "../api/policy_handle.hpp"
+#include "../kernels/comm_bounds.h"
 #include "../kernels/comm_dev.h"
 #include "../kernels/pol_ids.h"
 #include "../planner/plan.hpp"
@@ -146,7 +147,7 @@ struct ft_comm {
   size_t ll_max = 8 << 10;   // AUTO uses the low-latency protocol up to this size
   int nvls_ctas_per_sm = 1;   // measured on 8 GPUs: 2 or 3 CTAs per SM lose 5-15 % at 256 MiB and above
   ftk::NvlsConfig nvls_cfg;   // threads per CTA, vectors in flight per thread, instruction form
-  int nvls_max_lanes = 0;     // 0: as many lanes as SMs (times nvls_ctas_per_sm)
+  int nvls_max_lanes = 64;    // 0: as many lanes as SMs (times nvls_ctas_per_sm)
   size_t nvls_stripe = 0;
   bool phase_nvls = true;     // ft_reduce_scatter / ft_all_gather may use the multimem kernels (flat shape, eligible tensor)     // all-reduce: 0 = rank r owns block r, else round-robin stripes of this many bytes
   std::map<std::string, DevPlanEntry> plans;
@@ -250,13 +251,14 @@ bool in_heap(ft_comm* c, const void* p, size_t bytes) {
   return b && q >= b && q + bytes <= b + c->user_bytes && ((uintptr_t)q & 15) == 0;
 }
 
-// Elements per block: ceil(count/world) rounded up so that a block is a whole number of
-// 16-byte vectors (trailing blocks come out short or empty, like the reference's split).
+// Elements per block: ceil(count/world) rounded up so that a block is a whole number of 16-byte vectors
+// (trailing blocks come out short or empty, like the reference's split); blocks of 64 KiB and more are whole
+// multiples of 512 bytes, so that every block (and with it every lane's slice) starts on a warp-request boundary.
 uint64_t pick_block_elems(uint64_t count, int world, uint32_t es) {
-  const uint64_t per = 16 / es;
   uint64_t b = (count + world - 1) / (uint64_t)world;
+  const uint64_t per = (b * es >= (64u << 10) ? 512 : 16) / es;
   b = (b + per - 1) / per * per;
-  return b ? b : per;
+  return b ? b : 16 / es;
 }
 
 int pick_lanes(ft_comm* c, uint64_t region_bytes, uint64_t min_chunk, int ctas_per_sm = 1) {
@@ -635,6 +637,7 @@ int ft_comm_finalize(ft_comm* c) {
   d.rank = c->rank;
   d.world = c->world;
   d.timeout_ns = (unsigned long long)(c->timeout_ms * 1e6);
+  d.heap_bytes = c->total_bytes;
   c->finalized = true;
   // The selection policy: the calibration file named by FT_CALIBRATION, else the packaged one; without
   // either the cost model's built-in parameters decide.
@@ -972,6 +975,10 @@ int ft_all_gather(ft_comm* c, void* buf, size_t count, int dtype, const int* wid
   const int op = ftk::policy_id(FT_SUM, dtype) >= 0 ? FT_SUM : FT_BAND;
   return phase_call(c, buf, count, dtype, op, widths, nw, lonely, ring, 1.0f, true, stream);
 }
+uint64_t ft_block_elems(uint64_t count, int world, int elem_size) {
+  if (world < 1 || (elem_size != 1 && elem_size != 2 && elem_size != 4 && elem_size != 8)) return 0;
+  return pick_block_elems(count, world, (uint32_t)elem_size);
+}
 uint64_t ft_comm_block_elems(ft_comm* c, size_t count, int dtype) {
   const size_t es = ft_dtype_size((ft_dtype)dtype);
   if (!c || !es) return 0;
@@ -1040,6 +1047,19 @@ int ft_plan_num_stages_for(ft_comm* c, const int* widths, int nw, int lonely, in
   DevPlanEntry* pe = nullptr;
   if (get_plan(c, make_shape(c->world, widths, nw, lonely, ring), &pe) != FT_OK) return -1;
   return pe->nstages;
+}
+
+// 1 when the library was built with -DFT_BOUNDS (the kernels check every heap range before touching it)
+int ft_bounds_build(void) {
+#ifdef FT_BOUNDS
+  return 1;
+#else
+  return 0;
+#endif
+}
+// The predicate of the checked build, callable on the host (tests exercise its failing branch here, never on a GPU)
+int ft_bounds_check_host(uint64_t heap_bytes, int rank, int world, uint64_t off, uint64_t len) {
+  return ftk::range_in_heap(heap_bytes, rank, world, off, len) ? 1 : 0;
 }
 
 int ft_comm_status(ft_comm* c, int* out5) {

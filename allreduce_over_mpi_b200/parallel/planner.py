@@ -294,11 +294,10 @@ def owned_blocks(world: int, shape: Shape, rank: int) -> list[int]:
 
 
 def block_elems_for(count: int, world: int, elem_size: int) -> int:
-    """Elements per block as the GPU communicator cuts a tensor: ceil(count / world) rounded up to whole
-    16-byte vectors; block b covers [b * B, min((b + 1) * B, count))."""
-    per = max(1, 16 // elem_size)
-    b = -(-count // world)
-    return max(per, -(-b // per) * per)
+    """Elements per block as the GPU communicator cuts a tensor (the library's own arithmetic): ceil(count / world)
+    rounded up to whole 16-byte vectors, and to whole multiples of 512 bytes once a block reaches 64 KiB;
+    block b covers [b * B, min((b + 1) * B, count))."""
+    return int(lib().ft_block_elems(count, world, elem_size))
 
 
 class CpuWorld:

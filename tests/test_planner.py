@@ -97,7 +97,8 @@ def test_block_elems_matches_the_16_byte_rule():
     assert P.block_elems_for(1000, 8, 4) == 128          # ceil(1000/8) = 125 -> whole 16-byte vectors
     assert P.block_elems_for(1000, 8, 2) == 128
     assert P.block_elems_for(3, 8, 4) == 4
-    assert P.block_elems_for(1 << 20, 7, 1) == 149808
+    assert P.block_elems_for(1 << 20, 7, 1) == 150016      # blocks of 64 KiB and more: whole multiples of 512 bytes
+    assert P.block_elems_for(100_000, 7, 4) == 14288       # 57 KB blocks stay at 16-byte granularity
 
 
 def test_lonely_validity_rule_is_exact():

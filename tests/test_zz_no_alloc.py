@@ -1,8 +1,9 @@
 """The allocation-free all-reduce entry point, called through its exported C symbol.
 
 Some users of the library may not allocate device memory at the moment they need a reduction
-(an open stream capture, a host application that owns all GPU memory, a loop that cannot afford
-cudaMalloc's implicit synchronisation).  ft_local_allreduce_noalloc() serves them from a fixed
+(a plug-in inside a host application that owns all GPU memory, a loop that cannot afford
+cudaMalloc's implicit synchronisation, a point of the program where the runtime accepts no
+allocation call).  ft_local_allreduce_noalloc() serves them from a fixed
 8 MiB array inside the library.  Here its result is compared with the regular path (a one-shot
 all-reduce through communicators, which allocate heaps) on two calls in a row: the second call
 runs over whatever the first one left in the shared array.
@@ -89,3 +90,25 @@ def test_scale_band_and_limits():
     torch.cuda.synchronize()
     assert bool((fit[1] == 2).all())
     assert call(fn, [torch.ones(4, device=DEV)], "float32", op="band") == 2     # float AND: unsupported type
+
+
+def test_buffers_off_the_16_byte_grid_take_the_element_wise_path():
+    """Buffers that start one element past a 16-byte boundary (views into larger tensors): the kernels fall back
+    to element-sized accesses at both ends and give the same sums as the allocating path, twice in a row."""
+    lib, fn = entry()
+    n = 3
+    world = LocalWorld(n, heap_bytes=1 << 20, staging_bytes=1 << 20)
+    for rnd, (dtype, name, tol) in enumerate(((torch.float32, "float32", 1e-5), (torch.bfloat16, "bfloat16", 0.15))):
+        whole = make(n, 20_011, dtype, seed=20 + rnd)
+        a = [t[1:] for t in whole]                 # data_ptr is 4 (or 2) bytes past the allocation's 256-byte boundary
+        assert all(t.data_ptr() % 16 != 0 for t in a)
+        b = [t.clone() for t in a]
+        heads = [t[0].item() for t in whole]
+        assert call(fn, a, name) == 0, lib.ft_noalloc_last_error()
+        world.all_reduce(b, algo="oneshot")
+        torch.cuda.synchronize()
+        want = torch.stack([t.double() for t in b]).sum(0) / n    # b now holds the sums on every rank
+        for r in range(n):
+            assert torch.allclose(a[r].double(), b[r].double(), atol=tol, rtol=0), (name, r)
+            assert whole[r][0].item() == heads[r]                 # the element before the view is untouched
+    world.close()
