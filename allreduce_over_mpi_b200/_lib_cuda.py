@@ -57,6 +57,8 @@ def declare(lib) -> None:
         "ft_comm_choose": (i, [vp, sz, i, i, vp, vp]),
         "ft_allreduce_emulate_push": (i, [vp, vp, sz, i, i, f32, vp]),
         "ft_allreduce_emulate_ll": (i, [vp, vp, vp, sz, i, i, f32, i, u64, vp]),
+        "ft_allreduce_emulate_ll_tree": (i, [vp, vp, vp, sz, i, i, *shape, f32, i, i, u64, vp]),
+        "ft_comm_set_ll_tree_max": (None, [vp, sz]),
         "ft_allreduce": (i, [vp, vp, vp, sz, i, i, *shape, i, f32, vp]),
         "ft_reduce_scatter": (i, [vp, vp, sz, i, i, *shape, f32, vp]),
         "ft_all_gather": (i, [vp, vp, sz, i, *shape, vp]),

@@ -110,6 +110,10 @@ def sweep(a, comm: FlexTreeComm, rank: int, world: int) -> list[dict]:
             impls = []
             for shape in a.shapes:
                 for algo in a.algos:
+                    if algo == "lltree":   # the plan of every listed shape on tagged words (small messages)
+                        if shape != "auto" and nbytes <= (64 << 10) and not validate_shape(world, Shape.parse(shape)):
+                            impls.append((shape, algo))
+                        continue
                     if algo != "staged" and shape != a.shapes[0]:
                         continue
                     if algo == "oneshot" and nbytes > min(comm.staging_bytes, a.oneshot_cap):
@@ -143,13 +147,15 @@ def sweep(a, comm: FlexTreeComm, rank: int, world: int) -> list[dict]:
                     comm.set_hybrid(bf, lf)
                     fn = lambda: comm.all_reduce(sym, algo="hybrid")  # noqa: E731
                     label = f"flextree/hybrid-{bf}-{lf}/{world}"
+                elif algo == "lltree":
+                    fn = lambda shape=shape: comm.all_reduce(loc, shape=shape, algo="ll")  # noqa: E731
                 elif algo == "ll":
                     fn = lambda: comm.all_reduce(loc, algo="ll")  # noqa: E731
                 else:
                     fn = lambda: comm.all_reduce(loc, algo="oneshot")  # noqa: E731
                 row = {"bench": "allreduce", "impl": label, "bytes": nbytes, "dtype": dt_name, "world": world}
                 if a.check:
-                    tgt = loc if algo in ("oneshot", "ll") else sym
+                    tgt = loc if algo in ("oneshot", "ll", "lltree") else sym
                     fill(tgt, rank)
                     fn()
                     torch.cuda.synchronize()

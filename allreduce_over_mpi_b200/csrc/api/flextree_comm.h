@@ -141,6 +141,15 @@ int ft_allreduce_emulate_push(ft_comm* c, void* recvbuf, size_t count, int dtype
 /* low-latency push emulation: phase 1 = push (all ranks first), phase 2 = receive and reduce */
 int ft_allreduce_emulate_ll(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op, float scale,
                             int phase, uint64_t call, void* stream);
+/* A plan on tagged words: FT_ALGO_LL together with a shape runs that plan (tree, lonely layout, ring) with the
+ * low-latency protocol - every edge of a stage is a push of {data, tag} words into a receive slot of the destination, so
+ * a stage costs one one-way NVLink trip and no rendezvous (messages up to 256 KiB whose slots fit the receive area).
+ * FT_ALGO_AUTO with a shape takes this form up to ft_comm_set_ll_tree_max bytes (default 64 KiB), the staged kernel above.
+ * Emulation on one GPU: per stage, phase 1 (push) for every rank, then phase 2 (receive) for every rank. */
+int ft_allreduce_emulate_ll_tree(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op,
+                                 const int* widths, int nw, int lonely, int ring, float scale, int stage, int phase,
+                                 uint64_t call, void* stream);
+void ft_comm_set_ll_tree_max(ft_comm* c, size_t bytes);
 /* largest message AUTO sends through the low-latency push protocol (<= 256 KiB) */
 void ft_comm_set_ll_max(ft_comm* c, size_t bytes);
 /* CTAs per SM of the NVLS kernels (1..3, default 1) */

@@ -266,7 +266,9 @@ int MPI_Allreduce_FT_c(const void* sendbuf, void* recvbuf, size_t count, FT_Data
   const int nw = cfg.is_auto ? 0 : (int)shape.widths.size();
   const int* widths = cfg.is_auto ? nullptr : shape.widths.data();
   const int explicit_shape = !(cfg.is_auto || (!std::getenv("FT_TOPO") && !std::getenv("FT_LONELY")));
-  const int algo = explicit_shape ? FT_ALGO_STAGED : FT_ALGO_AUTO;
+  // AUTO either way: with a shape from the environment that plan runs (on tagged words while the message is small, through
+  // the staged kernel above that); without one the selection policy picks algorithm and shape
+  const int algo = FT_ALGO_AUTO;
   const bool dev_recv = is_device_pointer(recvbuf);
   const bool dev_send = in_place ? dev_recv : is_device_pointer(sendbuf);
   if (debug >= 2 && world > 1 && dev_recv && dev_send) {

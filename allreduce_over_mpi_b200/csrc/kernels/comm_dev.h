@@ -41,15 +41,25 @@ struct DevPull {
   uint8_t nsrc;
   uint8_t reduce;
   uint8_t src[FT_MAX_FANIN];
+  uint16_t slot;          // tagged-word protocol: receive slot of src[0] on this rank (src[k] lands in slot + k)
+};
+// The same edge seen from its source, for the tagged-word (push) form of a plan: in this stage the rank
+// sends its current copy of `block` into receive slot `slot` of rank `dst`.
+struct DevPush {
+  uint16_t block;
+  uint16_t slot;
+  uint8_t dst;
 };
 struct DevStage {
   uint32_t pull_begin, pull_end;
+  uint32_t push_begin, push_end;   // range in the rank's DevPush table
   uint64_t sync_mask;     // ranks met before this stage
   uint32_t last_rs;       // 1 when this is the final reduce-scatter stage (scale applies here)
   uint32_t is_ag;
 };
 struct DevPlan {
   uint32_t nstages, npulls;
+  uint32_t npushes, nslots;        // tagged-word form: pushes of this rank, receive slots it needs
   uint64_t end_sync_mask;
   DevStage stages[kMaxStages];
   // DevPull pulls[npulls] follow
@@ -97,6 +107,27 @@ struct LLArgs {
   uint32_t phase_mask;        // bit0 send, bit1 receive+reduce (both normally; split only for emulation)
   uint32_t user_vec_ok;
   uint32_t use_call_counter;  // 0: take the call number from emu_call (emulation)
+  uint64_t emu_call;
+  float scale;
+};
+
+// A plan run with the tagged-word protocol (small messages): every edge of a stage is a push of 8-byte words
+// {32 data bits, 32-bit tag} into a receive slot of the destination, so a tree level costs one one-way NVLink
+// trip and no rendezvous.  One thread owns 16-byte item i of every block from the first stage to the last.
+struct LLTreeArgs {
+  const DevPlan* plan;
+  const DevPull* pulls;
+  const DevPush* pushes;
+  uint64_t ll_off;            // receive area in every heap: [2 parities][world * kLLSrcStride]
+  const void* user_in;
+  void* user_out;
+  uint64_t count;
+  uint64_t block_elems;
+  uint32_t elem_size;
+  uint32_t stage_begin, stage_end;
+  uint32_t phase_mask;        // bit0 push, bit1 receive (both normally; split only for single-GPU emulation)
+  uint32_t user_vec_ok;
+  uint32_t use_call_counter;
   uint64_t emu_call;
   float scale;
 };

@@ -16,6 +16,8 @@
 //  * push_allreduce_kernel     flat two-shot in one pass: pull + sum + posted writes to every rank.
 //  * ll_allreduce_kernel       push protocol with the flag inside every 8-byte word, no
 //    rendezvous at all (smallest messages).
+//  * ll_tree_allreduce_kernel  any plan (tree, lonely, ring) with that protocol: one one-way NVLink
+//    trip per stage instead of a rendezvous.
 //
 // Work split: CTA c ("lane" c) of every rank owns the same byte sub-range of every
 // block, so all dependencies between ranks are lane-local and a rendezvous never needs
@@ -495,6 +497,94 @@ __global__ void __launch_bounds__(kThreads) ll_allreduce_kernel(const __grid_con
   else st_partial(dst, out, valid, es);
 }
 
+// ------------------------------------------------------------------------------- any plan, tagged words
+// The staged kernel pays one cross-GPU rendezvous per stage, which at a few KB is all there is to pay.
+// Here a plan (tree, lonely layout, ring) runs with the tagged-word protocol of ll_allreduce_kernel instead:
+// at the start of a stage a rank pushes its current copy of every block some peer will fold in or take over
+// into that peer's receive slot, then folds in (or takes over) what arrives in its own slots.  Nobody waits
+// for a rendezvous; a tree level costs one one-way NVLink trip.  Thread i owns 16-byte item i of EVERY block
+// from the first stage to the last and keeps the running values in the caller's output buffer, so stages need
+// no CTA barrier either.  Pushing before the own pulls of a stage sends the value a block had when the stage
+// began, which is what the pull plan means (check_hazards: nothing a peer reads in a stage is written in it).
+// Two receive areas alternate with the call parity as in ll_allreduce_kernel.
+template <int POL>
+__global__ void __launch_bounds__(256) ll_tree_allreduce_kernel(const __grid_constant__ CommDev c, const __grid_constant__ LLTreeArgs a) {
+  using P = typename PolById<POL>::type;
+  __shared__ unsigned long long call_slot;
+  unsigned long long call;
+  if (a.use_call_counter) call = begin_call(c, &call_slot);
+  else call = a.emu_call;
+  const uint32_t tag = (uint32_t)(call + 1) | 0x80000000u;
+  const uint32_t es = a.elem_size;
+  const uint64_t block_bytes = a.block_elems * es, total_bytes = a.count * es;
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i * 16 >= block_bytes) return;
+  const uint64_t area = a.ll_off + (call & 1) * (uint64_t)c.world * kLLSrcStride;
+  const uint64_t slot_wire = 2 * block_bytes;
+  unsigned char* out = (unsigned char*)a.user_out;
+  auto valid_of = [&](int b) -> uint32_t {   // bytes of my item of block b that hold data
+    const uint64_t off = (uint64_t)b * block_bytes + i * 16;
+    return off >= total_bytes ? 0u : (uint32_t)(total_bytes - off < 16 ? total_bytes - off : 16);
+  };
+  auto load_mine = [&](const unsigned char* base, int b, uint32_t valid) -> uint4 {
+    const unsigned char* p = base + (uint64_t)b * block_bytes + i * 16;
+    return (valid == 16 && a.user_vec_ok) ? ld_stream(p) : ld_partial(p, valid, es);
+  };
+  auto store_mine = [&](int b, uint32_t valid, uint4 v) {
+    unsigned char* p = out + (uint64_t)b * block_bytes + i * 16;
+    if (valid == 16 && a.user_vec_ok) st_vec(p, v);
+    else st_partial(p, v, valid, es);
+  };
+  if (a.stage_begin == 0 && (a.phase_mask & 1) && a.user_in != a.user_out)
+    for (int b = 0; b < c.world; ++b) {
+      const uint32_t valid = valid_of(b);
+      if (valid) store_mine(b, valid, load_mine((const unsigned char*)a.user_in, b, valid));
+    }
+  const unsigned long long t0 = globaltimer_ns();
+  for (uint32_t s = a.stage_begin; s < a.stage_end; ++s) {
+    const DevStage st = a.plan->stages[s];
+    if (a.phase_mask & 1)
+      for (uint32_t q = st.push_begin; q < st.push_end; ++q) {
+        const DevPush ps = a.pushes[q];
+        const uint32_t valid = valid_of(ps.block);
+        if (!valid) continue;
+        const uint4 v = load_mine(out, ps.block, valid);
+        unsigned char* dst = c.heap[ps.dst] + area + (uint64_t)ps.slot * slot_wire + i * 32;
+        st_ll(dst, v.x, v.y, tag);
+        st_ll(dst + 16, v.z, v.w, tag);
+      }
+    if (!(a.phase_mask & 2)) continue;
+    for (uint32_t q = st.pull_begin; q < st.pull_end; ++q) {
+      const DevPull pl = a.pulls[q];
+      const uint32_t valid = valid_of(pl.block);
+      if (!valid) continue;
+      typename P::Acc acc;
+      if (pl.reduce) P::init(acc, load_mine(out, pl.block, valid));
+      for (int k = 0; k < pl.nsrc; ++k) {
+        const unsigned char* src = c.heap[c.rank] + area + (uint64_t)(pl.slot + k) * slot_wire + i * 32;
+        uint4 lo, hi;
+        int spins = 0;
+        for (;;) {
+          lo = ld_ll(src);
+          hi = ld_ll(src + 16);
+          if (lo.y == tag && lo.w == tag && hi.y == tag && hi.w == tag) break;
+          if (++spins >= 64) {
+            spins = 0;
+            if (globaltimer_ns() - t0 > c.timeout_ns) {
+              report(c.status, FT_ERR_TIMEOUT, (int)s, pl.src[k], blockIdx.x);
+              return;
+            }
+          }
+        }
+        const uint4 v = make_uint4(lo.x, lo.z, hi.x, hi.z);
+        if (pl.reduce) P::add(acc, v);
+        else P::init(acc, v);
+      }
+      store_mine(pl.block, valid, (pl.reduce && st.last_rs && a.scale != 1.0f) ? P::fins(acc, a.scale) : P::fin(acc));
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------- NVLS
 // multimem.ld_reduce sums one 16-byte vector across every GPU bound to the multicast
 // object inside the switch; multimem.st writes one to all of them.  WEAK selects the
@@ -843,6 +933,18 @@ template <int POL> static cudaError_t launch_ll_t(const CommDev& c, const LLArgs
 cudaError_t launch_ll(int pol, const CommDev& c, const LLArgs& a, cudaStream_t st) {
   ft_count_launch(1);
 #define CALL(P) launch_ll_t<P>(c, a, st)
+  FT_POL_SWITCH(pol, CALL)
+#undef CALL
+}
+template <int POL> static cudaError_t launch_ll_tree_t(const CommDev& c, const LLTreeArgs& a, cudaStream_t st) {
+  const uint64_t items = (a.block_elems * a.elem_size + 15) / 16;
+  const int threads = items <= 32 ? 32 : (items <= 64 ? 64 : (items <= 128 ? 128 : 256));
+  ll_tree_allreduce_kernel<POL><<<(unsigned)((items + threads - 1) / threads), threads, 0, st>>>(c, a);
+  return cudaGetLastError();
+}
+cudaError_t launch_ll_tree(int pol, const CommDev& c, const LLTreeArgs& a, cudaStream_t st) {
+  ft_count_launch(1);
+#define CALL(P) launch_ll_tree_t<P>(c, a, st)
   FT_POL_SWITCH(pol, CALL)
 #undef CALL
 }

@@ -40,6 +40,7 @@ cudaError_t launch_nvls(int pol, const CommDev& c, const NvlsArgs& a, int lanes,
 cudaError_t launch_push(int pol, const CommDev& c, const NvlsArgs& a, int lanes, bool do_sync, cudaStream_t st);
 cudaError_t launch_ll(int pol, const CommDev& c, const LLArgs& a, cudaStream_t st);
 cudaError_t launch_hybrid(int pol, const CommDev& c, const NvlsArgs& a, int lanes, int nvls_lanes, uint64_t nvls_bytes, cudaStream_t st);
+cudaError_t launch_ll_tree(int pol, const CommDev& c, const LLTreeArgs& a, cudaStream_t st);
 cudaError_t launch_wait_probe(const CommDev& c, int peer, unsigned long long timeout_ns, cudaStream_t st);
 }  // namespace ftk
 
@@ -110,7 +111,9 @@ struct McOwner {
 struct DevPlanEntry {
   ftk::DevPlan* plan = nullptr;   // device
   ftk::DevPull* pulls = nullptr;  // device
+  ftk::DevPush* pushes = nullptr; // device: the plan's edges seen from their source (tagged-word form)
   int nstages = 0;
+  uint32_t nslots = 0;            // receive slots this rank needs in the tagged-word form
 };
 
 }  // namespace
@@ -161,6 +164,7 @@ struct ft_comm {
     bool used[kDepth] = {};
   } hp;
   size_t host_chunk_bytes = 32u << 20;
+  size_t ll_tree_max = 64u << 10;   // AUTO with an explicit shape: tagged-word form of the plan up to this size
   int forced_algo = FT_ALGO_AUTO;   // FT_ALGO=<name> in the environment: what AUTO resolves to, whatever the size
   ft_policy* policy = nullptr;   // algorithm / shape per message size (calibration table + cost model)
   ftk::CommDev dev{};
@@ -238,6 +242,10 @@ int get_plan(ft_comm* c, const ft::Shape& shape, DevPlanEntry** out) {
   FT_CUDA(c, cudaMalloc(&e.pulls, sizeof(ftk::DevPull) * (pulls.size() + 1)));
   FT_CUDA(c, cudaMemcpy(e.plan, &hp, sizeof hp, cudaMemcpyHostToDevice));
   if (!pulls.empty()) FT_CUDA(c, cudaMemcpy(e.pulls, pulls.data(), sizeof(ftk::DevPull) * pulls.size(), cudaMemcpyHostToDevice));
+  FT_CUDA(c, cudaMalloc(&e.pushes, sizeof(ftk::DevPush) * (hd.pushes.size() + 1)));
+  if (!hd.pushes.empty())
+    FT_CUDA(c, cudaMemcpy(e.pushes, hd.pushes.data(), sizeof(ftk::DevPush) * hd.pushes.size(), cudaMemcpyHostToDevice));
+  e.nslots = hp.nslots;
   *out = &c->plans.emplace(key, e).first->second;
   return FT_OK;
 }
@@ -378,6 +386,42 @@ int launch_push_call(ft_comm* c, const Prepared& pr, const void* sendbuf, void* 
   return FT_OK;
 }
 
+// A plan with the tagged-word protocol.  Fits when the message is at most kLLMaxBytes and this rank's receive slots
+// (two wire bytes per payload byte, one block each) fit one parity of the low-latency area.
+bool ll_tree_fits(ft_comm* c, const Prepared& pr, size_t count, uint32_t nslots) {
+  const uint64_t block_bytes = pick_block_elems(count, c->world, pr.es) * pr.es;
+  return pr.bytes <= ftk::kLLMaxBytes && (uint64_t)nslots * 2 * block_bytes <= (uint64_t)c->world * ftk::kLLSrcStride;
+}
+int launch_ll_tree_call(ft_comm* c, const Prepared& pr, const void* sendbuf, void* recvbuf, size_t count, const ft::Shape& shape,
+                        float scale, int stage_begin, int stage_end, uint32_t phase_mask, bool use_counter, uint64_t emu_call,
+                        cudaStream_t st) {
+  DevPlanEntry* pe = nullptr;
+  int rc = get_plan(c, shape, &pe);
+  if (rc != FT_OK) return rc;
+  if (!ll_tree_fits(c, pr, count, pe->nslots))
+    return fail(c, FT_ERR_TOO_LARGE, "message too large for the tagged-word form of plan " + shape.str());
+  ftk::LLTreeArgs a{};
+  a.plan = pe->plan;
+  a.pulls = pe->pulls;
+  a.pushes = pe->pushes;
+  a.ll_off = c->ll_off;
+  a.user_in = sendbuf ? sendbuf : recvbuf;
+  a.user_out = recvbuf;
+  a.count = count;
+  a.block_elems = pick_block_elems(count, c->world, pr.es);
+  a.elem_size = pr.es;
+  a.stage_begin = stage_begin < 0 ? 0 : (uint32_t)stage_begin;
+  a.stage_end = stage_end < 0 ? (uint32_t)pe->nstages : (uint32_t)stage_end;
+  a.phase_mask = phase_mask;
+  a.user_vec_ok = (((uintptr_t)a.user_in | (uintptr_t)a.user_out) & 15) == 0;
+  a.use_call_counter = use_counter ? 1 : 0;
+  a.emu_call = emu_call;
+  a.scale = scale;
+  cudaError_t e = ftk::launch_ll_tree(pr.pol, c->dev, a, st);
+  if (e != cudaSuccess) return fail(c, FT_ERR_CUDA, std::string("tagged-word plan launch: ") + cudaGetErrorString(e));
+  return FT_OK;
+}
+
 int launch_ll_call(ft_comm* c, const Prepared& pr, const void* sendbuf, void* recvbuf, size_t count, float scale,
                    uint32_t phase_mask, bool use_counter, uint64_t emu_call, cudaStream_t st) {
   if (pr.bytes > ftk::kLLMaxBytes) return fail(c, FT_ERR_TOO_LARGE, "low-latency all-reduce is limited to 256 KiB");
@@ -483,7 +527,7 @@ int ft_comm_destroy(ft_comm* c) {
   } else if (c->ipc_ptr) {
     cudaFree(c->ipc_ptr);
   }
-  for (auto& kv : c->plans) { cudaFree(kv.second.plan); cudaFree(kv.second.pulls); }
+  for (auto& kv : c->plans) { cudaFree(kv.second.plan); cudaFree(kv.second.pulls); cudaFree(kv.second.pushes); }
   if (c->hp.in) {
     cudaStreamDestroy(c->hp.in); cudaStreamDestroy(c->hp.run); cudaStreamDestroy(c->hp.out);
     cudaEventDestroy(c->hp.start);
@@ -783,6 +827,7 @@ int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, i
     return FT_OK;
   }
   ft::Shape auto_shape;
+  const bool was_auto = algo == FT_ALGO_AUTO;
   if (algo == FT_ALGO_AUTO) {
     if (nw > 0 || ring) {
       algo = FT_ALGO_STAGED;
@@ -817,6 +862,20 @@ int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, i
       if (rc != FT_OK) return rc;
     }
     return FT_OK;
+  }
+  // A shape together with the low-latency protocol: the plan runs on tagged words (one NVLink trip per stage).  An
+  // explicit shape under AUTO (FT_TOPO) takes that form too while the message is small enough for it to pay.
+  const bool shaped = nw > 0 || ring;
+  if (shaped && (algo == FT_ALGO_LL || (was_auto && algo == FT_ALGO_STAGED && pr.bytes <= c->ll_tree_max))) {
+    const ft::Shape shape = make_shape(c->world, widths, nw, lonely, ring);
+    DevPlanEntry* pe = nullptr;
+    rc = get_plan(c, shape, &pe);
+    if (rc != FT_OK) return rc;
+    if (algo == FT_ALGO_LL || ll_tree_fits(c, pr, count, pe->nslots)) {
+      c->stat_calls[FT_ALGO_LL]++;
+      c->stat_bytes[FT_ALGO_LL] += pr.bytes;
+      return launch_ll_tree_call(c, pr, sendbuf, recvbuf, count, shape, scale, -1, -1, 3, true, 0, st);
+    }
   }
   if (algo >= 0 && algo < 7) { c->stat_calls[algo]++; c->stat_bytes[algo] += pr.bytes; }
   if (algo == FT_ALGO_LL) return launch_ll_call(c, pr, sendbuf, recvbuf, count, scale, 3, true, 0, st);
@@ -1041,6 +1100,17 @@ int ft_comm_set_nvls_config(ft_comm* c, int threads, int unroll, int weak, int m
   return FT_OK;
 }
 void ft_comm_set_phase_nvls(ft_comm* c, int on) { if (c) c->phase_nvls = on != 0; }
+int ft_allreduce_emulate_ll_tree(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op,
+                                 const int* widths, int nw, int lonely, int ring, float scale, int stage, int phase,
+                                 uint64_t call, void* stream) {
+  Prepared pr;
+  int rc = prepare(c, sendbuf, recvbuf, count, dtype, op, &pr);
+  if (rc != FT_OK) return rc;
+  if (count == 0 || c->world == 1) return FT_OK;
+  return launch_ll_tree_call(c, pr, sendbuf, recvbuf, count, make_shape(c->world, widths, nw, lonely, ring), scale, stage, stage + 1,
+                             (uint32_t)phase & 3u, false, call, (cudaStream_t)stream);
+}
+void ft_comm_set_ll_tree_max(ft_comm* c, size_t bytes) { if (c) c->ll_tree_max = bytes < ftk::kLLMaxBytes ? bytes : ftk::kLLMaxBytes; }
 void ft_comm_set_ll_max(ft_comm* c, size_t bytes) { if (c) c->ll_max = bytes < ftk::kLLMaxBytes ? bytes : ftk::kLLMaxBytes; }
 
 int ft_plan_num_stages_for(ft_comm* c, const int* widths, int nw, int lonely, int ring) {

@@ -23,7 +23,20 @@ namespace ft {
 struct HostDevPlan {
   ftk::DevPlan plan{};
   std::vector<ftk::DevPull> pulls;
+  std::vector<ftk::DevPush> pushes;
 };
+
+// The order in which `rank` works through its pulls of stage `s` on the device.
+inline std::vector<Pull> device_order(const Plan& p, int rank, int s) {
+  std::vector<Pull> ordered = p.stages[rank][s].pulls;
+  // gathers start at the next rank up and wrap around, so that at any moment the ranks of a
+  // stage read from different peers instead of all queueing on the lowest-numbered one
+  if (std::none_of(ordered.begin(), ordered.end(), [](const Pull& x) { return x.reduce; }))
+    std::stable_sort(ordered.begin(), ordered.end(), [&](const Pull& x, const Pull& y) {
+      return (x.srcs[0] - rank + p.world) % p.world < (y.srcs[0] - rank + p.world) % p.world;
+    });
+  return ordered;
+}
 
 inline HostDevPlan build_dev_plan(const Plan& p, int rank) {
   HostDevPlan out;
@@ -38,13 +51,7 @@ inline HostDevPlan build_dev_plan(const Plan& p, int rank) {
   for (int s = 0; s < p.num_stages && s < ftk::kMaxStages; ++s) {
     ftk::DevStage& ds = hp.stages[s];
     ds.pull_begin = (uint32_t)out.pulls.size();
-    std::vector<Pull> ordered = p.stages[rank][s].pulls;
-    // gathers start at the next rank up and wrap around, so that at any moment the ranks of a
-    // stage read from different peers instead of all queueing on the lowest-numbered one
-    if (std::none_of(ordered.begin(), ordered.end(), [](const Pull& x) { return x.reduce; }))
-      std::stable_sort(ordered.begin(), ordered.end(), [&](const Pull& x, const Pull& y) {
-        return (x.srcs[0] - rank + p.world) % p.world < (y.srcs[0] - rank + p.world) % p.world;
-      });
+    const std::vector<Pull> ordered = device_order(p, rank, s);
     for (const Pull& pl : ordered) {
       ftk::DevPull dp{};
       dp.block = (uint16_t)pl.block;
@@ -60,6 +67,32 @@ inline HostDevPlan build_dev_plan(const Plan& p, int rank) {
   }
   hp.npulls = (uint32_t)out.pulls.size();
   hp.end_sync_mask = mask_of(p.sync[p.num_stages][rank]);
+  // Tagged-word (push) form.  Receive slots of a rank are numbered in the order it consumes them: stage by
+  // stage, pull by pull, source by source; a slot is written by exactly one rank in exactly one stage.
+  // This rank's pushes are then every pull of another rank that names it as a source.
+  std::vector<uint32_t> next_slot(p.world, 0);
+  uint32_t my_pull = 0;
+  for (int s = 0; s < p.num_stages && s < ftk::kMaxStages; ++s) {
+    hp.stages[s].push_begin = (uint32_t)out.pushes.size();
+    for (int d = 0; d < p.world; ++d) {
+      for (const Pull& pl : device_order(p, d, s)) {
+        if (d == rank && my_pull < out.pulls.size()) out.pulls[my_pull++].slot = (uint16_t)next_slot[d];
+        for (size_t k = 0; k < pl.srcs.size(); ++k) {
+          if (pl.srcs[k] == rank && d != rank) {
+            ftk::DevPush ps{};
+            ps.block = (uint16_t)pl.block;
+            ps.slot = (uint16_t)(next_slot[d] + k);
+            ps.dst = (uint8_t)d;
+            out.pushes.push_back(ps);
+          }
+        }
+        next_slot[d] += (uint32_t)pl.srcs.size();
+      }
+    }
+    hp.stages[s].push_end = (uint32_t)out.pushes.size();
+  }
+  hp.npushes = (uint32_t)out.pushes.size();
+  hp.nslots = next_slot[rank];
   return out;
 }
 
@@ -101,6 +134,25 @@ inline std::string check_dev_plan(const HostDevPlan& d, int world, int rank) {
     }
   }
   if (next != hp.npulls) return "pulls left over after the last stage";
+  // tagged-word form: pushes in stage order, destinations in the world and never the rank itself, every receive
+  // slot of this rank claimed by exactly one (pull, source)
+  if (hp.npushes != d.pushes.size()) return "push count does not match the table";
+  uint32_t next_push = 0, slots = 0;
+  for (uint32_t s = 0; s < hp.nstages; ++s) {
+    const ftk::DevStage& st = hp.stages[s];
+    if (st.push_begin != next_push || st.push_end < st.push_begin || st.push_end > hp.npushes) return bad(s, "push range out of order");
+    next_push = st.push_end;
+    for (uint32_t q = st.push_begin; q < st.push_end; ++q) {
+      if (d.pushes[q].dst >= world || d.pushes[q].dst == rank) return bad(s, "push to a rank outside the world or to itself");
+      if (d.pushes[q].block >= world) return bad(s, "pushed block id outside the buffer");
+    }
+    for (uint32_t q = st.pull_begin; q < st.pull_end; ++q) {
+      if (d.pulls[q].slot != slots) return bad(s, "receive slots are not consecutive");
+      slots += d.pulls[q].nsrc;
+    }
+  }
+  if (next_push != hp.npushes) return "pushes left over after the last stage";
+  if (slots != hp.nslots) return "receive slot count does not match the pulls";
   if (hp.nstages && last_rs_seen != 1) return "no single final reduce-scatter stage";
   return "";
 }

@@ -640,7 +640,8 @@ class LocalWorld:
         if not self.emulated:
             for r, c in enumerate(self.ranks):
                 with torch.cuda.device(c.device):
-                    c.all_reduce(tensors[r], op=op, shape=shp if algo == "staged" else None, algo=algo, scale=scale, out=outs[r])
+                    c.all_reduce(tensors[r], op=op, shape=shp if algo == "staged" or (algo == "ll" and shape is not None) else None,
+                                 algo=algo, scale=scale, out=outs[r])
             return outs
         L = lib()
         dt = ft_dtype(tensors[0].dtype)
@@ -659,6 +660,20 @@ class LocalWorld:
                     outs[r].copy_(tensors[r])
             for r, c in enumerate(self.ranks):
                 c._check(L.ft_allreduce_emulate_push(c._h, outs[r].data_ptr(), outs[r].numel(), dt, OPS[op], float(scale), st))
+            return outs
+        if algo == "ll" and shape is not None:
+            # a plan on tagged words: per stage every rank pushes, then every rank receives
+            nstages = planner.plan_num_stages(world, shp)
+            if nstages < 0:
+                raise FlexTreeError(4, f"invalid FT_TOPO {shp} ({planner.validate_shape(world, shp)})")
+            arr, nw, lonely, ring = shp.c_args()
+            for s in range(nstages):
+                for phase in (1, 2):
+                    for r, c in enumerate(self.ranks):
+                        src, dst = ptrs(r)
+                        c._check(L.ft_allreduce_emulate_ll_tree(c._h, src, dst, tensors[r].numel(), dt, OPS[op], arr, nw, lonely, ring,
+                                                                float(scale), s, phase, self._emu_call, st))
+            self._emu_call += 1
             return outs
         if algo == "ll":
             for phase in (1, 2):

@@ -274,6 +274,14 @@ def main():
                 fill(loc, rank, it)
                 comm.all_reduce(loc, shape=shape, algo="staged")
                 verify(loc, count, dtype, it, f"slots {shape} {dtype} {count}")
+            if count * 4 <= (64 << 10):
+                for shape in shapes:     # the same plans on tagged words (no rendezvous), two calls each: both receive areas
+                    for rep in range(2):
+                        it += 1
+                        loc = torch.empty(count, dtype=dtype, device=dev)
+                        fill(loc, rank, it)
+                        comm.all_reduce(loc, shape=shape, algo="ll")
+                        verify(loc, count, dtype, it, f"tagged words {shape} {dtype} {count}")
             if count * 4 <= comm.staging_bytes:
                 it += 1
                 loc = torch.empty(count, dtype=dtype, device=dev)

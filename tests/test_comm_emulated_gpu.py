@@ -217,3 +217,36 @@ def test_world_of_one_and_bounded_wait():
     c.all_reduce(y)
     torch.cuda.synchronize()
     w.close()
+
+
+@pytest.mark.parametrize("text", SHAPES)
+def test_plans_on_tagged_words(text):
+    """Every shape with the low-latency protocol (ll_tree_allreduce_kernel): each edge of a stage is a push of tagged
+    8-byte words, no rendezvous.  Same sums as the staged kernel bit for bit (same plan, same summation order), out of
+    place and in place, odd lengths, several calls in a row (the two receive areas alternate), averaging fused."""
+    shape = Shape.parse(text)
+    n = shape.world
+    w = LocalWorld(n, heap_bytes=1 << 20, staging_bytes=1 << 20)
+    for dtype in (torch.float32, torch.bfloat16):
+        for count in (1, 35, 4099, 30_001):
+            host = inputs(n, count, dtype, seed=5)
+            want = torch.stack(host).double().sum(0)
+            ref = [h.to(DEV) for h in host]
+            w.all_reduce(ref, shape=shape, algo="staged")
+            src = [h.to(DEV) for h in host]
+            out = [torch.full_like(s, float("nan")) for s in src]
+            w.all_reduce(src, shape=shape, algo="ll", outs=out)      # out of place
+            inp = [h.to(DEV) for h in host]
+            w.all_reduce(inp, shape=shape, algo="ll")                # in place, next call parity
+            torch.cuda.synchronize()
+            for r in range(n):
+                assert torch.allclose(out[r].double().cpu(), want, atol=tol(dtype) * n), (text, dtype, count, r)
+                assert torch.equal(out[r], ref[r]) and torch.equal(inp[r], ref[r]), (text, dtype, count, r)
+                assert torch.equal(src[r].cpu(), host[r])            # the input of an out-of-place call is untouched
+    avg = [torch.full((1000,), float(r + 1), device=DEV) for r in range(n)]
+    w.all_reduce(avg, shape=shape, algo="ll", op="avg")
+    torch.cuda.synchronize()
+    assert all(torch.allclose(a, torch.full_like(a, (n + 1) / 2), atol=1e-6) for a in avg)
+    for c in w.ranks:
+        assert c.status()["code"] == 0
+    w.close()

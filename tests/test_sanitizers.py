@@ -28,3 +28,17 @@ def test_asan_ubsan(tmp_path):
 
 def test_tsan_thread_world(tmp_path):
     build_and_run(tmp_path, ["-fsanitize=thread"], ["threads"])
+
+
+def test_range_predicate_of_the_bounds_checked_build():
+    """The test the FT_BOUNDS build of the kernels applies to every run of heap bytes before touching it, evaluated
+    on the host: its failing branch is exercised here and never on a GPU."""
+    from allreduce_over_mpi_b200._lib import lib
+    ok = lib().ft_bounds_check_host
+    heap = 1 << 20
+    assert ok(heap, 0, 8, 0, heap) == 1 and ok(heap, 7, 8, heap - 16, 16) == 1 and ok(heap, 3, 8, heap, 0) == 1
+    assert ok(heap, 0, 8, heap - 16, 32) == 0          # runs past the end
+    assert ok(heap, 0, 8, heap + 1, 0) == 0            # starts past the end
+    assert ok(heap, 8, 8, 0, 16) == 0 and ok(heap, -1, 8, 0, 16) == 0      # no such rank
+    assert ok(heap, 0, 8, (1 << 64) - 8, 16) == 0      # offset + length would wrap around
+    assert ok(0, 0, 1, 0, 1) == 0

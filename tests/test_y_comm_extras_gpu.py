@@ -197,3 +197,49 @@ def test_auto_goes_through_the_native_policy_and_counts_the_algorithm():
     torch.cuda.synchronize()
     assert bool((out == 1).all())
     w.close()
+
+
+def test_bounds_checked_build_runs_correct_plans_without_a_report():
+    """The debugging build (-DFT_BOUNDS, lib/libflextree_bounds.so, FT_LIB=bounds): emulated worlds over tree, lonely,
+    ring, one-shot, low-latency and reduce + push paths give the right sums and no kernel reports a range outside
+    the heap.  Runs in a child process, since one process loads one build of the library."""
+    import os
+    import subprocess
+    import sys
+    from allreduce_over_mpi_b200.build import BOUNDS_LIB, NVCC
+    if not BOUNDS_LIB.exists() and not os.path.exists(NVCC):
+        pytest.skip("no bounds-checked build and no nvcc to make one")
+    code = r"""
+import torch
+from allreduce_over_mpi_b200._lib import lib
+from allreduce_over_mpi_b200.parallel.comm import LocalWorld
+assert lib().ft_bounds_build() == 1
+for world, shape in ((4, "2*2"), (5, "2*2+1"), (6, "ring6"), (8, "2*4"), (3, "3")):
+    w = LocalWorld(world, heap_bytes=4 << 20, staging_bytes=1 << 20)
+    for algo, heap in (("staged", True), ("staged", False), ("oneshot", False), ("ll", False), ("push", True)):
+        for count in (5, 4099, 200_003):
+            if algo == "ll" and count * 4 > (256 << 10):
+                continue
+            xs = []
+            for r in range(world):
+                if heap:
+                    w.ranks[r].free_all()
+                    t = w.ranks[r].alloc(count, torch.float32)
+                else:
+                    t = torch.empty(count, device="cuda:0")
+                t.fill_(float(r + 1))
+                xs.append(t)
+            w.all_reduce(xs, shape=shape if algo == "staged" else None, algo=algo)
+            torch.cuda.synchronize()
+            want = world * (world + 1) / 2
+            assert all(bool((x == want).all()) for x in xs), (world, shape, algo, count)
+            for c in w.ranks:
+                s = c.status()
+                assert s["code"] == 0, (world, shape, algo, count, s)
+    w.close()
+print("BOUNDS-OK")
+"""
+    env = dict(os.environ, FT_LIB="bounds")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, cwd=root, timeout=900)
+    assert r.returncode == 0 and "BOUNDS-OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]

@@ -107,7 +107,6 @@ def test_buffers_off_the_16_byte_grid_take_the_element_wise_path():
         assert call(fn, a, name) == 0, lib.ft_noalloc_last_error()
         world.all_reduce(b, algo="oneshot")
         torch.cuda.synchronize()
-        want = torch.stack([t.double() for t in b]).sum(0) / n    # b now holds the sums on every rank
         for r in range(n):
             assert torch.allclose(a[r].double(), b[r].double(), atol=tol, rtol=0), (name, r)
             assert whole[r][0].item() == heads[r]                 # the element before the view is untouched
