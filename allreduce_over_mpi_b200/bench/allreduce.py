@@ -110,6 +110,8 @@ def sweep(a, comm: FlexTreeComm, rank: int, world: int) -> list[dict]:
             impls = []
             for shape in a.shapes:
                 for algo in a.algos:
+                    if algo == "none":     # only the comparison arm (--nccl)
+                        continue
                     if algo == "lltree":   # the plan of every listed shape on tagged words (small messages)
                         if shape != "auto" and nbytes <= (64 << 10) and not validate_shape(world, Shape.parse(shape)):
                             impls.append((shape, algo))

@@ -102,6 +102,8 @@ def main(argv=None):
     ap.add_argument("--bucket-mb", type=int, default=25)
     ap.add_argument("--lanes", type=int, default=0, help="cap on CTAs of the all-reduce kernel while it overlaps backward")
     ap.add_argument("--tiny", action="store_true")
+    ap.add_argument("--repeats", type=int, default=1, help="run the whole list of implementations this many times")
+    ap.add_argument("--clock-gpu", type=int, default=0, help="physical GPU index the clock sampler watches (0: this rank's device)")
     ap.add_argument("--out", default=None)
     a = ap.parse_args(argv)
     rank, world, local = init_dist()
@@ -110,14 +112,20 @@ def main(argv=None):
     if a.lanes:
         comm.set_max_lanes(a.lanes)
     rows = []
-    for impl in a.impl:
-        row = run(impl, a, rank, world, dev, comm)
-        rows.append(row)
-        if rank == 0:
-            print(json.dumps(row), flush=True)
-            if a.out:
-                with open(a.out, "a") as f:
-                    f.write(json.dumps(row) + "\n")
+    from ..utils import ClockSampler
+    for rep in range(a.repeats):
+        for impl in a.impl:
+            sampler = ClockSampler(gpu_index=a.clock_gpu or torch.cuda.current_device()).start() if rank == 0 else None
+            row = run(impl, a, rank, world, dev, comm)
+            row["repeat"] = rep
+            if sampler is not None:
+                row["clocks"] = sampler.stop()   # SM clock under load and throttle reasons during this run (read-only sampling)
+            rows.append(row)
+            if rank == 0:
+                print(json.dumps(row), flush=True)
+                if a.out:
+                    with open(a.out, "a") as f:
+                        f.write(json.dumps(row) + "\n")
     comm.close()
     if world > 1:
         dist.barrier()

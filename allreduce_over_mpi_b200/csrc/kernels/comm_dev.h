@@ -142,8 +142,10 @@ struct NvlsArgs {
 };
 
 // Launch shape of the NVLS kernels (tuning knobs of the communicator).
-// Measured on 8 and 4 B200 (64 MiB - 1 GiB): 256 threads x 4 vectors on 32-64 CTAs give 800-840 GB/s bus bandwidth at
-// 8 GPUs where 512 threads on all 148 SMs give 725-740: the switch serves a few hundred KB in flight per GPU best.
+// Measured on 8 B200 (64 MiB - 1 GiB) once every lane's slice starts on a 1 KiB boundary: the bus bandwidth sits on a
+// plateau (683 / 806 / 839 GB/s at 64 MiB / 256 MiB / 1 GiB) for anything between 16 and 64 CTAs of 128-512 threads with
+// 2-4 vectors in flight; 512 threads x 4 vectors on all 148 SMs fall off it (585 / 767 / 744).  The small launch also
+// leaves three quarters of the SMs to whatever else is running (a backward pass).
 struct NvlsConfig {
   int threads = 256;          // per CTA
   int unroll = 4;             // 16-byte vectors in flight per thread

@@ -150,7 +150,8 @@ struct ft_comm {
   size_t ll_max = 8 << 10;   // AUTO uses the low-latency protocol up to this size
   int nvls_ctas_per_sm = 1;   // measured on 8 GPUs: 2 or 3 CTAs per SM lose 5-15 % at 256 MiB and above
   ftk::NvlsConfig nvls_cfg;   // threads per CTA, vectors in flight per thread, instruction form
-  int nvls_max_lanes = 64;    // 0: as many lanes as SMs (times nvls_ctas_per_sm)
+  int nvls_max_lanes = 32;    // 0: as many lanes as SMs (times nvls_ctas_per_sm).  8 GPUs, 64 MiB / 256 MiB / 1 GiB: 32 CTAs of
+                              // 256 threads reach 683 / 806 / 839 GB/s, all 148 SMs 632 / 786 / 834, 16 CTAs 682 / 797 / 828
   size_t nvls_stripe = 0;
   bool phase_nvls = true;     // ft_reduce_scatter / ft_all_gather may use the multimem kernels (flat shape, eligible tensor)     // all-reduce: 0 = rank r owns block r, else round-robin stripes of this many bytes
   std::map<std::string, DevPlanEntry> plans;
@@ -898,7 +899,8 @@ int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, i
     if (algo == FT_ALGO_HYBRID && lanes >= 8) {
       // share of each block that goes through the switch, and the same share of the lanes
       const double f = c->hybrid_fraction;
-      uint64_t nvls_bytes = (uint64_t)(a.block_elems * pr.es * f) / 16 * 16;
+      uint64_t nvls_bytes = (uint64_t)(a.block_elems * pr.es * f);
+      nvls_bytes = nvls_bytes >= (64u << 10) ? nvls_bytes / 1024 * 1024 : nvls_bytes / 16 * 16;   // both parts start on a warp-request boundary
       int nvls_lanes = (int)(lanes * c->hybrid_lane_fraction + 0.5);
       if (nvls_lanes < 1) nvls_lanes = 1;
       if (nvls_lanes > lanes - 1) nvls_lanes = lanes - 1;
