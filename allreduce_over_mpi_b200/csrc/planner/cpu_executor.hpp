@@ -24,6 +24,7 @@
 #include <thread>
 #include <vector>
 
+#include "../runtime/dev_plan.hpp"
 #include "cpu_reduce.hpp"
 #include "plan.hpp"
 
@@ -365,6 +366,78 @@ inline RankStatus cpu_allreduce_ll(CpuWorld& w, int rank, ft_op op, ft_dtype dt,
   std::vector<uint32_t> out(words);
   st.code = reduce_nway_cpu_dispatch(op, dt, src, out.data(), w.n, count, 1);
   std::memcpy(recvbuf, out.data(), bytes);
+  return st;
+}
+
+// A plan on tagged words: the host twin of ll_tree_allreduce_kernel.  At the start of a stage a rank pushes its current
+// copy of every block some peer will fold in or take over into that peer's receive slot (slots numbered by
+// build_dev_plan, the table the device uses), then folds in / takes over what arrives in its own slots.  No rendezvous;
+// the two receive areas alternate with the call parity and are shared with cpu_allreduce_ll.
+inline RankStatus cpu_allreduce_ll_tree(CpuWorld& w, int rank, const Plan& p, ft_op op, ft_dtype dt, const void* sendbuf,
+                                        void* recvbuf, uint64_t count) {
+  RankStatus st;
+  if (!ft_op_supported(op, dt)) { st.code = FT_ERR_UNSUPPORTED_TYPE; return st; }
+  if (!p.ok() || p.world != w.n) { st.code = FT_ERR_INVALID_TOPO; return st; }
+  const size_t es = ft_dtype_size(dt), bytes = count * es;
+  if (sendbuf && sendbuf != recvbuf) std::memcpy(recvbuf, sendbuf, bytes);
+  if (w.n == 1 || count == 0) return st;
+  const HostDevPlan hd = build_dev_plan(p, rank);
+  const Blocks g(count, w.n);
+  const size_t block_words = (g.block_elems * es + 3) / 4;
+  if ((size_t)hd.plan.nslots * block_words > (size_t)w.n * CpuWorld::kLLWords) { st.code = FT_ERR_TOO_LARGE; return st; }
+  w.ensure_twins();
+  const uint64_t call = w.calls[rank]++;
+  const uint32_t tag = (uint32_t)(call + 1);
+  const size_t parity = call & 1;
+  auto slot_of = [&](int dst, uint32_t slot) { return w.ll.get() + ((size_t)dst * 2 + parity) * w.n * CpuWorld::kLLWords + (size_t)slot * block_words; };
+  char* out = (char*)recvbuf;
+  const auto t0 = std::chrono::steady_clock::now();
+  std::vector<uint32_t> tmp(block_words);
+  for (uint32_t s = 0; s < hd.plan.nstages; ++s) {
+    const ftk::DevStage& ds = hd.plan.stages[s];
+    for (uint32_t q = ds.push_begin; q < ds.push_end; ++q) {
+      const ftk::DevPush& ps = hd.pushes[q];
+      const size_t len = g.length(ps.block) * es, words = (len + 3) / 4;
+      if (!len) continue;
+      std::fill(tmp.begin(), tmp.end(), 0u);
+      std::memcpy(tmp.data(), out + g.offset(ps.block) * es, len);
+      std::atomic<uint64_t>* a = slot_of(ps.dst, ps.slot);
+      for (size_t i = 0; i < words; ++i) a[i].store(((uint64_t)tag << 32) | tmp[i], std::memory_order_release);
+    }
+    if (w.mid_call_hook) w.mid_call_hook(rank);
+    for (uint32_t q = ds.pull_begin; q < ds.pull_end; ++q) {
+      const ftk::DevPull& pl = hd.pulls[q];
+      const size_t elems = g.length(pl.block), len = elems * es, words = (len + 3) / 4;
+      if (!len) continue;
+      std::vector<std::vector<uint32_t>> got(pl.nsrc, std::vector<uint32_t>(words));
+      for (int k = 0; k < pl.nsrc; ++k) {
+        std::atomic<uint64_t>* a = slot_of(rank, pl.slot + k);
+        for (size_t i = 0; i < words; ++i)
+          for (;;) {
+            const uint64_t v = a[i].load(std::memory_order_acquire);
+            if ((uint32_t)(v >> 32) == tag) { got[k][i] = (uint32_t)v; break; }
+            if (std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() > w.timeout_s) {
+              st = {FT_ERR_TIMEOUT, (int)s, pl.src[k]};
+              return st;
+            }
+            std::this_thread::yield();
+          }
+      }
+      char* mine = out + g.offset(pl.block) * es;
+      if (pl.reduce) {
+        std::vector<uint32_t> own(words, 0), res(words, 0);
+        std::memcpy(own.data(), mine, len);
+        const void* src[FT_MAX_FANIN + 1];
+        src[0] = own.data();
+        for (int k = 0; k < pl.nsrc; ++k) src[k + 1] = got[k].data();
+        st.code = reduce_nway_cpu_dispatch(op, dt, src, res.data(), pl.nsrc + 1, elems, 1);
+        if (st.code != FT_OK) return st;
+        std::memcpy(mine, res.data(), len);
+      } else {
+        std::memcpy(mine, got[0].data(), len);
+      }
+    }
+  }
   return st;
 }
 

@@ -347,6 +347,13 @@ static void thread_world_small_message_twins() {
             case 2: case 3: case 5: st = ft::cpu_allreduce_oneshot(w, r, FT_SUM, FT_F32, nullptr, buf.data(), count); break;
             case 4: st = ft::cpu_allreduce(w, r, round % 16 == 4 ? flat : ring, FT_SUM, FT_F32, nullptr, buf.data(), count); break;
             case 9: st = ft::cpu_allreduce_push(w, r, FT_SUM, FT_F32, buf.data(), count); break;
+            case 8:   // a plan on tagged words, twice in a row (both receive areas), then the flat tagged-word call on the same areas
+              st = ft::cpu_allreduce_ll_tree(w, r, round % 20 == 8 ? tree : ring, FT_SUM, FT_F32, nullptr, buf.data(), count);
+              if (st.code == FT_OK) {
+                for (uint64_t i = 0; i < count; ++i) buf[i] = (float)(r + 1) + (float)(i % 7) + (float)round;
+                st = ft::cpu_allreduce_ll_tree(w, r, flat, FT_SUM, FT_F32, nullptr, buf.data(), count);
+              }
+              break;
             case 7:   // through the slots, twice in a row, with different shapes (no closing rendezvous in this mode)
               st = ft::cpu_allreduce_slots(w, r, round % 16 == 7 ? tree : ring, FT_SUM, FT_F32, nullptr, buf.data(), count);
               if (st.code == FT_OK) {
