@@ -186,7 +186,8 @@ class Policy {
     // the table speaks only for the range of sizes that was measured (one octave of slack)
     if (best && lo / 2 <= bytes && bytes <= hi * 2) {
       c.algo = best->algo;
-      c.shape = best->algo == "staged" ? best->shape : Shape::flat(world_);
+      // "staged" runs the row's plan; "ll" with a shape that is not flat runs that plan on tagged words
+      c.shape = (best->algo == "staged" || best->algo == "ll") ? best->shape : Shape::flat(world_);
       c.hybrid_bytes = best->hybrid_bytes;
       c.hybrid_lanes = best->hybrid_lanes;
       c.from_table = true;

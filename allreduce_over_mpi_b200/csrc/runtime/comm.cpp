@@ -829,6 +829,7 @@ int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, i
   }
   ft::Shape auto_shape;
   const bool was_auto = algo == FT_ALGO_AUTO;
+  const bool caller_shape = nw > 0 || ring;   // the caller (or FT_TOPO) named the plan, as opposed to the policy
   if (algo == FT_ALGO_AUTO) {
     if (nw > 0 || ring) {
       algo = FT_ALGO_STAGED;
@@ -839,7 +840,8 @@ int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, i
       ft_choice cc;
       ft_policy_fill_choice(ch, &cc);
       algo = cc.algo;
-      if (algo == FT_ALGO_STAGED) {
+      const bool flat_shape = !ch.shape.ring && ch.shape.lonely == 0 && ch.shape.widths.size() <= 1;
+      if (algo == FT_ALGO_STAGED || (algo == FT_ALGO_LL && !flat_shape)) {
         auto_shape = ch.shape;
         widths = auto_shape.widths.data();
         nw = (int)auto_shape.widths.size();
@@ -867,7 +869,7 @@ int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, i
   // A shape together with the low-latency protocol: the plan runs on tagged words (one NVLink trip per stage).  An
   // explicit shape under AUTO (FT_TOPO) takes that form too while the message is small enough for it to pay.
   const bool shaped = nw > 0 || ring;
-  if (shaped && (algo == FT_ALGO_LL || (was_auto && algo == FT_ALGO_STAGED && pr.bytes <= c->ll_tree_max))) {
+  if (shaped && (algo == FT_ALGO_LL || (was_auto && caller_shape && algo == FT_ALGO_STAGED && pr.bytes <= c->ll_tree_max))) {
     const ft::Shape shape = make_shape(c->world, widths, nw, lonely, ring);
     DevPlanEntry* pe = nullptr;
     rc = get_plan(c, shape, &pe);

@@ -46,9 +46,9 @@ def split_impl(impl: str):
         return None
     if parts[1].startswith("hybrid-"):
         return parts[1], parts[2]   # 'hybrid-<byte fraction>-<lane fraction>'
-    if parts[1] not in ("staged", "oneshot", "nvls", "ll", "push"):
+    if parts[1] not in ("staged", "oneshot", "nvls", "ll", "lltree", "push"):
         return None
-    return parts[1], parts[2]
+    return parts[1], parts[2]   # 'lltree' = a plan on tagged words: becomes an "ll" row that keeps its shape
 
 
 def best_table(rows) -> dict:
@@ -58,7 +58,9 @@ def best_table(rows) -> dict:
         if k is None or r.get("ok") is False:
             continue
         algo, shape = k
-        if algo != "staged":
+        if algo == "lltree":
+            algo = "ll"
+        elif algo != "staged":
             shape = str(r["world"])
         elif shape == "auto":
             continue

@@ -139,6 +139,13 @@ def test_native_policy_returns_every_row_of_the_committed_table(tmp_path):
                                "table": {"8": [[1024, "ll", "8", 1.0], [4096, "warp-drive", "8"], [8192, "staged", "3*3"]]}}))
     assert L.ft_policy_load(h, str(odd).encode(), err, 256) == 0 and b"2 table rows skipped" in err.value
     assert L.ft_policy_num_rows(h) == 1
+    # an "ll" row that names a tree keeps it: the plan then runs on tagged words
+    L.ft_policy_clear_rows(h)
+    assert L.ft_policy_add_row(h, 4096, b"ll", b"2*4") == 0 and L.ft_policy_add_row(h, 1 << 20, b"nvls", b"8") == 0
+    assert L.ft_policy_add_row(h, 4096, b"ll", b"3*3") != 0          # not a shape of 8 ranks
+    out = Choice()
+    assert L.ft_policy_choose(h, 4096, 0, 0, 64 << 20, 8 << 10, C.byref(out)) == 0
+    assert out.algo_name == b"ll" and [out.widths[i] for i in range(out.nw)] == [2, 4] and out.from_table == 1
     from allreduce_over_mpi_b200._lib import V1Params
     k = V1Params()
     assert L.ft_policy_get_params(h, C.byref(k)) == 0 and k.launch_us == 3.0 and k.peer_eff[2] == 0.5
