@@ -78,7 +78,7 @@ def _declare(lib):
         "ft_policy_clear_rows": (None, [vp]),
         "ft_policy_num_rows": (i, [vp]),
         "ft_policy_add_row": (i, [vp, u64, cp, cp]),
-        "ft_policy_choose": (i, [vp, u64, i, i, u64, u64, C.POINTER(Choice)]),
+        "ft_policy_choose": (i, [vp, u64, i, i, u64, u64, i, C.POINTER(Choice)]),
         "ft_parse_topo": (i, [cp, cp, i, ip, i, ip, ip, ip, ip, cp, sz]),
         "ft_validate_shape": (i, [i, *shape, cp, sz]),
         "ft_plan_check": (i, [i, *shape, cp, sz]),

@@ -51,6 +51,7 @@ def declare(lib) -> None:
         "ft_comm_set_nvls_ctas_per_sm": (None, [vp, i]),
         "ft_comm_set_nvls_config": (i, [vp, i, i, i, i, sz]),
         "ft_comm_set_phase_nvls": (None, [vp, i]),
+        "ft_comm_set_nvls1_max_lanes": (None, [vp, i]),
         "ft_bounds_build": (i, []),
         "ft_bounds_check_host": (i, [u64, i, i, u64, u64]),
         "ft_comm_policy": (vp, [vp]),

@@ -124,6 +124,8 @@ def sweep(a, comm: FlexTreeComm, rank: int, world: int) -> list[dict]:
                         continue
                     if algo in ("nvls", "hybrid") and (not comm.has_nvls or nbytes % 16):
                         continue
+                    if algo == "nvls1" and (not comm.has_nvls or nbytes > min(comm.staging_bytes, a.nvls1_cap)):
+                        continue
                     if algo == "hybrid":
                         if nbytes >= a.hybrid_min:
                             impls += [(f"{bf},{lf}", "hybrid") for bf, lf in a.hybrid]
@@ -149,6 +151,8 @@ def sweep(a, comm: FlexTreeComm, rank: int, world: int) -> list[dict]:
                     comm.set_hybrid(bf, lf)
                     fn = lambda: comm.all_reduce(sym, algo="hybrid")  # noqa: E731
                     label = f"flextree/hybrid-{bf}-{lf}/{world}"
+                elif algo == "nvls1":
+                    fn = lambda: comm.all_reduce(loc, algo="nvls1")  # noqa: E731
                 elif algo == "lltree":
                     fn = lambda shape=shape: comm.all_reduce(loc, shape=shape, algo="ll")  # noqa: E731
                 elif algo == "ll":
@@ -157,7 +161,7 @@ def sweep(a, comm: FlexTreeComm, rank: int, world: int) -> list[dict]:
                     fn = lambda: comm.all_reduce(loc, algo="oneshot")  # noqa: E731
                 row = {"bench": "allreduce", "impl": label, "bytes": nbytes, "dtype": dt_name, "world": world}
                 if a.check:
-                    tgt = loc if algo in ("oneshot", "ll", "lltree") else sym
+                    tgt = loc if algo in ("oneshot", "ll", "lltree", "nvls1") else sym
                     fill(tgt, rank)
                     fn()
                     torch.cuda.synchronize()
@@ -232,6 +236,7 @@ def main(argv=None):
     ap.add_argument("--shapes", nargs="+", default=["auto"])
     ap.add_argument("--algos", nargs="+", default=["staged", "ll", "oneshot", "nvls"])
     ap.add_argument("--oneshot-cap", type=int, default=4 << 20)
+    ap.add_argument("--nvls1-cap", type=int, default=16 << 20, help="largest message tried with the one-shot form through the switch")
     ap.add_argument("--hybrid", nargs="*", default=["0.7,0.5"], help="byte_fraction,lane_fraction pairs tried by algo hybrid")
     ap.add_argument("--hybrid-min", type=int, default=4 << 20)
     ap.add_argument("--iters", type=int, default=20)
@@ -338,7 +343,7 @@ def bench_allreduce_main(a) -> dict:
         res["e2e"] = e2e_allreduce(a, comm, buf, count, dtype, world)
     if not a.no_sweep:
         ns = argparse.Namespace(min_bytes=1024, max_bytes=min(a.bytes, 1 << 30), step=16, dtypes=[a.dtype], shapes=["auto"],
-                                algos=["staged"], oneshot_cap=4 << 20, iters=10, warmup=3, nccl=True, check=False,
+                                algos=["staged"], oneshot_cap=4 << 20, nvls1_cap=16 << 20, iters=10, warmup=3, nccl=True, check=False,
                                 no_flush=False, staged_copy=False, hybrid=[], hybrid_min=1 << 62)
         import contextlib
         import io

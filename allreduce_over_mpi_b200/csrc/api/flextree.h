@@ -61,7 +61,7 @@ size_t ft_executable_shapes(int world, char* buf, size_t cap);
  * Python front end all go through it.  A policy is built for one world size. ---- */
 typedef struct ft_policy ft_policy;
 typedef struct ft_choice {
-  int algo;            /* FT_ALGO_STAGED .. FT_ALGO_PUSH */
+  int algo;            /* FT_ALGO_STAGED .. FT_ALGO_PUSH, FT_ALGO_NVLS1 */
   int nw;              /* shape of the plan (FT_ALGO_STAGED); flat for the others */
   int widths[16];
   int lonely, ring;
@@ -81,13 +81,14 @@ int ft_policy_get_params(ft_policy* p, ft_v1_params* k);
 void ft_policy_clear_rows(ft_policy* p);
 int ft_policy_num_rows(ft_policy* p);
 /* one measured winner; algo as in the calibration file ("ll", "oneshot", "staged", "push", "nvls",
- * "hybrid-<bytes>-<lanes>"), shape as text ("8", "2*4", "2*3+1", "ring8") */
+ * "nvls1", "hybrid-<bytes>-<lanes>"), shape as text ("8", "2*4", "2*3+1", "ring8") */
 int ft_policy_add_row(ft_policy* p, uint64_t bytes, const char* algo, const char* shape);
 /* in_heap: 16-byte aligned tensor inside the symmetric heap; nvls_ok: multicast bound and the message
  * qualifies (float type, multiple of 16 bytes); staging_bytes: one staging slot; ll_auto_max: below it the
- * low-latency protocol is the default where neither table nor model speaks */
+ * low-latency protocol is the default where neither table nor model speaks; nvls1_ok: multicast bound and a float
+ * type (the one-shot form through the switch stages any tensor through the slots) */
 int ft_policy_choose(ft_policy* p, uint64_t bytes, int in_heap, int nvls_ok, uint64_t staging_bytes, uint64_t ll_auto_max,
-                     ft_choice* out);
+                     int nvls1_ok, ft_choice* out);
 
 /* ---- configuration (reference: get_stages, mpi_mod.hpp:1419-1486) ---- */
 /* returns FT_OK or FT_ERR_INVALID_TOPO (message in err) */

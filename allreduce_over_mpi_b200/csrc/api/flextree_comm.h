@@ -159,6 +159,10 @@ void ft_comm_set_nvls_ctas_per_sm(ft_comm* c, int n);
  * the CTAs of one launch (0 = one per SM; < 0 keeps), stripe_bytes: all-reduce ownership, 0 = rank r reduces block r,
  * else stripes of this size dealt round-robin ((size_t)-1 keeps). */
 int ft_comm_set_nvls_config(ft_comm* c, int threads, int unroll, int weak, int max_lanes, size_t stripe_bytes);
+/* FT_ALGO_NVLS1, one-shot through the switch: every rank publishes its input in its staging slot, one rendezvous, every
+ * rank reduces the whole message with multimem.ld_reduce into recvbuf.  Any float tensor (heap or not) up to one staging
+ * slot; needs NVLS.  ft_comm_set_nvls1_max_lanes caps its CTAs (default 64; 0 = one per SM). */
+void ft_comm_set_nvls1_max_lanes(ft_comm* c, int lanes);
 /* ft_reduce_scatter / ft_all_gather use the multimem kernels for the flat shape on eligible tensors (default on) */
 void ft_comm_set_phase_nvls(ft_comm* c, int on);
 /* one-shot emulation: phase 1 = publish input (all ranks first), phase 4 = reduce */
@@ -177,8 +181,8 @@ int ft_bounds_check_host(uint64_t heap_bytes, int rank, int world, uint64_t off,
  * after the stream is idle.  ft_comm_clear_status resets it. */
 int ft_comm_status(ft_comm* c, int* out5);
 /* usage so far, counted on the host at launch: calls and message bytes per algorithm, index FT_ALGO_STAGED ..
- * FT_ALGO_PUSH as resolved (index 0 stays empty), 7 = ft_reduce_scatter, 8 = ft_all_gather */
-int ft_comm_stats(ft_comm* c, uint64_t* calls9, uint64_t* bytes9);
+ * FT_ALGO_PUSH as resolved (index 0 stays empty), 7 = ft_reduce_scatter, 8 = ft_all_gather, 9 = FT_ALGO_NVLS1; ten entries each */
+int ft_comm_stats(ft_comm* c, uint64_t* calls10, uint64_t* bytes10);
 void ft_comm_clear_status(ft_comm* c);
 /* launches a kernel that waits `timeout_ms` for a signal from `peer` that never comes */
 int ft_comm_wait_probe(ft_comm* c, int peer, double timeout_ms, void* stream);

@@ -67,10 +67,10 @@ struct ft_cpu_world { ft::CpuWorld w; };
 // C form of a policy answer (also used by the communicator runtime)
 void ft_policy_fill_choice(const ft::PolicyChoice& c, ft_choice* out) {
   std::memset(out, 0, sizeof *out);
-  static const char* names[] = {"auto", "staged", "oneshot", "nvls", "hybrid", "ll", "push"};
+  static const char* names[] = {"auto", "staged", "oneshot", "nvls", "hybrid", "ll", "push", "", "", "nvls1"};
   out->algo = FT_ALGO_STAGED;
-  for (int i = 1; i < 7; ++i)
-    if (c.algo == names[i]) out->algo = i;
+  for (int i = 1; i < 10; ++i)
+    if (names[i][0] && c.algo == names[i]) out->algo = i;
   std::snprintf(out->algo_name, sizeof out->algo_name, "%s", names[out->algo]);
   out->nw = (int)(c.shape.widths.size() < 16 ? c.shape.widths.size() : 16);
   for (int i = 0; i < out->nw; ++i) out->widths[i] = c.shape.widths[i];
@@ -201,9 +201,9 @@ int ft_policy_add_row(ft_policy* p, uint64_t bytes, const char* algo, const char
   return p->p.add_row(bytes, algo, shape) ? FT_OK : FT_ERR_INVALID_ARG;
 }
 int ft_policy_choose(ft_policy* p, uint64_t bytes, int in_heap, int nvls_ok, uint64_t staging_bytes, uint64_t ll_auto_max,
-                     ft_choice* out) {
+                     int nvls1_ok, ft_choice* out) {
   if (!p || !out) return FT_ERR_INVALID_ARG;
-  ft_policy_fill_choice(p->p.choose(bytes, in_heap != 0, nvls_ok != 0, staging_bytes, ll_auto_max), out);
+  ft_policy_fill_choice(p->p.choose(bytes, in_heap != 0, nvls_ok != 0, staging_bytes, ll_auto_max, nvls1_ok != 0), out);
   return FT_OK;
 }
 

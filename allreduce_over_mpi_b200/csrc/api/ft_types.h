@@ -49,7 +49,8 @@ typedef enum ft_status {
 } ft_status;
 
 /* All-reduce algorithms of the GPU communicator (flextree_comm.h); AUTO asks the selection policy. */
-enum { FT_ALGO_AUTO = 0, FT_ALGO_STAGED = 1, FT_ALGO_ONESHOT = 2, FT_ALGO_NVLS = 3, FT_ALGO_HYBRID = 4, FT_ALGO_LL = 5, FT_ALGO_PUSH = 6 };
+enum { FT_ALGO_AUTO = 0, FT_ALGO_STAGED = 1, FT_ALGO_ONESHOT = 2, FT_ALGO_NVLS = 3, FT_ALGO_HYBRID = 4, FT_ALGO_LL = 5, FT_ALGO_PUSH = 6,
+       FT_ALGO_NVLS1 = 9 /* one-shot through the switch; 7 and 8 number the reduce-scatter / all-gather calls in the usage counters */ };
 
 /* Maximum number of sources of one n-way reduction (own copy included).  The
  * reference stops at 20 (MAX_NUM_BLOCKS, mpi_mod.hpp:811). */

@@ -12,6 +12,8 @@
 //  * nvls_kernel               multimem.ld_reduce / multimem.st through the NVSwitch
 //    multicast mapping (in-switch reduction), where the box exposes it: all-reduce, and
 //    its two halves (reduce-scatter, all-gather) as passes of their own.
+//  * nvls_oneshot_kernel       publish, one rendezvous, every rank reduces the whole message inside the
+//    switch (tens of KB to a few MB).
 //  * hybrid_allreduce_kernel   both at once on disjoint parts of the message.
 //  * push_allreduce_kernel     flat two-shot in one pass: pull + sum + posted writes to every rank.
 //  * ll_allreduce_kernel       push protocol with the flag inside every 8-byte word, no
@@ -697,6 +699,62 @@ __global__ void __launch_bounds__(1024) nvls_kernel(const __grid_constant__ Comm
   lane_rendezvous(sync, all, call * kCallStride + 2, 1);
 }
 
+// ------------------------------------------------------------------------------- one-shot through the switch
+// The one-shot all-reduce with the N peer loads per vector replaced by ONE multimem.ld_reduce: every rank
+// publishes its input in its staging slot (two slots by call parity, as in oneshot_allreduce_kernel), one
+// rendezvous, then every rank reduces the WHOLE message inside the switch and stores it to its own output.
+// One rendezvous instead of the two of the reduce + broadcast pass, at the price of N times the switch traffic:
+// the choice for messages of tens of KB to a few MB.
+template <int POL>
+__global__ void __launch_bounds__(kThreads) nvls_oneshot_kernel(const __grid_constant__ CommDev c, const __grid_constant__ OneShotArgs a,
+                                                                uint64_t slot_bytes) {
+  using P = typename PolById<POL>::type;
+  __shared__ int abort_flag;
+  __shared__ unsigned long long call_slot;
+  const int lane = blockIdx.x, nlanes = gridDim.x;
+  if (threadIdx.x == 0) abort_flag = 0;
+  const unsigned long long call = begin_call(c, &call_slot);
+  const uint32_t es = a.elem_size;
+  const uint64_t total_bytes = a.count * es;
+  const uint64_t chunk = lane_chunk(total_bytes, nlanes);
+  const LaneSlice sl = lane_slice(total_bytes, chunk, lane);
+  const uint64_t slot = a.slot_off + (call & 1) * slot_bytes;
+  bool inside = true;
+  FT_CHECK_RANGE(c, c.rank, slot + sl.off, (sl.bytes + 15) / 16 * 16, 140, lane, inside = false)
+  if (sl.bytes && inside)
+    copy_range((const unsigned char*)a.user_in + sl.off, a.user_vec_ok, c.heap[c.rank] + slot + sl.off, true, sl.bytes, es);
+  LaneSync sync{c.flags, c.flags[c.rank], c.rank, c.world, lane, FT_MAX_RANKS, c.timeout_ns, c.status, &abort_flag};
+  const unsigned long long all = c.world >= 64 ? ~0ull : ((1ull << c.world) - 1);
+  lane_rendezvous(sync, all, call * kCallStride + 1, 0);
+  if (abort_flag || !sl.bytes || !inside) return;
+  const unsigned char* mc = c.mc_heap + slot + sl.off;
+  unsigned char* out = (unsigned char*)a.user_out + sl.off;
+  const uint64_t nvec = (sl.bytes + 15) / 16;   // a ragged last vector reads slot bytes past the message; only the valid ones are stored
+  constexpr int KU = 4;
+  for (uint64_t base = 0; base < nvec; base += (uint64_t)blockDim.x * KU) {
+    uint4 v[KU];
+    uint64_t idx[KU];
+#pragma unroll
+    for (int u = 0; u < KU; ++u) {
+      idx[u] = base + (uint64_t)u * blockDim.x + threadIdx.x;
+      v[u] = idx[u] < nvec ? Nvls<POL, 0>::ld(mc + idx[u] * 16) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < KU; ++u) {
+      if (idx[u] >= nvec) continue;
+      if (a.scale != 1.0f) {
+        typename P::Acc t;
+        P::init(t, v[u]);
+        v[u] = P::fins(t, a.scale);
+      }
+      const uint64_t off = idx[u] * 16;
+      const uint32_t valid = (uint32_t)(sl.bytes - off < 16 ? sl.bytes - off : 16);
+      if (valid == 16 && a.user_vec_ok) st_vec(out + off, v[u]);
+      else st_partial(out + off, v[u], valid, es);
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------- hybrid NVLS + peer loads
 // The in-switch reduction tops out well below the bandwidth of the GPU's links, and a
 // two-shot all-reduce over plain peer loads uses the same links in a different way (no
@@ -935,6 +993,17 @@ cudaError_t launch_ll(int pol, const CommDev& c, const LLArgs& a, cudaStream_t s
 #define CALL(P) launch_ll_t<P>(c, a, st)
   FT_POL_SWITCH(pol, CALL)
 #undef CALL
+}
+cudaError_t launch_nvls_oneshot(int pol, const CommDev& c, const OneShotArgs& a, uint64_t slot_bytes, int lanes, int threads, cudaStream_t st) {
+  if (threads < 128 || threads > kThreads || threads % 32) return cudaErrorInvalidValue;
+  ft_count_launch(1);
+  switch (pol) {
+    case POL_F32: nvls_oneshot_kernel<POL_F32><<<lanes, threads, 0, st>>>(c, a, slot_bytes); break;
+    case POL_BF16: nvls_oneshot_kernel<POL_BF16><<<lanes, threads, 0, st>>>(c, a, slot_bytes); break;
+    case POL_F16: nvls_oneshot_kernel<POL_F16><<<lanes, threads, 0, st>>>(c, a, slot_bytes); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
 }
 template <int POL> static cudaError_t launch_ll_tree_t(const CommDev& c, const LLTreeArgs& a, cudaStream_t st) {
   const uint64_t items = (a.block_elems * a.elem_size + 15) / 16;

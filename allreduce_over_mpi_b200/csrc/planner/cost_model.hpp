@@ -127,6 +127,12 @@ inline double cost_v1_nvls(int world, uint64_t bytes, const V1Params& k) {
   return k.launch_us + 3 * k.sync_us + (double)bytes * (1.0 + 1.0 / world) / k.nvls_gbs * 1e-3;
 }
 
+// One-shot through the switch: one rendezvous, every rank reduces the whole message, so each GPU's links carry N * S.
+inline double cost_v1_nvls1(int world, uint64_t bytes, const V1Params& k) {
+  if (k.nvls_gbs <= 0) return std::numeric_limits<double>::infinity();
+  return k.launch_us + k.sync_us + (double)bytes * world / k.nvls_gbs * 1e-3;
+}
+
 // Low-latency push: no rendezvous; every rank writes 2x its payload (data + tags) to each of N-1 peers.
 inline double cost_v1_ll(int world, uint64_t bytes, const V1Params& k) {
   if (k.ll_us <= 0 || (double)bytes > k.ll_max_bytes) return std::numeric_limits<double>::infinity();
@@ -168,7 +174,7 @@ struct V1Choice {
 // NVLS and reduce+push work in place on a tensor in the symmetric heap only: allow_nvls says that the
 // message qualifies for the switch reduction, allow_push (< 0: same as allow_nvls) that it lives in the heap.
 inline V1Choice pick_algorithm(int world, uint64_t bytes, const V1Params& k, bool allow_oneshot = true,
-                               bool allow_nvls = true, int allow_push = -1) {
+                               bool allow_nvls = true, int allow_push = -1, bool allow_nvls1 = false) {
   V1Choice best;
   for (auto& s : executable_shapes(world)) {
     Plan p = build_plan(world, s);
@@ -182,6 +188,10 @@ inline V1Choice pick_algorithm(int world, uint64_t bytes, const V1Params& k, boo
   if (allow_nvls) {
     double c = cost_v1_nvls(world, bytes, k);
     if (c < best.us) { best.us = c; best.shape = Shape::flat(world); best.algo = "nvls"; }
+  }
+  if (allow_nvls1) {
+    double c = cost_v1_nvls1(world, bytes, k);
+    if (c < best.us) { best.us = c; best.shape = Shape::flat(world); best.algo = "nvls1"; }
   }
   if (allow_push < 0 ? allow_nvls : allow_push != 0) {
     double c = cost_v1_push(world, bytes, k);

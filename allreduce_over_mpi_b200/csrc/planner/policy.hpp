@@ -66,7 +66,7 @@ inline bool parse_shape_text(const std::string& text_in, Shape* out) {
 }
 
 struct PolicyChoice {
-  std::string algo;   // "ll", "oneshot", "staged", "push", "nvls", "hybrid"
+  std::string algo;   // "ll", "oneshot", "staged", "push", "nvls", "nvls1", "hybrid"
   Shape shape;        // the plan for "staged"; flat for the others
   double hybrid_bytes = 0.7, hybrid_lanes = 0.5;   // split of "hybrid" (share of each block / of the CTAs in the switch)
   bool from_table = false;
@@ -93,7 +93,8 @@ class Policy {
       double a = 0.7, b = 0.5;
       if (std::sscanf(algo.c_str(), "hybrid-%lf-%lf", &a, &b) == 2) { r.hybrid_bytes = a; r.hybrid_lanes = b; }
     }
-    if (r.algo != "ll" && r.algo != "oneshot" && r.algo != "staged" && r.algo != "push" && r.algo != "nvls" && r.algo != "hybrid")
+    if (r.algo != "ll" && r.algo != "oneshot" && r.algo != "staged" && r.algo != "push" && r.algo != "nvls" && r.algo != "hybrid" &&
+        r.algo != "nvls1")
       return false;
     if (!parse_shape_text(shape_text, &r.shape) || !validate_shape(world_, r.shape).empty()) return false;
     std::lock_guard<std::mutex> lk(mu_);
@@ -162,9 +163,11 @@ class Policy {
   // nvls_ok: multicast is bound and the message qualifies (in_heap, float type, multiple of 16 bytes);
   // staging_bytes: size of one staging slot (one-shot must fit); ll_auto_max: below it the low-latency protocol
   // is taken when neither the table nor the model speaks.
-  PolicyChoice choose(uint64_t bytes, bool in_heap, bool nvls_ok, uint64_t staging_bytes, uint64_t ll_auto_max) {
+  // nvls1_ok: multicast is bound and the type is one the switch reduces (the one-shot form stages through the slots,
+  // so the tensor need not live in the heap).
+  PolicyChoice choose(uint64_t bytes, bool in_heap, bool nvls_ok, uint64_t staging_bytes, uint64_t ll_auto_max, bool nvls1_ok = false) {
     if (!in_heap) nvls_ok = false;
-    const Key key{bytes, in_heap, nvls_ok, staging_bytes, ll_auto_max};
+    const Key key{bytes, in_heap, nvls_ok, staging_bytes, ll_auto_max, nvls1_ok};
     std::lock_guard<std::mutex> lk(mu_);
     auto it = cache_.find(key);
     if (it != cache_.end()) return it->second;
@@ -177,6 +180,7 @@ class Policy {
       if (!nvls_ok && (r.algo == "nvls" || r.algo == "hybrid")) continue;
       if (!in_heap && r.algo == "push") continue;
       if (r.algo == "oneshot" && bytes > staging_bytes) continue;
+      if (r.algo == "nvls1" && (!nvls1_ok || bytes > staging_bytes)) continue;
       if (r.algo == "ll" && bytes > kLLMaxBytes) continue;
       lo = r.bytes < lo ? r.bytes : lo;
       hi = r.bytes > hi ? r.bytes : hi;
@@ -195,7 +199,7 @@ class Policy {
       c.algo = "ll";
       c.shape = Shape::flat(world_);
     } else {
-      V1Choice m = pick_algorithm(world_, bytes, params_, bytes <= staging_bytes, nvls_ok, in_heap);
+      V1Choice m = pick_algorithm(world_, bytes, params_, bytes <= staging_bytes, nvls_ok, in_heap, nvls1_ok && bytes <= staging_bytes);
       c.algo = m.algo;
       c.shape = m.shape;
     }
@@ -210,7 +214,7 @@ class Policy {
     Shape shape;
     double hybrid_bytes = 0.7, hybrid_lanes = 0.5;
   };
-  using Key = std::tuple<uint64_t, bool, bool, uint64_t, uint64_t>;
+  using Key = std::tuple<uint64_t, bool, bool, uint64_t, uint64_t, bool>;
   static double field(const Json* obj, const char* name, double dflt) {
     const Json* v = obj->get(name);
     return v ? v->number_or(dflt) : dflt;

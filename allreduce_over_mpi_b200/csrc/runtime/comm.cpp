@@ -41,6 +41,7 @@ cudaError_t launch_push(int pol, const CommDev& c, const NvlsArgs& a, int lanes,
 cudaError_t launch_ll(int pol, const CommDev& c, const LLArgs& a, cudaStream_t st);
 cudaError_t launch_hybrid(int pol, const CommDev& c, const NvlsArgs& a, int lanes, int nvls_lanes, uint64_t nvls_bytes, cudaStream_t st);
 cudaError_t launch_ll_tree(int pol, const CommDev& c, const LLTreeArgs& a, cudaStream_t st);
+cudaError_t launch_nvls_oneshot(int pol, const CommDev& c, const OneShotArgs& a, uint64_t slot_bytes, int lanes, int threads, cudaStream_t st);
 cudaError_t launch_wait_probe(const CommDev& c, int peer, unsigned long long timeout_ns, cudaStream_t st);
 }  // namespace ftk
 
@@ -122,8 +123,8 @@ struct ft_comm {
   int rank = 0, world = 1, device = 0, mem_kind = FT_MEM_VMM;
   size_t user_bytes = 0, staging_bytes = 0, total_bytes = 0, staging_off = 0, ll_off = 0, flags_off = 0;
   ft::HeapAllocator heap_alloc;   // offsets of the tensors handed out from the user part of the heap
-  // host-side usage counters per algorithm (FT_ALGO_* index; 7 = reduce-scatter alone, 8 = all-gather alone)
-  uint64_t stat_calls[9] = {}, stat_bytes[9] = {};
+  // host-side usage counters per algorithm (FT_ALGO_* index; 7 = reduce-scatter alone, 8 = all-gather alone, 9 = FT_ALGO_NVLS1)
+  uint64_t stat_calls[10] = {}, stat_bytes[10] = {};
   // local allocation
   CUmemGenericAllocationHandle handle = 0;
   CUdeviceptr va = 0;
@@ -153,6 +154,7 @@ struct ft_comm {
   int nvls_max_lanes = 32;    // 0: as many lanes as SMs (times nvls_ctas_per_sm).  8 GPUs, 64 MiB / 256 MiB / 1 GiB: 32 CTAs of
                               // 256 threads reach 683 / 806 / 839 GB/s, all 148 SMs 632 / 786 / 834, 16 CTAs 682 / 797 / 828
   size_t nvls_stripe = 0;
+  int nvls1_max_lanes = 64;   // CTAs of the one-shot-through-the-switch kernel (0: one per SM)
   bool phase_nvls = true;     // ft_reduce_scatter / ft_all_gather may use the multimem kernels (flat shape, eligible tensor)     // all-reduce: 0 = rank r owns block r, else round-robin stripes of this many bytes
   std::map<std::string, DevPlanEntry> plans;
   // ft_allreduce_host: chunk buffers in the heap + three streams, made on first use
@@ -307,7 +309,8 @@ ft::PolicyChoice choose_for(ft_comm* c, const Prepared& pr) {
   if (!c->policy) {   // a communicator that was never finalized still answers from the model
     c->policy = new ft_policy(c->world);
   }
-  return c->policy->p.choose(pr.bytes, pr.heap_resident, nvls_eligible(c, pr), c->staging_bytes, c->ll_max);
+  const bool nvls1_ok = c->mc_bound && c->mc_va && (pr.pol == ftk::POL_F32 || pr.pol == ftk::POL_BF16 || pr.pol == ftk::POL_F16);
+  return c->policy->p.choose(pr.bytes, pr.heap_resident, nvls_eligible(c, pr), c->staging_bytes, c->ll_max, nvls1_ok);
 }
 
 int launch_staged_call(ft_comm* c, const Prepared& pr, const void* sendbuf, void* recvbuf, size_t count,
@@ -692,9 +695,9 @@ int ft_comm_finalize(ft_comm* c) {
     ft_policy_load(c->policy, nullptr, why, sizeof why);
   }
   if (const char* e = std::getenv("FT_ALGO"); e && *e) {
-    static const char* names[] = {"auto", "staged", "oneshot", "nvls", "hybrid", "ll", "push"};
-    for (int i = 0; i < 7; ++i)
-      if (!std::strcmp(e, names[i])) c->forced_algo = i;
+    static const char* names[] = {"auto", "staged", "oneshot", "nvls", "hybrid", "ll", "push", "", "", "nvls1"};
+    for (int i = 0; i < 10; ++i)
+      if (names[i][0] && !std::strcmp(e, names[i])) c->forced_algo = i;
   }
   // Device tables of the shapes a call is likely to ask for are built now, so that the first step of a
   // training loop (or a CUDA graph capture) never stops for an allocation and a synchronous upload.
@@ -880,7 +883,27 @@ int ft_allreduce(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, i
       return launch_ll_tree_call(c, pr, sendbuf, recvbuf, count, shape, scale, -1, -1, 3, true, 0, st);
     }
   }
-  if (algo >= 0 && algo < 7) { c->stat_calls[algo]++; c->stat_bytes[algo] += pr.bytes; }
+  if ((algo >= 0 && algo < 7) || algo == FT_ALGO_NVLS1) { c->stat_calls[algo]++; c->stat_bytes[algo] += pr.bytes; }
+  if (algo == FT_ALGO_NVLS1) {
+    if (!ft_comm_has_nvls(c)) return fail(c, FT_ERR_NOT_AVAILABLE, "NVLS multicast is not bound on this communicator");
+    if (pr.pol != ftk::POL_F32 && pr.pol != ftk::POL_BF16 && pr.pol != ftk::POL_F16)
+      return fail(c, FT_ERR_UNSUPPORTED_TYPE, "the switch reduces floating types only");
+    if (pr.bytes > c->staging_bytes) return fail(c, FT_ERR_TOO_LARGE, "one-shot message exceeds the staging slot");
+    ftk::OneShotArgs a{};
+    a.slot_off = c->staging_off;
+    a.user_in = sendbuf ? sendbuf : recvbuf;
+    a.user_out = recvbuf;
+    a.count = count;
+    a.elem_size = pr.es;
+    a.phase_mask = 7;
+    a.user_vec_ok = (((uintptr_t)a.user_in | (uintptr_t)a.user_out) & 15) == 0;
+    a.scale = scale;
+    int lanes = pick_lanes(c, pr.bytes, 4096);
+    if (c->nvls1_max_lanes > 0 && lanes > c->nvls1_max_lanes) lanes = c->nvls1_max_lanes;
+    cudaError_t e = ftk::launch_nvls_oneshot(pr.pol, c->dev, a, c->staging_bytes, lanes, c->nvls_cfg.threads > 512 ? 512 : c->nvls_cfg.threads, st);
+    if (e != cudaSuccess) return fail(c, FT_ERR_CUDA, std::string("NVLS one-shot launch: ") + cudaGetErrorString(e));
+    return FT_OK;
+  }
   if (algo == FT_ALGO_LL) return launch_ll_call(c, pr, sendbuf, recvbuf, count, scale, 3, true, 0, st);
   if (algo == FT_ALGO_ONESHOT) return launch_oneshot_call(c, pr, sendbuf, recvbuf, count, scale, 7, 0, st);
   if (algo == FT_ALGO_PUSH) return launch_push_call(c, pr, sendbuf, recvbuf, count, scale, true, st);
@@ -1104,6 +1127,7 @@ int ft_comm_set_nvls_config(ft_comm* c, int threads, int unroll, int weak, int m
   return FT_OK;
 }
 void ft_comm_set_phase_nvls(ft_comm* c, int on) { if (c) c->phase_nvls = on != 0; }
+void ft_comm_set_nvls1_max_lanes(ft_comm* c, int lanes) { if (c && lanes >= 0) c->nvls1_max_lanes = lanes; }
 int ft_allreduce_emulate_ll_tree(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op,
                                  const int* widths, int nw, int lonely, int ring, float scale, int stage, int phase,
                                  uint64_t call, void* stream) {
@@ -1142,9 +1166,9 @@ int ft_comm_status(ft_comm* c, int* out5) {
   out5[3] = c->status_host->lane; out5[4] = (int)c->status_host->calls;
   return c->status_host->code;
 }
-int ft_comm_stats(ft_comm* c, uint64_t* calls9, uint64_t* bytes9) {
-  if (!c || !calls9 || !bytes9) return FT_ERR_INVALID_ARG;
-  for (int i = 0; i < 9; ++i) { calls9[i] = c->stat_calls[i]; bytes9[i] = c->stat_bytes[i]; }
+int ft_comm_stats(ft_comm* c, uint64_t* calls10, uint64_t* bytes10) {
+  if (!c || !calls10 || !bytes10) return FT_ERR_INVALID_ARG;
+  for (int i = 0; i < 10; ++i) { calls10[i] = c->stat_calls[i]; bytes10[i] = c->stat_bytes[i]; }
   return FT_OK;
 }
 void ft_comm_clear_status(ft_comm* c) {

@@ -30,7 +30,7 @@ from ..utils import log
 from . import planner
 from .planner import Shape
 
-ALGOS = {"auto": 0, "staged": 1, "oneshot": 2, "nvls": 3, "hybrid": 4, "ll": 5, "push": 6}
+ALGOS = {"auto": 0, "staged": 1, "oneshot": 2, "nvls": 3, "hybrid": 4, "ll": 5, "push": 6, "nvls1": 9}
 LL_MAX_BYTES = 256 << 10
 CANARY_BYTES, CANARY_BYTE = 256, 0xA5
 MEM_IPC, MEM_VMM = 0, 1
@@ -227,9 +227,10 @@ class _CommBase:
         table, else the calibrated cost model.  This asks the same native policy object that
         ``ft_allreduce(FT_ALGO_AUTO)``, ``MPI_Allreduce_FT`` and ``ft_bench`` use (csrc/planner/policy.hpp)."""
         nvls_ok = self.has_nvls and in_heap and dtype in (torch.float32, torch.bfloat16, torch.float16) and nbytes % 16 == 0
+        nvls1_ok = self.has_nvls and dtype in (torch.float32, torch.bfloat16, torch.float16)
         out = Choice()
         code = lib().ft_policy_choose(self._policy_handle(), nbytes, int(bool(in_heap)), int(bool(nvls_ok)),
-                                      int(self.staging_bytes), int(self.ll_auto_max), C.byref(out))
+                                      int(self.staging_bytes), int(self.ll_auto_max), int(bool(nvls1_ok)), C.byref(out))
         if code:
             raise FlexTreeError(code, "selection policy")
         name = out.algo_name.decode()
@@ -400,11 +401,11 @@ class _CommBase:
     def stats(self) -> dict:
         """Calls and message bytes so far per algorithm as resolved at launch (host-side counters), e.g.
         ``{"nvls": {"calls": 12, "bytes": 3221225472}, "ll": {...}, "reduce_scatter": {...}}``."""
-        calls, nbytes = (C.c_uint64 * 9)(), (C.c_uint64 * 9)()
+        calls, nbytes = (C.c_uint64 * 10)(), (C.c_uint64 * 10)()
         self._check(lib().ft_comm_stats(self._h, calls, nbytes))
         names = {v: k for k, v in ALGOS.items()}
         names.update({7: "reduce_scatter", 8: "all_gather"})
-        return {names[k]: {"calls": int(calls[k]), "bytes": int(nbytes[k])} for k in range(1, 9) if calls[k]}
+        return {names[k]: {"calls": int(calls[k]), "bytes": int(nbytes[k])} for k in range(1, 10) if calls[k]}
 
     def check(self, synchronize: bool = True):
         """Raise if a device-side wait timed out (a peer never arrived)."""

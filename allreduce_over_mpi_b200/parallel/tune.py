@@ -46,7 +46,7 @@ def split_impl(impl: str):
         return None
     if parts[1].startswith("hybrid-"):
         return parts[1], parts[2]   # 'hybrid-<byte fraction>-<lane fraction>'
-    if parts[1] not in ("staged", "oneshot", "nvls", "ll", "lltree", "push"):
+    if parts[1] not in ("staged", "oneshot", "nvls", "nvls1", "ll", "lltree", "push"):
         return None
     return parts[1], parts[2]   # 'lltree' = a plan on tagged words: becomes an "ll" row that keeps its shape
 

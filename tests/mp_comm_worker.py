@@ -295,6 +295,13 @@ def main():
                     fill(loc, rank, it)
                     comm.all_reduce(loc, algo="ll")
                     verify(loc, count, dtype, it, f"ll {dtype} {count}")
+            if comm.has_nvls and count * loc.element_size() <= comm.staging_bytes:
+                for rep in range(2):   # one-shot through the switch: any tensor, odd lengths too; both staging slots
+                    it += 1
+                    loc = torch.empty(count, dtype=dtype, device=dev)
+                    fill(loc, rank, it)
+                    comm.all_reduce(loc, algo="nvls1")
+                    verify(loc, count, dtype, it, f"nvls1 {dtype} {count}")
             if comm.has_nvls and (count * loc.element_size()) % 16 == 0:
                 it += 1
                 comm.free_all()
@@ -338,6 +345,8 @@ def main():
         comm.all_reduce(sym, op="avg", algo="push")
         if comm.has_nvls:
             comm.all_reduce(sym, op="avg", algo="nvls")
+            comm.all_reduce(small, op="avg", algo="nvls1")
+            comm.all_reduce(loc, op="avg", algo="nvls1")
     torch.cuda.synchronize()
     comm.check()
     for t, name in ((sym, "sym"), (loc, "loc"), (small, "small")):
@@ -357,6 +366,7 @@ def main():
         comm.all_reduce(small, op="avg", algo="oneshot")
         if comm.has_nvls:
             comm.all_reduce(sym, op="avg", algo="nvls")
+            comm.all_reduce(small, op="avg", algo="nvls1")
     for _ in range(5):
         graph.replay()
     torch.cuda.synchronize()

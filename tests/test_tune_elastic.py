@@ -121,7 +121,7 @@ def test_native_policy_returns_every_row_of_the_committed_table(tmp_path):
         for r in rows:
             nbytes, algo, shape = r[0], r[1], r[2]
             out = Choice()
-            assert L.ft_policy_choose(h, nbytes, 1, 1, 64 << 20, 8 << 10, C.byref(out)) == 0
+            assert L.ft_policy_choose(h, nbytes, 1, 1, 64 << 20, 8 << 10, 1, C.byref(out)) == 0
             assert out.from_table == 1
             assert out.algo_name.decode() == algo.split("-")[0], (world, r, out.algo_name)
             if algo == "staged":
@@ -144,7 +144,7 @@ def test_native_policy_returns_every_row_of_the_committed_table(tmp_path):
     assert L.ft_policy_add_row(h, 4096, b"ll", b"2*4") == 0 and L.ft_policy_add_row(h, 1 << 20, b"nvls", b"8") == 0
     assert L.ft_policy_add_row(h, 4096, b"ll", b"3*3") != 0          # not a shape of 8 ranks
     out = Choice()
-    assert L.ft_policy_choose(h, 4096, 0, 0, 64 << 20, 8 << 10, C.byref(out)) == 0
+    assert L.ft_policy_choose(h, 4096, 0, 0, 64 << 20, 8 << 10, 0, C.byref(out)) == 0
     assert out.algo_name == b"ll" and [out.widths[i] for i in range(out.nw)] == [2, 4] and out.from_table == 1
     from allreduce_over_mpi_b200._lib import V1Params
     k = V1Params()
