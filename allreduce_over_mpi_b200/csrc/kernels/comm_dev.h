@@ -130,6 +130,8 @@ struct LLTreeArgs {
   uint32_t use_call_counter;
   uint64_t emu_call;
   float scale;
+  uint32_t table_bytes;       // > 0: the kernel keeps the plan's tables in this much dynamic shared memory ...
+  uint32_t table_counts[3];   // ... holding this many stages, pulls and pushes
 };
 
 struct NvlsArgs {

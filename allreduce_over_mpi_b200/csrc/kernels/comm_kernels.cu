@@ -513,9 +513,29 @@ template <int POL>
 __global__ void __launch_bounds__(256) ll_tree_allreduce_kernel(const __grid_constant__ CommDev c, const __grid_constant__ LLTreeArgs a) {
   using P = typename PolById<POL>::type;
   __shared__ unsigned long long call_slot;
+  // The plan's tables are walked entry after entry by every thread; from global memory that is a chain of a few
+  // dozen dependent loads (~0.5 us each) on the critical path of a message that takes 20 us in all.  When they fit,
+  // the CTA copies them into shared memory once, all loads in flight together.
+  extern __shared__ __align__(16) unsigned char ll_tree_tables[];
+  const DevStage* stages = a.plan->stages;
+  const DevPull* pulls = a.pulls;
+  const DevPush* pushes = a.pushes;
+  if (a.table_bytes) {
+    const uint32_t nst = a.table_counts[0], npl = a.table_counts[1], nps = a.table_counts[2];
+    DevStage* s_st = (DevStage*)ll_tree_tables;
+    DevPull* s_pl = (DevPull*)(s_st + nst);
+    DevPush* s_ps = (DevPush*)(s_pl + npl);
+    const uint16_t* g0 = (const uint16_t*)a.plan->stages;
+    const uint16_t* g1 = (const uint16_t*)a.pulls;
+    const uint16_t* g2 = (const uint16_t*)a.pushes;
+    for (uint32_t k = threadIdx.x; k < nst * sizeof(DevStage) / 2; k += blockDim.x) ((uint16_t*)s_st)[k] = g0[k];
+    for (uint32_t k = threadIdx.x; k < npl * sizeof(DevPull) / 2; k += blockDim.x) ((uint16_t*)s_pl)[k] = g1[k];
+    for (uint32_t k = threadIdx.x; k < nps * sizeof(DevPush) / 2; k += blockDim.x) ((uint16_t*)s_ps)[k] = g2[k];
+    stages = s_st; pulls = s_pl; pushes = s_ps;
+  }
   unsigned long long call;
-  if (a.use_call_counter) call = begin_call(c, &call_slot);
-  else call = a.emu_call;
+  if (a.use_call_counter) call = begin_call(c, &call_slot);   // (its barrier also publishes the tables to the CTA)
+  else { call = a.emu_call; __syncthreads(); }
   const uint32_t tag = (uint32_t)(call + 1) | 0x80000000u;
   const uint32_t es = a.elem_size;
   const uint64_t block_bytes = a.block_elems * es, total_bytes = a.count * es;
@@ -544,10 +564,10 @@ __global__ void __launch_bounds__(256) ll_tree_allreduce_kernel(const __grid_con
     }
   const unsigned long long t0 = globaltimer_ns();
   for (uint32_t s = a.stage_begin; s < a.stage_end; ++s) {
-    const DevStage st = a.plan->stages[s];
+    const DevStage st = stages[s];
     if (a.phase_mask & 1)
       for (uint32_t q = st.push_begin; q < st.push_end; ++q) {
-        const DevPush ps = a.pushes[q];
+        const DevPush ps = pushes[q];
         const uint32_t valid = valid_of(ps.block);
         if (!valid) continue;
         const uint4 v = load_mine(out, ps.block, valid);
@@ -557,7 +577,7 @@ __global__ void __launch_bounds__(256) ll_tree_allreduce_kernel(const __grid_con
       }
     if (!(a.phase_mask & 2)) continue;
     for (uint32_t q = st.pull_begin; q < st.pull_end; ++q) {
-      const DevPull pl = a.pulls[q];
+      const DevPull pl = pulls[q];
       const uint32_t valid = valid_of(pl.block);
       if (!valid) continue;
       typename P::Acc acc;
@@ -1008,7 +1028,7 @@ cudaError_t launch_nvls_oneshot(int pol, const CommDev& c, const OneShotArgs& a,
 template <int POL> static cudaError_t launch_ll_tree_t(const CommDev& c, const LLTreeArgs& a, cudaStream_t st) {
   const uint64_t items = (a.block_elems * a.elem_size + 15) / 16;
   const int threads = items <= 32 ? 32 : (items <= 64 ? 64 : (items <= 128 ? 128 : 256));
-  ll_tree_allreduce_kernel<POL><<<(unsigned)((items + threads - 1) / threads), threads, 0, st>>>(c, a);
+  ll_tree_allreduce_kernel<POL><<<(unsigned)((items + threads - 1) / threads), threads, a.table_bytes, st>>>(c, a);
   return cudaGetLastError();
 }
 cudaError_t launch_ll_tree(int pol, const CommDev& c, const LLTreeArgs& a, cudaStream_t st) {

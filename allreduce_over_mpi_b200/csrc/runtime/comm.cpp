@@ -115,6 +115,7 @@ struct DevPlanEntry {
   ftk::DevPush* pushes = nullptr; // device: the plan's edges seen from their source (tagged-word form)
   int nstages = 0;
   uint32_t nslots = 0;            // receive slots this rank needs in the tagged-word form
+  uint32_t npulls = 0, npushes = 0;
 };
 
 }  // namespace
@@ -249,6 +250,8 @@ int get_plan(ft_comm* c, const ft::Shape& shape, DevPlanEntry** out) {
   if (!hd.pushes.empty())
     FT_CUDA(c, cudaMemcpy(e.pushes, hd.pushes.data(), sizeof(ftk::DevPush) * hd.pushes.size(), cudaMemcpyHostToDevice));
   e.nslots = hp.nslots;
+  e.npulls = (uint32_t)pulls.size();
+  e.npushes = (uint32_t)hd.pushes.size();
   *out = &c->plans.emplace(key, e).first->second;
   return FT_OK;
 }
@@ -421,6 +424,14 @@ int launch_ll_tree_call(ft_comm* c, const Prepared& pr, const void* sendbuf, voi
   a.use_call_counter = use_counter ? 1 : 0;
   a.emu_call = emu_call;
   a.scale = scale;
+  const size_t tables = (size_t)pe->nstages * sizeof(ftk::DevStage) + (size_t)pe->npulls * sizeof(ftk::DevPull) +
+                        (size_t)pe->npushes * sizeof(ftk::DevPush);
+  if (tables <= 40 * 1024) {   // below the 48 KiB a kernel may use without opting in
+    a.table_bytes = (uint32_t)((tables + 15) / 16 * 16);
+    a.table_counts[0] = (uint32_t)pe->nstages;
+    a.table_counts[1] = pe->npulls;
+    a.table_counts[2] = pe->npushes;
+  }
   cudaError_t e = ftk::launch_ll_tree(pr.pol, c->dev, a, st);
   if (e != cudaSuccess) return fail(c, FT_ERR_CUDA, std::string("tagged-word plan launch: ") + cudaGetErrorString(e));
   return FT_OK;
