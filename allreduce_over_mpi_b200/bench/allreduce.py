@@ -361,6 +361,9 @@ def e2e_allreduce(a, comm, buf, count, dtype, world) -> dict:
     (``comm.all_reduce_host``, what ``MPI_Allreduce_FT`` runs for host buffers): every step takes the whole input
     from pinned host memory and leaves the WHOLE result in pinned host memory; both copies are inside the timed
     region and are pipelined chunk by chunk with the NVLink all-reduce."""
+    # the pinned buffers go on the GPU's side of the host (first touch after moving this process next to the GPU)
+    from ..utils.numa import bind_to_gpu_node
+    placed = bind_to_gpu_node(comm.device.index) if os.environ.get("FT_NUMA_BIND", "1") != "0" else None
     g = torch.Generator().manual_seed(77 + comm.rank)
     host = torch.empty(count, dtype=dtype).pin_memory()
     host.copy_((torch.rand(count, generator=g) * 2 - 1).to(dtype))
@@ -394,7 +397,7 @@ def e2e_allreduce(a, comm, buf, count, dtype, world) -> dict:
     per_gpu = busbw(nbytes, ms, world)
     return {"value": round(per_gpu, 1), "per_gpu_busbw_GBps": round(per_gpu, 1), "whole_job_GBps": round(per_gpu * world, 1),
             "unit": "GB/s", "ms_per_step": round(ms, 4), "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes, "steps": steps,
-            "max_abs_err": err, "chunk_bytes": lib_chunk,
+            "max_abs_err": err, "chunk_bytes": lib_chunk, "host_buffers_next_to_gpu": placed,
             "api": "FlexTreeComm.all_reduce_host (pinned host in, whole result to pinned host, chunked and overlapped)"}
 
 

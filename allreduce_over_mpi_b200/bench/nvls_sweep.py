@@ -84,7 +84,7 @@ def main(argv=None):
                       "ms": round(ms, 5), "busbw_GBps": round(busbw(nbytes, ms, world), 1)})
         if a.phases:
             halves = {}
-            for label, on in (("multimem", 1), ("peer loads", 0)):
+            for label, on in (("multimem", 2), ("peer loads", 0)):
                 if on and not comm.has_nvls:
                     continue
                 lib().ft_comm_set_phase_nvls(comm._h, on)

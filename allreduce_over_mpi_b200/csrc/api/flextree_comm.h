@@ -117,7 +117,7 @@ void ft_comm_set_host_chunk(ft_comm* c, size_t bytes);
  * ft_reduce_scatter followed by ft_all_gather on the same buffer and shape equals ft_allreduce
  * with FT_ALGO_STAGED.  Each call closes with a rendezvous of all ranks, so the buffer may be
  * rewritten as soon as the call has completed on the caller's stream.
- * With the flat shape, on a float tensor of a multiple of 16 bytes and NVLS multicast bound, each half is one
+ * With the flat shape, on a float tensor of a multiple of 16 bytes, NVLS multicast bound and five or more ranks, each half is one
  * multimem pass through the switch: multimem.ld_reduce of block `rank` into the own buffer (reduce-scatter),
  * multimem.st of block `rank` to every rank (all-gather). */
 int ft_reduce_scatter(ft_comm* c, void* buf, size_t count, int dtype, int op, const int* widths, int nw, int lonely,
@@ -163,8 +163,9 @@ int ft_comm_set_nvls_config(ft_comm* c, int threads, int unroll, int weak, int m
  * rank reduces the whole message with multimem.ld_reduce into recvbuf.  Any float tensor (heap or not) up to one staging
  * slot; needs NVLS.  ft_comm_set_nvls1_max_lanes caps its CTAs (default 64; 0 = one per SM). */
 void ft_comm_set_nvls1_max_lanes(ft_comm* c, int lanes);
-/* ft_reduce_scatter / ft_all_gather use the multimem kernels for the flat shape on eligible tensors (default on) */
-void ft_comm_set_phase_nvls(ft_comm* c, int on);
+/* ft_reduce_scatter / ft_all_gather through the multimem kernels (flat shape, eligible tensor): 0 never, 1 where it
+ * measured faster than peer loads (five ranks and more; the default), 2 whenever possible */
+void ft_comm_set_phase_nvls(ft_comm* c, int mode);
 /* one-shot emulation: phase 1 = publish input (all ranks first), phase 4 = reduce */
 int ft_allreduce_emulate_oneshot(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op,
                                  float scale, int phase, uint64_t call, void* stream);

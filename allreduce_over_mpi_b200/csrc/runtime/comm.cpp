@@ -156,7 +156,8 @@ struct ft_comm {
                               // 256 threads reach 683 / 806 / 839 GB/s, all 148 SMs 632 / 786 / 834, 16 CTAs 682 / 797 / 828
   size_t nvls_stripe = 0;
   int nvls1_max_lanes = 64;   // CTAs of the one-shot-through-the-switch kernel (0: one per SM)
-  bool phase_nvls = true;     // ft_reduce_scatter / ft_all_gather may use the multimem kernels (flat shape, eligible tensor)     // all-reduce: 0 = rank r owns block r, else round-robin stripes of this many bytes
+  int phase_nvls = 1;         // ft_reduce_scatter / ft_all_gather through the multimem kernels (flat shape, eligible tensor):
+                              // 0 never, 1 where it measured faster (five ranks and more), 2 whenever possible     // all-reduce: 0 = rank r owns block r, else round-robin stripes of this many bytes
   std::map<std::string, DevPlanEntry> plans;
   // ft_allreduce_host: chunk buffers in the heap + three streams, made on first use
   struct HostPipe {
@@ -1043,8 +1044,10 @@ static int phase_call(ft_comm* c, void* buf, size_t count, int dtype, int op, co
   // buffer, or multimem.st of the own block to everyone) instead of N-1 peer loads per vector.  Block r ends up
   // on / comes from rank r, exactly as in the flat plan.
   const bool flat = !shape.ring && shape.lonely == 0 && shape.widths.size() == 1;
-  // (with two ranks a multimem pass moves twice the bytes of a plain peer read, and measures slower)
-  if (flat && c->phase_nvls && c->world > 2 && nvls_eligible(c, pr)) {
+  // (measured, 256 MiB fp32, reduce-scatter / all-gather: 8 GPUs 0.405 / 0.405 ms through the switch against 0.465 / 0.420 ms
+  //  with peer loads; 4 GPUs 0.409 / 0.405 against 0.357 / 0.352; with two ranks a multimem pass moves twice the bytes
+  //  of a plain peer read - so the switch takes over from five ranks up)
+  if (flat && (c->phase_nvls == 2 || (c->phase_nvls == 1 && c->world > 4)) && nvls_eligible(c, pr)) {
     ftk::NvlsArgs a{};
     a.work_off = (uint64_t)((unsigned char*)buf - local_base(c));
     a.count = count;
@@ -1137,7 +1140,7 @@ int ft_comm_set_nvls_config(ft_comm* c, int threads, int unroll, int weak, int m
   }
   return FT_OK;
 }
-void ft_comm_set_phase_nvls(ft_comm* c, int on) { if (c) c->phase_nvls = on != 0; }
+void ft_comm_set_phase_nvls(ft_comm* c, int mode) { if (c && mode >= 0 && mode <= 2) c->phase_nvls = mode; }
 void ft_comm_set_nvls1_max_lanes(ft_comm* c, int lanes) { if (c && lanes >= 0) c->nvls1_max_lanes = lanes; }
 int ft_allreduce_emulate_ll_tree(ft_comm* c, const void* sendbuf, void* recvbuf, size_t count, int dtype, int op,
                                  const int* widths, int nw, int lonely, int ring, float scale, int stage, int phase,

@@ -132,3 +132,14 @@ def test_cmake_build_of_the_native_library(tmp_path):
     rc, out, err = run([str(tmp_path / "ft_bench"), "--comm-type", "threads", "--ranks", "5", "--size", "1000", "--check"],
                        env={"FT_TOPO": "2,2", "FT_LONELY": "1"})
     assert rc == 0 and "CHECK (test passed)" in out, err
+
+
+def test_numa_placement_helper_is_best_effort():
+    """The helper that moves a benchmark process next to its GPU parses the kernel's CPU lists and does nothing
+    (returns None) where the system gives no information, e.g. without a GPU."""
+    from allreduce_over_mpi_b200.utils import numa
+    assert numa._parse_cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    assert numa._parse_cpulist("") == set()
+    import torch
+    if not torch.cuda.is_available():
+        assert numa.gpu_local_cpus(0) == (set(), None) and numa.bind_to_gpu_node(0) is None
