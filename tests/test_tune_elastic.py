@@ -72,13 +72,17 @@ def test_selection_from_the_committed_calibration():
     name, shape = c8.choose(32 << 20, False, torch.float32)
     assert name in ("staged", "oneshot") and planner.validate_shape(8, shape) == ""
     assert c8.choose(128 << 20, False, torch.float32)[0] == "staged"
+    # without multicast nothing that needs the switch is ever picked, whatever the table says for the size
+    for world in (4, 8):
+        for nbytes in (1 << 20, 4 << 20, 256 << 20):
+            assert comm(world, False).choose(nbytes, True, torch.float32)[0] not in ("nvls", "nvls1", "hybrid")
     # every world size from 2 to 8 gets a valid answer at every size, cached on the second ask
     for world in range(2, 9):
         c = comm(world, True)
         for nbytes in (16, 4096, 1 << 20, 48 << 20, 3 << 30):
             for in_heap in (True, False):
                 name, shape = c.choose(nbytes, in_heap, torch.float32)
-                assert name.split("-")[0] in ("ll", "oneshot", "staged", "push", "nvls", "hybrid")
+                assert name.split("-")[0] in ("ll", "oneshot", "staged", "push", "nvls", "nvls1", "hybrid")
                 assert planner.validate_shape(world, shape) == ""
                 assert c.choose(nbytes, in_heap, torch.float32) == (name, shape)
 
