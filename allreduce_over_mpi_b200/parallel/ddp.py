@@ -6,7 +6,8 @@ Two integrations:
   in flat buckets (25 MB by default) allocated *inside the symmetric heap*, every parameter's
   ``.grad`` is a view into its bucket, and as soon as the last gradient of a bucket has been
   accumulated the bucket is all-reduced in place on a side stream (zero copy, averaging fused
-  into the kernel) while backward continues on the main stream.
+  into the kernel) while backward continues on the main stream.  With ``sharded=True`` the bucket
+  is only reduce-scattered; ``parallel/zero.py`` builds the optimizer with split state on that.
 * :func:`flextree_allreduce_hook` - a communication hook for ``torch.nn.parallel.
   DistributedDataParallel.register_comm_hook``; DDP keeps its own buckets, which are staged
   through the communicator's slots.
@@ -33,6 +34,7 @@ class Bucket:
     dtype: torch.dtype = torch.float32
     flat: torch.Tensor | None = None
     pending: int = 0
+    owned: list = field(default_factory=list)     # sharded mode: views of the blocks of `flat` this rank holds reduced
 
 
 def build_buckets(params: Iterable[nn.Parameter], bucket_bytes: int = 25 << 20, align_elems: int = 64) -> list[Bucket]:
@@ -58,11 +60,16 @@ class FlexTreeDDP(nn.Module):
     ``alloc``, ``all_reduce``, ``world`` and ``device``)."""
 
     def __init__(self, module: nn.Module, comm, bucket_bytes: int = 25 << 20, shape=None, algo: str = "auto",
-                 broadcast_from: int | None = 0, stream: torch.cuda.Stream | None = None):
+                 broadcast_from: int | None = 0, stream: torch.cuda.Stream | None = None, sharded: bool = False):
+        """``sharded=True``: a bucket is only reduce-scattered (the first half of the all-reduce): afterwards each
+        rank holds the averaged gradient of ITS blocks of the bucket (``Bucket.owned``) and partial sums elsewhere.
+        That is the gradient side of an optimizer whose state is split over the ranks
+        (:class:`~allreduce_over_mpi_b200.parallel.zero.ShardedOptimizer`)."""
         super().__init__()
         self.module = module
         self.comm = comm
         self.shape, self.algo = shape, algo
+        self.sharded = sharded
         self.buckets = build_buckets(module.parameters(), bucket_bytes)
         self._bucket_of: dict[int, tuple[Bucket, int]] = {}
         on_gpu = torch.cuda.is_available() and getattr(comm, "device", torch.device("cpu")).type == "cuda"
@@ -132,14 +139,20 @@ class FlexTreeDDP(nn.Module):
         if b.pending == 0:
             self._launch(b)
 
+    def _reduce(self, b: Bucket):
+        if self.sharded:
+            b.owned = self.comm.reduce_scatter(b.flat, op="avg", shape=self.shape)
+        else:
+            self.comm.all_reduce(b.flat, op="avg", shape=self.shape, algo=self.algo)
+
     def _launch(self, b: Bucket):
         self.launched += 1
         if self.stream is None:
-            self.comm.all_reduce(b.flat, op="avg", shape=self.shape, algo=self.algo)
+            self._reduce(b)
             return
         self.stream.wait_stream(torch.cuda.current_stream(self.comm.device))
         with torch.cuda.stream(self.stream):
-            self.comm.all_reduce(b.flat, op="avg", shape=self.shape, algo=self.algo)
+            self._reduce(b)
 
     def _finish(self):
         """End of backward: flush buckets only part of whose parameters got a gradient, join the side stream.

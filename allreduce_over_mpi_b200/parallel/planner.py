@@ -400,14 +400,23 @@ class ProcWorld:
 
     def reduce_scatter(self, tensor: torch.Tensor, shape: Shape | None = None, op: str = "sum") -> list[torch.Tensor]:
         """Reduce-scatter half alone, in place; returns views of the block(s) this rank then holds complete
-        (block b covers elements [b * B, (b + 1) * B), B = ceil(numel / world))."""
-        shp = self._phase(tensor, shape, op, 1)
+        (block b covers elements [b * B, (b + 1) * B), B = ceil(numel / world)).  ``op="avg"`` divides those
+        blocks by the world size."""
+        if isinstance(shape, str):
+            shape = Shape.parse(shape)
+        shp = self._phase(tensor, shape, "sum" if op == "avg" else op, 1)
         B = -(-tensor.numel() // self.world)
         flat = tensor.view(-1)
-        return [flat[min(flat.numel(), b * B):min(flat.numel(), (b + 1) * B)] for b in owned_blocks(self.world, shp, self.rank)]
+        mine = [flat[min(flat.numel(), b * B):min(flat.numel(), (b + 1) * B)] for b in owned_blocks(self.world, shp, self.rank)]
+        if op == "avg":
+            for v in mine:
+                v.div_(self.world)
+        return mine
 
     def all_gather(self, tensor: torch.Tensor, shape: Shape | None = None) -> torch.Tensor:
         """All-gather half alone: every rank's own blocks are taken as final and copied to all the others."""
+        if isinstance(shape, str):
+            shape = Shape.parse(shape)
         self._phase(tensor, shape, "sum", 2)
         return tensor
 

@@ -89,6 +89,63 @@ def main():
         dist.destroy_process_group()
         return 0 if all(flags) else 1
 
+    if mode == "zero":
+        # three AdamW steps of a small fp32 GPT-2 with rank-specific tokens: gradients reduce-scattered, optimizer state
+        # split over the ranks, parameters all-gathered - against torch DDP over NCCL with a whole AdamW on every rank
+        from torch.nn.parallel import DistributedDataParallel as DDP
+        from allreduce_over_mpi_b200.models.gpt2 import GPT2, GPT2Config
+        from allreduce_over_mpi_b200.parallel.ddp import FlexTreeDDP
+        from allreduce_over_mpi_b200.parallel.zero import ShardedOptimizer
+        cfg = GPT2Config.tiny()
+        gen = torch.Generator().manual_seed(500 + rank)
+        tok = torch.randint(0, cfg.vocab_size, (4, 33), generator=gen).to(dev)
+
+        def make_opt(ps):
+            return torch.optim.AdamW(ps, lr=1e-3, weight_decay=0.0)
+
+        def train(kind):
+            torch.manual_seed(77)
+            model = GPT2(cfg).to(dev)
+            comm.free_all()
+            if kind == "sharded":
+                wrap = FlexTreeDDP(model, comm, bucket_bytes=64 << 10, sharded=True)
+                opt = ShardedOptimizer(wrap, make_opt)
+            else:
+                wrap = DDP(model, device_ids=[dev.index], bucket_cap_mb=1)
+                opt = make_opt(model.parameters())
+            losses = []
+            for _ in range(3):
+                opt.zero_grad()
+                loss = wrap(tok[:, :-1], tok[:, 1:])
+                loss.backward()
+                opt.step()
+                losses.append(float(loss.item()))
+            torch.cuda.synchronize()
+            comm.check()
+            flat = torch.cat([p.detach().float().reshape(-1) for p in model.parameters()]).clone()
+            state = opt.state_elements() if kind == "sharded" else None
+            return flat, losses, state
+
+        ref, loss_ref, _ = train("nccl")
+        got, loss_got, state = train("sharded")
+        err = (got - ref).abs().max().item()
+        nparam = ref.numel()
+        report.update({"cases": 1, "max_abs_err": err, "loss_ref": loss_ref, "loss": loss_got, "state_elements": state, "params": nparam})
+        good = err <= 2e-5 and all(abs(a - b) <= 1e-4 for a, b in zip(loss_got, loss_ref)) and state <= 2 * (nparam / world) * 1.5 + 4096
+        # every rank must end with the same parameters, bit for bit
+        mine = torch.tensor([float(got.double().sum().item())], device=dev, dtype=torch.float64)
+        sums = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(sums, mine)
+        good = good and all(bool((t == sums[0]).all()) for t in sums)
+        flags = [None] * world
+        dist.all_gather_object(flags, bool(good))
+        if rank == 0:
+            print("RESULT " + json.dumps({"ok": all(flags), **report}), flush=True)
+        comm.close()
+        dist.barrier()
+        dist.destroy_process_group()
+        return 0 if all(flags) else 1
+
     if mode == "mpi":
         # the MPI-style C entry on a GPU communicator: device buffers (in and out of place, AUTO selection and an
         # explicit FT_TOPO), host buffers through the pipelined path, and the Python all_reduce_host

@@ -184,6 +184,43 @@ def test_world_of_one_scales_every_float_type_like_larger_worlds(dtype):
     w.close()
 
 
+def test_split_optimizer_state_on_a_world_of_one():
+    """The optimizer with split state on a single rank owns everything: same parameters as a plain AdamW, the module's
+    parameters living in the communicator's heap meanwhile and in ordinary memory again after release()."""
+    import torch.nn as nn
+    from allreduce_over_mpi_b200.parallel.ddp import FlexTreeDDP
+    from allreduce_over_mpi_b200.parallel.zero import ShardedOptimizer
+
+    def make():
+        torch.manual_seed(3)
+        return nn.Sequential(nn.Linear(24, 48), nn.GELU(), nn.Linear(48, 7)).to(DEV)
+
+    w = LocalWorld(1, heap_bytes=4 << 20, staging_bytes=1 << 16)
+    c = w.ranks[0]
+    model, ref = make(), make()
+    ddp = FlexTreeDDP(model, c, bucket_bytes=4096, sharded=True)
+    opt = ShardedOptimizer(ddp, lambda ps: torch.optim.AdamW(ps, lr=1e-2, weight_decay=0.0))
+    ropt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.0)
+    assert all(c.in_heap(p.data) for p in model.parameters())
+    x, y = torch.randn(16, 24, device=DEV), torch.randn(16, 7, device=DEV)
+    for _ in range(3):
+        opt.zero_grad()
+        nn.functional.mse_loss(ddp(x), y).backward()
+        opt.step()
+        ropt.zero_grad()
+        nn.functional.mse_loss(ref(x), y).backward()
+        ropt.step()
+    torch.cuda.synchronize()
+    for p, r in zip(model.parameters(), ref.parameters()):
+        assert torch.allclose(p, r, atol=1e-6, rtol=1e-5)
+    total = sum(p.numel() for p in ref.parameters())
+    assert opt.state_elements() >= 2 * total
+    opt.release()
+    ddp.release()
+    assert not any(c.in_heap(p.data) for p in model.parameters())
+    w.close()
+
+
 def test_auto_goes_through_the_native_policy_and_counts_the_algorithm():
     """algo="auto" leaves the choice to the native policy inside ft_allreduce: what choose() reports for a size is
     what the usage counters show afterwards; a device tensor larger than one staging slot is split natively."""

@@ -30,6 +30,17 @@ def test_ddp_gradients_equal_nccl_ddp():
     assert res["flextree_max_abs_err"] < 1e-4 and res["hook_max_abs_err"] < 1e-4
 
 
+def test_split_optimizer_state_trains_like_nccl_ddp():
+    """Three AdamW steps of a small GPT-2 with the optimizer's state split over the ranks (reduce-scatter of the
+    gradients, all-gather of the parameters) end with the parameters torch DDP over NCCL gives with a whole AdamW per rank."""
+    n = min(ngpu(), 4)
+    if n < 2:
+        pytest.skip("needs 2 GPUs")
+    res = run_worker(n, "zero", port=29595)
+    assert res["ok"], res
+    assert res["max_abs_err"] < 2e-5 and res["state_elements"] < res["params"] * 2
+
+
 def test_mpi_style_entry_on_gpu_communicators():
     """MPI_Allreduce_FT (the reference's entry point, mpi_mod.hpp:1723-1778) on GPU communicators: device buffers in and
     out of the heap, host buffers through the pipelined path, with the automatic choice and with FT_TOPO set."""
