@@ -30,8 +30,14 @@ def run(impl: str, a, rank: int, world: int, dev, comm) -> dict:
     cfg = GPT2Config.small() if not a.tiny else GPT2Config.tiny()
     model = GPT2(cfg).to(dev).to(torch.bfloat16)
     comm.free_all()   # every implementation starts from an empty symmetric heap
+    sharded = None
     if impl == "flextree":
         ddp = FlexTreeDDP(model, comm, bucket_bytes=a.bucket_mb << 20)
+        fwd, zero = ddp, ddp.zero_grad
+    elif impl == "sharded":   # gradients reduce-scattered, AdamW state and update on this rank's blocks, parameters all-gathered
+        from ..parallel.zero import ShardedOptimizer
+        ddp = FlexTreeDDP(model, comm, bucket_bytes=a.bucket_mb << 20, sharded=True)
+        sharded = ShardedOptimizer(ddp, lambda ps: torch.optim.AdamW(ps, lr=1e-4, fused=True))
         fwd, zero = ddp, ddp.zero_grad
     else:
         from torch.nn.parallel import DistributedDataParallel as DDP
@@ -40,7 +46,7 @@ def run(impl: str, a, rank: int, world: int, dev, comm) -> dict:
             ddp.register_comm_hook(HookState(comm), flextree_allreduce_hook)
         fwd = ddp
         zero = lambda: model.zero_grad(set_to_none=False)  # noqa: E731
-    opt = torch.optim.AdamW(model.parameters(), lr=1e-4, fused=True)
+    opt = sharded if sharded is not None else torch.optim.AdamW(model.parameters(), lr=1e-4, fused=True)
     B, T = a.batch, min(a.seq, cfg.n_ctx)
     g = torch.Generator().manual_seed(100 + rank)
     host_tokens = [torch.randint(0, cfg.vocab_size, (B, T + 1), generator=g).pin_memory() for _ in range(4)]
@@ -87,6 +93,8 @@ def run(impl: str, a, rank: int, world: int, dev, comm) -> dict:
            "params_in_sync": bool(abs(lo.item() - hi.item()) <= 1e-3 * max(1.0, abs(hi.item()))),
            "model_params": model.num_params(), "batch_per_gpu": B, "seq": T, "bucket_mb": a.bucket_mb,
            "h2d_bytes_per_step": tok.numel() * 8, "d2h_bytes_per_step": 4}
+    if sharded is not None:
+        row["optimizer_state_elements_this_rank"] = sharded.state_elements()
     del opt, ddp, model
     torch.cuda.empty_cache()
     return row
@@ -94,7 +102,7 @@ def run(impl: str, a, rank: int, world: int, dev, comm) -> dict:
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--impl", nargs="+", default=["flextree", "nccl"], choices=["flextree", "nccl", "hook"])
+    ap.add_argument("--impl", nargs="+", default=["flextree", "nccl"], choices=["flextree", "nccl", "hook", "sharded"])
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=8)
