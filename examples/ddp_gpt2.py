@@ -1,6 +1,8 @@
 """Minimal data-parallel training loop with FlexTree gradient all-reduce (one process per GPU):
 
-    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 examples/ddp_gpt2.py
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 examples/ddp_gpt2.py [--sharded]
+
+--sharded: the optimizer's state is split over the ranks (gradients reduce-scattered, parameters all-gathered).
 """
 import os
 import sys
@@ -18,8 +20,13 @@ torch.cuda.set_device(local)
 dist.init_process_group("nccl", device_id=torch.device("cuda", local))   # bootstrap only
 comm = FlexTreeComm(heap_bytes=1 << 30)
 model = GPT2(GPT2Config.small()).cuda().bfloat16()
-ddp = FlexTreeDDP(model, comm)                 # gradients live in the symmetric heap, 25 MB buckets
-opt = torch.optim.AdamW(model.parameters(), lr=3e-4, fused=True)
+if "--sharded" in sys.argv:
+    from allreduce_over_mpi_b200.parallel.zero import ShardedOptimizer
+    ddp = FlexTreeDDP(model, comm, sharded=True)   # buckets are only reduce-scattered: each rank gets its blocks' gradient
+    opt = ShardedOptimizer(ddp, lambda ps: torch.optim.AdamW(ps, lr=3e-4, fused=True))   # 1/N of AdamW's state per rank
+else:
+    ddp = FlexTreeDDP(model, comm)             # gradients live in the symmetric heap, 25 MB buckets
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, fused=True)
 for step in range(10):
     tok = torch.randint(0, 50257, (8, 1025), device="cuda")
     ddp.zero_grad()
