@@ -21,14 +21,14 @@ def make_opt(params):
     return torch.optim.AdamW(params, lr=0.01, weight_decay=0.0)
 
 
-def worker(rank, world, session, out):
+def worker(rank, world, session, shape, out):
     from allreduce_over_mpi_b200.parallel.ddp import FlexTreeDDP
     from allreduce_over_mpi_b200.parallel.planner import ProcWorld
     from allreduce_over_mpi_b200.parallel.zero import ShardedOptimizer
     w = ProcWorld(session, rank, world, timeout_s=60)
     w.heap_create(1 << 20)
     model = make_model(seed=100 + rank)                   # different weights per rank on purpose
-    ddp = FlexTreeDDP(model, w, bucket_bytes=2048, broadcast_from=0, sharded=True)
+    ddp = FlexTreeDDP(model, w, bucket_bytes=2048, broadcast_from=0, sharded=True, shape=shape)
     opt = ShardedOptimizer(ddp, make_opt)
     assert all(w.symmetric(t) for t in opt.param_flats)
     torch.manual_seed(7)
@@ -48,12 +48,13 @@ def worker(rank, world, session, out):
     w.close()
 
 
-def test_three_processes_with_split_adam_state_train_like_one():
+@pytest.mark.parametrize("shape", [None, "ring3"])     # flat tree: rank r owns block r; ring: block r + 1
+def test_three_processes_with_split_adam_state_train_like_one(shape):
     world = 3
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     session = "zero-" + uuid.uuid4().hex[:10]
-    procs = [ctx.Process(target=worker, args=(r, world, session, out)) for r in range(world)]
+    procs = [ctx.Process(target=worker, args=(r, world, session, shape, out)) for r in range(world)]
     [p.start() for p in procs]
     got = sorted((out.get(timeout=180) for _ in range(world)), key=lambda g: g[0])
     [p.join(timeout=60) for p in procs]
