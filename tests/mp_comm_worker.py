@@ -221,6 +221,35 @@ def main():
         torch.cuda.synchronize()
         close_enough(out * world, big.numel(), torch.float32, it, "all_reduce_host pageable avg")
         comm.check()
+        # FT_DEBUG=2 on GPU ranks: the call runs as its two halves and prints the first 100 values after each
+        # ("Med CHECK" after the reduce-scatter, "Tail CHECK" after the all-gather); the text goes to the C stderr,
+        # which is pointed at a temporary file for the length of the call
+        import tempfile
+        it += 1
+        comm.free_all()
+        sym = comm.alloc(1000, torch.float32)
+        fill(sym, rank, it)
+        os.environ["FT_DEBUG"] = "2"
+        with tempfile.TemporaryFile() as tf:
+            sys.stderr.flush()
+            saved = os.dup(2)
+            os.dup2(tf.fileno(), 2)
+            try:
+                rc = L.MPI_Allreduce_FT_c(IN_PLACE, sym.data_ptr(), 1000, DTYPES["float32"], OPS["sum"], mc)
+            finally:
+                os.dup2(saved, 2)
+                os.close(saved)
+                os.environ.pop("FT_DEBUG", None)
+            tf.seek(0)
+            text = tf.read().decode(errors="replace")
+        torch.cuda.synchronize()
+        good = good and rc == 0
+        close_enough(sym, 1000, torch.float32, it, "FT_DEBUG=2 halves")
+        report["debug2"] = {"med": text.count("Med CHECK"), "tail": text.count("Tail CHECK")}
+        if text.count("Med CHECK") != 1 or text.count("Tail CHECK") != 1:
+            good = False
+            print(f"[rank {rank}] FT_DEBUG=2 printed: {text[:300]!r}", flush=True)
+        comm.check()
         L.ft_mpi_comm_free(mc)
         report["stats"] = comm.stats()
         flags = [None] * world

@@ -43,12 +43,14 @@ def test_split_optimizer_state_trains_like_nccl_ddp():
 
 def test_mpi_style_entry_on_gpu_communicators():
     """MPI_Allreduce_FT (the reference's entry point, mpi_mod.hpp:1723-1778) on GPU communicators: device buffers in and
-    out of the heap, host buffers through the pipelined path, with the automatic choice and with FT_TOPO set."""
+    out of the heap, host buffers through the pipelined path, with the automatic choice and with FT_TOPO set; with
+    FT_DEBUG=2 the call runs as its two halves and prints one value dump after each (mpi_mod.hpp:1601-1613, :1657-1670)."""
     n = min(ngpu(), 8)
     if n < 2:
         pytest.skip("needs 2 GPUs")
     res = run_worker(n, "mpi", port=29601)
     assert res["ok"] and res["cases"] >= 40, res
+    assert res["debug2"] == {"med": 1, "tail": 1}
 
 
 def test_native_benchmark_checks_itself_on_gpus():
