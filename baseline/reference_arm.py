@@ -54,9 +54,9 @@ def _nway(a) -> dict:
             "unit": "GB/s", "n_gpus": 1, "steps": a.steps, "warmup": warm, "ms_per_step": d["ms_per_step"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "float32",
             "data": "synthetic uniform[-1,1) seeded", "impl": "reference",
-            "config": {"model": "n-way reduce-sum, n in {2,3,4,8}", "elems_per_vector": a.elems, "parallelism": "single GPU",
-                       "kernel": "reference reduce_sum_gpu<float>, 256 threads/block, one element per thread, recompiled for sm_100a",
-                       "l2": "inputs larger than L2"},
+            "config": {"model": "n-way reduce-sum, n in {2,3,4,8}", "elems_per_vector": a.elems, "global_batch": None,
+                       "seq_len": None, "parallelism": "single GPU", "l2": "inputs larger than L2"},
+            "details": {"kernel": "reference reduce_sum_gpu<float>, 256 threads/block, one element per thread, recompiled for sm_100a"},
             "per_fanin": {str(n): {"ms": ms, "GBps": round((n + 1) * nbytes / (ms * 1e-3) / 1e9, 1)}
                           for n, ms in zip(FANINS, d["per_fanin_ms"])},
             "max_abs_err": d["max_abs_err"], "gpu_launches": 4 * a.steps,
@@ -130,8 +130,10 @@ def _mpi(a, world: int, rank: int) -> dict:
                    "unit": "GB/s", "n_gpus": world, "steps": a.steps, "warmup": warm, "ms_per_step": round(sec * 1e3, 3),
                    "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "float32",
                    "data": "reference benchmark's own fill (i * 0.1 on every rank)", "impl": "reference",
-                   "config": {"model": "all-reduce", "message_bytes": a.bytes, "parallelism": f"dp{world}",
-                              "path": "reference MPI_Allreduce_FT (benchmark.cpp --size --repeat --to-file), CPU ranks in host "
+                   "config": {"model": "all-reduce", "message_bytes": a.bytes, "global_batch": None, "seq_len": None,
+                              "parallelism": f"dp{world}",
+                              "l2": "input larger than L2" if a.bytes > (126 << 20) else "input smaller than L2, not flushed inside the back-to-back loop"},
+                   "details": {"path": "reference MPI_Allreduce_FT (benchmark.cpp --size --repeat --to-file), CPU ranks in host "
                                       "memory over a shared-memory MPI shim; time is the reference's own host MPI_Wtime on rank 0",
                               "FT_TOPO": best["_topo"], "FT_LONELY": os.environ.get("FT_LONELY", "0"),
                               "openmp": "stock (14 threads per reduction loop)" if not best["_limit"] else

@@ -28,7 +28,7 @@ def test_reference_arm_multi_rank(world, topo, lonely):
     assert r.returncode == 0 and len(lines) == 1, (r.stdout[-1500:], r.stderr[-1500:])
     out = json.loads(lines[0])
     assert out["impl"] == "reference" and "unavailable" not in out, out
-    assert out["n_gpus"] == world and out["value"] > 0 and out["config"]["FT_TOPO"] == (topo or str(world))
+    assert out["n_gpus"] == world and out["value"] > 0 and out["details"]["FT_TOPO"] == (topo or str(world))
     assert not os.path.exists(f"/dev/shm/ftshim-{29800 + world}")      # the shim removed its segment
 
 
