@@ -156,7 +156,7 @@ def test_native_policy_returns_every_row_of_the_committed_table(tmp_path):
     L.ft_policy_destroy(h)
 
 
-def _liveness_worker(rank, world, port, leave_after, q):
+def _liveness_worker(rank, world, port, leave_after, q, session=None):
     import time
     import torch.distributed as dist
     from datetime import timedelta
@@ -176,6 +176,15 @@ def _liveness_worker(rank, world, port, leave_after, q):
     except RankLost as e:
         plan = replan_after_failure(world, e.lost, 64 << 20, CostParams(link_gbs=600, sync_us=5, launch_us=20))
         q.put((rank, "lost", sorted(e.lost), plan.world, plan.rank_map[rank], str(plan.shape)))
+        if session is not None:
+            # the survivors form the smaller world under their new ranks and carry on with the re-planned shape
+            from allreduce_over_mpi_b200.parallel.planner import ProcWorld
+            w = ProcWorld(f"{session}-minus{len(e.lost)}", plan.rank_map[rank], plan.world, timeout_s=30)
+            x = torch.full((1000,), float(rank + 1))          # 4 kB: travels through the control segment
+            w.all_reduce(x, shape=plan.shape)
+            q.put((rank, "recovered", float(x[0]), float(x[-1])))
+            w.barrier()
+            w.close()
         time.sleep(1.0)
 
 
@@ -198,6 +207,30 @@ def test_lost_rank_is_noticed_on_the_host_between_steps():
     for r in (0, 1):
         assert by_rank[r][1] == "lost" and by_rank[r][2] == [2], by_rank
         assert by_rank[r][3] == 2 and by_rank[r][4] == r and by_rank[r][5] in ("2", "ring2")
+    assert all(p.exitcode == 0 for p in procs)
+
+
+def test_survivors_form_a_smaller_world_and_carry_on():
+    """Four CPU processes; rank 1 goes quiet.  Ranks 0, 2 and 3 notice, re-plan for three ranks, join a new process world
+    as ranks 0, 1, 2 and all-reduce there: the sum holds exactly the survivors' contributions."""
+    import multiprocessing as mp
+    import socket
+    import uuid
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        port = sk.getsockname()[1]
+    session = "elastic-" + uuid.uuid4().hex[:10]
+    procs = [ctx.Process(target=_liveness_worker, args=(r, 4, port, (1, 8), q, session)) for r in range(4)]
+    [p.start() for p in procs]
+    got = [q.get(timeout=90) for _ in range(7)]          # one "left", three "lost", three "recovered"
+    [p.join(timeout=30) for p in procs]
+    lost = {g[0]: g for g in got if g[1] == "lost"}
+    rec = {g[0]: g for g in got if g[1] == "recovered"}
+    assert sorted(lost) == sorted(rec) == [0, 2, 3], got
+    assert [lost[r][4] for r in (0, 2, 3)] == [0, 1, 2] and all(lost[r][2] == [1] and lost[r][3] == 3 for r in lost)
+    assert all(rec[r][2] == rec[r][3] == 1.0 + 3.0 + 4.0 for r in rec), rec
     assert all(p.exitcode == 0 for p in procs)
 
 
