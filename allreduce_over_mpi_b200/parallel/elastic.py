@@ -70,10 +70,24 @@ class Liveness:
         self._count += 1
         self.store.set(f"{self.prefix}{self.rank}", str(self._count))
 
+    def leave(self):
+        """Announce that this rank takes part in ONE more step and then stops.  Call it right before the
+        :meth:`guard` of that last step.  The note carries the number of that step (ranks call :meth:`guard` once per
+        step, so their counters agree): a peer that reads it while still on the same step carries on and launches; a
+        peer on the step after it can only have got there by finishing a collective this rank took part in, which this
+        rank launched after writing the note - so that peer is certain to see it before its next launch.  No peer ever
+        launches a kernel that waits for a rank that has left, and nobody has to wait for a silence to time out."""
+        self.store.set(f"{self.prefix}gone/{self.rank}", str(self._count + 1))
+
     def poll(self) -> set[int]:
-        """Ranks that have been silent for longer than the timeout."""
+        """Ranks that announced their departure, or have been silent for longer than the timeout."""
         now, lost = self._now(), set()
         for r, (last, since) in self._seen.items():
+            gone = f"{self.prefix}gone/{r}"
+            if self.store.check([gone]):
+                if self._count > int(bytes(self.store.get(gone))):   # its last step is behind this rank
+                    lost.add(r)
+                continue
             key = f"{self.prefix}{r}"
             val = bytes(self.store.get(key)) if self.store.check([key]) else None
             if val != last:

@@ -12,8 +12,83 @@ from allreduce_over_mpi_b200.parallel import planner  # noqa: E402
 from allreduce_over_mpi_b200.parallel.comm import FlexTreeComm  # noqa: E402
 
 
+def elastic_main():
+    """A rank leaves between steps; the survivors learn of it on the host before their next launch, take the old
+    communicator down together with the leaver, form a smaller world and carry on.  Control traffic over gloo and a
+    TCP store, NVLS off, no kernel ever waits for the rank that left."""
+    import time
+    from datetime import timedelta
+    from allreduce_over_mpi_b200.parallel.elastic import Liveness, RankLost, replan_after_failure
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", 0))
+    port = int(os.environ["MASTER_PORT"])
+    os.environ["FT_NVLS"] = "0"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("gloo", rank=rank, world_size=world)       # rendezvous from the launcher's environment
+    store = dist.TCPStore("127.0.0.1", port + 1, world, is_master=(rank == 0), timeout=timedelta(seconds=60))
+    comm = FlexTreeComm(heap_bytes=32 << 20, staging_bytes=4 << 20, nvls=False, device=local)
+    live = Liveness(store, rank, world, timeout_s=10.0)
+    leaver, last_step = (world - 2 if world > 2 else 1), 4
+    x = comm.alloc(1 << 16, torch.float32)
+    report = {"world": world, "leaver": leaver, "steps_before": 0, "steps_after": 0}
+    good = True
+    plan = None
+    try:
+        for step in range(50):
+            if rank == leaver and step == last_step:
+                live.leave()                         # written before this rank's last launch
+            live.guard()                             # between steps, before the next launch
+            x.fill_(float(rank + 1))
+            comm.all_reduce(x)
+            torch.cuda.synchronize()
+            comm.check()
+            good = good and float(x[0]) == float(x[-1]) == world * (world + 1) / 2
+            report["steps_before"] += 1
+            if rank == leaver and step == last_step:
+                break
+    except RankLost as e:
+        plan = replan_after_failure(world, e.lost, x.numel() * 4)
+        report["lost"] = sorted(e.lost)
+    # every rank of the old world, the leaver included, takes the old communicator down together: nobody maps the
+    # leaver's heap any more when it exits
+    comm.close()
+    dist.destroy_process_group()
+    if rank == leaver:
+        good = good and report["steps_before"] == last_step + 1
+        store.set(f"done/{rank}", json.dumps({"ok": bool(good), **report}))
+        print(f"[rank {rank}] left after step {last_step}", flush=True)
+        time.sleep(3.0)                              # the store's clients may still be reading
+        return 0
+    good = good and plan is not None and report.get("lost") == [leaver] and report["steps_before"] == last_step + 1
+    new_rank, new_world = plan.rank_map[rank], plan.world
+    # an explicit store: under torch.distributed.run a tcp:// or env:// rendezvous would look for the launcher's own store
+    dist.init_process_group("gloo", store=dist.PrefixStore("survivors", store), rank=new_rank, world_size=new_world)
+    comm = FlexTreeComm(heap_bytes=32 << 20, staging_bytes=4 << 20, nvls=False, device=local)
+    y = comm.alloc(1 << 16, torch.float32)
+    want = sum(r + 1 for r in range(world) if r != leaver)
+    for _ in range(5):
+        y.fill_(float(rank + 1))
+        comm.all_reduce(y, shape=str(plan.shape))
+        torch.cuda.synchronize()
+        comm.check()
+        good = good and float(y[0]) == float(y[-1]) == float(want)
+        report["steps_after"] += 1
+    report.update({"new_world": new_world, "new_rank": new_rank, "shape": str(plan.shape)})
+    flags = [None] * new_world
+    dist.all_gather_object(flags, bool(good))
+    if new_rank == 0:
+        print("RESULT " + json.dumps({"ok": all(flags), **report}), flush=True)
+    comm.close()
+    dist.destroy_process_group()
+    if rank == 0:
+        time.sleep(1.0)                              # rank 0 hosts the TCP store
+    return 0 if all(flags) else 1
+
+
 def main():
     mode = sys.argv[1] if len(sys.argv) > 1 else "correctness"
+    if mode == "elastic":
+        return elastic_main()
     rank, world, local = init_dist()
     comm = FlexTreeComm(heap_bytes=96 << 20, staging_bytes=8 << 20, mem=os.environ.get("FT_MEM", "auto"))
     dev = comm.device

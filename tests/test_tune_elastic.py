@@ -253,6 +253,16 @@ def test_liveness_in_one_process():
     except RankLost as e:
         assert e.lost == {1}
     assert b.poll() == set()       # b still sees a's counter moving
+    c, d = Liveness(dist.HashStore(), 0, 2, timeout_s=60.0), None
+    d = Liveness(c.store, 1, 2, timeout_s=60.0)
+    d.leave()                      # "my next step is my last": d's counter is 1, so that step is number 2
+    d.guard()
+    c.guard()                      # c's step 2: d still takes part in it
+    try:
+        c.guard()                  # c's step 3: d is gone, known at once, long before any silence would time out
+        raise AssertionError("expected RankLost")
+    except RankLost as e:
+        assert e.lost == {1}
 
 
 def test_fit_report_reads_the_committed_calibration():

@@ -41,6 +41,19 @@ def test_split_optimizer_state_trains_like_nccl_ddp():
     assert res["max_abs_err"] < 2e-5 and res["state_elements"] < res["params"] * 2
 
 
+def test_a_rank_leaves_between_steps_and_the_survivors_carry_on():
+    """Elastic recovery on GPUs without any GPU-side failure: a rank announces its departure on the host (a TCP store)
+    before its last step, the others see it before their next launch, the old communicator is taken down by everyone
+    together, and the survivors build a smaller communicator (new ranks, re-planned shape) and keep all-reducing.
+    NVLS is off and no kernel ever waits for the rank that left."""
+    n = min(ngpu(), 4)
+    if n < 2:
+        pytest.skip("needs 2 GPUs")
+    res = run_worker(n, "elastic", {"FT_NVLS": "0", "NCCL_NVLS_ENABLE": "0"}, port=29611)
+    assert res["ok"], res
+    assert res["new_world"] == n - 1 and res["lost"] == [res["leaver"]] and res["steps_before"] == 5 and res["steps_after"] == 5
+
+
 def test_mpi_style_entry_on_gpu_communicators():
     """MPI_Allreduce_FT (the reference's entry point, mpi_mod.hpp:1723-1778) on GPU communicators: device buffers in and
     out of the heap, host buffers through the pipelined path, with the automatic choice and with FT_TOPO set; with
