@@ -89,6 +89,24 @@ class ShardedOptimizer:
         for pflat in self.param_flats:
             self.comm.all_gather(pflat, shape=self.ddp.shape)
 
+    @torch.no_grad()
+    def clip_grad_norm_(self, max_norm: float, eps: float = 1e-6) -> torch.Tensor:
+        """Scale the owned gradient blocks so that the 2-norm of the WHOLE averaged gradient is at most ``max_norm``
+        (what ``torch.nn.utils.clip_grad_norm_`` does for an unsplit gradient).  Every block has exactly one owner,
+        so the squared norms of the shards add up to the squared global norm: one all-reduce of a single number.
+        Call between ``backward()`` and :meth:`step`, on every rank.  Returns the global norm."""
+        dev = self.comm.device
+        sq = torch.zeros(1, dtype=torch.float32, device=dev)
+        for shard in self.shards:
+            sq += shard.grad.float().pow(2).sum()
+        if self.comm.world > 1:
+            self.comm.all_reduce(sq, op="sum")
+        norm = sq.sqrt()
+        scale = (max_norm / (norm + eps)).clamp(max=1.0)
+        for shard in self.shards:
+            shard.grad.mul_(scale.to(shard.grad.dtype))
+        return norm[0]
+
     def zero_grad(self, set_to_none: bool = False):
         """The shards' gradients are views of the gradient buckets, which are zeroed in place."""
         self.ddp.zero_grad()

@@ -17,6 +17,9 @@ def make_model(seed):
     return nn.Sequential(nn.Linear(12, 32), nn.GELU(), nn.Linear(32, 32), nn.GELU(), nn.Linear(32, 5))
 
 
+CLIP = 0.5     # below the gradient norm of the first steps, so that clipping really scales
+
+
 def make_opt(params):
     return torch.optim.AdamW(params, lr=0.01, weight_decay=0.0)
 
@@ -34,14 +37,16 @@ def worker(rank, world, session, shape, out):
     torch.manual_seed(7)
     x, y = torch.randn(8 * world, 12), torch.randn(8 * world, 5)
     xs, ys = x[rank * 8:(rank + 1) * 8], y[rank * 8:(rank + 1) * 8]
+    norms = []
     for _ in range(4):
         opt.zero_grad()
         nn.functional.mse_loss(ddp(xs), ys, reduction="sum").backward()
+        norms.append(float(opt.clip_grad_norm_(CLIP)))
         opt.step()
     sd = opt.state_dict()
     opt.load_state_dict(sd)                               # round trip of this rank's part
     owned = sum(hi - lo for rng in opt.ranges for lo, hi in rng)
-    out.put((rank, [p.detach().numpy().copy() for p in model.parameters()], owned, opt.state_elements()))
+    out.put((rank, [p.detach().numpy().copy() for p in model.parameters()], owned, opt.state_elements(), norms))
     w.barrier()
     opt.release()
     ddp.release()
@@ -63,10 +68,15 @@ def test_three_processes_with_split_adam_state_train_like_one(shape):
     opt = make_opt(ref.parameters())
     torch.manual_seed(7)
     x, y = torch.randn(8 * world, 12), torch.randn(8 * world, 5)
+    ref_norms = []
     for _ in range(4):
         ref.zero_grad()
         (nn.functional.mse_loss(ref(x), y, reduction="sum") / world).backward()
+        ref_norms.append(float(torch.nn.utils.clip_grad_norm_(ref.parameters(), CLIP)))
         opt.step()
+    assert ref_norms[0] > CLIP                                   # the clip was active
+    for g in got:
+        assert all(abs(a - b) <= 1e-4 * max(1.0, b) for a, b in zip(g[4], ref_norms)), (g[4], ref_norms)
     for a, b, c, r in zip(got[0][1], got[1][1], got[2][1], ref.parameters()):
         assert (a == b).all() and (a == c).all()                # every rank holds the same weights, bit for bit
         assert torch.allclose(torch.from_numpy(a), r.detach(), atol=2e-5, rtol=1e-4)
