@@ -6,6 +6,7 @@ reasons were active.  Nothing here changes a GPU setting.
 """
 from __future__ import annotations
 
+import os
 import shutil
 import statistics
 import subprocess
@@ -57,6 +58,10 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         self._file.close()
+        try:
+            os.unlink(self._file.name)
+        except OSError:
+            pass
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         busy = [c for c, p in zip(sm, power) if p >= 0.5 * max(power)] or sm

@@ -143,3 +143,30 @@ def test_numa_placement_helper_is_best_effort():
     import torch
     if not torch.cuda.is_available():
         assert numa.gpu_local_cpus(0) == (set(), None) and numa.bind_to_gpu_node(0) is None
+
+
+def test_clock_sampler_reads_a_fake_nvidia_smi(tmp_path, monkeypatch):
+    """The sampler only reads: it starts `nvidia-smi --query-gpu=... -lms`, and summarises median SM clock under load,
+    max clock and the throttle reasons seen.  Here the program on PATH is a script that prints three samples."""
+    import os
+    import stat
+    import time
+    from allreduce_over_mpi_b200.utils.clocks import ClockSampler
+    fake = tmp_path / "nvidia-smi"
+    fake.write_text("#!/bin/sh\n"
+                    "echo '0, 1965, 1965, 120.5, 0x0, Not Active, Not Active, Not Active, Not Active'\n"
+                    "echo '0, 1710, 1965, 940.0, 0x4, Not Active, Not Active, Not Active, Active'\n"
+                    "echo '0, 1650, 1965, 950.0, 0x4, Not Active, Not Active, Not Active, Active'\n"
+                    "echo 'garbage line'\n"
+                    "sleep 30\n")
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    monkeypatch.setenv("PATH", f"{tmp_path}{os.pathsep}{os.environ['PATH']}")
+    s = ClockSampler(gpu_index=0).start()
+    time.sleep(0.5)
+    name = s._file.name
+    got = s.stop()
+    assert got["samples"] == 3 and got["sm_max_mhz"] == 1965.0 and got["reasons"] == ["sw_power_cap"]
+    assert got["sm_mhz"] == 1680.0 and got["power_w_max"] == 950.0      # median of the two samples under load
+    assert not os.path.exists(name)                                      # the sample file is removed
+    monkeypatch.setenv("PATH", str(tmp_path / "nowhere"))
+    assert ClockSampler().start().stop()["samples"] == 0                 # no nvidia-smi: an empty record, no error
