@@ -75,6 +75,7 @@ struct PolicyChoice {
 class Policy {
  public:
   static constexpr uint64_t kLLMaxBytes = 256u << 10;   // largest message of the low-latency protocol
+  static constexpr size_t kCacheEntries = 4096;         // answers remembered per policy before the cache starts over
 
   explicit Policy(int world) : world_(world) {}
   int world() const { return world_; }
@@ -203,6 +204,7 @@ class Policy {
       c.algo = m.algo;
       c.shape = m.shape;
     }
+    if (cache_.size() >= kCacheEntries) cache_.clear();   // a caller with endlessly varying sizes must not grow it without bound
     cache_.emplace(key, c);
     return c;
   }
