@@ -271,3 +271,42 @@ def test_fit_report_reads_the_committed_calibration():
     assert lines[0].startswith("cost model v1 fit:") and "| 8 |" in text and "fitted constants:" in text
     # every world size with several measured shapes reports how often the model's first choice was the fastest
     assert sum(" of " in l for l in lines if l.startswith("| ")) >= 5
+
+
+def test_calibration_loader_survives_damaged_files(tmp_path):
+    """Whatever is in the calibration file, loading returns a status: truncated, mutated and random files never crash the
+    library, and a file that was refused leaves the policy answering from the built-in model."""
+    import ctypes as C
+    import random
+    from allreduce_over_mpi_b200._lib import Choice, lib
+    L = lib()
+    good = open(planner.calibration_path(), "rb").read()
+    rng = random.Random(12345)
+    h = L.ft_policy_create(8)
+    err = C.create_string_buffer(512)
+    f = tmp_path / "cal.json"
+    cases = [good[:n] for n in (0, 1, 17, len(good) // 3, len(good) - 1)]
+    for _ in range(150):
+        b = bytearray(good)
+        for _ in range(rng.randint(1, 8)):
+            i = rng.randrange(len(b))
+            kind = rng.random()
+            if kind < 0.4:
+                b[i] = rng.randrange(256)
+            elif kind < 0.7:
+                del b[i:i + rng.randint(1, 40)]
+            else:
+                b[i:i] = bytes(rng.choice(b'{}[]",:0123456789eE+-.\\u') for _ in range(rng.randint(1, 12)))
+        cases.append(bytes(b))
+    cases += [bytes(rng.randrange(256) for _ in range(rng.randint(1, 300))) for _ in range(30)]
+    cases += [b"[" * 5000, b'{"table": ' + b"[" * 3000, b'{"params": {"launch_us": 1e999}, "table": {"8": [[1e30, "ll", "8"]]}}']
+    refused = 0
+    for blob in cases:
+        f.write_bytes(blob)
+        rc = L.ft_policy_load(h, str(f).encode(), err, 512)
+        refused += rc != 0
+        out = Choice()
+        assert L.ft_policy_choose(h, 1 << 20, 1, 0, 64 << 20, 8 << 10, 0, C.byref(out)) == 0
+        assert out.algo_name.decode() in ("ll", "oneshot", "staged", "push", "nvls", "nvls1", "hybrid")
+    assert refused > 10
+    L.ft_policy_destroy(h)
