@@ -5,6 +5,7 @@
 #include <map>
 #include <memory>
 #include <string>
+#include <utility>
 #include <vector>
 
 namespace ft {
@@ -27,7 +28,7 @@ struct Json {
 
 class JsonParser {
  public:
-  explicit JsonParser(const std::string& text) : s_(text) {}
+  explicit JsonParser(std::string text) : s_(std::move(text)) {}   // owns its text: a temporary is a valid argument
   // false (and a reason in err()) on malformed input or trailing garbage
   bool parse(Json* out) {
     if (!value(out, 0)) return false;
@@ -38,7 +39,7 @@ class JsonParser {
   const std::string& err() const { return err_; }
 
  private:
-  const std::string& s_;
+  const std::string s_;
   size_t i_ = 0;
   std::string err_;
 

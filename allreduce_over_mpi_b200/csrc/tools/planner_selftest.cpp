@@ -18,6 +18,7 @@
 #include "../planner/config.hpp"
 #include "../planner/cost_model.hpp"
 #include "../planner/cpu_executor.hpp"
+#include "../planner/policy.hpp"
 #include "../planner/proc_world.hpp"
 #include "../runtime/dev_plan.hpp"
 #include "../runtime/heap_alloc.hpp"
@@ -193,6 +194,46 @@ static void enumerators_and_models() {
   k.nvls_gbs = 500;
   for (int n = 2; n <= 16; ++n)
     for (uint64_t b : {1024ull, 1ull << 20, 1ull << 30}) EXPECT(std::isfinite(ft::pick_algorithm(n, b, k).us));
+}
+
+// The selection policy and its JSON reader under the sanitizers: well-formed, damaged and hostile texts, rows that
+// parse but do not apply, and more distinct message sizes than the answer cache holds.
+static void policy_and_json() {
+  const char* texts[] = {
+      "{\"params\": {\"launch_us\": 3.5, \"peer_eff\": {\"2\": 0.5, \"99\": 1.0, \"x\": 2}}, \"table\": {\"8\": [[1024, \"ll\", \"2*4\"], "
+      "[1048576, \"nvls\", \"8\"], [4096, \"warp\", \"8\"], [8192, \"staged\", \"3*3\"], [1, 2], \"row\", [65536, \"hybrid-0.8-0.25\", \"8\"]]}}",
+      "", "{", "{\"table\": [[[[[[[[[[", "{\"a\": \"\\u12", "{\"a\": 1e99999, \"b\": -}", "[1, 2, 3]", "nul", "{\"params\": 5, \"table\": 7}",
+      "{\"table\": {\"8\": {\"not\": \"a list\"}}}"};
+  int i = 0;
+  for (const char* t : texts) {
+    ft::Json root;
+    ft::JsonParser jp(t);
+    const bool ok = jp.parse(&root);
+    EXPECT(ok == (i == 0 || i == 6 || i == 8 || i == 9));
+    ++i;
+  }
+  std::string deep(5000, '[');
+  ft::Json root;
+  ft::JsonParser jp(deep);
+  EXPECT(!jp.parse(&root));
+  ft::Policy pol(8);
+  EXPECT(pol.add_row(1024, "ll", "2*4") && pol.add_row(1 << 20, "nvls", "8") && pol.add_row(65536, "hybrid-0.8-0.25", "8"));
+  EXPECT(!pol.add_row(4096, "warp", "8") && !pol.add_row(8192, "staged", "3*3") && !pol.add_row(8192, "staged", "2**"));
+  ft::PolicyChoice c = pol.choose(1024, false, false, 64 << 20, 8 << 10);
+  EXPECT(c.algo == "ll" && c.shape.widths.size() == 2 && c.from_table);
+  c = pol.choose(1 << 20, true, true, 64 << 20, 8 << 10);
+  EXPECT(c.algo == "nvls");
+  c = pol.choose(1 << 20, true, false, 64 << 20, 8 << 10);     // the switch is not available: the row does not apply
+  EXPECT(c.algo != "nvls" && c.algo != "hybrid");
+  for (uint64_t b = 16; b < 16 * 3 * ft::Policy::kCacheEntries; b += 16) {   // the cache starts over instead of growing
+    c = pol.choose(b, (b / 16) % 2 == 0, false, 64 << 20, 8 << 10);
+    EXPECT(!c.algo.empty() && ft::validate_shape(8, c.shape).empty());
+  }
+  ft::Shape sh;
+  EXPECT(ft::parse_shape_text(" 2 x 2 + 1 ", &sh) && sh.lonely == 1 && sh.widths.size() == 2);
+  EXPECT(ft::parse_shape_text("RING8", &sh) && sh.ring);
+  EXPECT(!ft::parse_shape_text("2*-4", &sh) && !ft::parse_shape_text("", &sh) && !ft::parse_shape_text("ring", &sh) &&
+         !ft::parse_shape_text("99999999*2", &sh));
 }
 
 static void thread_world(bool with_fault) {
@@ -379,7 +420,7 @@ static void thread_world_small_message_twins() {
 
 int main(int argc, char** argv) {
   const bool threads = argc > 1 && !std::strcmp(argv[1], "threads");
-  if (!threads) { proc_world_forked(); plans_and_snapshot(); device_tables(); heap_offsets(); enumerators_and_models(); }
+  if (!threads) { proc_world_forked(); plans_and_snapshot(); device_tables(); heap_offsets(); enumerators_and_models(); policy_and_json(); }
   thread_world(false);
   thread_world_phases();
   thread_world_small_message_twins();
