@@ -22,6 +22,7 @@
 #include "../planner/proc_world.hpp"
 #include "../runtime/dev_plan.hpp"
 #include "../runtime/heap_alloc.hpp"
+#include "../runtime/fd_channel.cpp"   // descriptor passing over abstract unix sockets: plain host code, compiled in here
 
 static int fails = 0;
 #define EXPECT(c) do { if (!(c)) { std::printf("FAIL %s:%d %s\n", __FILE__, __LINE__, #c); ++fails; } } while (0)
@@ -236,6 +237,32 @@ static void policy_and_json() {
          !ft::parse_shape_text("99999999*2", &sh));
 }
 
+// Descriptor passing (how VMM heaps and multicast objects reach the other ranks): a pipe's read end travels from a thread
+// to this one with its tag, the received descriptor reads what the sender wrote, waits run out instead of blocking.
+static void fd_passing() {
+  const std::string name = "ft-selftest-" + std::to_string((long)getpid());
+  const int sock = ft_fd_listen(name.c_str());
+  EXPECT(sock >= 0);
+  int tag = -1;
+  EXPECT(ft_fd_recv(sock, &tag, 50) < 0);                        // nobody sent: the wait is bounded
+  EXPECT(ft_fd_send("ft-selftest-nobody-listens", 0, 1, 50) != 0);
+  int pipefd[2];
+  EXPECT(pipe(pipefd) == 0);
+  std::thread sender([&] {
+    EXPECT(write(pipefd[1], "heap", 4) == 4);
+    EXPECT(ft_fd_send(name.c_str(), pipefd[0], 7, 2000) == 0);
+  });
+  const int got = ft_fd_recv(sock, &tag, 2000);
+  sender.join();
+  EXPECT(got >= 0 && tag == 7);
+  char buf[8] = {0};
+  EXPECT(got >= 0 && read(got, buf, 4) == 4 && !std::memcmp(buf, "heap", 4));
+  if (got >= 0) ft_fd_close(got);
+  ft_fd_close(pipefd[0]);
+  ft_fd_close(pipefd[1]);
+  ft_fd_close(sock);
+}
+
 static void thread_world(bool with_fault) {
   for (const char* text : {"2,2", "2,3", "2,2,2"}) {
     ft::ShapeConfig cfg = ft::parse_topo(text, std::string(text) == "2,3" ? "1" : "", std::string(text) == "2,2" ? 4 : (std::string(text) == "2,3" ? 7 : 8));
@@ -420,7 +447,7 @@ static void thread_world_small_message_twins() {
 
 int main(int argc, char** argv) {
   const bool threads = argc > 1 && !std::strcmp(argv[1], "threads");
-  if (!threads) { proc_world_forked(); plans_and_snapshot(); device_tables(); heap_offsets(); enumerators_and_models(); policy_and_json(); }
+  if (!threads) { proc_world_forked(); plans_and_snapshot(); device_tables(); heap_offsets(); enumerators_and_models(); policy_and_json(); fd_passing(); }
   thread_world(false);
   thread_world_phases();
   thread_world_small_message_twins();
